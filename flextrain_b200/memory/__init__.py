@@ -1,0 +1,334 @@
+"""Memory primitives shared by the coordinators.
+
+Parity: flextrain/memory/__init__.py:1-412 - data ids and swap-file names
+:20-49, ``free_tensor`` :52-60, ``move_into_contiguous`` :63-84,
+``copy_segments`` :87-135, ``ContiguousParaGroup`` :138-184, waitable handles
+:187-237, ``RotateContainer`` :240-248, accounted allocation :251-312 and the
+alignment helpers :315-363.  The single side stream of the reference
+(``FlexTrainDataStream`` :366-412) is replaced by the event-ordered stream set
+of ``utils/device.py``; ``get_data_stream`` returns that set.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from dataclasses import dataclass
+from enum import Enum
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..defaults import PAGE_SIZE
+from ..utils import distributed as dist
+from ..utils.device import StreamSet, get_streams
+from ..utils.logging import rank0_logger
+
+
+# ---------------------------------------------------------------- data ids
+class FlexTrainDataType(Enum):
+    CKPT = 0
+    PARA = 1
+    GRAD = 2
+    OPTS = 3
+
+
+@dataclass(frozen=True)
+class FlexTrainDataID:
+    """Names one swappable object; ``str()`` is its swap-file name
+    ``rank{r}_{TYPE}_layer{i}.swp`` (the on-disk format of the reference)."""
+    data_type: FlexTrainDataType
+    layer_index: object          # int or "i-j" for multi-index objects
+
+    def __str__(self):
+        return f"rank{dist.get_rank()}_{self.data_type.name}_layer{self.layer_index}.swp"
+
+
+# ------------------------------------------------------------------ handles
+class Waitable:
+    def wait(self):
+        raise NotImplementedError
+
+    def is_completed(self) -> bool:
+        raise NotImplementedError
+
+
+class DummyHandle(Waitable):
+    def wait(self):
+        return None
+
+    def is_completed(self):
+        return True
+
+
+class FunctionHandle(Waitable):
+    """Runs ``fn`` once, at the first ``wait``."""
+
+    def __init__(self, fn: Callable[[], None]):
+        self._fn = fn
+
+    def wait(self):
+        fn, self._fn = self._fn, None
+        if fn is not None:
+            fn()
+
+    def is_completed(self):
+        return self._fn is None
+
+
+class EventHandle(Waitable):
+    """Completion of GPU work up to a recorded event."""
+
+    def __init__(self, event):
+        self._event = event
+
+    def wait(self):
+        self._event.synchronize()
+
+    def is_completed(self):
+        return self._event.query()
+
+
+class FutureHandle(Waitable):
+    """Completion of a ``concurrent.futures.Future`` (host worker threads)."""
+
+    def __init__(self, future):
+        self._future = future
+
+    def wait(self):
+        return self._future.result()
+
+    def is_completed(self):
+        return self._future.done()
+
+
+class FusedHandle(Waitable):
+    def __init__(self, handles: Iterable[Waitable]):
+        self._handles = list(handles)
+
+    def wait(self):
+        for h in self._handles:
+            h.wait()
+        self._handles = []
+
+    def is_completed(self):
+        return all(h.is_completed() for h in self._handles)
+
+
+class RotateContainer:
+    """Fixed ring of buffers; ``rotate`` advances which one is at index 0."""
+
+    def __init__(self, items: Sequence):
+        self._items = list(items)
+
+    def __getitem__(self, i):
+        return self._items[i]
+
+    def __setitem__(self, i, v):
+        self._items[i] = v
+
+    def __len__(self):
+        return len(self._items)
+
+    def rotate(self):
+        self._items.append(self._items.pop(0))
+
+
+# --------------------------------------------------------------- alignment
+def page_aligned_numel(numel: int, itemsize: int, page: int = PAGE_SIZE) -> int:
+    """Smallest element count >= ``numel`` whose byte size is a page multiple."""
+    per_page = page // itemsize
+    return -(-numel // per_page) * per_page
+
+
+def get_page_aligned_padding_numel(numel: int, itemsize: int) -> int:
+    return page_aligned_numel(numel, itemsize) - numel
+
+
+def partition_aligned_numel(numel: int, parts: int, itemsize: int, page: int = PAGE_SIZE) -> int:
+    """Smallest count >= ``numel`` that splits into ``parts`` page-sized-multiple
+    pieces (flextrain/memory/__init__.py:322-323)."""
+    quantum = parts * (page // itemsize)
+    return -(-numel // quantum) * quantum
+
+
+def get_split_numels(total: int, ratios: Sequence[float], itemsize: int,
+                     num_levels: int = 3, page: int = PAGE_SIZE) -> Tuple[int, ...]:
+    """Cut ``total`` elements into ``num_levels`` consecutive tiers.  ``ratios``
+    gives the share of every tier but the last; interior cut points are rounded
+    to page boundaries and the last tier takes what is left."""
+    per_page = max(1, page // itemsize)
+    ratios = list(ratios)[: num_levels - 1]
+    ratios += [0.0] * (num_levels - 1 - len(ratios))
+    out, used, acc = [], 0, 0.0
+    for r in ratios:
+        acc += r
+        cut = min(total, int(round(acc * total / per_page)) * per_page)
+        cut = max(cut, used)
+        out.append(cut - used)
+        used = cut
+    out.append(total - used)
+    return tuple(out)
+
+
+# -------------------------------------------------------------- allocation
+class _Accounting:
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.bytes: Dict[str, int] = {"hbm": 0, "pinned": 0, "dram": 0}
+
+    def add(self, kind: str, nbytes: int):
+        with self.lock:
+            self.bytes[kind] += nbytes
+
+
+_ACCOUNT = _Accounting()
+_PINNED_KEEPALIVE: List[object] = []
+
+
+def allocated_bytes() -> Dict[str, int]:
+    return dict(_ACCOUNT.bytes)
+
+
+def _pinned_exact(nbytes: int) -> torch.Tensor:
+    """Exact-size page-locked allocation from the native pool (PyTorch's pinned
+    allocator rounds every request up to a power of two, which wastes up to
+    half of a large buffer)."""
+    from ..ops.native import cuda_lib
+    lib = cuda_lib()
+    addr = lib.ft_pinned_alloc(ctypes.c_size_t(max(nbytes, 1)))
+    if not addr:
+        raise MemoryError(f"page-locked allocation of {nbytes} bytes failed")
+    buf = (ctypes.c_uint8 * max(nbytes, 1)).from_address(addr)
+    t = torch.frombuffer(buf, dtype=torch.uint8, count=max(nbytes, 1))
+    _PINNED_KEEPALIVE.append(buf)
+    return t[:nbytes]
+
+
+def allocate_memory(numel: int, dtype: torch.dtype, device, pinned: bool = True,
+                    zero: bool = False) -> torch.Tensor:
+    """Accounted flat allocation.  ``device`` cpu + ``pinned`` gives exact-size
+    page-locked memory when CUDA is in use, plain memory otherwise."""
+    device = torch.device(device)
+    itemsize = torch.empty((), dtype=dtype).element_size()
+    nbytes = numel * itemsize
+    if device.type == "cuda":
+        _ACCOUNT.add("hbm", nbytes)
+        t = torch.empty(numel, dtype=dtype, device=device)
+        return t.zero_() if zero else t
+    if pinned and dist.is_cuda() and numel > 0:
+        _ACCOUNT.add("pinned", nbytes)
+        try:
+            t = _pinned_exact(nbytes).view(dtype)
+        except Exception:
+            t = torch.empty(numel, dtype=dtype).pin_memory()
+        return t.zero_() if zero else t
+    _ACCOUNT.add("dram", nbytes)
+    return torch.zeros(numel, dtype=dtype) if zero else torch.empty(numel, dtype=dtype)
+
+
+def allocate_memory_chunks(numel: int, chunks, dtype: torch.dtype, device,
+                           pinned: bool = True, zero: bool = False):
+    """``chunks`` (an int or a tuple of ints) equal flat buffers, returned as
+    nested lists; they are carved from one allocation."""
+    if isinstance(chunks, int):
+        chunks = (chunks,)
+    total = 1
+    for c in chunks:
+        total *= c
+    flat = allocate_memory(numel * total, dtype, device, pinned, zero)
+
+    def carve(level, offset):
+        if level == len(chunks):
+            return flat[offset * numel:(offset + 1) * numel]
+        stride = 1
+        for c in chunks[level + 1:]:
+            stride *= c
+        return [carve(level + 1, offset + i * stride) for i in range(chunks[level])]
+
+    return carve(0, 0)
+
+
+def free_tensor(t: torch.Tensor, record_stream: bool = False):
+    """Release ``t``'s storage while the Python object stays alive."""
+    if record_stream and t.is_cuda:
+        t.record_stream(torch.cuda.current_stream())
+    t.data = torch.empty(0, dtype=t.dtype, device=t.device)
+
+
+def move_into_contiguous(srcs: Iterable[torch.Tensor], dst: torch.Tensor):
+    """Copy every tensor of ``srcs`` back to back into flat ``dst`` and re-point
+    each source's ``.data`` at its new home."""
+    offset = 0
+    for s in srcs:
+        n = s.numel()
+        view = dst[offset:offset + n].view(s.shape)
+        view.copy_(s.data, non_blocking=True)
+        s.data = view
+        offset += n
+    return offset
+
+
+def copy_segments(srcs: Sequence[torch.Tensor], dsts: Sequence[torch.Tensor]):
+    """Ragged copy: the concatenation of ``srcs`` is written over the
+    concatenation of ``dsts`` (flat tensors; dtype conversion allowed)."""
+    if sum(s.numel() for s in srcs) != sum(d.numel() for d in dsts):
+        raise ValueError("copy_segments: source and destination sizes differ")
+    si = di = so = do = 0
+    while si < len(srcs) and di < len(dsts):
+        s, d = srcs[si], dsts[di]
+        n = min(s.numel() - so, d.numel() - do)
+        if n:
+            d[do:do + n].copy_(s[so:so + n], non_blocking=True)
+        so += n
+        do += n
+        if so == s.numel():
+            si, so = si + 1, 0
+        if do == d.numel():
+            di, do = di + 1, 0
+
+
+class ContiguousParaGroup:
+    """The parameters of one unit in their flat order.
+
+    Parameters with equal ``grouping`` id are made adjacent (stable order inside
+    a group), so every optimizer param group covers few contiguous ranges.
+    ``link_para_to(buffer)`` points every parameter's ``.data`` at its slice of
+    a flat buffer; ``link_grad_to`` does the same for ``.grad``; ``detach_*``
+    drop the views again so the buffer can be reused.
+    """
+
+    def __init__(self, params: Sequence[torch.nn.Parameter],
+                 grouping: Optional[Sequence[int]] = None):
+        params = list(params)
+        if grouping is None:
+            grouping = [0] * len(params)
+        order = sorted(range(len(params)), key=lambda i: (grouping[i], i))
+        self.paras = [params[i] for i in order]
+        self.grouping = [grouping[i] for i in order]
+        self.shapes = [tuple(p.shape) for p in self.paras]
+        self.numels = [p.numel() for p in self.paras]
+        self.numel = sum(self.numels)
+        self.offsets = [0]
+        for n in self.numels:
+            self.offsets.append(self.offsets[-1] + n)
+
+    def link_para_to(self, buffer: torch.Tensor):
+        for p, off, n, shape in zip(self.paras, self.offsets, self.numels, self.shapes):
+            p.data = buffer[off:off + n].view(shape)
+
+    def link_grad_to(self, buffer: torch.Tensor):
+        for p, off, n, shape in zip(self.paras, self.offsets, self.numels, self.shapes):
+            p.grad = buffer[off:off + n].view(shape)
+
+    def detach_para(self):
+        for p in self.paras:
+            p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+
+    def detach_grad(self):
+        for p in self.paras:
+            p.grad = None
+
+
+def get_data_stream() -> StreamSet:
+    """The rank's stream set (compute / h2d / d2h / opt)."""
+    return get_streams()
