@@ -36,9 +36,9 @@ std::map<int, AdamConfig> g_registry;
 
 struct StepConsts {
   float beta1, beta2, one_m_beta1, one_m_beta2;
-  float eps, step_size, inv_sqrt_bc2;
+  float eps, step_size, sqrt_bc2;
   float l2_decay;      // added to the gradient (classic Adam)
-  float decoupled;     // lr * wd, AdamW
+  float decay_factor;  // 1 - lr * wd, AdamW (1 when classic)
   float grad_scale;
 };
 
@@ -56,9 +56,9 @@ inline StepConsts make_consts(int64_t step, float lr, float b1, float b2, float 
     bc2 = 1.0 - std::pow((double)b2, (double)step);
   }
   c.step_size = (float)((double)lr / bc1);
-  c.inv_sqrt_bc2 = (float)(1.0 / std::sqrt(bc2));
+  c.sqrt_bc2 = (float)std::sqrt(bc2);
   c.l2_decay = adamw ? 0.0f : wd;
-  c.decoupled = adamw ? lr * wd : 0.0f;
+  c.decay_factor = adamw ? (float)(1.0 - (double)lr * (double)wd) : 1.0f;
   c.grad_scale = grad_scale;
   return c;
 }
@@ -108,10 +108,10 @@ __attribute__((target("f16c"))) bool adam_block_scalar(
     bad |= !std::isfinite(grad);
     float param = p[i];
     grad += c.l2_decay * param;
-    float mi = c.beta1 * m[i] + c.one_m_beta1 * grad;
-    float vi = c.beta2 * v[i] + c.one_m_beta2 * grad * grad;
-    float denom = std::sqrt(vi) * c.inv_sqrt_bc2 + c.eps;
-    param -= c.decoupled * param;
+    float mi = m[i] + (grad - m[i]) * c.one_m_beta1;
+    float vi = c.beta2 * v[i] + (c.one_m_beta2 * grad) * grad;
+    float denom = std::sqrt(vi) / c.sqrt_bc2 + c.eps;
+    param *= c.decay_factor;
     param -= c.step_size * (mi / denom);
     m[i] = mi;
     v[i] = vi;
@@ -155,11 +155,11 @@ FT_AVX512 inline void store_copy16(void* out, int dtype, int64_t i, __m512 p) {
 
 FT_AVX512 bool adam_block_avx512(const StepConsts& c, float* p, const void* g, int gdt, float* m,
                                  float* v, void* out, int odt, int64_t lo, int64_t hi) {
-  const __m512 b1 = _mm512_set1_ps(c.beta1), b2 = _mm512_set1_ps(c.beta2);
+  const __m512 b2 = _mm512_set1_ps(c.beta2);
   const __m512 ob1 = _mm512_set1_ps(c.one_m_beta1), ob2 = _mm512_set1_ps(c.one_m_beta2);
   const __m512 eps = _mm512_set1_ps(c.eps), step = _mm512_set1_ps(c.step_size);
-  const __m512 ibc2 = _mm512_set1_ps(c.inv_sqrt_bc2), l2 = _mm512_set1_ps(c.l2_decay);
-  const __m512 dec = _mm512_set1_ps(c.decoupled), gs = _mm512_set1_ps(c.grad_scale);
+  const __m512 sbc2 = _mm512_set1_ps(c.sqrt_bc2), l2 = _mm512_set1_ps(c.l2_decay);
+  const __m512 dec = _mm512_set1_ps(c.decay_factor), gs = _mm512_set1_ps(c.grad_scale);
   const __m512 inf = _mm512_set1_ps(INFINITY);
   const __m512 absmask = _mm512_castsi512_ps(_mm512_set1_epi32(0x7fffffff));
   __mmask16 bad = 0;
@@ -170,11 +170,12 @@ FT_AVX512 bool adam_block_avx512(const StepConsts& c, float* p, const void* g, i
     bad |= (__mmask16)~_mm512_cmp_ps_mask(_mm512_and_ps(grad, absmask), inf, _CMP_LT_OQ);
     __m512 param = _mm512_loadu_ps(p + i);
     grad = _mm512_add_ps(grad, _mm512_mul_ps(l2, param));
-    __m512 mi = _mm512_add_ps(_mm512_mul_ps(b1, _mm512_loadu_ps(m + i)), _mm512_mul_ps(ob1, grad));
+    __m512 m_old = _mm512_loadu_ps(m + i);
+    __m512 mi = _mm512_add_ps(m_old, _mm512_mul_ps(_mm512_sub_ps(grad, m_old), ob1));
     __m512 vi = _mm512_add_ps(_mm512_mul_ps(b2, _mm512_loadu_ps(v + i)),
                               _mm512_mul_ps(_mm512_mul_ps(ob2, grad), grad));
-    __m512 denom = _mm512_add_ps(_mm512_mul_ps(_mm512_sqrt_ps(vi), ibc2), eps);
-    param = _mm512_sub_ps(param, _mm512_mul_ps(dec, param));
+    __m512 denom = _mm512_add_ps(_mm512_div_ps(_mm512_sqrt_ps(vi), sbc2), eps);
+    param = _mm512_mul_ps(param, dec);
     param = _mm512_sub_ps(param, _mm512_mul_ps(step, _mm512_div_ps(mi, denom)));
     _mm512_storeu_ps(m + i, mi);
     _mm512_storeu_ps(v + i, vi);

@@ -1,0 +1,341 @@
+"""Step driver: runs the user's pre / layer / post callbacks unit by unit and
+micro-batch by micro-batch in greedy-snake order, with recompute in backward.
+
+Parity: flextrain/engine.py:1-406 - ``_conduct_first_unit`` :116-143,
+``_conduct_forward`` :145-209, ``_conduct_last_unit`` :211-258,
+``_conduct_backward`` :260-324, ``train_iteration`` :368-406, loss-scale
+accessors :326-343, ``step`` no-op :345-346, post-step hooks :348-349.
+
+What differs from the reference
+  * stream ordering uses events only; there is no device-wide synchronise per
+    micro-batch (flextrain/engine.py:174,288);
+  * gradients really are unscaled, checked for inf/nan and the loss scaler is
+    updated once per step (the reference never calls ``update_scale``);
+  * ``every_layer`` may be empty (flextrain/engine.py:313 slices with ``[:-0]``);
+  * throughput, per-tier traffic and health words are reported.
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from .checkpointing import (FWDContext, RNGStatePack, checkpointed_backward, checkpointed_forward,
+                            detach_variable, retrieve_tensor)
+from .config import get_flextrain_config
+from .llm_func import LLMFunc, retrieve_llm_loss
+from .loss_scaler import create_loss_scaler
+from .memory.coordinator.interlayer import get_interlayer_coordinator
+from .memory.coordinator.optimizer import get_opts_coordinator
+from .memory.coordinator.parameter import get_para_coordinator
+from .scheduler import GreedySnakeBlockScheduler, LLMTask
+from .utils import distributed as dist
+from .utils.device import get_streams
+from .utils.logging import rank0_logger
+from .utils.timer import StepTimer
+
+
+def _split_passed_down(passed_down) -> Tuple[torch.Tensor, Tuple, int]:
+    """The one tensor of a passed-down tuple, the tuple with that position
+    blanked, and the position."""
+    if torch.is_tensor(passed_down):
+        return passed_down, (None,), 0
+    items = tuple(passed_down)
+    idx = [i for i, v in enumerate(items) if torch.is_tensor(v)]
+    if len(idx) != 1:
+        raise ValueError("passed_down must contain exactly one tensor")
+    i = idx[0]
+    return items[i], items[:i] + (None,) + items[i + 1:], i
+
+
+def _join_passed_down(template: Tuple, pos: int, tensor: torch.Tensor) -> Tuple:
+    return template[:pos] + (tensor,) + template[pos + 1:]
+
+
+class FlexTrainEngine:
+    """ZeRO-3 data-parallel training of a layer-stacked model whose parameters,
+    optimizer state and activation checkpoints are tiered over HBM, pinned host
+    DRAM and NVMe."""
+
+    def __init__(self, model: torch.nn.Module, optimizer):
+        cfg = get_flextrain_config()
+        self.config = cfg
+        self.model = model
+        self.optimizer = optimizer
+        self.device = dist.current_device()
+        self.streams = get_streams()
+        self.world = dist.get_world_size()
+        self.para = get_para_coordinator()
+        if not self.para.is_initialized:
+            raise RuntimeError("no layer was built inside flextrain.Init(...)")
+        self.inter = get_interlayer_coordinator()
+        self.opts = get_opts_coordinator()
+        self.loss_scaler = create_loss_scaler(cfg.mixed_precision)
+        self._custom_loss_scale: Optional[float] = None
+        self._move_buffers()
+        self.opts.initialize(optimizer, self.loss_scaler)
+
+        self.micro_batch_per_rank = cfg.micro_batches_per_rank(self.world)
+        self.micro_batch_per_batch = self.micro_batch_per_rank      # reference name
+        self.num_units = self.para.num_units
+        self.num_layers = self.para.num_layers
+        self.interval = cfg.checkpoint_interval
+        self.scheduler = GreedySnakeBlockScheduler(self.micro_batch_per_rank, self.num_units)
+        self._post_step_functions: List[Callable[[], Any]] = []
+        self._training = True
+        self.global_steps = 0
+        self.skipped_steps = 0
+        self.timer = StepTimer()
+        self._last_overflow = False
+        self._status: Dict[str, Any] = {"last_step_seconds": None, "watchdog_tripped": False}
+        if cfg.engine.gradient_clipping > 0:
+            rank0_logger.warning("gradient_clipping is ignored: updates are applied unit by unit "
+                                 "while backward is still running, before a global norm exists")
+
+    def _move_buffers(self):
+        for mod in self.model.modules():
+            for name, buf in list(mod.named_buffers(recurse=False)):
+                if buf is not None and buf.device != self.device:
+                    mod._buffers[name] = buf.to(self.device)
+
+    # --------------------------------------------------------------- modes
+    def train(self):
+        self._training = True
+        self.model.train()
+        return self
+
+    def eval(self):
+        self._training = False
+        self.model.eval()
+        return self
+
+    def step(self):
+        """No-op kept for Megatron-style loops: the update happens inside
+        ``train_iteration``."""
+        return None
+
+    def register_post_step_function(self, fn: Callable[[], Any]):
+        self._post_step_functions.append(fn)
+
+    @property
+    def loss_scale(self) -> float:
+        return self._custom_loss_scale if self._custom_loss_scale is not None \
+            else self.loss_scaler.loss_scale
+
+    def override_loss_scale(self, loss_scale: float):
+        self._custom_loss_scale = float(loss_scale)
+        self.loss_scaler.cur_scale = float(loss_scale)
+
+    @property
+    def dynamic_loss_scaling(self) -> bool:
+        return self.loss_scaler.dynamic
+
+    # ------------------------------------------------------- per-step state
+    def _reset_context(self):
+        n = self.micro_batch_per_rank
+        self._pre_inputs: List[Any] = [None] * n
+        self._post_inputs: List[Any] = [None] * n
+        self._loss_inputs: List[Any] = [None] * n
+        self._every_layer: List[Tuple] = [()] * n
+        self._pd_template: List[Tuple] = [(None,)] * n
+        self._pd_pos: List[int] = [0] * n
+        self._rng: Dict[Tuple[int, int], RNGStatePack] = {}
+        self._loss_results: List[Any] = [None] * n
+
+    def _layer_range(self, unit: int) -> Tuple[int, int]:
+        start = unit * self.interval
+        return start, min(start + self.interval, self.num_layers)
+
+    # -------------------------------------------------------------- forward
+    def _unit_function(self, unit: int, mb: int) -> Callable:
+        """The function a unit runs for one micro-batch.  Unit 0 also runs
+        ``pre_process`` (so its backward reaches the embedding); every other
+        unit maps the incoming activation through its layers."""
+        start, end = self._layer_range(unit)
+        if unit == 0:
+            def first_unit():
+                passed_down, every_layer = LLMFunc.pre_process(self._pre_inputs[mb])
+                every_layer = tuple(every_layer)
+                self._every_layer[mb] = every_layer
+                x, template, pos = _split_passed_down(passed_down)
+                self._pd_template[mb], self._pd_pos[mb] = template, pos
+                out = LLMFunc.layer_forward(start, end)(*_join_passed_down(template, pos, x),
+                                                        *every_layer)
+                return retrieve_tensor(out)
+            return first_unit
+
+        def other_unit(x):
+            args = _join_passed_down(self._pd_template[mb], self._pd_pos[mb], x)
+            out = LLMFunc.layer_forward(start, end)(*args, *self._every_layer[mb])
+            return retrieve_tensor(out)
+        return other_unit
+
+    def _enter_unit(self, unit: int, prev_unit: Optional[int], next_unit: Optional[int],
+                    backward: bool):
+        if prev_unit is not None and prev_unit != unit:
+            self.para.release(prev_unit, keep=True)
+        self.para.acquire(unit)
+        if next_unit is not None and next_unit != unit:
+            self.para.submit_gather(next_unit)
+        if backward:
+            self.opts.pre_unit_backward(unit)
+
+    def _conduct_forward(self, task: LLMTask, nxt: Optional[LLMTask]):
+        u, mb = task.unit, task.micro_batch
+        ckpt = self.inter.ckpt
+        if nxt is not None and nxt.unit > 0 and (nxt.unit, nxt.micro_batch) != (u + 1, mb):
+            ckpt.prefetch((nxt.unit, nxt.micro_batch))
+        fn = self._unit_function(u, mb)
+        rng = RNGStatePack()
+        if u == 0:
+            pre, post, loss_in = LLMFunc.get_batch()
+            self._pre_inputs[mb], self._post_inputs[mb], self._loss_inputs[mb] = pre, post, loss_in
+            with torch.no_grad():
+                out = fn()
+        else:
+            x = ckpt.get((u, mb))
+            with torch.no_grad():
+                out = fn(x)
+            ckpt.done_with((u, mb))
+        self._rng[(u, mb)] = rng
+        consumed_next = nxt is not None and (nxt.unit, nxt.micro_batch) == (u + 1, mb)
+        n = self.micro_batch_per_rank
+        order_pos = self._pos_in_unit(task)
+        margin = order_pos < 1 or order_pos >= n - 1
+        ckpt.put((u + 1, mb), out, pin_to_dram=margin, hot=consumed_next)
+
+    def _pos_in_unit(self, task: LLMTask) -> int:
+        tasks = self.scheduler.tasks
+        idx = tasks.index(task)
+        return idx % self.micro_batch_per_rank
+
+    # ------------------------------------------------------------- backward
+    def _conduct_last_unit(self, task: LLMTask):
+        u, mb = task.unit, task.micro_batch
+        start, end = self._layer_range(u)
+        scale = self.loss_scale / self.micro_batch_per_rank
+        with torch.enable_grad():
+            if u == 0:
+                pre, post, loss_in = LLMFunc.get_batch()
+                self._pre_inputs[mb], self._post_inputs[mb], self._loss_inputs[mb] = pre, post, loss_in
+                out = self._unit_function(0, mb)()
+                x = None
+            else:
+                x = detach_variable(self.inter.ckpt.get((u, mb)))
+                out = self._unit_function(u, mb)(x)
+            passed = _join_passed_down(self._pd_template[mb], self._pd_pos[mb], out)
+            outputs = LLMFunc.post_process(passed, self._post_inputs[mb])
+            loss_rst = LLMFunc.loss(outputs, self._loss_inputs[mb])
+            self._loss_results[mb] = loss_rst
+            loss = retrieve_llm_loss(loss_rst).float() * scale
+            torch.autograd.backward(loss)
+        return None if x is None else x.grad
+
+    def _conduct_backward(self, task: LLMTask, nxt: Optional[LLMTask]):
+        u, mb = task.unit, task.micro_batch
+        ckpt, grads = self.inter.ckpt, self.inter.grad
+        if nxt is not None:
+            if nxt.unit > 0:
+                ckpt.prefetch((nxt.unit, nxt.micro_batch))
+            if nxt.micro_batch != mb:
+                grads.prefetch(nxt.micro_batch)
+        if u == self.num_units - 1:
+            dx = self._conduct_last_unit(task)
+        else:
+            fn = self._unit_function(u, mb)
+            dy = grads.get(mb)
+            if u == 0:
+                ctx = FWDContext(fn, self._rng[(u, mb)], ())
+                checkpointed_backward(ctx, dy)
+                dx = None
+            else:
+                x = ckpt.get((u, mb))
+                ctx = FWDContext(fn, self._rng[(u, mb)], (x,))
+                dx = checkpointed_backward(ctx, dy)[0]
+            grads.done_with(mb)
+        if u > 0:
+            ckpt.done_with((u, mb), drop=True)
+            hot = nxt is not None and nxt.micro_batch == mb and nxt.unit == u - 1
+            grads.put(mb, dx, hot=hot, store=not hot)
+        else:
+            grads.drop(mb)
+        self.opts.post_micro_batch_backward(u)
+
+    # ------------------------------------------------------------ iteration
+    def train_iteration(self):
+        """One optimizer step over ``batch_size`` samples.  Returns the list of
+        per-micro-batch loss results (whatever the ``loss`` callback returned)."""
+        cfg = self.config
+        self.timer.start_step()
+        self._reset_context()
+        self.opts.prune_pending()
+        fwd, bwd = self.scheduler.forward_tasks, self.scheduler.backward_tasks
+        self.para.submit_gather(fwd[0].unit if fwd else bwd[0].unit)
+
+        prev_unit = None
+        for i, task in enumerate(fwd):
+            nxt = fwd[i + 1] if i + 1 < len(fwd) else bwd[0]
+            if task.unit != prev_unit:
+                following = task.unit + 1 if task.unit + 1 < self.num_units else None
+                self._enter_unit(task.unit, prev_unit, following, backward=False)
+                prev_unit = task.unit
+            self._conduct_forward(task, nxt)
+
+        self.optimizer.update_states()
+        for i, task in enumerate(bwd):
+            nxt = bwd[i + 1] if i + 1 < len(bwd) else None
+            if task.unit != prev_unit or i == 0:
+                following = task.unit - 1 if task.unit > 0 else None
+                self._enter_unit(task.unit, prev_unit, following, backward=True)
+                prev_unit = task.unit
+            self._conduct_backward(task, nxt)
+            if nxt is None or nxt.unit != task.unit:
+                self.opts.post_unit_backward(task.unit)
+        self.para.release(prev_unit)
+
+        overflow = self._finish_step()
+        self.global_steps += 1
+        if overflow:
+            self.skipped_steps += 1
+        for fn in self._post_step_functions:
+            fn()
+        self.timer.end_step()
+        if cfg.auto_config and self.global_steps == 1:
+            from .auto_config import system_auto_config
+            system_auto_config(self)
+        return list(self._loss_results)
+
+    def _finish_step(self) -> bool:
+        grad_scale = 1.0 / float(self.loss_scale)
+        overflow = self.opts.finish_step()
+        overflow |= self.optimizer.step(grad_scale=grad_scale,
+                                        check_overflow=self.opts.check_overflow)
+        if self.opts.check_overflow:
+            if self.world > 1:
+                overflow = dist.all_reduce_scalar(float(overflow), dist.ReduceOp.MAX) > 0
+            self.loss_scaler.update_scale(overflow)
+            if self._custom_loss_scale is not None:
+                self._custom_loss_scale = self.loss_scaler.loss_scale
+        self._last_overflow = overflow
+        return overflow
+
+    # --------------------------------------------------------------- extras
+    def synchronize(self):
+        """Wait for every queued device and host task of this rank."""
+        self.opts.wait_all()
+        self.streams.synchronize()
+
+    def health(self) -> Dict[str, Any]:
+        """Status words of the runtime: pending host updates, traffic counters,
+        skipped steps, last step time, watchdog."""
+        out = dict(self._status)
+        out.update(global_steps=self.global_steps, skipped_steps=self.skipped_steps,
+                   loss_scale=self.loss_scale, last_overflow=self._last_overflow,
+                   pending_host_updates=len(self.opts._pending),
+                   traffic=self.inter.traffic(), opt_d2h_bytes=self.opts.bytes_d2h)
+        out.update(self.timer.summary())
+        return out
+
+    def shutdown(self):
+        self.opts.shutdown()

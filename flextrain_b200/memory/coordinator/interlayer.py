@@ -1,0 +1,274 @@
+"""Inter-layer coordinator: tiering of the activation checkpoint of every
+``(unit, micro_batch)`` and of the activation gradient handed from unit to unit
+in backward.
+
+Parity: flextrain/memory/coordinator/interlayer.py:1-373 (lazy init on first
+offload :41-147, landing buffers :79-93, NVMe margin :108-113, prefetch /
+offload bodies :203-231,280-294, hooks :252-360).
+
+Each tensor is cut ``[HBM | pinned DRAM | NVMe]`` by ``split_ratio.checkpoint``
+(checkpoints) or ``[HBM | DRAM]`` by ``split_ratio.gradient`` (activation
+gradients).  ``put`` copies the non-HBM pieces out on the d2h stream behind a
+compute event and drops the producer's tensor once that is done; ``prefetch``
+re-assembles a tensor into one of two HBM landing buffers on the h2d stream one
+task ahead of its consumer; ``get`` makes the compute stream wait for it.  With
+an HBM share of 1.0 the store keeps the tensor itself and nothing is copied -
+the normal case on a 180 GB part.  The NVMe piece of a checkpoint is the file
+``rank{r}_CKPT_layer{u}-{mb}.swp``; the first and last micro-batch of every
+unit (the snake turn) never go to NVMe.
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, Optional, Tuple
+
+import torch
+
+from ...config import get_flextrain_config
+from ...utils import distributed as dist
+from ...utils.device import DONE, Event, get_streams
+from .. import (FlexTrainDataID, FlexTrainDataType, allocate_memory, get_split_numels)
+from ..nvme_swapper import get_nvme_swapper
+
+
+class _Slot:
+    __slots__ = ("shape", "dtype", "whole", "hot", "gpu", "cpu", "nvme_id", "stored", "landing",
+                 "ready", "io")
+
+    def __init__(self):
+        self.whole = None      # the tensor itself when everything stays in HBM
+        self.hot = None        # the producer's tensor, kept for an immediate consumer
+        self.gpu = None
+        self.cpu = None
+        self.nvme_id = None
+        self.stored: Event = DONE
+        self.landing = None
+        self.ready: Optional[Event] = None
+        self.io = None
+
+
+class TieredTensorStore:
+    """Keyed store of equally sized tensors with a fixed tier split."""
+
+    def __init__(self, data_type: FlexTrainDataType, ratios: Tuple[float, float], allow_nvme: bool):
+        self.data_type = data_type
+        self.ratios = ratios
+        self.allow_nvme = allow_nvme
+        self.device = dist.current_device()
+        self.streams = get_streams()
+        self._slots: Dict[Hashable, _Slot] = {}
+        self._numel = None
+        self._tiers = None
+        self._landing = []
+        self._landing_free = []
+        self._nvme_stage = []
+        self._pool_cpu = []        # recycled pinned pieces
+        self._pool_gpu = []
+        self.bytes_d2h = 0
+        self.bytes_h2d = 0
+
+    # ----------------------------------------------------------------- init
+    def _lazy_init(self, t: torch.Tensor):
+        self._numel = t.numel()
+        self._dtype = t.dtype
+        itemsize = t.element_size()
+        gpu, cpu = self.ratios
+        if not self.allow_nvme:
+            cpu = 1.0 - gpu
+        self._tiers = get_split_numels(self._numel, (gpu, cpu), itemsize)
+        self.all_hbm = self._tiers[1] == 0 and self._tiers[2] == 0
+        if not self.all_hbm:
+            self._landing = [allocate_memory(self._numel, t.dtype, self.device) for _ in range(2)]
+            self._landing_free = [DONE, DONE]
+            if self._tiers[2]:
+                self._nvme_stage = [allocate_memory(self._tiers[2], t.dtype, "cpu", True)
+                                    for _ in range(2)]
+                self._stage_busy = [None, None]
+                self._stage_next = 0
+
+    def _data_id(self, key):
+        if isinstance(key, tuple):
+            return FlexTrainDataID(self.data_type, "-".join(str(k) for k in key))
+        return FlexTrainDataID(self.data_type, key)
+
+    # ------------------------------------------------------------------ put
+    @torch.no_grad()
+    def put(self, key, tensor: torch.Tensor, pin_to_dram: bool = False, hot: bool = False,
+            store: bool = True):
+        """Store ``tensor`` (produced on the compute stream).  ``pin_to_dram``
+        keeps the would-be NVMe piece in DRAM (margin micro-batches).  ``hot``
+        keeps the tensor itself for the very next consumer (the snake turn);
+        ``store=False`` then skips the tier copies because nobody else will
+        ever ask for it."""
+        if self._numel is None:
+            self._lazy_init(tensor)
+        if tensor.numel() != self._numel:
+            raise ValueError("all tensors of one store must have the same size")
+        slot = self._slots.get(key) or _Slot()
+        self._slots[key] = slot
+        slot.shape, slot.dtype = tensor.shape, tensor.dtype
+        if slot.landing is not None:
+            self._landing_free[slot.landing] = self.streams.compute.record()
+        slot.ready, slot.landing = None, None
+        slot.hot = tensor if hot else None
+        if self.all_hbm:
+            slot.whole = tensor
+            return
+        if hot and not store:
+            return
+        g, c, n = self._tiers
+        flat = tensor.reshape(-1)
+        produced = self.streams.compute.record()
+        st = self.streams
+        with st.d2h.use():
+            st.d2h.wait(produced)
+            if g:
+                slot.gpu = slot.gpu if slot.gpu is not None else (
+                    self._pool_gpu.pop() if self._pool_gpu else
+                    allocate_memory(g, tensor.dtype, self.device))
+                slot.gpu.copy_(flat[:g], non_blocking=True)
+            host_n = c + (n if (pin_to_dram or not n) else 0)
+            if pin_to_dram and n:
+                # whole non-HBM part stays in DRAM
+                if slot.cpu is None or slot.cpu.numel() != c + n:
+                    slot.cpu = allocate_memory(c + n, tensor.dtype, "cpu", True)
+                slot.cpu.copy_(flat[g:], non_blocking=True)
+                slot.nvme_id = None
+            else:
+                if c:
+                    if slot.cpu is None or slot.cpu.numel() != c:
+                        slot.cpu = self._pool_cpu.pop() if self._pool_cpu else \
+                            allocate_memory(c, tensor.dtype, "cpu", True)
+                    slot.cpu.copy_(flat[g:g + c], non_blocking=True)
+                if n:
+                    i = self._stage_next
+                    self._stage_next = (i + 1) % 2
+                    if self._stage_busy[i] is not None:
+                        self._stage_busy[i].wait()
+                    stage = self._nvme_stage[i]
+                    stage.copy_(flat[g + c:], non_blocking=True)
+                    copied = st.d2h.record()
+                    copied.synchronize()
+                    slot.nvme_id = self._data_id(key)
+                    slot.io = get_nvme_swapper().swap_out(slot.nvme_id, stage, async_op=True)
+                    self._stage_busy[i] = slot.io
+            self.bytes_d2h += (self._numel - g) * tensor.element_size()
+            slot.stored = st.d2h.record()
+        # the producer's storage may be recycled only after the copies have read it
+        if tensor.is_cuda:
+            tensor.record_stream(st.d2h.raw)
+
+    # ------------------------------------------------------------- prefetch
+    @torch.no_grad()
+    def prefetch(self, key):
+        """Start re-assembling ``key`` into a landing buffer (h2d stream)."""
+        slot = self._slots.get(key)
+        if slot is None or self.all_hbm or slot.ready is not None or slot.hot is not None:
+            return
+        g, c, n = self._tiers
+        idx = 0 if self._landing_free[0] is not None else 1
+        if self._landing_free[idx] is None:
+            raise RuntimeError("both landing buffers are in use: consume one before prefetching")
+        free_ev = self._landing_free[idx]
+        self._landing_free[idx] = None
+        land = self._landing[idx]
+        st = self.streams
+        stage = None
+        if slot.nvme_id is not None:
+            if slot.io is not None:
+                slot.io.wait()
+                slot.io = None
+            i = self._stage_next
+            self._stage_next = (i + 1) % 2
+            if self._stage_busy[i] is not None:
+                self._stage_busy[i].wait()
+                self._stage_busy[i] = None
+            stage = self._nvme_stage[i]
+            get_nvme_swapper().swap_in(slot.nvme_id, stage)
+        with st.h2d.use():
+            st.h2d.wait(free_ev)
+            st.h2d.wait(slot.stored)
+            if g:
+                land[:g].copy_(slot.gpu, non_blocking=True)
+            if slot.cpu is not None:
+                land[g:g + slot.cpu.numel()].copy_(slot.cpu, non_blocking=True)
+            if stage is not None:
+                land[g + c:].copy_(stage, non_blocking=True)
+            self.bytes_h2d += (self._numel - g) * land.element_size()
+            slot.ready = st.h2d.record()
+        if stage is not None:
+            slot.ready.synchronize()      # the stage buffer is reused by the next transfer
+        slot.landing = idx
+
+    # ------------------------------------------------------------------ get
+    def get(self, key) -> torch.Tensor:
+        """The tensor on the device, valid on the compute stream."""
+        slot = self._slots[key]
+        if self.all_hbm:
+            return slot.whole
+        if slot.hot is not None:
+            hot, slot.hot = slot.hot, None
+            return hot
+        if slot.ready is None:
+            self.prefetch(key)
+        self.streams.compute.wait(slot.ready)
+        return self._landing[slot.landing].view(slot.shape)
+
+    def done_with(self, key, drop: bool = False):
+        """The consumer has queued its last read of ``key`` on the compute stream."""
+        slot = self._slots.get(key)
+        if slot is None:
+            return
+        if slot.landing is not None:
+            self._landing_free[slot.landing] = self.streams.compute.record()
+            slot.landing, slot.ready = None, None
+        if drop:
+            self.drop(key)
+
+    def drop(self, key):
+        slot = self._slots.pop(key, None)
+        if slot is None:
+            return
+        if slot.landing is not None:
+            self._landing_free[slot.landing] = self.streams.compute.record()
+        if slot.cpu is not None and self._tiers and slot.cpu.numel() == self._tiers[1]:
+            self._pool_cpu.append(slot.cpu)
+        if slot.gpu is not None:
+            self._pool_gpu.append(slot.gpu)
+        if slot.nvme_id is not None and slot.io is not None:
+            slot.io.wait()
+
+    def __contains__(self, key):
+        return key in self._slots
+
+    def clear(self):
+        for key in list(self._slots):
+            self.drop(key)
+
+
+class FlexTrainInterLayerCoordinator:
+    """Two stores: activation checkpoints keyed ``(unit, micro_batch)`` and
+    activation gradients keyed ``micro_batch``."""
+
+    def __init__(self):
+        cfg = get_flextrain_config()
+        self.ckpt = TieredTensorStore(FlexTrainDataType.CKPT, cfg.split_ratio.checkpoint, True)
+        self.grad = TieredTensorStore(FlexTrainDataType.GRAD, cfg.split_ratio.gradient, False)
+
+    def traffic(self):
+        return {"ckpt_d2h": self.ckpt.bytes_d2h, "ckpt_h2d": self.ckpt.bytes_h2d,
+                "grad_d2h": self.grad.bytes_d2h, "grad_h2d": self.grad.bytes_h2d}
+
+
+_INTER: Optional[FlexTrainInterLayerCoordinator] = None
+
+
+def get_interlayer_coordinator() -> FlexTrainInterLayerCoordinator:
+    global _INTER
+    if _INTER is None:
+        _INTER = FlexTrainInterLayerCoordinator()
+    return _INTER
+
+
+def reset_interlayer_coordinator():
+    global _INTER
+    _INTER = None

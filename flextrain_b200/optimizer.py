@@ -1,0 +1,244 @@
+"""Optimizer front-end: maps param groups onto the partitioned unit buffers and
+owns the parameters that live outside the layer stack.
+
+Parity: flextrain/optimizer.py:1-272 - ``FlexTrainCPUOptimizer`` ABC :24-95
+(``_init_optimizer_states``, ``_step``, ``step(step_contexts)``,
+``profile_step``), ``FlexTrainOptimizer`` :98-272 (param -> group map, per-unit
+``GroupSegment`` lists, non-layerwise parameters in one contiguous device
+buffer with fp32 master and states, ``step`` = all-reduce AVG -> Adam -> copy
+back, ``update_states`` increments ``group["step"]``).
+
+Differences: ``param_groups`` may also be a plain iterable of tensors; the
+non-layerwise parameters are stepped on the device when their state fits there
+(the reference always round-trips them through the host), with gradient
+unscaling and the overflow flag folded into the same kernel.
+"""
+from __future__ import annotations
+
+import time
+from abc import ABC, abstractmethod
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import torch
+
+from .param_group import (GroupSegment, StepContext, create_group_segments, create_step_contexts,
+                          slice_segments)
+from .utils import distributed as dist
+
+STEP_KEY = "step"
+PARAMS_KEY = "params"
+
+
+class FlexTrainCPUOptimizer(ABC):
+    """Host optimizer over flat fp32 state.  Sub-classes supply the state
+    layout and the fused update of one contiguous range."""
+
+    optimizer_state_per_element = 0
+
+    def __init__(self, param_groups=None):
+        self.param_groups_arg = param_groups
+
+    @abstractmethod
+    def _init_optimizer_states(self, numel: int, dtype: torch.dtype, pin: bool = False) -> List[torch.Tensor]:
+        ...
+
+    @abstractmethod
+    def _step(self, ctx: StepContext, step: int, grad_scale: float = 1.0) -> bool:
+        ...
+
+    @torch.no_grad()
+    def step(self, step_contexts, step: Optional[int] = None, grad_scale: float = 1.0) -> bool:
+        """Update every non-empty context.  ``step`` defaults to the group's own
+        counter.  Returns True if a non-finite gradient was met."""
+        if isinstance(step_contexts, StepContext):
+            step_contexts = [step_contexts]
+        bad = False
+        for ctx in step_contexts:
+            if ctx.grad.numel() == 0:
+                continue
+            s = step if step is not None else int(ctx.group.get(STEP_KEY, 1))
+            bad |= bool(self._step(ctx, max(s, 1), grad_scale))
+        return bad
+
+    @torch.no_grad()
+    def profile_step(self, numel: int, device_dtype: torch.dtype, master_dtype: torch.dtype) -> float:
+        """One timed update over ``numel`` synthetic elements; seconds."""
+        cache = getattr(self, "_profile", None)
+        if cache is None or cache["numel"] != numel:
+            cache = dict(numel=numel, group={STEP_KEY: 0, **getattr(self, "defaults", {})},
+                         half=torch.empty(numel, dtype=device_dtype),
+                         full=torch.randn(numel, dtype=master_dtype),
+                         grad=torch.randn(numel, dtype=master_dtype),
+                         states=self._init_optimizer_states(numel, master_dtype))
+            self._profile = cache
+        cache["group"][STEP_KEY] += 1
+        ctx = StepContext(cache["group"], cache["full"], cache["grad"], cache["states"], cache["half"])
+        t0 = time.perf_counter()
+        self._step(ctx, cache["group"][STEP_KEY])
+        return time.perf_counter() - t0
+
+
+def _normalise_param_groups(param_groups, defaults: Dict) -> List[Dict]:
+    groups = list(param_groups)
+    if not groups:
+        raise ValueError("optimizer got an empty parameter list")
+    if not isinstance(groups[0], dict):
+        groups = [{PARAMS_KEY: groups}]
+    out = []
+    for g in groups:
+        g = dict(g)
+        params = g[PARAMS_KEY]
+        g[PARAMS_KEY] = [params] if isinstance(params, torch.Tensor) else list(params)
+        for k, v in defaults.items():
+            g.setdefault(k, v)
+        g.setdefault(STEP_KEY, 0)
+        out.append(g)
+    return out
+
+
+class FlexTrainOptimizer:
+    """Holds the param groups, the per-unit group segments the coordinators
+    need, and the optimizer state of the non-layerwise parameters."""
+
+    def __init__(self, param_groups, cpu_optimizer: FlexTrainCPUOptimizer):
+        from .config import get_flextrain_config
+        from .memory.coordinator.parameter import get_para_coordinator
+        self.cpu_optimizer = cpu_optimizer
+        self.param_groups: List[Dict] = _normalise_param_groups(param_groups, cpu_optimizer.defaults)
+        self.optimizer_state_per_element = cpu_optimizer.optimizer_state_per_element
+        cfg = get_flextrain_config()
+        para = get_para_coordinator()
+        self._cfg = cfg
+        self.device = dist.current_device()
+        self.device_dtype = cfg.mixed_precision.device_dtype
+        self.master_dtype = cfg.mixed_precision.master_dtype
+
+        # ---- parameter -> group index
+        group_of: Dict[int, int] = {}
+        for gi, g in enumerate(self.param_groups):
+            for p in g[PARAMS_KEY]:
+                if id(p) in group_of:
+                    raise ValueError("a parameter appears in more than one param group")
+                group_of[id(p)] = gi
+
+        # ---- layer parameters: segments over each unit's flat buffer
+        self.unit_group_segments: List[List[GroupSegment]] = []
+        layer_param_ids = set()
+        for u in range(para.num_units):
+            grp = para.unit_group(u)
+            gids = []
+            for p in grp.paras:
+                layer_param_ids.add(id(p))
+                if id(p) not in group_of:
+                    raise ValueError("a layer parameter is missing from the optimizer's param groups")
+                gids.append(group_of[id(p)])
+            segs = create_group_segments(grp.numels, gids)
+            # padding up to the aligned unit size follows the last group
+            pad = para.aligned_unit_numel - grp.numel
+            if pad:
+                last = segs[-1].group if segs else 0
+                segs = segs + [GroupSegment(last, grp.numel, para.aligned_unit_numel)]
+                from .param_group import merge_segments
+                segs = merge_segments(segs)
+            self.unit_group_segments.append(segs)
+
+        # ---- everything else is replicated on every rank ("non-layerwise")
+        self.non_layerwise_params: List[torch.nn.Parameter] = []
+        nl_groups: List[int] = []
+        for gi, g in enumerate(self.param_groups):
+            for p in g[PARAMS_KEY]:
+                if id(p) not in layer_param_ids:
+                    self.non_layerwise_params.append(p)
+                    nl_groups.append(gi)
+        self._build_non_layerwise(nl_groups)
+        para.detach_all_parameters()
+
+    # ------------------------------------------------------ non-layerwise
+    def _build_non_layerwise(self, groups: Sequence[int]):
+        params = self.non_layerwise_params
+        numels = [p.numel() for p in params]
+        total = sum(numels)
+        self._nl_numel = total
+        self._nl_segments = create_group_segments(numels, groups) if params else []
+        if not params:
+            return
+        from .memory import allocate_memory, move_into_contiguous
+        dev, mp = self.device, self._cfg.mixed_precision
+        where = self._cfg.engine.nonlayer_optimizer_device
+        self._nl_on_device = (where == "gpu") or (where == "auto")
+        self._nl_para = allocate_memory(total, self.device_dtype, dev)
+        self._nl_grad = allocate_memory(total, self.device_dtype, dev, zero=True)
+        move_into_contiguous(params, self._nl_para)
+        off = 0
+        for p, n in zip(params, numels):
+            p.grad = self._nl_grad[off:off + n].view(p.shape)
+            off += n
+        state_dev = dev if self._nl_on_device else torch.device("cpu")
+        pinned = not self._nl_on_device
+        self._nl_master = allocate_memory(total, self.master_dtype, state_dev, pinned)
+        self._nl_master.copy_(self._nl_para)
+        self._nl_states = [allocate_memory(total, self.master_dtype, state_dev, pinned, zero=True)
+                           for _ in range(self.optimizer_state_per_element)]
+        if not self._nl_on_device:
+            self._nl_host_grad = allocate_memory(total, torch.float32, "cpu", True)
+            self._nl_host_para = allocate_memory(total, self.device_dtype, "cpu", True)
+        self._nl_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    @torch.no_grad()
+    def step(self, grad_scale: float = 1.0, check_overflow: bool = False) -> bool:
+        """Average the replicated gradients over ranks and apply one update to
+        the non-layerwise parameters.  Returns True if the step was skipped
+        because of a non-finite gradient."""
+        if not self.non_layerwise_params:
+            return False
+        from .ops.adam.gpu_adam import device_adam_update, has_nonfinite
+        dist.all_reduce(self._nl_grad, dist.ReduceOp.AVG)
+        overflow = False
+        if check_overflow:
+            overflow = has_nonfinite(self._nl_grad)
+        if not overflow:
+            if self._nl_on_device:
+                for seg in self._nl_segments:
+                    g = self.param_groups[seg.group]
+                    sl = slice(seg.start, seg.end)
+                    device_adam_update(g, max(int(g[STEP_KEY]), 1), self.cpu_optimizer,
+                                       self._nl_master[sl], self._nl_grad[sl],
+                                       [s[sl] for s in self._nl_states], self._nl_para[sl],
+                                       grad_scale=grad_scale)
+            else:
+                self._nl_host_grad.copy_(self._nl_grad)     # synchronous: pageable semantics
+                if self.device.type == "cuda":
+                    torch.cuda.current_stream().synchronize()
+                ctxs = create_step_contexts(self.param_groups, self._nl_segments, self._nl_master,
+                                            self._nl_host_grad, self._nl_states, self._nl_host_para)
+                self.cpu_optimizer.step(ctxs, grad_scale=grad_scale)
+                self._nl_para.copy_(self._nl_host_para, non_blocking=True)
+        self._nl_grad.zero_()
+        return overflow
+
+    def update_states(self):
+        """Advance every group's step counter (once per training iteration)."""
+        for g in self.param_groups:
+            g[STEP_KEY] += 1
+
+    # -------------------------------------------------- state (save / load)
+    def non_layerwise_state(self):
+        if not self.non_layerwise_params:
+            return {}
+        return {"master": self._nl_master.detach().cpu().clone(),
+                "states": [s.detach().cpu().clone() for s in self._nl_states]}
+
+    def load_non_layerwise_state(self, state):
+        if not state:
+            return
+        self._nl_master.copy_(state["master"])
+        for dst, src in zip(self._nl_states, state["states"]):
+            dst.copy_(src)
+        self._nl_para.copy_(self._nl_master)
+
+    def hyper_state(self):
+        return [{k: v for k, v in g.items() if k != PARAMS_KEY} for g in self.param_groups]
+
+    def load_hyper_state(self, state):
+        for g, s in zip(self.param_groups, state):
+            g.update(s)
