@@ -92,10 +92,14 @@ class LlamaBlock(nn.Module):
         d, nh, nkv = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
         h = F.rmsnorm(x, self.attn_norm, cfg.eps)
         qkv = F.linear(h, self.wqkv)
-        q = qkv[..., : nh * d].reshape(B, S, nh, d)
-        k = qkv[..., nh * d: (nh + nkv) * d].reshape(B, S, nkv, d)
-        v = qkv[..., (nh + nkv) * d:].reshape(B, S, nkv, d)
-        q, k = F.rope(q, cos, sin), F.rope(k, cos, sin)
+        if qkv.is_cuda:
+            # rotate the q and k heads inside the fused projection; q, k, v stay views
+            qkv = F.rope_heads_inplace(qkv, cos, sin, nh + nkv, d)
+        q = qkv[..., : nh * d].unflatten(-1, (nh, d))
+        k = qkv[..., nh * d: (nh + nkv) * d].unflatten(-1, (nkv, d))
+        v = qkv[..., (nh + nkv) * d:].unflatten(-1, (nkv, d))
+        if not qkv.is_cuda:
+            q, k = F.rope(q, cos, sin), F.rope(k, cos, sin)
         a = F.causal_attention(q, k, v).reshape(B, S, H)
         x = x + F.linear(a, self.wo)
         h = F.rmsnorm(x, self.ffn_norm, cfg.eps)

@@ -1,0 +1,289 @@
+"""Autograd bindings of the hand-written sm_100a kernels.
+
+Each op is a ``torch.autograd.Function`` whose forward and backward launch the
+kernels of ``csrc/kernels`` on the current CUDA stream.  There is no eager
+fallback here: if the CUDA library is missing these raise.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+
+import torch
+
+from .native import cuda_lib, dtype_code, ptr, stream_handle
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed (code {rc})")
+
+
+# --------------------------------------------------------------------- GEMM
+def gemm(a: torch.Tensor, a_mn: bool, b: torch.Tensor, b_mn: bool, m: int, n: int, k: int,
+         out: Optional[torch.Tensor] = None, accumulate: bool = False,
+         out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``out[m, n] (+)= sum_k A(m, k) B(n, k)`` on the tcgen05 tensor cores.
+    ``a`` is stored ``[m, k]`` (``a_mn=False``) or ``[k, m]`` (``a_mn=True``);
+    ``b`` is stored ``[n, k]`` or ``[k, n]`` likewise.  Inputs are 2-D with unit
+    inner stride."""
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("gemm operands must both be bf16 or both fp16")
+    if a.stride(-1) != 1 or b.stride(-1) != 1:
+        raise ValueError("gemm operands need unit inner stride")
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype or a.dtype, device=a.device)
+        accumulate = False
+    rc = cuda_lib().ft_gemm(ptr(a), int(a_mn), a.stride(0), ptr(b), int(b_mn), b.stride(0), ptr(out),
+                            out.stride(0), dtype_code(out.dtype), int(accumulate), m, n, k,
+                            dtype_code(a.dtype), stream_handle())
+    _check(rc, "ft_gemm")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        k = x.shape[-1]
+        x2 = x.reshape(-1, k)
+        if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
+            x2 = x2.contiguous()
+        n = w.shape[0]
+        y = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+        gemm(x2, False, w, False, x2.shape[0], n, k, out=y.view(-1, n))
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        n, k = w.shape
+        dy2 = dy.reshape(-1, n)
+        if dy2.stride(-1) != 1 or (dy2.stride(0) * dy2.element_size()) % 16:
+            dy2 = dy2.contiguous()
+        m = dy2.shape[0]
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, False, w, True, m, k, n).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            g = w.grad
+            if g is not None and g.shape == w.shape and g.is_contiguous() and g.dtype == w.dtype:
+                # accumulate straight into the engine's gradient buffer
+                gemm(dy2, True, x2, True, n, k, m, out=g, accumulate=True)
+            else:
+                dw = gemm(dy2, True, x2, True, n, k, m)
+        return dx, dw
+
+
+def linear(x, w):
+    return _Linear.apply(x, w)
+
+
+# ------------------------------------------------------------------ RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        h = x.shape[-1]
+        x2 = x.reshape(-1, h).contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        inv = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(cuda_lib().ft_rmsnorm_fwd(ptr(x2), ptr(w), ptr(y), ptr(inv), rows, h, float(eps),
+                                         dtype_code(x.dtype), stream_handle()), "ft_rmsnorm_fwd")
+        ctx.save_for_backward(x2, w, inv)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, inv = ctx.saved_tensors
+        rows, h = x2.shape
+        dy2 = dy.reshape(rows, h).contiguous()
+        dx = torch.empty_like(x2)
+        dw = torch.empty_like(w)
+        lib = cuda_lib()
+        part = torch.empty(lib.ft_rmsnorm_bwd_parts() * h, dtype=torch.float32, device=x2.device)
+        _check(lib.ft_rmsnorm_bwd(ptr(x2), ptr(w), ptr(dy2), ptr(inv), ptr(dx), ptr(dw), ptr(part), rows,
+                                  h, dtype_code(x2.dtype), stream_handle()), "ft_rmsnorm_bwd")
+        return dx.view(dy.shape), dw, None
+
+
+def rmsnorm(x, w, eps):
+    return _RMSNorm.apply(x, w, eps)
+
+
+# --------------------------------------------------------------------- RoPE
+def _rope_launch(x, y, cos, sin, heads, d, seq_len, sign):
+    tokens = x.numel() // x.shape[-1] if x.dim() > 1 else 1
+    xs = x.reshape(-1, x.shape[-1]) if x.is_contiguous() else x
+    tok_stride_x = x.stride(-2) if x.dim() >= 2 else x.shape[-1]
+    tok_stride_y = y.stride(-2) if y.dim() >= 2 else y.shape[-1]
+    _check(cuda_lib().ft_rope(ptr(x), tok_stride_x, ptr(y), tok_stride_y, ptr(cos), ptr(sin), tokens,
+                              heads, d, seq_len, float(sign), dtype_code(x.dtype), stream_handle()),
+           "ft_rope")
+
+
+class _RopeHeads(torch.autograd.Function):
+    """Rotate the first ``heads`` heads of every row of ``x`` ``[B, S, W]`` in
+    place (rows may be wider than ``heads * d``: the rest is left untouched)."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin, heads, d):
+        B, S = x.shape[0], x.shape[1]
+        _check(cuda_lib().ft_rope(ptr(x), x.stride(1), ptr(x), x.stride(1), ptr(cos), ptr(sin), B * S,
+                                  heads, d, S, 1.0, dtype_code(x.dtype), stream_handle()), "ft_rope")
+        ctx.mark_dirty(x)
+        ctx.save_for_backward(cos, sin)
+        ctx.meta = (heads, d)
+        return x
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        heads, d = ctx.meta
+        dy = dy.contiguous()
+        B, S = dy.shape[0], dy.shape[1]
+        _check(cuda_lib().ft_rope(ptr(dy), dy.stride(1), ptr(dy), dy.stride(1), ptr(cos), ptr(sin), B * S,
+                                  heads, d, S, -1.0, dtype_code(dy.dtype), stream_handle()), "ft_rope")
+        return dy, None, None, None, None
+
+
+def rope_heads_inplace(x, cos, sin, heads, d):
+    """In-place rotary embedding of the leading ``heads`` heads of ``x [B, S, W]``."""
+    if x.stride(2) != 1 or x.stride(0) != x.shape[1] * x.stride(1):
+        raise ValueError("rope_heads_inplace needs a [B, S, W] tensor with contiguous rows")
+    return _RopeHeads.apply(x, cos.float().contiguous(), sin.float().contiguous(), heads, d)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        B, S, H, D = x.shape
+        xc = x if (x.stride(3) == 1 and x.stride(2) == D and x.stride(0) == S * x.stride(1)) \
+            else x.contiguous()
+        y = torch.empty(B, S, H, D, dtype=x.dtype, device=x.device)
+        _check(cuda_lib().ft_rope(ptr(xc), xc.stride(1), ptr(y), y.stride(1), ptr(cos), ptr(sin), B * S,
+                                  H, D, S, 1.0, dtype_code(x.dtype), stream_handle()), "ft_rope")
+        ctx.save_for_backward(cos, sin)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        dy = dy.contiguous()
+        B, S, H, D = dy.shape
+        dx = torch.empty_like(dy)
+        _check(cuda_lib().ft_rope(ptr(dy), dy.stride(1), ptr(dx), dx.stride(1), ptr(cos), ptr(sin), B * S,
+                                  H, D, S, -1.0, dtype_code(dy.dtype), stream_handle()), "ft_rope")
+        return dx, None, None
+
+
+def rope(x, cos, sin):
+    return _Rope.apply(x, cos.float().contiguous(), sin.float().contiguous())
+
+
+# ------------------------------------------------------------------- SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        f = gu.shape[-1] // 2
+        g2 = gu.reshape(-1, 2 * f).contiguous()
+        out = torch.empty(g2.shape[0], f, dtype=gu.dtype, device=gu.device)
+        _check(cuda_lib().ft_swiglu_fwd(ptr(g2), ptr(out), g2.shape[0], f, dtype_code(gu.dtype),
+                                        stream_handle()), "ft_swiglu_fwd")
+        ctx.save_for_backward(g2)
+        return out.view(*gu.shape[:-1], f)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (g2,) = ctx.saved_tensors
+        rows, f2 = g2.shape
+        d2 = dout.reshape(rows, f2 // 2).contiguous()
+        dgu = torch.empty_like(g2)
+        _check(cuda_lib().ft_swiglu_bwd(ptr(g2), ptr(d2), ptr(dgu), rows, f2 // 2, dtype_code(g2.dtype),
+                                        stream_handle()), "ft_swiglu_bwd")
+        return dgu.view(*dout.shape[:-1], f2)
+
+
+def swiglu(gate_up):
+    return _SwiGLU.apply(gate_up)
+
+
+# ---------------------------------------------------------------- attention
+def _attn_impl() -> str:
+    return os.environ.get("FLEXTRAIN_ATTN", "native")
+
+
+def causal_attention(q, k, v, scale=None):
+    """``q [B,S,H,D]``, ``k``/``v`` ``[B,S,Hkv,D]`` (views with a common row
+    stride are fine) -> ``[B,S,H,D]``."""
+    from . import attention
+    return attention.causal_attention(q, k, v, scale)
+
+
+# ------------------------------------------------- head + cross-entropy
+class _LinearCrossEntropy(torch.autograd.Function):
+    """Mean token cross-entropy of ``hidden @ weight.T`` without ever holding the
+    full logits: rows are processed in chunks; forward keeps only the per-row
+    log-sum-exp, backward recomputes each chunk's logits, turns them into
+    gradients in place and feeds the two gradient GEMMs."""
+
+    CHUNK = 4096
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index):
+        lib = cuda_lib()
+        n, h = hidden.shape
+        v = weight.shape[0]
+        hidden = hidden.contiguous()
+        labels = labels.contiguous()
+        dev = hidden.device
+        lse = torch.empty(n, dtype=torch.float32, device=dev)
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
+        count = torch.zeros(1, dtype=torch.int32, device=dev)
+        _check(lib.ft_count_valid(ptr(labels), n, ignore_index, v, ptr(count), stream_handle()),
+               "ft_count_valid")
+        chunk = _LinearCrossEntropy.CHUNK
+        logits = torch.empty(min(chunk, n), v, dtype=hidden.dtype, device=dev)
+        for lo in range(0, n, chunk):
+            rows = min(chunk, n - lo)
+            gemm(hidden[lo:lo + rows], False, weight, False, rows, v, h, out=logits[:rows])
+            _check(lib.ft_xent_fwd(ptr(logits), logits.stride(0), ptr(labels[lo:]), rows, v,
+                                   ignore_index, ptr(lse[lo:]), ptr(loss_sum),
+                                   dtype_code(logits.dtype), stream_handle()), "ft_xent_fwd")
+        countf = count.float().clamp_(min=1.0)
+        ctx.save_for_backward(hidden, weight, labels, lse, countf)
+        ctx.ignore_index = ignore_index
+        return (loss_sum / countf).squeeze(0)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        hidden, weight, labels, lse, countf = ctx.saved_tensors
+        lib = cuda_lib()
+        n, h = hidden.shape
+        v = weight.shape[0]
+        dev = hidden.device
+        chunk = _LinearCrossEntropy.CHUNK
+        scale = (grad_out.float().reshape(1) / countf).contiguous()
+        dh = torch.empty_like(hidden)
+        wg = weight.grad
+        inplace = wg is not None and wg.shape == weight.shape and wg.is_contiguous() \
+            and wg.dtype == weight.dtype
+        dw = wg if inplace else torch.zeros_like(weight)
+        logits = torch.empty(min(chunk, n), v, dtype=hidden.dtype, device=dev)
+        for lo in range(0, n, chunk):
+            rows = min(chunk, n - lo)
+            hc = hidden[lo:lo + rows]
+            lg = logits[:rows]
+            gemm(hc, False, weight, False, rows, v, h, out=lg)
+            _check(lib.ft_xent_bwd(ptr(lg), lg.stride(0), ptr(labels[lo:]), rows, v, ctx.ignore_index,
+                                   ptr(lse[lo:]), ptr(scale), 1.0, dtype_code(lg.dtype),
+                                   stream_handle()), "ft_xent_bwd")
+            gemm(lg, False, weight, True, rows, h, v, out=dh[lo:lo + rows])
+            gemm(lg, True, hc, True, v, h, rows, out=dw, accumulate=True)
+        return dh, (None if inplace else dw), None, None
+
+
+def linear_cross_entropy(hidden, weight, labels, ignore_index=-100):
+    return _LinearCrossEntropy.apply(hidden, weight, labels, int(ignore_index))

@@ -36,6 +36,11 @@ def rope(x, cos, sin):
     return ref.rope(x, cos, sin)
 
 
+def rope_heads_inplace(x, cos, sin, heads, d):
+    from . import cuda_ops
+    return cuda_ops.rope_heads_inplace(x, cos, sin, heads, d)
+
+
 def swiglu(gate_up):
     if _cuda(gate_up):
         from . import cuda_ops

@@ -1,0 +1,243 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 statement of
+the same op (small and odd shapes, canary words around outputs)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from flextrain_b200.ops import reference as ref
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _gemm_error_word():
+    yield
+    from flextrain_b200.ops.native import cuda_lib
+    torch.cuda.synchronize()
+    assert cuda_lib().ft_gemm_error() == 0, "a bounded wait inside the GEMM kernel expired"
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (200, 264, 136), (1024, 1024, 1024),
+               (4096, 1536, 512), (136, 4096, 8192)]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_layouts(m, n, k, a_mn, b_mn, dtype):
+    from flextrain_b200.ops.cuda_ops import gemm
+    torch.manual_seed(m * 7 + n * 3 + k)
+    if dtype == torch.float16 and (m, n, k) not in GEMM_SHAPES[:4]:
+        pytest.skip("fp16 covered on the small shapes")
+    a = torch.randn(m, k, device=_dev(), dtype=dtype)
+    b = torch.randn(n, k, device=_dev(), dtype=dtype)
+    a_st = a.t().contiguous() if a_mn else a
+    b_st = b.t().contiguous() if b_mn else b
+    # canary rows around the output
+    pad = torch.full((m + 2, n), 7.0, device=_dev(), dtype=dtype)
+    out = pad[1:-1]
+    gemm(a_st, a_mn, b_st, b_mn, m, n, k, out=out)
+    want = a.float() @ b.float().t()
+    assert _rel_err(out, want) < 1e-2
+    assert torch.all(pad[0] == 7.0) and torch.all(pad[-1] == 7.0)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_accumulate_and_fp32_out(out_dtype):
+    from flextrain_b200.ops.cuda_ops import gemm
+    m, n, k = 256, 512, 192
+    a = torch.randn(m, k, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn(n, k, device=_dev(), dtype=torch.bfloat16)
+    c0 = torch.randn(m, n, device=_dev(), dtype=out_dtype)
+    c = c0.clone()
+    gemm(a, False, b, False, m, n, k, out=c, accumulate=True)
+    want = c0.float() + a.float() @ b.float().t()
+    assert _rel_err(c, want) < (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * 50)
+    c2 = torch.empty(m, n, device=_dev(), dtype=out_dtype)
+    gemm(a, False, b, False, m, n, k, out=c2)
+    assert _rel_err(c2, a.float() @ b.float().t()) < (1e-2 if out_dtype == torch.bfloat16 else 1e-4)
+
+
+def test_linear_autograd_matches_reference():
+    from flextrain_b200.ops.cuda_ops import linear
+    x = torch.randn(2, 96, 320, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(520, 320, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(2, 96, 520, device=_dev(), dtype=torch.bfloat16)
+    y = linear(x, w)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+
+
+def test_linear_accumulates_into_existing_grad():
+    from flextrain_b200.ops.cuda_ops import linear
+    x = torch.randn(256, 128, device=_dev(), dtype=torch.bfloat16)
+    w = torch.randn(256, 128, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w.grad = torch.ones_like(w)
+    linear(x, w).sum().backward()
+    want = 1.0 + x.float().sum(0)[None, :].expand(256, 128)
+    assert _rel_err(w.grad, want) < 1e-2
+
+
+@pytest.mark.parametrize("rows,h", [(1, 256), (37, 1024), (300, 4096), (16, 8192)])
+def test_rmsnorm(rows, h):
+    from flextrain_b200.ops.cuda_ops import rmsnorm
+    x = torch.randn(rows, h, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(h, device=_dev())).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(rows, h, device=_dev(), dtype=torch.bfloat16)
+    y = rmsnorm(x, w, 1e-5)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.rmsnorm(xr, wr, 1e-5)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_rope_and_inplace_heads(d):
+    from flextrain_b200.ops.cuda_ops import rope, rope_heads_inplace
+    B, S, H = 2, 48, 6
+    cos, sin = ref.rope_tables(S, d, 10000.0, device=_dev())
+    x = torch.randn(B, S, H, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn_like(x)
+    y = rope(x, cos, sin)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = ref.rope(xr, cos, sin)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2
+    # fused-QKV style: rotate the first 4 of 6 heads in place, leave the rest
+    packed = torch.randn(B, S, H * d, device=_dev(), dtype=torch.bfloat16)
+    want = packed.clone().view(B, S, H, d)
+    want[:, :, :4] = ref.rope(want[:, :, :4].float(), cos, sin).to(torch.bfloat16)
+    leaf = packed.clone().requires_grad_()
+    out = rope_heads_inplace(leaf * 1.0, cos, sin, 4, d)
+    assert _rel_err(out, want.view(B, S, H * d)) < 1e-2
+    out.backward(torch.ones_like(out))
+    gr = torch.ones(B, S, H, d, device=_dev())
+    gr_ref = gr.clone().requires_grad_()
+    tmp = torch.cat([ref.rope(gr_ref[:, :, :4], cos, sin), gr_ref[:, :, 4:]], dim=2)
+    tmp.backward(torch.ones_like(tmp))
+    assert _rel_err(leaf.grad.view(B, S, H, d), gr_ref.grad) < 1e-2
+
+
+def test_swiglu():
+    from flextrain_b200.ops.cuda_ops import swiglu
+    gu = torch.randn(70, 2 * 344, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    d = torch.randn(70, 344, device=_dev(), dtype=torch.bfloat16)
+    y = swiglu(gu)
+    y.backward(d)
+    gr = gu.detach().float().requires_grad_()
+    yr = ref.swiglu(gr)
+    yr.backward(d.float())
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(gu.grad, gr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("n,h,v", [(100, 256, 1000), (5000, 128, 1024), (64, 512, 32000)])
+def test_linear_cross_entropy(n, h, v):
+    from flextrain_b200.ops.cuda_ops import linear_cross_entropy
+    hid = (0.5 * torch.randn(n, h, device=_dev())).to(torch.bfloat16).requires_grad_()
+    w = (0.05 * torch.randn(v, h, device=_dev())).to(torch.bfloat16).requires_grad_()
+    labels = torch.randint(0, v, (n,), device=_dev())
+    labels[::7] = -100
+    loss = linear_cross_entropy(hid, w, labels)
+    (loss * 3.0).backward()
+    hr, wr = hid.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = ref.linear_cross_entropy(hr, wr, labels)
+    (lr * 3.0).backward()
+    assert abs(loss.item() - lr.item()) < 2e-2
+    assert _rel_err(hid.grad, hr.grad) < 3e-2
+    assert _rel_err(w.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("gdt", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n", [1, 1000, 65536 + 13])
+def test_adam_cuda_matches_host_kernel(gdt, n):
+    from flextrain_b200.ops.adam.cpu_adam import cpu_adam_update
+    from flextrain_b200.ops.adam.gpu_adam import device_adam_update
+
+    class Owner:
+        defaults = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, bias_correction=True)
+        adamw_mode = True
+
+    torch.manual_seed(n)
+    p = torch.randn(n)
+    g = (torch.randn(n) * 64).to(gdt)
+    m, v = torch.rand(n) * 0.1, torch.rand(n) * 0.1
+    pd, gd, md, vd = (t.to(_dev()) for t in (p, g, m, v))
+    out = torch.empty(n, device=_dev(), dtype=torch.bfloat16)
+    outc = torch.empty(n, dtype=torch.bfloat16)
+    flag = torch.zeros(1, dtype=torch.int32, device=_dev())
+    for step in (1, 2, 3):
+        device_adam_update({}, step, Owner, pd, gd, [md, vd], out, grad_scale=1 / 64, skip_flag=flag)
+        cpu_adam_update(step, 1e-3, 0.9, 0.999, 1e-8, 0.01, True, True, p, g, m, v, outc,
+                        grad_scale=1 / 64)
+    assert torch.allclose(pd.cpu(), p, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(md.cpu(), m, rtol=1e-5, atol=1e-7)
+    assert torch.allclose(vd.cpu(), v, rtol=1e-5, atol=1e-7)
+    assert torch.allclose(out.cpu().float(), outc.float(), rtol=1e-2, atol=1e-3)
+    # a raised skip flag leaves everything untouched
+    flag.fill_(1)
+    before = pd.clone()
+    device_adam_update({}, 4, Owner, pd, gd, [md, vd], out, skip_flag=flag)
+    assert torch.equal(before, pd)
+
+
+def test_finite_flag_and_accumulate():
+    from flextrain_b200.ops.adam.gpu_adam import has_nonfinite
+    from flextrain_b200.ops.elementwise import accumulate_and_zero, cast_copy
+    x = torch.randn(100003, device=_dev(), dtype=torch.bfloat16)
+    assert not has_nonfinite(x)
+    x[77777] = float("inf")
+    assert has_nonfinite(x)
+    x[77777] = float("nan")
+    assert has_nonfinite(x)
+    acc = torch.randn(4096 * 3 + 5, device=_dev())
+    src = torch.randn(4096 * 3 + 5, device=_dev()).to(torch.bfloat16)
+    want = acc + src.float()
+    accumulate_and_zero(acc, src)
+    assert torch.allclose(acc, want) and torch.all(src == 0)
+    acc8 = torch.randn(8192, device=_dev())
+    src8 = torch.randn(8192, device=_dev()).to(torch.bfloat16)
+    want8 = acc8 + src8.float()
+    accumulate_and_zero(acc8, src8)
+    assert torch.allclose(acc8, want8) and torch.all(src8 == 0)
+    dst = torch.empty(1001, device=_dev(), dtype=torch.bfloat16)
+    srcf = torch.randn(1001, device=_dev())
+    cast_copy(dst, srcf)
+    assert torch.equal(dst, srcf.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(4, 4, 64), (8, 2, 128)])
+def test_causal_attention(hq, hkv, d):
+    from flextrain_b200.ops.functional import causal_attention
+    B, S = 2, 320
+    q = torch.randn(B, S, hq, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, S, hkv, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, S, hkv, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    do = torch.randn(B, S, hq, d, device=_dev(), dtype=torch.bfloat16)
+    o = causal_attention(q, k, v)
+    o.backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf = ref.causal_attention(qr, kr, vr)
+    orf.backward(do.float())
+    assert _rel_err(o, orf) < 2e-2
+    assert _rel_err(q.grad, qr.grad) < 3e-2
+    assert _rel_err(k.grad, kr.grad) < 3e-2
+    assert _rel_err(v.grad, vr.grad) < 3e-2
