@@ -1,0 +1,200 @@
+"""Reference arm of bench.py: trains the benchmark model with the UNMODIFIED
+reference package from ``baseline/_ref`` through its own public API
+(``Init`` / ``FlexTrainAdam`` / ``set_llm_func`` / ``initialize`` /
+``engine.train_iteration``) and prints the same JSON line as the other arm.
+
+Constraints of the reference that shape its config (all are its own asserts or
+defects, none is patched): parameters and optimizer state cannot live in HBM
+(GPU share asserted to 0), the NVMe tier needs libaio which this image lacks
+(so every tier is host DRAM), and its fused Adam writes fp16 bit patterns
+whatever the device dtype, so it runs in fp16 with its default loss scaling.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import sys
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _unavailable(why: str):
+    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+
+
+def main(args, metric, micro_batch_table):
+    ref_root = os.path.join(HERE, "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "flextrain")):
+        return _unavailable("reference is not installed under baseline/_ref")
+    # the reference and its stand-in dependency come first; this repository's package is not used
+    sys.path.insert(0, os.path.join(HERE, "shims"))
+    sys.path.insert(0, ref_root)
+    try:
+        import torch
+        import flextrain
+        from flextrain.config import init_flextrain_config
+        from flextrain.ops.adam import FlexTrainAdam
+    except Exception as exc:
+        return _unavailable(f"import of the reference failed: {type(exc).__name__}: {exc}")
+    import psutil
+    from baseline.llama_torch import SHAPES, Block, Llama
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    try:
+        if world > 1:
+            flextrain.init_distributed(dist_backend="nccl")
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        name = args.model
+        if name == "auto":
+            name = _auto_model(world, torch, psutil, SHAPES)
+        shape = dict(SHAPES[name])
+        if args.seq_len:
+            shape["seq_len"] = args.seq_len
+        if args.layers:
+            shape["num_layers"] = args.layers
+        mbs = micro_batch_table.get(name, 2)
+        mbpr = args.micro_batches_per_rank or 1
+        seq = shape["seq_len"]
+        cfg = {"max_dram_usage": psutil.virtual_memory().available / 2 ** 30,
+               "batch_size": mbs * mbpr * world, "micro_batch_size": mbs, "checkpoint_interval": 1,
+               # checkpoints stay in host DRAM (the reference's default): its alpha split
+               # borrows that buffer for the deferred gradients and refuses alpha > 0 without it
+               "split_ratio": {"checkpoint": [0.0, 1.0], "gradient": [1.0, 0.0],
+                               "parameter": [0.0, 1.0], "optimizer": [0.0, 1.0], "alpha": 0.25},
+               "mixed_precision": {"device_dtype": "fp16", "gradacc_dtype": "fp32",
+                                   "master_dtype": "fp32"}}
+        init_flextrain_config(cfg)
+        torch.manual_seed(0)
+        t0 = time.time()
+        with flextrain.Init(layer_class=Block, num_layers=shape["num_layers"],
+                            param_grouping_func=lambda n, p: 1 if p.dim() == 1 else 0):
+            model = Llama(shape, torch.float16, layer_device=dev, device=dev)
+        decay = [p for p in model.parameters() if p.dim() > 1]
+        no_decay = [p for p in model.parameters() if p.dim() <= 1]
+        opt = FlexTrainAdam([{"params": decay, "weight_decay": 0.1},
+                             {"params": no_decay, "weight_decay": 0.0}], lr=1e-4, betas=(0.9, 0.95))
+
+        gen = torch.Generator().manual_seed(1 + rank)
+        pool = [torch.randint(0, shape["vocab"], (mbs, seq + 1), generator=gen).pin_memory()
+                for _ in range(max(2, mbpr))]
+        dev_pool = [t.to(dev) for t in pool]
+        state = {"i": 0, "host": False, "h2d": 0}
+
+        def get_batch():
+            i = state["i"] % len(pool)
+            state["i"] += 1
+            if state["host"]:
+                t = pool[i].to(dev, non_blocking=True)
+                state["h2d"] += pool[i].numel() * pool[i].element_size()
+            else:
+                t = dev_pool[i]
+            return (t[:, :-1],), (), (t[:, 1:],)
+
+        def pre_process(pre_inputs):
+            (tokens,) = pre_inputs
+            x = torch.nn.functional.embedding(tokens, model.embed)
+            cos, sin = model.rope(tokens.shape[1], tokens.device, x.dtype)
+            return (x,), (cos, sin)
+
+        def layer_forward(start, end):
+            def run(x, cos, sin):
+                for i in range(start, min(end, len(model.blocks))):
+                    x = model.blocks[i](x, cos, sin)
+                return (x,)
+            return run
+
+        def post_process(passed_down, post_inputs):
+            from baseline.llama_torch import rms_norm
+            (x,) = passed_down
+            return (rms_norm(x, model.final_norm),)
+
+        def loss_fn(outputs, loss_inputs):
+            (hidden,) = outputs
+            (labels,) = loss_inputs
+            logits = torch.nn.functional.linear(hidden, model.lm_head)
+            return torch.nn.functional.cross_entropy(logits.float().view(-1, logits.shape[-1]),
+                                                     labels.reshape(-1))
+
+        flextrain.set_llm_func(lambda i: model.blocks[i], get_batch, pre_process, layer_forward,
+                               post_process, loss_fn)
+        engine = flextrain.initialize(model, opt)
+        torch.cuda.synchronize()
+        init_s = time.time() - t0
+
+        def barrier():
+            if world > 1:
+                torch.distributed.barrier()
+            torch.cuda.synchronize()
+
+        def timed(steps, read_loss):
+            barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            last, d2h = None, 0
+            for _ in range(steps):
+                out = engine.train_iteration()
+                if read_loss:
+                    last = [float(l.detach().float().item()) for l in out]
+                    d2h += 4 * len(out)
+            torch.cuda.synchronize()
+            e.record()
+            barrier()
+            ms = s.elapsed_time(e)
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                torch.distributed.all_reduce(t, torch.distributed.ReduceOp.MAX)
+                ms = t.item()
+            return ms / steps, d2h / max(steps, 1), last
+
+        for _ in range(args.warmup):
+            engine.train_iteration()
+        torch.cuda.synchronize()
+        ms_dev, _, _ = timed(args.steps, False)
+        e2e = None
+        if not args.no_e2e:
+            state["host"], state["h2d"] = True, 0
+            ms_e2e, d2h, last = timed(args.steps, True)
+            tokens = mbs * mbpr * world * seq
+            e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                   "h2d_bytes_per_step": state["h2d"] // args.steps, "d2h_bytes_per_step": int(d2h),
+                   "last_loss": last}
+        tokens = mbs * mbpr * world * seq
+        if rank == 0:
+            print(json.dumps({
+                "metric": metric, "value": tokens / (ms_dev / 1e3), "unit": "tokens/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
+                "data": "synthetic", "impl": "reference",
+                "config": {"model": name + (f"-{args.layers}L-DEBUG" if args.layers else ""),
+                           "global_batch": mbs * mbpr * world, "micro_batch": mbs,
+                           "micro_batches_per_rank": mbpr, "seq_len": seq,
+                           "parallelism": f"zero3-dp{world}", "split_ratio": cfg["split_ratio"],
+                           "note": "fp16 because the reference's fused Adam mis-encodes bf16; "
+                                   "parameters and optimizer state in host DRAM because the "
+                                   "reference asserts their GPU share to 0"},
+                "e2e": e2e, "gpu_launches": 0, "init_seconds": init_s}), flush=True)
+    except Exception as exc:                                   # OOM, assert inside the reference, ...
+        import traceback
+        traceback.print_exc(file=sys.stderr)
+        if rank == 0:
+            _unavailable(f"reference run failed: {type(exc).__name__}: {str(exc)[:300]}")
+
+
+def _auto_model(world, torch, psutil, shapes):
+    """Same rule as the other arm: the largest model whose 14 bytes/parameter of
+    state fit the HBM + host DRAM of the ranks."""
+    hbm, _ = torch.cuda.mem_get_info()
+    dram = psutil.virtual_memory().available * 0.85
+    for name in ("llama3-70b", "llama2-13b", "llama2-7b"):
+        s = shapes[name]
+        kv = s["num_kv_heads"] * (s["hidden"] // s["num_heads"])
+        layer = 2 * s["hidden"] + s["hidden"] * (s["hidden"] + 2 * kv) + s["hidden"] ** 2 \
+            + 3 * s["hidden"] * s["ffn"]
+        total = s["num_layers"] * layer + 2 * s["vocab"] * s["hidden"] + s["hidden"]
+        if total * 14 < world * hbm * 0.8 + dram:
+            return name
+    return "llama2-7b"
