@@ -1,0 +1,295 @@
+// Gradient reduce-scatter over NVSwitch peer memory fused with loss-scale
+// unscale, the non-finite check, the HBM-resident share of the partitioned Adam
+// update and the hand-off of the host-resident share.
+//
+// Every rank exposes its full unit gradient buffer to its peers.  The owner of
+// shard r pulls slice r of all `world` buffers with plain peer loads (its own
+// slice from local HBM), sums in fp32, multiplies by 1/(world*loss_scale) and,
+// per element: [0, og) - applies Adam to the fp32 master / moments kept in HBM
+// and writes the device-dtype parameter; [og, S) - writes the reduced gradient
+// straight into pinned host memory for the AVX-512 Adam.  Optionally the reduced
+// shard is also written back in place (two-phase mode used with dynamic loss
+// scaling, where the update must wait for the whole shard's finite flag).
+//
+// Synchronisation: a start barrier (this rank's gradients are complete when its
+// kernel starts; every CTA waits for all peers' start words) and an end barrier
+// (the last CTA to finish tells all peers it no longer reads their buffers and
+// waits for the same from them, so kernel completion means the local gradient
+// buffer may be overwritten).  CTAs never wait for each other, only for other
+// GPUs, so no co-residency is assumed.  All spins are bounded; on expiry an
+// error word is set and the kernel returns.
+//
+// Replaces, on the reference's path, the NCCL reduce-scatter of
+// flextrain/memory/coordinator/optimizer.py:550-552, the D2H scatter :554-580 and
+// (for the HBM share, which the reference cannot have) the CPU Adam.
+#include "../kernels/common.cuh"
+#include "peer.cuh"
+
+namespace {
+
+using namespace ft;
+using namespace ft::peer;
+
+constexpr int kMaxSeg = 8;
+
+struct Segment {
+  int64_t lo, hi;                 // shard coordinates, multiples of 8
+  float beta2, one_m_beta1, one_m_beta2, eps, step_size, sqrt_bc2, l2_decay, decay_factor;
+};
+
+struct RsAdamParams {
+  Peers peers;
+  const void* grads[kMaxRanks];   // every rank's full gradient buffer
+  int grad_dtype;
+  int64_t shard;                  // S
+  float scale;                    // 1 / (world * loss_scale)
+  uint32_t seq;
+  int start_slot, done_slot;      // rows of the flag page used by this call site
+  unsigned int* block_counter;
+  int* err;
+  long long spin_budget;
+  // outputs
+  void* reduced_out;              // own shard slice of the local buffer, or nullptr
+  int64_t og;                     // elements [0, og) are updated here
+  int do_adam;
+  float *master, *m, *v;
+  void* param_a; int64_t a_hi;    // device-dtype parameters: [0, a_hi) -> param_a
+  void* param_b;                  //                          [a_hi, og) -> param_b (indexed from a_hi)
+  int param_dtype;
+  void* host_grad;                // [og, S) -> host_grad (indexed from og), or nullptr
+  int host_grad_dtype;
+  int* finite_flag;               // or nullptr
+  int nseg;
+  Segment seg[kMaxSeg];
+};
+
+template <typename G>
+__device__ __forceinline__ void load8(const void* base, int64_t idx, float (&out)[8]) {
+  if constexpr (sizeof(G) == 4) {
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
+    float4 a = __ldcg(p), b = __ldcg(p + 1);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else {
+    uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const G*>(base) + idx));
+    unpack8<G>(raw, out);
+  }
+}
+
+__device__ __forceinline__ void store8(void* base, int dtype, int64_t idx, const float (&v)[8]) {
+  if (dtype == kF32) {
+    float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx);
+    p[0] = make_float4(v[0], v[1], v[2], v[3]);
+    p[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else if (dtype == kBF16) {
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + idx) = pack8<__nv_bfloat16>(v);
+  } else {
+    *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(base) + idx) = pack8<__half>(v);
+  }
+}
+
+template <typename G>
+__global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ RsAdamParams P) {
+  __shared__ int s_ok;
+  const int W = P.peers.world, R = P.peers.rank;
+  uint32_t* mine = P.peers.flags[R];
+
+  // ---- start barrier
+  if (blockIdx.x == 0 && threadIdx.x < W && W > 1) {
+    __threadfence_system();
+    st_release_sys(P.peers.flags[threadIdx.x] + P.start_slot * kMaxRanks + R, P.seq);
+  }
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int p = 0; p < W && ok && W > 1; ++p)
+      if (p != R && !wait_seq(mine + P.start_slot * kMaxRanks + p, P.seq, P.spin_budget)) ok = 0;
+    if (!ok) atomicCAS(P.err, 0, 101);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+
+  // ---- reduce + update
+  const int64_t base = (int64_t)R * P.shard;
+  bool bad = false;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < P.shard;
+       i += (int64_t)gridDim.x * blockDim.x * 8) {
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < W; ++k) {
+      const int p = (R + k) % W;             // start with the local copy, spread peers over links
+      float t[8];
+      load8<G>(P.grads[p], base + i, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] += t[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      g[j] *= P.scale;
+      bad |= !(fabsf(g[j]) < INFINITY);
+    }
+    if (P.reduced_out) store8(P.reduced_out, P.grad_dtype, i, g);
+    if (i < P.og) {
+      if (P.do_adam) {
+        int s = 0;
+        while (s + 1 < P.nseg && i >= P.seg[s].hi) ++s;
+        const Segment& a = P.seg[s];
+        float4* pm = reinterpret_cast<float4*>(P.master + i);
+        float4* mm = reinterpret_cast<float4*>(P.m + i);
+        float4* vm = reinterpret_cast<float4*>(P.v + i);
+        float pv[8], mv[8], vv[8];
+        *reinterpret_cast<float4*>(pv) = pm[0]; *reinterpret_cast<float4*>(pv + 4) = pm[1];
+        *reinterpret_cast<float4*>(mv) = mm[0]; *reinterpret_cast<float4*>(mv + 4) = mm[1];
+        *reinterpret_cast<float4*>(vv) = vm[0]; *reinterpret_cast<float4*>(vv + 4) = vm[1];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float gr = g[j] + a.l2_decay * pv[j];
+          mv[j] = mv[j] + (gr - mv[j]) * a.one_m_beta1;
+          vv[j] = a.beta2 * vv[j] + (a.one_m_beta2 * gr) * gr;
+          float denom = sqrtf(vv[j]) / a.sqrt_bc2 + a.eps;
+          pv[j] = pv[j] * a.decay_factor - a.step_size * (mv[j] / denom);
+        }
+        pm[0] = *reinterpret_cast<float4*>(pv); pm[1] = *reinterpret_cast<float4*>(pv + 4);
+        mm[0] = *reinterpret_cast<float4*>(mv); mm[1] = *reinterpret_cast<float4*>(mv + 4);
+        vm[0] = *reinterpret_cast<float4*>(vv); vm[1] = *reinterpret_cast<float4*>(vv + 4);
+        if (i < P.a_hi) {
+          if (P.param_a) store8(P.param_a, P.param_dtype, i, pv);
+        } else if (P.param_b) {
+          store8(P.param_b, P.param_dtype, i - P.a_hi, pv);
+        }
+      }
+    } else if (P.host_grad) {
+      store8(P.host_grad, P.host_grad_dtype, i - P.og, g);
+    }
+  }
+  if (bad && P.finite_flag) atomicOr(P.finite_flag, 1);
+
+  // ---- end barrier (last CTA only)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int done = atomicAdd(P.block_counter, 1u);
+    if (done == gridDim.x - 1) {
+      *P.block_counter = 0;
+      if (W > 1) {
+        for (int p = 0; p < W; ++p)
+          if (p != R) st_release_sys(P.peers.flags[p] + P.done_slot * kMaxRanks + R, P.seq);
+        for (int p = 0; p < W; ++p)
+          if (p != R && !wait_seq(mine + P.done_slot * kMaxRanks + p, P.seq, P.spin_budget)) atomicCAS(P.err, 0, 102);
+      }
+    }
+  }
+}
+
+long long g_spin_budget = 0;   // 0: default
+unsigned int* g_counter[16] = {nullptr};
+int* g_err[16] = {nullptr};
+
+int ensure_state(int dev) {
+  if (!g_counter[dev]) {
+    if (cudaMalloc(&g_counter[dev], sizeof(unsigned int)) != cudaSuccess) return -1;
+    cudaMemset(g_counter[dev], 0, sizeof(unsigned int));
+    if (cudaMalloc(&g_err[dev], sizeof(int)) != cudaSuccess) return -1;
+    cudaMemset(g_err[dev], 0, sizeof(int));
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+struct FtAdamSegment {
+  int64_t lo, hi;
+  float lr, beta1, beta2, eps, weight_decay;
+  int adamw, bias_correction;
+  int64_t step;
+};
+
+// See the file comment.  `grads[r]` / `flags[r]` are this process's mappings of
+// rank r's gradient buffer and flag page.  Alignment: shard, og, a_hi and every
+// segment bound must be multiples of 8 elements; returns -2 otherwise.
+int ft_rs_adam(int world, int rank, const void* const* grads, uint32_t* const* flags, int grad_dtype,
+               int64_t shard, float scale, uint32_t seq, int start_slot, int done_slot,
+               void* reduced_out, int64_t og, int do_adam, float* master, float* m, float* v,
+               void* param_a, int64_t a_hi, void* param_b, int param_dtype, void* host_grad,
+               int host_grad_dtype, int* finite_flag, int nseg, const FtAdamSegment* segs,
+               int max_blocks, cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -1;
+  if (shard % 8 || og % 8 || a_hi % 8 || nseg > kMaxSeg) return -2;
+  if (shard <= 0) return 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (ensure_state(dev)) return -3;
+  RsAdamParams P;
+  memset(&P, 0, sizeof(P));
+  P.peers.world = world;
+  P.peers.rank = rank;
+  for (int r = 0; r < world; ++r) {
+    P.peers.flags[r] = flags ? flags[r] : nullptr;
+    P.grads[r] = grads[r];
+  }
+  P.grad_dtype = grad_dtype;
+  P.shard = shard;
+  P.scale = scale;
+  P.seq = seq;
+  P.start_slot = start_slot;
+  P.done_slot = done_slot;
+  P.block_counter = g_counter[dev];
+  P.err = g_err[dev];
+  P.spin_budget = g_spin_budget > 0 ? g_spin_budget : kSpinCycles;
+  P.reduced_out = reduced_out;
+  P.og = og;
+  P.do_adam = do_adam;
+  P.master = master; P.m = m; P.v = v;
+  P.param_a = param_a; P.a_hi = a_hi; P.param_b = param_b; P.param_dtype = param_dtype;
+  P.host_grad = host_grad; P.host_grad_dtype = host_grad_dtype;
+  P.finite_flag = finite_flag;
+  P.nseg = nseg;
+  for (int s = 0; s < nseg; ++s) {
+    const FtAdamSegment& in = segs[s];
+    if (in.lo % 8 || in.hi % 8) return -2;
+    Segment& o = P.seg[s];
+    o.lo = in.lo; o.hi = in.hi;
+    const int64_t step = in.step < 1 ? 1 : in.step;
+    double bc1 = 1.0, bc2 = 1.0;
+    if (in.bias_correction) {
+      bc1 = 1.0 - pow((double)in.beta1, (double)step);
+      bc2 = 1.0 - pow((double)in.beta2, (double)step);
+    }
+    o.beta2 = in.beta2;
+    o.one_m_beta1 = 1.0f - in.beta1;
+    o.one_m_beta2 = 1.0f - in.beta2;
+    o.eps = in.eps;
+    o.step_size = (float)((double)in.lr / bc1);
+    o.sqrt_bc2 = (float)sqrt(bc2);
+    o.l2_decay = in.adamw ? 0.f : in.weight_decay;
+    o.decay_factor = in.adamw ? (float)(1.0 - (double)in.lr * (double)in.weight_decay) : 1.f;
+  }
+  int64_t work = (shard / 8 + 511) / 512;
+  int grid = (int)(work < (int64_t)max_blocks ? work : max_blocks);
+  if (grid < 1) grid = 1;
+  if (grad_dtype == kF32) rs_adam_kernel<float><<<grid, 512, 0, stream>>>(P);
+  else if (grad_dtype == kBF16) rs_adam_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(P);
+  else rs_adam_kernel<__half><<<grid, 512, 0, stream>>>(P);
+  FT_LAUNCHED(1);
+  FT_CUDA_RETURN_IF_ERROR();
+  return 0;
+}
+
+// Clock-cycle budget of every cross-GPU wait (0 restores the default of ~10 s).
+// Tests shorten it to make a wait run out on purpose.
+void ft_comm_set_spin_budget(long long cycles) { g_spin_budget = cycles; }
+long long ft_comm_spin_budget() { return g_spin_budget > 0 ? g_spin_budget : kSpinCycles; }
+
+// Reads and clears the error word of the fused collective kernels (synchronises).
+int ft_comm_error() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (ensure_state(dev)) return -1;
+  int host = 0;
+  if (cudaMemcpy(&host, g_err[dev], sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (host) cudaMemset(g_err[dev], 0, sizeof(int));
+  return host;
+}
+
+}  // extern "C"

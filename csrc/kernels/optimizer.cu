@@ -264,7 +264,7 @@ int ft_cast_copy(void* dst, int ddt, const void* src, int sdt, int64_t n, cudaSt
 // power of two).  Capability parity: flextrain/ops/csrc/aio/py_lib/deepspeed_pin_tensor.cpp:23-61.
 void* ft_pinned_alloc(size_t nbytes) {
   void* p = nullptr;
-  if (cudaHostAlloc(&p, nbytes, cudaHostAllocPortable) != cudaSuccess) {
+  if (cudaHostAlloc(&p, nbytes, cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
     cudaGetLastError();
     return nullptr;
   }

@@ -130,12 +130,31 @@ class FlexTrainOptsCoordinator:
         self.opt_tiers, self.para_tiers = (og, oc, on), (g, c, n)
         self.host_numel = S - og
 
-        # gradient buffers (autograd target) and optional wide accumulators
+        # gradient buffers (autograd target) and optional wide accumulators; the buffer the
+        # reduction reads is peer-mapped when the fused reduce-scatter kernel is in use
         unit = para.aligned_unit_numel
-        self._grad_bufs = [allocate_memory(unit, self.device_dtype, self.device, zero=True)
+        self._fused = self._want_fused(cfg, S, og, min(g, og))
+        self._symm = []
+        self._flag_page = None
+
+        def grad_buffer(dtype, symmetric):
+            if not symmetric:
+                return allocate_memory(unit, dtype, self.device, zero=True)
+            from ...parallel.symm_mem import SymmetricBuffer
+            itemsize = torch.empty((), dtype=dtype).element_size()
+            sb = SymmetricBuffer(unit * itemsize)
+            self._symm.append(sb)
+            return sb.tensor(dtype)
+
+        self._grad_bufs = [grad_buffer(self.device_dtype, self._fused and self.acc_dtype is None)
                            for _ in range(2)]
-        self._acc_bufs = [allocate_memory(unit, self.acc_dtype, self.device, zero=True)
+        self._acc_bufs = [grad_buffer(self.acc_dtype, self._fused)
                           for _ in range(2)] if self.acc_dtype is not None else None
+        if self._fused:
+            from ...parallel.symm_mem import get_flag_page
+            self._flag_page = get_flag_page()
+            # _symm holds the reduce-source buffers in order [buf0, buf1]
+            self._reduce_symm = self._symm[-2:]
         self._buf_free: List[Event] = [DONE, DONE]
         self._buf_next = 0
         self._linked: Dict[int, int] = {}
@@ -198,6 +217,18 @@ class FlexTrainOptsCoordinator:
             f"reduce dtype={self.reduce_dtype} overflow check={self.check_overflow} "
             f"host pool depth={getattr(self, '_pool_depth', 0)}")
 
+    def _want_fused(self, cfg, S, og, a_hi) -> bool:
+        want = cfg.engine.fused_collectives
+        if want is False or self.device.type != "cuda":
+            return False
+        from ...parallel.symm_mem import peer_access_available
+        ok = S % 8 == 0 and og % 8 == 0 and a_hi % 8 == 0 and self.world <= 8 and \
+            peer_access_available()
+        if want is True and not ok:
+            raise RuntimeError("engine.fused_collectives=true needs peer access between all ranks, "
+                               "at most 8 ranks and shard / tier sizes that are multiples of 8")
+        return bool(ok)
+
     def _opts_id(self, unit):
         return FlexTrainDataID(FlexTrainDataType.OPTS, unit)
 
@@ -247,18 +278,23 @@ class FlexTrainOptsCoordinator:
         grad_scale = 1.0 / float(self.loss_scaler.loss_scale)
         entry = self._pool.get() if self.host_numel else None    # back-pressure on the host side
         self._para.invalidate(unit)
+        host_scale = grad_scale
         with st.opt.use():
             st.opt.wait(produced)
             shard = src[lo:hi]
-            self._reduce_scatter(shard, src)
             flag = self._flags[unit:unit + 1] if self.check_overflow else None
-            if flag is not None:
-                from ...ops.adam.gpu_adam import nonfinite_flag
-                nonfinite_flag(shard, flag)
-            if og:
-                self._device_update(unit, shard, step, grad_scale, flag, i)
+            if self._fused and self._fused_reduce(unit, i, shard, step, grad_scale, flag, entry):
+                host_scale = 1.0                    # the kernel already unscaled what it handed over
+            else:
+                self._reduce_scatter(shard, src)
+                if flag is not None:
+                    from ...ops.adam.gpu_adam import nonfinite_flag
+                    nonfinite_flag(shard, flag)
+                if og:
+                    self._device_update(unit, shard, step, grad_scale, flag, i)
+                if entry is not None:
+                    entry.grad.copy_(shard[og:], non_blocking=True)
             if entry is not None:
-                entry.grad.copy_(shard[og:], non_blocking=True)
                 if flag is not None:
                     entry.flag.copy_(flag, non_blocking=True)
                 self.bytes_d2h += self.host_numel * entry.grad.element_size()
@@ -268,9 +304,46 @@ class FlexTrainOptsCoordinator:
             self._para.note_gpu_base_write(unit, done)
         if entry is not None:
             fut = self._worker.submit(
-                unit, lambda: self._host_update(unit, entry, done, step, grad_scale))
+                unit, lambda: self._host_update(unit, entry, done, step, host_scale))
             self._para.add_host_update(unit, FutureHandle(fut))
             self._pending.append(fut)
+
+    def _fused_reduce(self, unit, buf_index, shard, step, grad_scale, flag, entry) -> bool:
+        """One kernel: peer reduce-scatter + unscale (+ Adam on the HBM share and the
+        host hand-off when no overflow check has to come first).  Returns False when
+        this unit's segments cannot be expressed to the kernel."""
+        from ...parallel import fused
+        og = self.opt_tiers[0]
+        g = self.para_tiers[0]
+        segs = slice_segments(self._segments[unit], 0, og, rebase=False)
+        a_hi = min(g, og)
+        if not fused.segments_aligned(segs, og, a_hi):
+            return False
+        symm = self._reduce_symm[buf_index]
+        page = self._flag_page
+        seq = page.next_seq("rs")
+        scale = grad_scale / self.world
+        two_phase = flag is not None
+        if flag is not None:
+            flag.zero_()
+        opts = self._gpu_opts.get(unit)
+        stage = self._dev_out_stage[buf_index] if self._dev_out_stage is not None else None
+        fused.rs_adam(
+            self.world, self.rank, symm.ptr_array(), page.ptr_array(), self.reduce_dtype, self.S, scale,
+            seq, reduced_out=shard if two_phase else None, og=og, do_adam=(not two_phase) and og > 0,
+            master=opts[0] if opts else None, m=opts[1] if opts else None, v=opts[2] if opts else None,
+            param_a=self._para.gpu_base(unit), a_hi=a_hi, param_b=stage, param_dtype=self.device_dtype,
+            host_grad=None if (two_phase or entry is None) else entry.grad, finite_flag=flag,
+            segments=fused.make_segments(segs, self.optimizer.param_groups, self.cpu_optimizer, step),
+            nseg=len(segs), max_blocks=self._cfg.engine.fused_blocks)
+        if two_phase:
+            if og:
+                self._device_update(unit, shard, step, 1.0, flag, buf_index)
+            if entry is not None:
+                entry.grad.copy_(shard[og:], non_blocking=True)
+        elif og > g:
+            self._para.cpu_base(unit)[: og - g].copy_(stage[: og - g], non_blocking=True)
+        return True
 
     def _reduce_scatter(self, shard: torch.Tensor, full: torch.Tensor):
         dist.reduce_scatter(shard, full, dist.ReduceOp.AVG)
@@ -388,6 +461,12 @@ class FlexTrainOptsCoordinator:
             self.wait_all()
             self._worker.shutdown()
             self._worker = None
+        if getattr(self, "_symm", None):
+            self.streams.synchronize()
+            self._grad_bufs, self._acc_bufs = [], None
+            for sb in self._symm:
+                sb.close()
+            self._symm = []
 
     # ---------------------------------------------------------- state access
     @torch.no_grad()

@@ -1,0 +1,83 @@
+"""Python front of the fused compute + collective kernels.
+
+``FusedReduceScatterAdam``: gradient reduce-scatter over peer memory fused with
+unscale, finite check, the HBM share of Adam and the hand-off of the host share
+(``csrc/comm/rs_adam.cu``).  It replaces, call for call, the sequence NCCL
+reduce-scatter -> finite flag -> device Adam -> device-to-host gradient copy of
+``memory/coordinator/optimizer.py``.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_uint32, c_void_p
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..ops.native import cuda_lib, dtype_code, ptr, stream_handle
+from ..param_group import GroupSegment
+from .symm_mem import FlagPage, SymmetricBuffer
+
+
+class _AdamSegment(ctypes.Structure):
+    _fields_ = [("lo", c_int64), ("hi", c_int64), ("lr", c_float), ("beta1", c_float),
+                ("beta2", c_float), ("eps", c_float), ("weight_decay", c_float), ("adamw", c_int),
+                ("bias_correction", c_int), ("step", c_int64)]
+
+
+_DECLARED = False
+
+
+def _lib():
+    global _DECLARED
+    lib = cuda_lib()
+    if not _DECLARED:
+        lib.ft_rs_adam.argtypes = [
+            c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_float, c_uint32, c_int, c_int,
+            c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int,
+            c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p]
+        lib.ft_comm_error.restype = c_int
+        _DECLARED = True
+    return lib
+
+
+def make_segments(segments: Sequence[GroupSegment], param_groups: Sequence[Dict], defaults_owner,
+                  step: int):
+    d = defaults_owner.defaults
+    arr = (_AdamSegment * max(len(segments), 1))()
+    for i, seg in enumerate(segments):
+        g = param_groups[seg.group]
+        b1, b2 = g.get("betas", d["betas"])
+        arr[i] = _AdamSegment(seg.start, seg.end, g.get("lr", d["lr"]), b1, b2, g.get("eps", d["eps"]),
+                              g.get("weight_decay", d["weight_decay"]),
+                              int(getattr(defaults_owner, "adamw_mode", True)),
+                              int(g.get("bias_correction", d["bias_correction"])), int(step))
+    return arr
+
+
+def segments_aligned(segments: Sequence[GroupSegment], *bounds: int) -> bool:
+    return all(s.start % 8 == 0 and s.end % 8 == 0 for s in segments) and \
+        all(b % 8 == 0 for b in bounds) and len(segments) <= 8
+
+
+def rs_adam(world: int, rank: int, grad_ptrs, flag_ptrs, grad_dtype: torch.dtype, shard: int,
+            scale: float, seq: int, reduced_out: Optional[torch.Tensor], og: int, do_adam: bool,
+            master: Optional[torch.Tensor], m: Optional[torch.Tensor], v: Optional[torch.Tensor],
+            param_a: Optional[torch.Tensor], a_hi: int, param_b: Optional[torch.Tensor],
+            param_dtype: torch.dtype, host_grad: Optional[torch.Tensor],
+            finite_flag: Optional[torch.Tensor], segments, nseg: int, max_blocks: int = 64,
+            start_slot: int = 0, done_slot: int = 1):
+    """Thin wrapper over ``ft_rs_adam``; see ``csrc/comm/rs_adam.cu``."""
+    rc = _lib().ft_rs_adam(
+        world, rank, ctypes.cast(grad_ptrs, c_void_p), ctypes.cast(flag_ptrs, c_void_p) if flag_ptrs
+        is not None else None, dtype_code(grad_dtype), shard, float(scale), seq, start_slot, done_slot,
+        ptr(reduced_out), og, int(do_adam), ptr(master), ptr(m), ptr(v), ptr(param_a), a_hi,
+        ptr(param_b), dtype_code(param_dtype), ptr(host_grad),
+        -1 if host_grad is None else dtype_code(host_grad.dtype), ptr(finite_flag), nseg,
+        ctypes.cast(segments, c_void_p), max_blocks, stream_handle())
+    if rc != 0:
+        raise RuntimeError(f"ft_rs_adam failed (code {rc})")
+
+
+def comm_error() -> int:
+    return _lib().ft_comm_error()

@@ -17,6 +17,11 @@ def reset_runtime():
     from .utils import distributed as dist
     from .utils.device import reset_streams
     reset_opts_coordinator()
+    try:
+        from .parallel.symm_mem import reset_flag_page
+        reset_flag_page()
+    except Exception:
+        pass
     reset_para_coordinator()
     reset_interlayer_coordinator()
     reset_nvme_swapper()

@@ -1,0 +1,109 @@
+"""Worker launched by tests/test_fused_multi_gpu.py under torch.distributed.run
+(one process per GPU, NCCL).  Exits non-zero on any mismatch."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def case_rs_adam():
+    import ctypes
+    import torch.distributed as tdist
+    import flextrain_b200 as ft
+    from flextrain_b200.parallel import fused
+    from flextrain_b200.parallel.symm_mem import FlagPage, SymmetricBuffer
+    from flextrain_b200.param_group import GroupSegment
+    ft.init_distributed("nccl")
+    world, rank = ft.distributed.get_world_size(), ft.distributed.get_rank()
+    dev = ft.distributed.current_device()
+
+    class Owner:
+        defaults = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, bias_correction=True)
+        adamw_mode = True
+
+    S = 8 * 100_000
+    og = 8 * 60_000
+    page = FlagPage()
+    for gdt in (torch.bfloat16, torch.float32):
+        symm = SymmetricBuffer(world * S * torch.empty((), dtype=gdt).element_size())
+        for it in range(3):
+            torch.manual_seed(100 * it + rank)
+            mine = symm.tensor(gdt)
+            mine.copy_((torch.randn(world * S, device=dev) * 4).to(gdt))
+            ref_full = mine.float().clone()
+            tdist.all_reduce(ref_full)
+            want = ref_full[rank * S:(rank + 1) * S] / (world * 8.0)
+            master = torch.zeros(og, device=dev)
+            m, v = torch.zeros(og, device=dev), torch.zeros(og, device=dev)
+            out = torch.zeros(og, device=dev, dtype=torch.bfloat16)
+            host = torch.zeros(S - og, dtype=gdt).pin_memory()
+            segs = [GroupSegment(0, 0, og)]
+            torch.cuda.synchronize()
+            tdist.barrier()
+            fused.rs_adam(world, rank, symm.ptr_array(), page.ptr_array(), gdt, S, 1.0 / (world * 8.0),
+                          page.next_seq("t"), None, og, True, master, m, v, out, og, None, torch.bfloat16,
+                          host, None, fused.make_segments(segs, [{}], Owner, 1), 1, max_blocks=32)
+            torch.cuda.synchronize()
+            assert fused.comm_error() == 0
+            tol = 2e-2 if gdt == torch.bfloat16 else 1e-5
+            assert torch.allclose(host.float().to(dev), want[og:], rtol=tol, atol=tol), "host grads"
+            # first Adam step from zero state: p = -lr * g / (|g| + eps)
+            g = want[:og]
+            expect = -1e-3 * g / (g.abs() + 1e-8)
+            assert torch.allclose(master, expect, rtol=1e-3, atol=1e-6), "adam"
+            tdist.barrier()
+        symm.close()
+    page.close()
+    print(f"rank {rank}: rs_adam ok", flush=True)
+
+
+def case_engine():
+    import flextrain_b200 as ft
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine, reset_runtime
+    results = {}
+    for fused_mode in (False, True):
+        reset_runtime()
+        ft.init_distributed("nccl")
+        world, rank = ft.distributed.get_world_size(), ft.distributed.get_rank()
+        dev = ft.distributed.current_device()
+        cfg = preset("tiny", num_layers=4, hidden=256, num_heads=4, ffn=768, vocab=1024, seq_len=256)
+        gen = torch.Generator().manual_seed(1 + rank)
+        data = [torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=gen).to(dev) for _ in range(2)]
+        it = {"i": 0}
+
+        def batch_fn():
+            t = data[it["i"] % 2]
+            it["i"] += 1
+            return t[:, :-1], t[:, 1:]
+
+        ft_cfg = {"batch_size": 4 * world, "micro_batch_size": 2,
+                  "mixed_precision": {"device_dtype": "bf16", "dynamic_loss_scaling": False},
+                  "split_ratio": {"parameter": [0.5, 0.5], "optimizer": [0.5, 0.5],
+                                  "checkpoint": [1.0, 0.0], "gradient": [1.0, 0.0]},
+                  "engine": {"fused_collectives": fused_mode, "num_unit_buffers": 3}}
+        model, opt, eng = build_llama_engine(cfg, ft_cfg, batch_fn, lr=1e-3, init_device=dev,
+                                             dtype=torch.bfloat16)
+        assert eng.opts._fused == fused_mode
+        losses = []
+        for _ in range(4):
+            r = eng.train_iteration()
+            losses.append(sum(float(x.detach()) for x in r) / len(r))
+        eng.synchronize()
+        eng.shutdown()
+        results[fused_mode] = losses
+    a, b = results[False], results[True]
+    assert max(abs(x - y) for x, y in zip(a, b)) < 5e-3, (a, b)
+    assert b[-1] < b[0]
+    from flextrain_b200.parallel.fused import comm_error
+    assert comm_error() == 0
+    print(f"engine fused == nccl: {a} vs {b}", flush=True)
+
+
+if __name__ == "__main__":
+    {"rs_adam": case_rs_adam, "engine": case_engine}[sys.argv[1]]()
+    if torch.distributed.is_initialized():
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()

@@ -1,0 +1,119 @@
+"""Fused reduce-scatter + unscale + Adam kernel on ONE GPU.
+
+Several ranks cannot be run as separate waiting kernels on one device, so the
+ranks are emulated: all "peer" buffers live on this GPU and every flag word is
+set to the call's sequence number beforehand, which makes both barriers pass at
+once.  What is checked is the math: the slice owner's sum over ranks, the
+unscale, Adam on the HBM share against the host kernel, and the gradient
+hand-off of the host share."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+class _Owner:
+    defaults = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, bias_correction=True)
+    adamw_mode = True
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("gdt", [torch.bfloat16, torch.float32])
+def test_rs_adam_emulated_ranks(world, gdt):
+    from flextrain_b200.ops.adam.cpu_adam import cpu_adam_update
+    from flextrain_b200.parallel import fused
+    from flextrain_b200.param_group import GroupSegment
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(world)
+    S, og, a_hi = 8 * 4099, 8 * 2048, 8 * 1000
+    grads = [(torch.randn(world * S, device=dev) * 8).to(gdt) for _ in range(world)]
+    flags = [torch.zeros(128 * 8, dtype=torch.int32, device=dev) for _ in range(world)]
+    seq = 3
+    for f in flags:
+        f.fill_(seq)
+    loss_scale = 16.0
+    groups = [dict(weight_decay=0.01), dict(weight_decay=0.0, lr=5e-4)]
+    segs = [GroupSegment(0, 0, 8 * 1500), GroupSegment(1, 8 * 1500, og)]
+    for rank in range(world):
+        master = torch.randn(og, device=dev)
+        m, v = torch.rand(og, device=dev) * 0.1, torch.rand(og, device=dev) * 0.1
+        ref_master, ref_m, ref_v = master.cpu().clone(), m.cpu().clone(), v.cpu().clone()
+        param_a = torch.zeros(a_hi, device=dev, dtype=torch.bfloat16)
+        param_b = torch.zeros(og - a_hi, device=dev, dtype=torch.bfloat16)
+        host_grad = torch.zeros(S - og, dtype=gdt).pin_memory()
+        flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        gp = (ctypes.c_void_p * world)(*[g.data_ptr() for g in grads])
+        fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+        arr = fused.make_segments(segs, groups, _Owner, step=2)
+        fused.rs_adam(world, rank, gp, fp, gdt, S, 1.0 / (world * loss_scale), seq, None, og, True,
+                      master, m, v, param_a, a_hi, param_b, torch.bfloat16, host_grad, flag, arr,
+                      len(segs), max_blocks=16)
+        torch.cuda.synchronize()
+        assert fused.comm_error() == 0
+        want = sum(g[rank * S:(rank + 1) * S].float() for g in grads) / (world * loss_scale)
+        want = want.cpu()
+        assert torch.allclose(host_grad.float(), want[og:].to(gdt).float(), rtol=1e-2, atol=1e-3)
+        for seg in segs:
+            grp = {**_Owner.defaults, **groups[seg.group]}
+            sl = slice(seg.start, seg.end)
+            cpu_adam_update(2, grp["lr"], 0.9, 0.999, 1e-8, grp["weight_decay"], True, True,
+                            ref_master[sl], want[sl].contiguous(), ref_m[sl], ref_v[sl])
+        assert torch.allclose(master.cpu(), ref_master, rtol=1e-5, atol=1e-6)
+        assert torch.allclose(m.cpu(), ref_m, rtol=1e-5, atol=1e-7)
+        assert torch.allclose(v.cpu(), ref_v, rtol=1e-5, atol=1e-7)
+        out = torch.cat([param_a, param_b]).cpu().float()
+        assert torch.allclose(out, ref_master.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-3)
+        assert flag.item() == 0
+
+
+def test_rs_adam_two_phase_and_overflow_flag():
+    from flextrain_b200.parallel import fused
+    dev = torch.device("cuda", 0)
+    world, S = 2, 8 * 512
+    grads = [torch.randn(world * S, device=dev).to(torch.float16) for _ in range(world)]
+    grads[1][S + 17] = float("inf")          # inside rank 1's slice
+    flags = [torch.full((128 * 8,), 1, dtype=torch.int32, device=dev) for _ in range(world)]
+    gp = (ctypes.c_void_p * world)(*[g.data_ptr() for g in grads])
+    fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    for rank, expect in ((0, 0), (1, 1)):
+        flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        want = sum(g[rank * S:(rank + 1) * S].float() for g in grads) / world
+        reduced = grads[rank][rank * S:(rank + 1) * S]
+        fused.rs_adam(world, rank, gp, fp, torch.float16, S, 1.0 / world, 1, reduced, 0, False, None,
+                      None, None, None, 0, None, torch.float16, None, flag,
+                      fused.make_segments([], [], None, 1) if False else (fused._AdamSegment * 1)(), 0)
+        torch.cuda.synchronize()
+        assert flag.item() == expect
+        if not expect:
+            assert torch.allclose(reduced.float(), want.to(torch.float16).float(), rtol=1e-2, atol=1e-2)
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A start flag that nobody sets: the kernel must give up, raise the error
+    word and leave the context usable (checked by running another kernel)."""
+    import os
+    from flextrain_b200.parallel import fused
+    dev = torch.device("cuda", 0)
+    if os.environ.get("FLEXTRAIN_SKIP_TIMEOUT_TEST"):
+        pytest.skip("disabled by environment")
+    world, S = 2, 8 * 64
+    grads = [torch.randn(world * S, device=dev).to(torch.bfloat16) for _ in range(world)]
+    flags = [torch.zeros(128 * 8, dtype=torch.int32, device=dev) for _ in range(world)]
+    gp = (ctypes.c_void_p * world)(*[g.data_ptr() for g in grads])
+    fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    from flextrain_b200.ops.native import cuda_lib
+    lib = cuda_lib()
+    lib.ft_comm_set_spin_budget.argtypes = [ctypes.c_longlong]
+    lib.ft_comm_set_spin_budget(20_000_000)          # ~10 ms
+    try:
+        fused.rs_adam(world, 0, gp, fp, torch.bfloat16, S, 0.5, 7, None, 0, False, None, None, None,
+                      None, 0, None, torch.bfloat16, None, None, (fused._AdamSegment * 1)(), 0,
+                      max_blocks=1)
+        torch.cuda.synchronize()
+        assert fused.comm_error() == 101
+    finally:
+        lib.ft_comm_set_spin_budget(0)
+    x = torch.ones(1024, device=dev)
+    assert float((x * 2).sum()) == 2048.0

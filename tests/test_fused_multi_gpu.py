@@ -1,0 +1,37 @@
+"""Fused collective kernels across real GPUs (needs >= 2 devices on the box).
+Each case runs as child processes, one per GPU, over NCCL; NVLS is switched off
+and the kernels use plain peer loads, so a failing rank cannot fault its peers."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(case, nproc):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29400 + os.getpid() % 500),
+           os.path.join(HERE, "_multi_gpu_worker.py"), case]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+
+
+def _gpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("case", ["rs_adam", "engine"])
+def test_two_ranks(case):
+    _launch(case, 2)
+
+
+@pytest.mark.skipif(_gpus() < 4, reason="needs at least 4 GPUs")
+def test_rs_adam_four_ranks():
+    _launch("rs_adam", 4)
