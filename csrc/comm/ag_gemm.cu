@@ -1,0 +1,170 @@
+// Parameter all-gather over NVSwitch peer memory fused with the GEMM that
+// consumes the gathered weight, and the stand-alone peer gather the engine uses
+// for whole units.
+//
+// ft_ag_gemm: y[M,N] = x[M,K] * W[N,K]^T where W is row-sharded over `world`
+// ranks (rank r owns rows [r*N/world, (r+1)*N/world) of every rank's peer-mapped
+// [N,K] buffer).  One persistent launch: the first `num_copiers` CTAs pull the
+// remote shards into the local buffer with non-multicast bulk copies (peer HBM
+// -> shared memory -> local HBM), publishing one counter per 256-row block; the
+// other CTAs run the tcgen05 GEMM pipeline of kernels/gemm_kernel.cuh, walking
+// the output tiles from the local shard outwards in arrival order, their TMA
+// producers waiting (bounded) for a block's counter before loading it.  The
+// transfer therefore overlaps the math tile by tile and the weight crosses
+// NVLink exactly once.
+//
+// ft_peer_gather: the copier role alone, for any flat sharded buffer.
+//
+// Both replace the NCCL all_gather_into_tensor of
+// flextrain/memory/coordinator/parameter.py:516 (and, for ft_ag_gemm, the cuBLAS
+// GEMM that follows it).
+#include <cstdio>
+
+#include "../kernels/gemm_host.h"
+#include "../kernels/gemm_kernel.cuh"
+
+namespace {
+
+using namespace ft;
+using namespace ft::gemm;
+
+constexpr int kReadyWords = 8192;
+
+uint32_t* g_ready[16] = {nullptr};
+unsigned int* g_counter[16] = {nullptr};
+long long g_spin_budget = 0;
+
+int ensure_state(int dev) {
+  if (!g_ready[dev]) {
+    if (cudaMalloc(&g_ready[dev], kReadyWords * sizeof(uint32_t)) != cudaSuccess) return -1;
+    if (cudaMalloc(&g_counter[dev], sizeof(unsigned int)) != cudaSuccess) return -1;
+    cudaMemset(g_counter[dev], 0, sizeof(unsigned int));
+  }
+  return 0;
+}
+
+__global__ void __launch_bounds__(32, 1)
+peer_gather_kernel(const __grid_constant__ GatherArgs gather, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&bars->full[s], 1);
+    fence_barrier_init();
+    gather_role(gather, smem, bars, err);
+  }
+}
+
+int fill_gather(GatherArgs& G, int world, int rank, const void* const* w_ptrs, uint32_t* const* flags,
+                uint32_t seq, int start_slot, int done_slot, int num_copiers, int dev) {
+  memset(&G, 0, sizeof(G));
+  G.peers.world = world;
+  G.peers.rank = rank;
+  for (int r = 0; r < world; ++r) {
+    G.peers.flags[r] = flags ? flags[r] : nullptr;
+    G.w_peer[r] = w_ptrs[r];
+  }
+  G.w_local = const_cast<void*>(w_ptrs[rank]);
+  G.seq = seq;
+  G.start_slot = start_slot;
+  G.done_slot = done_slot;
+  G.spin_budget = g_spin_budget > 0 ? g_spin_budget : peer::kSpinCycles;
+  G.num_copiers = num_copiers;
+  G.ready = g_ready[dev];
+  G.block_counter = g_counter[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+void ft_ag_set_spin_budget(long long cycles) { g_spin_budget = cycles; }
+
+// y[M,N] = x[M,K] * W^T with W gathered from its row shards inside the same launch.
+// w_ptrs[r]: this process's mapping of rank r's [N,K] buffer (16-bit dtype `ab_dtype`).
+// Requires N % (world * 256) == 0 and K % 64 == 0.  Returns 0, <0 for bad arguments,
+// >0 for a CUDA error.
+int ft_ag_gemm(int world, int rank, const void* const* w_ptrs, uint32_t* const* flags, uint32_t seq,
+               int start_slot, int done_slot, const void* x, int64_t lda, void* y, int64_t ldc,
+               int c_dtype, int M, int N, int K, int ab_dtype, int num_copiers, cudaStream_t stream) {
+  if (world < 1 || world > peer::kMaxRanks || rank < 0 || rank >= world) return -1;
+  if (N % (world * BN) || K % 64 || M <= 0) return -2;
+  if (ab_dtype != kBF16 && ab_dtype != kF16) return -3;
+  if (c_dtype != ab_dtype && c_dtype != kF32) return -3;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (ensure_state(dev)) return -4;
+  const int nt = N / BN;
+  if (nt > kReadyWords) return -5;
+  const int sms = sm_count(dev);
+  if (world == 1) num_copiers = 0;
+  if (num_copiers < 0 || num_copiers >= sms) return -6;
+  if (world > 1 && num_copiers == 0) return -6;
+  GatherArgs G;
+  fill_gather(G, world, rank, w_ptrs, flags, seq, start_slot, done_slot, num_copiers, dev);
+  G.row_bytes = (int64_t)K * 2;
+  G.rows_per_rank = N / world;
+  G.shard_bytes = (int64_t)G.rows_per_rank * G.row_bytes;
+  G.block_bytes = (int64_t)BN * G.row_bytes;
+  CUtensorMap ta, tb;
+  int rc = make_tmap(&ta, x, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM, ab_dtype);
+  if (rc) return rc;
+  rc = make_tmap(&tb, w_ptrs[rank], (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN, ab_dtype);
+  if (rc) return rc;
+  cudaMemsetAsync(g_ready[dev], 0, nt * sizeof(uint32_t), stream);
+  const int tiles = ((M + BM - 1) / BM) * nt;
+  int grid = tiles + num_copiers < sms ? tiles + num_copiers : sms;
+  int* err = error_word(dev);
+#define FT_AG_LAUNCH(T, MODE)                                                                   \
+  {                                                                                             \
+    auto kern = gemm_kernel<T, false, false, MODE, true>;                                       \
+    static bool configured = false;                                                             \
+    if (!configured) {                                                                          \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);      \
+      configured = true;                                                                        \
+    }                                                                                           \
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, y, ldc, M, N, K, err, G);           \
+  }
+  if (ab_dtype == kBF16) {
+    if (c_dtype == kF32) FT_AG_LAUNCH(__nv_bfloat16, kStore32) else FT_AG_LAUNCH(__nv_bfloat16, kStore16)
+  } else {
+    if (c_dtype == kF32) FT_AG_LAUNCH(__half, kStore32) else FT_AG_LAUNCH(__half, kStore16)
+  }
+#undef FT_AG_LAUNCH
+  FT_LAUNCHED(1);
+  FT_CUDA_RETURN_IF_ERROR();
+  return 0;
+}
+
+// Pull every remote shard of a flat buffer sharded in `shard_bytes` pieces
+// (rank r owns bytes [r*shard_bytes, (r+1)*shard_bytes) of every rank's buffer)
+// into the local buffer.  shard_bytes must be a multiple of 16.
+int ft_peer_gather(int world, int rank, const void* const* buf_ptrs, uint32_t* const* flags,
+                   uint32_t seq, int start_slot, int done_slot, int64_t shard_bytes, int num_copiers,
+                   cudaStream_t stream) {
+  if (world < 1 || world > peer::kMaxRanks || rank < 0 || rank >= world) return -1;
+  if (shard_bytes % 16 || shard_bytes <= 0) return -2;
+  if (world == 1) return 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (ensure_state(dev)) return -4;
+  if (num_copiers < 1) num_copiers = 1;
+  GatherArgs G;
+  fill_gather(G, world, rank, buf_ptrs, flags, seq, start_slot, done_slot, num_copiers, dev);
+  G.shard_bytes = shard_bytes;
+  G.block_bytes = (shard_bytes * world + kReadyWords - 1) / kReadyWords;
+  if (G.block_bytes < COPY_CHUNK) G.block_bytes = COPY_CHUNK;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(peer_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    configured = true;
+  }
+  peer_gather_kernel<<<num_copiers, 32, SMEM_BYTES, stream>>>(G, error_word(dev));
+  FT_LAUNCHED(1);
+  FT_CUDA_RETURN_IF_ERROR();
+  return 0;
+}
+
+}  // extern "C"

@@ -26,241 +26,13 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
-#include "tcgen05.cuh"
+#include "gemm_kernel.cuh"
+#include "gemm_host.h"
 
 namespace {
 
 using namespace ft;
-using namespace ft::sm100;
-
-constexpr int BM = 128, BN = 256, BK = 64, UK = 16, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int GROUP_M = 16;
-constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-
-enum OutMode : int { kStore16 = 0, kStore32 = 1, kAcc16 = 2, kAcc32 = 3 };
-
-struct Barriers {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
-  uint32_t tmem_base;
-  uint32_t abort;
-};
-
-__device__ __forceinline__ void tile_coords(int t, int mt, int nt, int& mb, int& nb) {
-  const int group_size = GROUP_M * nt;
-  const int group = t / group_size;
-  const int first_m = group * GROUP_M;
-  const int gm = min(mt - first_m, GROUP_M);
-  const int in_group = t - group * group_size;
-  mb = first_m + in_group % gm;
-  nb = in_group / gm;
-}
-
-template <typename T, int MODE>
-__device__ __forceinline__ void store_chunk(const uint32_t (&acc)[32], void* C, int64_t ldc, int row,
-                                            int col0, int M, int N) {
-  if (row >= M) return;
-  float v[32];
-#pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
-  if constexpr (MODE == kStore32 || MODE == kAcc32) {
-    float* p = reinterpret_cast<float*>(C) + (int64_t)row * ldc + col0;
-    if (col0 + 32 <= N && (ldc % 4 == 0)) {
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        if constexpr (MODE == kAcc32) {
-          float4 old = reinterpret_cast<float4*>(p)[q];
-          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-        }
-        reinterpret_cast<float4*>(p)[q] = o;
-      }
-    } else {
-      for (int j = 0; j < 32 && col0 + j < N; ++j) p[j] = (MODE == kAcc32 ? p[j] : 0.f) + v[j];
-    }
-  } else {
-    T* p = reinterpret_cast<T*>(C) + (int64_t)row * ldc + col0;
-    if (col0 + 32 <= N && (ldc % 8 == 0)) {
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = v[8 * q + j];
-        if constexpr (MODE == kAcc16) {
-          float old[8];
-          unpack8<T>(reinterpret_cast<uint4*>(p)[q], old);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += old[j];
-        }
-        reinterpret_cast<uint4*>(p)[q] = pack8<T>(o);
-      }
-    } else {
-      for (int j = 0; j < 32 && col0 + j < N; ++j)
-        p[j] = from_float<T>((MODE == kAcc16 ? to_float(p[j]) : 0.f) + v[j]);
-    }
-  }
-}
-
-template <typename T, bool A_MN, bool B_MN, int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            void* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mt = (M + BM - 1) / BM, nt = (N + BN - 1) / BN, kt = (K + BK - 1) / BK;
-  const int num_tiles = mt * nt;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->empty[s], 1);
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&bars->tmem_full[a], 1);
-      mbar_init(&bars->tmem_empty[a], 4);
-    }
-    bars->abort = 0;
-    fence_barrier_init();
-    prefetch_tmap(&tmap_a);
-    prefetch_tmap(&tmap_b);
-  }
-  if (warp == 1) {
-    tmem_alloc(&bars->tmem_base, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = bars->tmem_base;
-  volatile uint32_t* abort_flag = &bars->abort;
-
-  if (warp == 0) {
-    // ------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
-        int mb, nb;
-        tile_coords(t, mt, nt, mb, nb);
-        for (int kb = 0; kb < kt; ++kb) {
-          if (!mbar_wait(&bars->empty[stage], phase ^ 1)) {
-            *abort_flag = 1;
-            atomicCAS(err, 0, 1);
-            break;
-          }
-          uint8_t* sa = smem + stage * STAGE_BYTES;
-          uint8_t* sb = sa + A_BYTES;
-          mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
-          if constexpr (A_MN) {
-#pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(sa + j * (64 * BK * 2), &tmap_a, &bars->full[stage], mb * BM + j * 64, kb * BK);
-          } else {
-            tma_load_2d(sa, &tmap_a, &bars->full[stage], kb * BK, mb * BM);
-          }
-          if constexpr (B_MN) {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (64 * BK * 2), &tmap_b, &bars->full[stage], nb * BN + j * 64, kb * BK);
-          } else {
-            tma_load_2d(sb, &tmap_b, &bars->full[stage], kb * BK, nb * BN);
-          }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // -------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc =
-          make_idesc_f16(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0, A_MN ? 1 : 0,
-                         B_MN ? 1 : 0, BM, BN);
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++it) {
-        const int acc = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1)) {
-          *abort_flag = 1;
-          atomicCAS(err, 0, 2);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
-        bool failed = false;
-        for (int kb = 0; kb < kt; ++kb) {
-          if (!mbar_wait(&bars->full[stage], phase)) {
-            *abort_flag = 1;
-            atomicCAS(err, 0, 3);
-            failed = true;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sb = sa + A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UK; ++k) {
-            const uint64_t da = A_MN ? make_smem_desc(sa + k * (UK * 128), 64 * BK * 2, 1024)
-                                     : make_smem_desc(sa + k * (UK * 2), 16, 1024);
-            const uint64_t db = B_MN ? make_smem_desc(sb + k * (UK * 128), 64 * BK * 2, 1024)
-                                     : make_smem_desc(sb + k * (UK * 2), 16, 1024);
-            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
-          umma_commit(&bars->empty[stage]);          // frees the stage once the MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-        if (failed) break;
-        umma_commit(&bars->tmem_full[acc]);          // accumulator complete
-      }
-    }
-  } else {
-    // ---------------------------------------------------------- epilogue
-    const int quarter = warp & 3;                    // TMEM lane quarter this warp may read
-    int it = 0;
-    for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++it) {
-      int mb, nb;
-      tile_coords(t, mt, nt, mb, nb);
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait(&bars->tmem_full[acc], acc_phase)) {
-        *abort_flag = 1;
-        atomicCAS(err, 0, 4);
-        break;
-      }
-      tc_fence_after();
-      const int row = mb * BM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = nb * BN + c * 32;
-        if (col0 >= N) break;                        // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        store_chunk<T, MODE>(r, C, ldc, row, col0, M, N);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
+using namespace ft::gemm;
 
 // ------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -302,6 +74,11 @@ struct MapKeyHash {
 std::mutex g_map_mu;
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
+}  // namespace
+
+namespace ft {
+namespace gemm {
+
 // 2-D row-major tensor [outer, inner] with row stride ld (elements), 128B swizzle.
 int make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
               uint32_t box_inner, uint32_t box_outer, int dtype) {
@@ -341,8 +118,8 @@ int make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer,
   return 0;
 }
 
-int* g_err_word[16] = {nullptr};
-int g_sm_count[16] = {0};
+static int* g_err_word[16] = {nullptr};
+static int g_sm_count[16] = {0};
 
 int* error_word(int dev) {
   if (!g_err_word[dev]) {
@@ -352,6 +129,16 @@ int* error_word(int dev) {
   }
   return g_err_word[dev];
 }
+
+int sm_count(int dev) {
+  error_word(dev);
+  return g_sm_count[dev];
+}
+
+}  // namespace gemm
+}  // namespace ft
+
+namespace {
 
 template <typename T, bool A_MN, bool B_MN>
 int launch_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64_t ldc, int M, int N,
@@ -364,7 +151,7 @@ int launch_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);           \
       configured = true;                                                                             \
     }                                                                                                \
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, C, ldc, M, N, K, err);                        \
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, C, ldc, M, N, K, err, GatherArgs{});                        \
   }
   switch (mode) {
     case kStore16: FT_LAUNCH(kStore16); break;
@@ -414,7 +201,7 @@ int ft_gemm(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64
   else rc = make_tmap(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN, ab_dtype);
   if (rc) return rc;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < g_sm_count[dev] ? tiles : g_sm_count[dev];
+  const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
   const int mode = c_dtype == kF32 ? (accumulate ? kAcc32 : kStore32) : (accumulate ? kAcc16 : kStore16);
   if (ab_dtype == kBF16)
     rc = launch_layout<__nv_bfloat16>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);

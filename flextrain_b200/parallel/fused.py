@@ -81,3 +81,50 @@ def rs_adam(world: int, rank: int, grad_ptrs, flag_ptrs, grad_dtype: torch.dtype
 
 def comm_error() -> int:
     return _lib().ft_comm_error()
+
+
+# ------------------------------------------------------------ all-gather + GEMM
+_AG_DECLARED = False
+
+
+def _ag_lib():
+    global _AG_DECLARED
+    lib = cuda_lib()
+    if not _AG_DECLARED:
+        lib.ft_ag_gemm.argtypes = [c_int, c_int, c_void_p, c_void_p, c_uint32, c_int, c_int, c_void_p,
+                                   c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p]
+        lib.ft_peer_gather.argtypes = [c_int, c_int, c_void_p, c_void_p, c_uint32, c_int, c_int, c_int64,
+                                       c_int, c_void_p]
+        lib.ft_ag_set_spin_budget.argtypes = [ctypes.c_longlong]
+        _AG_DECLARED = True
+    return lib
+
+
+def ag_gemm(world: int, rank: int, w_ptrs, flag_ptrs, seq: int, x: torch.Tensor, n: int,
+            out: Optional[torch.Tensor] = None, num_copiers: int = 16, start_slot: int = 2,
+            done_slot: int = 3) -> torch.Tensor:
+    """``out[M, n] = x[M, K] @ W.T`` where ``W [n, K]`` is row-sharded over the
+    ranks and gathered inside the same kernel.  ``w_ptrs`` are the peer mappings
+    of every rank's full-size weight buffer (own shard already in place)."""
+    m, k = x.shape
+    if out is None:
+        out = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    rc = _ag_lib().ft_ag_gemm(world, rank, ctypes.cast(w_ptrs, c_void_p),
+                              ctypes.cast(flag_ptrs, c_void_p) if flag_ptrs is not None else None, seq,
+                              start_slot, done_slot, ptr(x), x.stride(0), ptr(out), out.stride(0),
+                              dtype_code(out.dtype), m, n, k, dtype_code(x.dtype), num_copiers,
+                              stream_handle())
+    if rc != 0:
+        raise RuntimeError(f"ft_ag_gemm failed (code {rc})")
+    return out
+
+
+def peer_gather(world: int, rank: int, buf_ptrs, flag_ptrs, seq: int, shard_bytes: int,
+                num_copiers: int = 16, start_slot: int = 4, done_slot: int = 5):
+    """Pull every remote shard of a flat peer-mapped buffer into the local copy."""
+    rc = _ag_lib().ft_peer_gather(world, rank, ctypes.cast(buf_ptrs, c_void_p),
+                                  ctypes.cast(flag_ptrs, c_void_p), seq, start_slot, done_slot,
+                                  shard_bytes, num_copiers, stream_handle())
+    if rc != 0:
+        raise RuntimeError(f"ft_peer_gather failed (code {rc})")

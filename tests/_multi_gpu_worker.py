@@ -102,8 +102,56 @@ def case_engine():
     print(f"engine fused == nccl: {a} vs {b}", flush=True)
 
 
+def case_ag_gemm():
+    import torch.distributed as tdist
+    import flextrain_b200 as ft
+    from flextrain_b200.ops.native import cuda_lib
+    from flextrain_b200.parallel import fused
+    from flextrain_b200.parallel.symm_mem import FlagPage, SymmetricBuffer
+    ft.init_distributed("nccl")
+    world, rank = ft.distributed.get_world_size(), ft.distributed.get_rank()
+    dev = ft.distributed.current_device()
+    page = FlagPage()
+    M, N, K = 1024, 256 * world * 3, 512
+    torch.manual_seed(3)
+    full = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    rows = N // world
+    symm = SymmetricBuffer(N * K * 2)
+    w = symm.tensor(torch.bfloat16).view(N, K)
+    want = x.float() @ full.float().t()
+    for it in range(3):
+        w.zero_()
+        w[rank * rows:(rank + 1) * rows].copy_(full[rank * rows:(rank + 1) * rows])
+        torch.cuda.synchronize()
+        tdist.barrier()
+        y = fused.ag_gemm(world, rank, symm.ptr_array(), page.ptr_array(), page.next_seq("ag"), x, N,
+                          num_copiers=8)
+        torch.cuda.synchronize()
+        assert cuda_lib().ft_gemm_error() == 0
+        assert ((y.float() - want).norm() / want.norm()).item() < 1e-2
+        assert torch.equal(w, full)
+        tdist.barrier()
+    # whole-buffer peer gather
+    flat = symm.tensor(torch.uint8)
+    shard = symm.nbytes // world
+    ref = torch.arange(symm.nbytes, device=dev, dtype=torch.int64).remainder_(251).to(torch.uint8)
+    flat.zero_()
+    flat[rank * shard:(rank + 1) * shard].copy_(ref[rank * shard:(rank + 1) * shard])
+    torch.cuda.synchronize()
+    tdist.barrier()
+    fused.peer_gather(world, rank, symm.ptr_array(), page.ptr_array(), page.next_seq("pg"), shard, 8)
+    torch.cuda.synchronize()
+    assert cuda_lib().ft_gemm_error() == 0
+    assert torch.equal(flat, ref)
+    tdist.barrier()
+    symm.close()
+    page.close()
+    print(f"rank {rank}: ag_gemm ok", flush=True)
+
+
 if __name__ == "__main__":
-    {"rs_adam": case_rs_adam, "engine": case_engine}[sys.argv[1]]()
+    {"rs_adam": case_rs_adam, "engine": case_engine, "ag_gemm": case_ag_gemm}[sys.argv[1]]()
     if torch.distributed.is_initialized():
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()

@@ -117,3 +117,55 @@ def test_bounded_wait_reports_instead_of_hanging():
         lib.ft_comm_set_spin_budget(0)
     x = torch.ones(1024, device=dev)
     assert float((x * 2).sum()) == 2048.0
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_ag_gemm_emulated_ranks(world):
+    """All ranks' weight buffers on one GPU, barriers pre-satisfied: the copier
+    CTAs pull the 'remote' row shards while the other CTAs multiply."""
+    from flextrain_b200.ops.native import cuda_lib
+    from flextrain_b200.parallel import fused
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(7)
+    M, N, K = 512, 256 * world * 2, 320
+    W = (torch.randn(N, K, device=dev) * 0.1).to(torch.bfloat16)
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    rows = N // world
+    bufs = []
+    for r in range(world):
+        b = torch.zeros(N, K, device=dev, dtype=torch.bfloat16)
+        b[r * rows:(r + 1) * rows] = W[r * rows:(r + 1) * rows]     # only the own shard is in place
+        bufs.append(b)
+    flags = [torch.full((128 * 8,), 5, dtype=torch.int32, device=dev) for _ in range(world)]
+    wp = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    want = x.float() @ W.float().t()
+    for rank in range(world):
+        y = fused.ag_gemm(world, rank, wp, fp, 5, x, N, num_copiers=4)
+        torch.cuda.synchronize()
+        assert cuda_lib().ft_gemm_error() == 0
+        err = ((y.float() - want).norm() / want.norm()).item()
+        assert err < 1e-2, f"rank {rank}: {err}"
+        assert torch.equal(bufs[rank], W), "the local buffer must hold the whole weight afterwards"
+        # put the buffer back to 'own shard only' for the next emulated rank's peers
+    
+
+def test_peer_gather_emulated_ranks():
+    from flextrain_b200.ops.native import cuda_lib
+    from flextrain_b200.parallel import fused
+    dev = torch.device("cuda", 0)
+    world = 4
+    shard = 4096 * 37 + 4096                      # bytes, page aligned, not a multiple of 32 KiB
+    full = torch.randint(0, 255, (world * shard,), dtype=torch.uint8, device=dev)
+    bufs = []
+    for r in range(world):
+        b = torch.zeros(world * shard, dtype=torch.uint8, device=dev)
+        b[r * shard:(r + 1) * shard] = full[r * shard:(r + 1) * shard]
+        bufs.append(b)
+    flags = [torch.full((128 * 8,), 9, dtype=torch.int32, device=dev) for _ in range(world)]
+    bp = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    fused.peer_gather(world, 2, bp, fp, 9, shard, num_copiers=3)
+    torch.cuda.synchronize()
+    assert cuda_lib().ft_gemm_error() == 0
+    assert torch.equal(bufs[2], full)

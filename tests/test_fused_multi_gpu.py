@@ -27,7 +27,7 @@ def _gpus():
 
 
 @pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("case", ["rs_adam", "engine"])
+@pytest.mark.parametrize("case", ["rs_adam", "engine", "ag_gemm"])
 def test_two_ranks(case):
     _launch(case, 2)
 
