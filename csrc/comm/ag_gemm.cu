@@ -43,16 +43,19 @@ int ensure_state(int dev) {
   return 0;
 }
 
-__global__ void __launch_bounds__(32, 1)
+// Small footprint on purpose (3 x 8 KiB of shared memory, one warp): these CTAs
+// must fit on an SM beside a resident GEMM CTA, otherwise a gather that runs on
+// a side stream would take whole SMs away from the compute stream.
+constexpr int PG_CHUNK = 8192, PG_STAGES = 3;
+
+__global__ void __launch_bounds__(32)
 peer_gather_kernel(const __grid_constant__ GatherArgs gather, int* __restrict__ err) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  __shared__ __align__(128) uint8_t ring[PG_STAGES * PG_CHUNK];
+  __shared__ uint64_t full_bars[PG_STAGES];
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&bars->full[s], 1);
+    for (int s = 0; s < PG_STAGES; ++s) mbar_init(&full_bars[s], 1);
     fence_barrier_init();
-    gather_role(gather, smem, bars, err);
+    gather_role<PG_CHUNK, PG_STAGES, PG_CHUNK>(gather, ring, full_bars, err);
   }
 }
 
@@ -155,13 +158,8 @@ int ft_peer_gather(int world, int rank, const void* const* buf_ptrs, uint32_t* c
   fill_gather(G, world, rank, buf_ptrs, flags, seq, start_slot, done_slot, num_copiers, dev);
   G.shard_bytes = shard_bytes;
   G.block_bytes = (shard_bytes * world + kReadyWords - 1) / kReadyWords;
-  if (G.block_bytes < COPY_CHUNK) G.block_bytes = COPY_CHUNK;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(peer_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    configured = true;
-  }
-  peer_gather_kernel<<<num_copiers, 32, SMEM_BYTES, stream>>>(G, error_word(dev));
+  if (G.block_bytes < PG_CHUNK) G.block_bytes = PG_CHUNK;
+  peer_gather_kernel<<<num_copiers, 32, 0, stream>>>(G, error_word(dev));
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;

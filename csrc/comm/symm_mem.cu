@@ -17,12 +17,12 @@ void* ft_symm_alloc(size_t nbytes) {
     cudaGetLastError();
     return nullptr;
   }
-  if (cudaMemset(p, 0, nbytes) != cudaSuccess) {
+  if (cudaMemset(p, 0, nbytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
     cudaGetLastError();
     cudaFree(p);
     return nullptr;
   }
-  return p;
+  return p;   // zeroed before any peer can learn the address
 }
 
 int ft_symm_free(void* p) { return (int)cudaFree(p); }

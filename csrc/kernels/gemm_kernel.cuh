@@ -147,7 +147,9 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 
 // The copier role of one CTA: thread 0 streams this CTA's share of the remote
 // chunks through the shared-memory ring, STAGES - 1 loads in flight.
-__device__ __forceinline__ void gather_role(const GatherArgs& G, uint8_t* smem, Barriers* bars, int* err) {
+// CHUNK bytes per bulk copy, NSTAGE ring slots of STRIDE bytes, one mbarrier per slot.
+template <int CHUNK, int NSTAGE, int STRIDE>
+__device__ __forceinline__ void gather_role(const GatherArgs& G, uint8_t* smem, uint64_t* full_bars, int* err) {
   const int W = G.peers.world, R = G.peers.rank;
   if (W <= 1) return;
   uint32_t* mine = G.peers.flags[R];
@@ -163,7 +165,7 @@ __device__ __forceinline__ void gather_role(const GatherArgs& G, uint8_t* smem, 
     atomicCAS(err, 0, 201);
   } else {
     const int64_t shard_bytes = G.shard_bytes;
-    const int64_t chunks_per_shard = (shard_bytes + COPY_CHUNK - 1) / COPY_CHUNK;
+    const int64_t chunks_per_shard = (shard_bytes + CHUNK - 1) / CHUNK;
     const int64_t total = chunks_per_shard * (W - 1);
     const int64_t block_bytes = G.block_bytes;
     // chunk q of this CTA: global index blockIdx.x + q * num_copiers (the last chunk of a
@@ -172,32 +174,32 @@ __device__ __forceinline__ void gather_role(const GatherArgs& G, uint8_t* smem, 
       const int64_t gq = blockIdx.x + q * G.num_copiers;
       const int k = (int)(gq / chunks_per_shard);
       const int p = (R + 1 + k) % W;
-      const int64_t in_shard = (gq % chunks_per_shard) * COPY_CHUNK;
+      const int64_t in_shard = (gq % chunks_per_shard) * CHUNK;
       const int64_t off = (int64_t)p * shard_bytes + in_shard;
       const int64_t left = shard_bytes - in_shard;
-      bytes = (uint32_t)(left < COPY_CHUNK ? left : COPY_CHUNK);
+      bytes = (uint32_t)(left < CHUNK ? left : CHUNK);
       src = reinterpret_cast<const uint8_t*>(G.w_peer[p]) + off;
       dst = reinterpret_cast<uint8_t*>(G.w_local) + off;
       nblk = (int)(off / block_bytes);
     };
     const int64_t n = total > blockIdx.x ? (total - blockIdx.x + G.num_copiers - 1) / G.num_copiers : 0;
-    uint32_t phase[STAGES];
-    for (int s = 0; s < STAGES; ++s) phase[s] = 0;
-    for (int64_t q = 0; q < n && q < STAGES - 1; ++q) {
+    uint32_t phase[NSTAGE];
+    for (int s = 0; s < NSTAGE; ++s) phase[s] = 0;
+    for (int64_t q = 0; q < n && q < NSTAGE - 1; ++q) {
       const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
       locate(q, src, dst, nb, bytes);
-      const int s = (int)(q % STAGES);
-      mbar_expect_tx(&bars->full[s], bytes);
-      bulk_load(smem + s * STAGE_BYTES, src, bytes, &bars->full[s]);
+      const int s = (int)(q % NSTAGE);
+      mbar_expect_tx(&full_bars[s], bytes);
+      bulk_load(smem + s * STRIDE, src, bytes, &full_bars[s]);
     }
     int prev_nb = -1;
     for (int64_t q = 0; q < n; ++q) {
       const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
       locate(q, src, dst, nb, bytes);
-      const int s = (int)(q % STAGES);
-      if (!mbar_wait(&bars->full[s], phase[s])) { atomicCAS(err, 0, 202); break; }
+      const int s = (int)(q % NSTAGE);
+      if (!mbar_wait(&full_bars[s], phase[s])) { atomicCAS(err, 0, 202); break; }
       phase[s] ^= 1;
-      bulk_store(dst, smem + s * STAGE_BYTES, bytes);
+      bulk_store(dst, smem + s * STRIDE, bytes);
       bulk_commit();
       bulk_wait_all_but_1();                  // every chunk before this one is in local memory
       if (q >= 1) {
@@ -206,13 +208,13 @@ __device__ __forceinline__ void gather_role(const GatherArgs& G, uint8_t* smem, 
         red_release_add(G.ready + prev_nb, 1u);
       }
       prev_nb = nb;
-      const int64_t nq = q + STAGES - 1;
+      const int64_t nq = q + NSTAGE - 1;
       if (nq < n) {
         const uint8_t* src2; uint8_t* dst2; int nb2; uint32_t bytes2;
         locate(nq, src2, dst2, nb2, bytes2);
-        const int s2 = (int)(nq % STAGES);    // stage of chunk q - 1, whose store has completed
-        mbar_expect_tx(&bars->full[s2], bytes2);
-        bulk_load(smem + s2 * STAGE_BYTES, src2, bytes2, &bars->full[s2]);
+        const int s2 = (int)(nq % NSTAGE);    // stage of chunk q - 1, whose store has completed
+        mbar_expect_tx(&full_bars[s2], bytes2);
+        bulk_load(smem + s2 * STRIDE, src2, bytes2, &full_bars[s2]);
       }
     }
     bulk_wait_all();
@@ -280,7 +282,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   if (GATHER && first_tile < 0) {
     // ------------------------------------------------------- gather role
-    if (threadIdx.x == 0) gather_role(gather, smem, bars, err);
+    if (threadIdx.x == 0) gather_role<COPY_CHUNK, STAGES, STAGE_BYTES>(gather, smem, bars->full, err);
   } else if (warp == 0) {
     // ------------------------------------------------------ TMA producer
     if (lane == 0) {

@@ -339,3 +339,5 @@ class FlexTrainEngine:
 
     def shutdown(self):
         self.opts.shutdown()
+        self.para.drain()
+        self.para.close()

@@ -70,8 +70,19 @@ class FlexTrainParaCoordinator:
         self.tier_numels = get_split_numels(self.shard_numel, cfg.split_ratio.parameter, self.itemsize)
         g, c, n = self.tier_numels
         self.num_buffers = cfg.engine.num_unit_buffers
-        self._buffers = [allocate_memory(self.aligned_unit_numel, self.device_dtype, self.device)
-                         for _ in range(self.num_buffers)]
+        # with the fused collectives the ring buffers are peer-mapped: every rank pulls
+        # the other ranks' shards straight out of their ring buffers (no NCCL all-gather)
+        self._peer_gather = self._want_peer_gather(cfg)
+        self._symm = []
+        if self._peer_gather:
+            from ...parallel.symm_mem import SymmetricBuffer, get_flag_page
+            self._flag_page = get_flag_page()
+            self._symm = [SymmetricBuffer(self.aligned_unit_numel * self.itemsize)
+                          for _ in range(self.num_buffers)]
+            self._buffers = [sb.tensor(self.device_dtype) for sb in self._symm]
+        else:
+            self._buffers = [allocate_memory(self.aligned_unit_numel, self.device_dtype, self.device)
+                             for _ in range(self.num_buffers)]
         self._free = deque((i, DONE) for i in range(self.num_buffers))
         self._inflight: Dict[int, tuple] = {}      # unit -> (buffer index, ready event)
         self._held: Dict[int, int] = {}            # unit -> buffer index (linked)
@@ -94,6 +105,16 @@ class FlexTrainParaCoordinator:
             f"parameter geometry: units={self.num_units} unit_numel={self.unit_numel} "
             f"aligned={self.aligned_unit_numel} shard={self.shard_numel} "
             f"tiers(HBM,DRAM,NVMe)={self.tier_numels} dtype={self.device_dtype}")
+
+    def _want_peer_gather(self, cfg) -> bool:
+        want = cfg.engine.fused_collectives
+        if want is False or self.device.type != "cuda" or self.world == 1 or self.world > 8:
+            return False
+        from ...parallel.symm_mem import peer_access_available
+        ok = peer_access_available()
+        if want is True and not ok:
+            raise RuntimeError("engine.fused_collectives=true needs peer access between all ranks")
+        return bool(ok)
 
     def shard_range(self):
         return self.rank * self.shard_numel, (self.rank + 1) * self.shard_numel
@@ -249,12 +270,19 @@ class FlexTrainParaCoordinator:
                 shard[g + c:].copy_(self._nvme_landing[land_idx], non_blocking=True)
                 self._landing_busy[land_idx] = st.h2d.record()
             if self.world > 1:
-                self._all_gather(buf, shard)
+                self._all_gather(buf, shard, idx)
             ready = st.h2d.record()
         self._inflight[unit] = (idx, ready)
 
-    def _all_gather(self, buf: torch.Tensor, shard: torch.Tensor):
-        dist.all_gather(buf, shard)
+    def _all_gather(self, buf: torch.Tensor, shard: torch.Tensor, idx: int = -1):
+        if self._peer_gather and idx >= 0:
+            from ...parallel import fused
+            page = self._flag_page
+            fused.peer_gather(self.world, self.rank, self._symm[idx].ptr_array(), page.ptr_array(),
+                              page.next_seq("gather"), self.shard_numel * self.itemsize,
+                              num_copiers=self._cfg.engine.fused_blocks)
+        else:
+            dist.all_gather(buf, shard)
 
     def acquire(self, unit: int):
         """Block the compute stream until ``unit`` is gathered; link its parameters."""
@@ -311,6 +339,14 @@ class FlexTrainParaCoordinator:
             self._free.append(self._cached.pop(unit))
         self.detach_all_parameters()
 
+    def close(self):
+        if self._initialized and self._symm:
+            self.streams.synchronize()
+            self._buffers = []
+            for sb in self._symm:
+                sb.close()
+            self._symm = []
+
     # ----------------------------------------------------------- accounting
     def hbm_bytes(self) -> int:
         g = self.tier_numels[0]
@@ -329,4 +365,6 @@ def get_para_coordinator() -> FlexTrainParaCoordinator:
 
 def reset_para_coordinator():
     global _PARA
+    if _PARA is not None and _PARA.is_initialized:
+        _PARA.close()
     _PARA = None

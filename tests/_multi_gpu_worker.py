@@ -87,6 +87,7 @@ def case_engine():
         model, opt, eng = build_llama_engine(cfg, ft_cfg, batch_fn, lr=1e-3, init_device=dev,
                                              dtype=torch.bfloat16)
         assert eng.opts._fused == fused_mode
+        assert eng.para._peer_gather == fused_mode
         losses = []
         for _ in range(4):
             r = eng.train_iteration()
