@@ -118,7 +118,7 @@ def pick_model(args, world, hbm_free, dram_avail):
         if args.layers:
             cfg.num_layers = args.layers
         mbs = MICRO_BATCH.get(name, 2)
-        mbpr = args.micro_batches_per_rank or 2
+        mbpr = args.micro_batches_per_rank or 1
         shape = planner.shape_of(cfg, mbs)
         budget = planner.MemoryBudget(hbm_free, dram_avail / world * 0.85, 0.0)
         split = planner.plan(shape, world, mbpr, budget, unit_buffers=args.unit_buffers,

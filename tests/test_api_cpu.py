@@ -1,0 +1,59 @@
+import argparse
+
+import pytest
+import torch
+
+import flextrain_b200 as ft
+from flextrain_b200.llm_func import LLMFunc, retrieve_llm_loss, set_llm_func
+
+
+def test_config_arguments():
+    p = ft.add_config_arguments(argparse.ArgumentParser())
+    a = p.parse_args(["--flextrain", "--flextrain-config", "c.json"])
+    assert a.flextrain and a.flextrain_config == "c.json"
+    assert not p.parse_args([]).flextrain
+
+
+def test_llm_func_registry_and_loss_retrieval():
+    with pytest.raises(NotImplementedError):
+        LLMFunc.get_batch()
+    set_llm_func(lambda i: i, lambda: ((1,), (), ()), lambda x: (x, ()), lambda s, e: (lambda *a: a),
+                 lambda p, q: p, lambda o, l: o)
+    assert LLMFunc.get_layer(3) == 3 and LLMFunc.get_batch() == ((1,), (), ())
+    t = torch.tensor(2.0)
+    assert retrieve_llm_loss(t) is t
+    assert retrieve_llm_loss(["x", torch.ones(3), torch.tensor([4.0])]).item() == 4.0
+    with pytest.raises(ValueError):
+        retrieve_llm_loss([torch.ones(3)])
+
+
+def test_public_names():
+    for name in ("Init", "LLMFunc", "set_llm_func", "initialize", "init_distributed", "distributed",
+                 "add_config_arguments", "shutdown_init_context", "restore_init_context"):
+        assert hasattr(ft, name)
+    from flextrain_b200.checkpointing import (checkpointed_backward, checkpointed_forward,  # noqa
+                                              detach_variable, get_cuda_rng_tracker,
+                                              model_parallel_cuda_manual_seed)
+    from flextrain_b200.ops.adam import FlexTrainAdam  # noqa
+    from flextrain_b200.ops.adam.cpu_adam import FlexTrainCPUAdam  # noqa
+    from flextrain_b200.optimizer import FlexTrainCPUOptimizer, FlexTrainOptimizer  # noqa
+
+
+def test_engine_shims_and_health(fresh_runtime):
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine
+    cfg = preset("tiny", num_layers=2, hidden=64, num_heads=2, ffn=128, vocab=128, seq_len=16)
+    tok = torch.randint(0, 128, (2, 17))
+    ft_cfg = {"batch_size": 2, "micro_batch_size": 2, "mixed_precision": {"device_dtype": "fp32"}}
+    model, opt, eng = build_llama_engine(cfg, ft_cfg, lambda: (tok[:, :-1], tok[:, 1:]), backend="gloo")
+    calls = []
+    eng.register_post_step_function(lambda: calls.append(1))
+    assert eng.step() is None and eng.loss_scale == 1.0 and not eng.dynamic_loss_scaling
+    eng.override_loss_scale(8.0)
+    l0 = float(eng.train_iteration()[0].detach())
+    l1 = float(eng.train_iteration()[0].detach())
+    assert calls == [1, 1] and eng.loss_scale == 8.0 and l1 < l0    # scale-invariant update
+    h = eng.health()
+    assert h["global_steps"] == 2 and h["skipped_steps"] == 0 and h["last_step_seconds"] > 0
+    assert eng.train() is eng and eng.eval() is eng
+    eng.shutdown()

