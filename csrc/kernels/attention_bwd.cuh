@@ -1,0 +1,323 @@
+// Causal grouped-query flash attention, backward, on tcgen05 tensor cores.
+//
+// One CTA per (batch, kv head, 128-row kv block n).  K_n and V_n stay in shared
+// memory; the CTA walks every query head of the group and every query block
+// m >= n, and per (head, m):
+//   TMA      Q_m, dO_m                      ([64-col chunk][row][64], 128B swizzle)
+//   MMA      S  = Q K^T,  dP = dO V^T       -> TMEM
+//   warps    P  = exp(scale*S - lse),  dS = scale * P * (dP - delta)
+//            written as 16-bit tiles [q][kv] into shared memory
+//   MMA      dV += P^T dO,  dK += dS^T Q    (accumulated in TMEM over the whole walk)
+//            dQ_m = dS K                    -> TMEM, then fp32 vector atomics into dq_acc
+// The same shared-memory bytes serve as K-major operand (reduction over the 64
+// contiguous columns) and as MN-major operand (reduction over the rows), so no
+// tile is ever transposed.  dK / dV are written once at the end; dq_acc is
+// converted to the 16-bit dq by a separate pass.  All waits are bounded.
+#pragma once
+#include "attention_fwd.cuh"
+
+namespace ft {
+namespace attn {
+
+template <int D>
+struct BwdSmem {
+  static constexpr int TILE = BQ * D * 2;
+  static constexpr int P_BYTES = BQ * BKV * 2;
+  static constexpr int BYTES = 4 * TILE + 2 * P_BYTES + 1024 + 256;
+};
+
+struct BwdBars {
+  uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_full, dq_full, s_free, acc_full;
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+struct BwdParams {
+  const float* lse;        // [B, Hq, S]
+  const float* delta;      // [B, Hq, S]  rowsum(dO * O)
+  float* dq_acc;           // [B, S, Hq, D] fp32, zeroed by the caller
+  void* dk; int64_t dk_stride;   // [B, S, Hkv, D] with token stride
+  void* dv; int64_t dv_stride;
+  int B, S, Hq, Hkv;
+  float scale, scale_log2;
+  int* err;
+  int debug_skip;          // profiling aid: bit 0 skips the dq atomics, bit 1 skips exp
+};
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                const __grid_constant__ BwdParams P) {
+  constexpr int TILE = BwdSmem<D>::TILE;
+  constexpr int CHUNKS = D / 64;
+  constexpr int CHUNK_BYTES = BQ * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sQ = sV + TILE;
+  uint8_t* sdO = sQ + TILE;
+  uint8_t* sP = sdO + TILE;
+  uint8_t* sdS = sP + BwdSmem<D>::P_BYTES;
+  BwdBars* bars = reinterpret_cast<BwdBars*>(sdS + BwdSmem<D>::P_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_blk = (P.S + BQ - 1) / BQ;
+  const int nb = (int)(blockIdx.x % num_blk);        // kv block; low blocks (most work) first
+  const int kv_head = (int)((blockIdx.x / num_blk) % P.Hkv);
+  const int batch = (int)(blockIdx.x / (num_blk * P.Hkv));
+  const int group = P.Hq / P.Hkv;
+  const int q_blocks = num_blk - nb;                 // m = nb .. num_blk-1
+  const int iters = group * q_blocks;
+  const int kv_row0 = batch * P.S + nb * BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    mbar_init(&bars->qdo_full, 1);
+    mbar_init(&bars->qdo_empty, 1);
+    mbar_init(&bars->sdp_full, 1);
+    mbar_init(&bars->pds_full, 128);
+    mbar_init(&bars->dq_full, 1);
+    mbar_init(&bars->s_free, 128);
+    mbar_init(&bars->acc_full, 1);
+    bars->abort = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  volatile uint32_t* abort_flag = &bars->abort;
+  const uint32_t tm_s = tmem, tm_dp = tmem + 128, tm_dv = tmem + 256, tm_dk = tmem + 384;
+  const uint32_t tm_dq = tmem;                       // reuses the S columns once P is extracted
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&bars->kv_full, 2 * TILE);
+      for (int c = 0; c < CHUNKS; ++c) {
+        tma_load_2d(sK + c * CHUNK_BYTES, &tmap_k, &bars->kv_full, kv_head * D + c * 64, kv_row0);
+        tma_load_2d(sV + c * CHUNK_BYTES, &tmap_v, &bars->kv_full, kv_head * D + c * 64, kv_row0);
+      }
+      for (int it = 0; it < iters && !*abort_flag; ++it) {
+        const int head = kv_head * group + it / q_blocks;
+        const int m = nb + it % q_blocks;
+        const int q_row0 = batch * P.S + m * BQ;
+        if (!mbar_wait(&bars->qdo_empty, (it & 1) ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 401); break; }
+        mbar_expect_tx(&bars->qdo_full, 2 * TILE);
+        for (int c = 0; c < CHUNKS; ++c) {
+          tma_load_2d(sQ + c * CHUNK_BYTES, &tmap_q, &bars->qdo_full, head * D + c * 64, q_row0);
+          tma_load_2d(sdO + c * CHUNK_BYTES, &tmap_do, &bars->qdo_full, head * D + c * 64, q_row0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t id_s = make_idesc_f16(AB, 0, 0, BQ, BKV);     // K-major x K-major
+      constexpr uint32_t id_t = make_idesc_f16(AB, 1, 1, BKV, D);      // MN-major x MN-major
+      constexpr uint32_t id_q = make_idesc_f16(AB, 0, 1, BQ, D);       // K-major x MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sdO),
+                     aP = smem_u32(sP), aDS = smem_u32(sdS);
+      bool ok = mbar_wait(&bars->kv_full, 0);
+      if (!ok) atomicCAS(P.err, 0, 402);
+      for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(&bars->qdo_full, ph)) { atomicCAS(P.err, 0, 403); ok = false; break; }
+        if (!mbar_wait(&bars->s_free, ph ^ 1)) { atomicCAS(P.err, 0, 404); ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
+          umma_f16(tm_s, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), id_s,
+                   kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
+          umma_f16(tm_dp, make_smem_desc(aDO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024), id_s,
+                   kk != 0);
+        }
+        umma_commit(&bars->sdp_full);
+        if (!mbar_wait(&bars->pds_full, ph)) { atomicCAS(P.err, 0, 405); ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) {       // reduction over the 128 query rows
+          const uint32_t row_off = kk * 2048;
+          umma_f16(tm_dv, make_smem_desc(aP + row_off, CHUNK_BYTES, 1024),
+                   make_smem_desc(aDO + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
+          umma_f16(tm_dk, make_smem_desc(aDS + row_off, CHUNK_BYTES, 1024),
+                   make_smem_desc(aQ + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {      // reduction over the 128 kv rows
+          const uint32_t a_off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
+          umma_f16(tm_dq, make_smem_desc(aDS + a_off, 16, 1024),
+                   make_smem_desc(aK + kk * 2048, CHUNK_BYTES, 1024), id_q, kk != 0);
+        }
+        umma_commit(&bars->qdo_empty);
+        umma_commit(&bars->dq_full);
+      }
+      if (ok) umma_commit(&bars->acc_full);
+      else *abort_flag = 1;
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float log2e = 1.4426950408889634f;
+    bool ok = true;
+    for (int it = 0; it < iters; ++it) {
+      const uint32_t ph = it & 1;
+      const int head = kv_head * group + it / q_blocks;
+      const int m = nb + it % q_blocks;
+      const int q_pos = m * BQ + r;
+      const bool valid = q_pos < P.S;
+      const int64_t stat = ((int64_t)batch * P.Hq + head) * P.S + q_pos;
+      const float lse2 = valid ? P.lse[stat] * log2e : 0.f;
+      const float delta = valid ? P.delta[stat] : 0.f;
+      if (!mbar_wait(&bars->sdp_full, ph)) { atomicCAS(P.err, 0, 406); ok = false; break; }
+      tc_fence_after();
+      const bool diag = (m == nb);
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tm_s + lane_addr + c * 32, sv);
+        tmem_ld_32x32(tm_dp + lane_addr + c * 32, dv);
+        tmem_ld_wait();
+        float p[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kv_pos = nb * BKV + c * 32 + i;
+          float pi = exp2f(__uint_as_float(sv[i]) * P.scale_log2 - lse2);
+          if (!valid || (diag && kv_pos > q_pos)) pi = 0.f;
+          p[i] = pi;
+          ds[i] = pi * (__uint_as_float(dv[i]) - delta) * P.scale;
+        }
+        uint8_t* pc = sP + (c / 2) * CHUNK_BYTES;
+        uint8_t* dc = sdS + (c / 2) * CHUNK_BYTES;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float t[8], d8[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { t[i] = p[u * 8 + i]; d8[i] = ds[u * 8 + i]; }
+          const uint32_t o = swz(r, (c % 2) * 4 + u);
+          *reinterpret_cast<uint4*>(pc + o) = pack8<T>(t);
+          *reinterpret_cast<uint4*>(dc + o) = pack8<T>(d8);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      mbar_arrive(&bars->pds_full);
+      if (!mbar_wait(&bars->dq_full, ph)) { atomicCAS(P.err, 0, 407); ok = false; break; }
+      tc_fence_after();
+      float* dq_row = P.dq_acc + ((int64_t)(batch * P.S + q_pos) * P.Hq + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_dq + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        if (valid && !(P.debug_skip & 1)) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            red_add_v4(dq_row + c * 32 + u * 4, __uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]),
+                       __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->s_free);
+    }
+    if (ok && !mbar_wait(&bars->acc_full, 0)) { atomicCAS(P.err, 0, 408); ok = false; }
+    if (ok) {
+      tc_fence_after();
+      const int kv_pos = nb * BKV + r;
+      if (kv_pos < P.S) {
+        T* dk_row = reinterpret_cast<T*>(P.dk) + (int64_t)(batch * P.S + kv_pos) * P.dk_stride + kv_head * D;
+        T* dv_row = reinterpret_cast<T*>(P.dv) + (int64_t)(batch * P.S + kv_pos) * P.dv_stride + kv_head * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t a[32], b[32];
+          tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
+          tmem_ld_32x32(tm_dv + lane_addr + c * 32, b);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float t[8], w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { t[i] = __uint_as_float(a[u * 8 + i]); w[i] = __uint_as_float(b[u * 8 + i]); }
+            *reinterpret_cast<uint4*>(dk_row + c * 32 + u * 8) = pack8<T>(t);
+            *reinterpret_cast<uint4*>(dv_row + c * 32 + u * 8) = pack8<T>(w);
+          }
+        }
+      } else {
+        // rows past the end of the sequence still have to drain their TMEM loads uniformly
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t a[32];
+          tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
+          tmem_ld_wait();
+        }
+      }
+    } else {
+      *abort_flag = 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// delta[b,h,s] = sum_d dO * O   (one warp per (token, head) row)
+template <typename T>
+__global__ void __launch_bounds__(256) attn_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
+                                                         int64_t do_stride, float* __restrict__ delta,
+                                                         int B, int S, int Hq, int D) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * S * Hq) return;
+  const int64_t tok = row / Hq;
+  const int h = (int)(row % Hq);
+  const T* op = o + row * D;
+  const T* dp = d_o + tok * do_stride + (int64_t)h * D;
+  float acc = 0.f;
+  for (int i = lane * 8; i < D; i += 256) {
+    float a[8], b[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(op + i), a);
+    unpack8<T>(*reinterpret_cast<const uint4*>(dp + i), b);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc += a[k] * b[k];
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    const int64_t b_idx = tok / S, s_idx = tok % S;
+    delta[(b_idx * Hq + h) * S + s_idx] = acc;
+  }
+}
+
+// dq (16-bit, token stride) <- dq_acc (fp32, contiguous [tokens, W])
+template <typename T>
+__global__ void __launch_bounds__(256) attn_dq_cast_kernel(const float* __restrict__ acc, T* __restrict__ dq,
+                                                           int64_t dq_stride, int64_t tokens, int W) {
+  const int vec = W / 8;
+  const int64_t total = tokens * vec;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / vec;
+    const int c = (int)(idx % vec) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(acc + t * W + c);
+    const float4 b = *reinterpret_cast<const float4*>(acc + t * W + c + 4);
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    *reinterpret_cast<uint4*>(dq + t * dq_stride + c) = pack8<T>(v);
+  }
+}
+
+}  // namespace attn
+}  // namespace ft

@@ -337,6 +337,56 @@ class FlexTrainEngine:
         out.update(self.timer.summary())
         return out
 
+    # ------------------------------------------------------ save / resume
+    def save(self, directory: str):
+        """Write this rank's training state to ``directory/rank{r}_state.pt``:
+        the fp32 master weights and optimizer states of every unit shard
+        (whatever tier they live in), the non-layerwise parameters' state, the
+        param groups' hyper-parameters and step counters, the loss scaler and
+        the RNG state.  The reference has no persistent checkpoint at all
+        (its only on-disk artefacts are transient swap files)."""
+        import os
+        self.synchronize()
+        os.makedirs(directory, exist_ok=True)
+        state = {
+            "world_size": self.world, "rank": dist.get_rank(), "global_steps": self.global_steps,
+            "skipped_steps": self.skipped_steps, "num_units": self.num_units,
+            "shard_numel": self.para.shard_numel,
+            "units": [self.opts.read_states(u) for u in range(self.num_units)],
+            "non_layerwise": self.optimizer.non_layerwise_state(),
+            "param_groups": self.optimizer.hyper_state(),
+            "loss_scaler": self.loss_scaler.state_dict(),
+            "rng_cpu": torch.get_rng_state(),
+            "rng_cuda": torch.cuda.get_rng_state() if self.device.type == "cuda" else None,
+        }
+        path = os.path.join(directory, f"rank{dist.get_rank()}_state.pt")
+        torch.save(state, path)
+        dist.barrier()
+        return path
+
+    def load(self, directory: str):
+        """Restore what ``save`` wrote (same world size and partition geometry)."""
+        import os
+        self.synchronize()
+        path = os.path.join(directory, f"rank{dist.get_rank()}_state.pt")
+        state = torch.load(path, map_location="cpu", weights_only=False)
+        if state["world_size"] != self.world or state["num_units"] != self.num_units \
+                or state["shard_numel"] != self.para.shard_numel:
+            raise ValueError("checkpoint was written with a different world size or model partition")
+        for u, states in enumerate(state["units"]):
+            self.opts.write_states(u, states)
+        self.optimizer.load_non_layerwise_state(state["non_layerwise"])
+        self.optimizer.load_hyper_state(state["param_groups"])
+        self.loss_scaler.load_state_dict(state["loss_scaler"])
+        self.global_steps = state["global_steps"]
+        self.skipped_steps = state["skipped_steps"]
+        torch.set_rng_state(state["rng_cpu"])
+        if state.get("rng_cuda") is not None and self.device.type == "cuda":
+            torch.cuda.set_rng_state(state["rng_cuda"])
+        self.para.drain()
+        self.synchronize()
+        dist.barrier()
+
     def shutdown(self):
         self.opts.shutdown()
         self.para.drain()

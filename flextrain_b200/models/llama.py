@@ -95,6 +95,11 @@ class LlamaBlock(nn.Module):
         if qkv.is_cuda:
             # rotate the q and k heads inside the fused projection; q, k, v stay views
             qkv = F.rope_heads_inplace(qkv, cos, sin, nh + nkv, d)
+            packed = F.attention_packed(qkv, nh, nkv, d)
+            if packed is not None:
+                x = x + F.linear(packed, self.wo)
+                h = F.rmsnorm(x, self.ffn_norm, cfg.eps)
+                return x + F.linear(F.swiglu(F.linear(h, self.w_gate_up)), self.w_down)
         q = qkv[..., : nh * d].unflatten(-1, (nh, d))
         k = qkv[..., nh * d: (nh + nkv) * d].unflatten(-1, (nkv, d))
         v = qkv[..., (nh + nkv) * d:].unflatten(-1, (nkv, d))

@@ -41,6 +41,19 @@ def rope_heads_inplace(x, cos, sin, heads, d):
     return cuda_ops.rope_heads_inplace(x, cos, sin, heads, d)
 
 
+def attention_packed(qkv, hq, hkv, d, scale=None):
+    """Causal attention over a packed, already rotated ``qkv [B, S, (hq+2*hkv)*d]``
+    with the native kernels; None when they do not cover this head size or
+    ``FLEXTRAIN_ATTN=sdpa`` asks for the library path."""
+    import math
+    import os
+    from .attention import native_available
+    if os.environ.get("FLEXTRAIN_ATTN", "native") != "native" or not native_available(d):
+        return None
+    from .attention_native import attention_packed as impl
+    return impl(qkv, hq, hkv, d, scale if scale is not None else 1.0 / math.sqrt(d))
+
+
 def swiglu(gate_up):
     if _cuda(gate_up):
         from . import cuda_ops
