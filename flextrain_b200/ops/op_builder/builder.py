@@ -99,12 +99,15 @@ class OpBuilder:
         return os.path.join(NATIVE_DIR, f"lib{self.name}.so")
 
     def signature(self) -> str:
+        # paths enter relative to the repository so that a copy of the tree made
+        # elsewhere (another checkout, a snapshot on a GPU box) still matches
         h = hashlib.sha256()
         for path in sorted(self.sources + self.headers):
             with open(path, "rb") as f:
-                h.update(path.encode())
+                h.update(os.path.relpath(path, REPO_ROOT).encode())
                 h.update(f.read())
-        h.update(" ".join(self.compile_cmd("S", "O") + self.link_cmd(["O"], "L")).encode())
+        flags = " ".join(self.compile_cmd("S", "O") + self.link_cmd(["O"], "L"))
+        h.update(flags.replace(REPO_ROOT, "<repo>").encode())
         return h.hexdigest()
 
     def is_current(self) -> bool:
@@ -126,10 +129,13 @@ class OpBuilder:
         return proc
 
     def build(self, force: bool = False, verbose: bool = False) -> str:
-        with _LOCK:
+        import fcntl
+        os.makedirs(NATIVE_DIR, exist_ok=True)
+        # one builder at a time per tree: ranks of one job start together
+        with _LOCK, open(os.path.join(NATIVE_DIR, f".{self.name}.lock"), "w") as lock_file:
+            fcntl.flock(lock_file, fcntl.LOCK_EX)
             if not force and self.is_current():
                 return self.lib_path
-            os.makedirs(NATIVE_DIR, exist_ok=True)
             obj_dir = os.path.join(NATIVE_DIR, "obj", self.name)
             os.makedirs(obj_dir, exist_ok=True)
             objs = [os.path.join(obj_dir, os.path.basename(s) + ".o") for s in self.sources]
