@@ -98,7 +98,7 @@ ENGINE = "engine"
 FUSED_COLLECTIVES = "fused_collectives"    # peer-memory kernels instead of NCCL
 FUSED_COLLECTIVES_DEFAULT = "auto"         # "auto" | True | False
 FUSED_BLOCKS = "fused_blocks"              # CTAs of the fused collective kernels
-FUSED_BLOCKS_DEFAULT = 64
+FUSED_BLOCKS_DEFAULT = 148
 NUM_UNIT_BUFFERS = "num_unit_buffers"      # HBM unit buffers in the gather ring
 NUM_UNIT_BUFFERS_DEFAULT = 2
 STRICT_OVERFLOW = "strict_overflow"        # hold every update until the step's

@@ -33,6 +33,7 @@ from .scheduler import GreedySnakeBlockScheduler, LLMTask
 from .utils import distributed as dist
 from .utils.device import get_streams
 from .utils.logging import rank0_logger
+from .utils.health import Heartbeat, PeerFailure, StepWatchdog
 from .utils.timer import StepTimer
 
 
@@ -89,6 +90,8 @@ class FlexTrainEngine:
         self.timer = StepTimer()
         self._last_overflow = False
         self._status: Dict[str, Any] = {"last_step_seconds": None, "watchdog_tripped": False}
+        self.heartbeat = Heartbeat()
+        self.watchdog = StepWatchdog(cfg.engine.watchdog_seconds)
         if cfg.engine.gradient_clipping > 0:
             rank0_logger.warning("gradient_clipping is ignored: updates are applied unit by unit "
                                  "while backward is still running, before a global norm exists")
@@ -267,6 +270,25 @@ class FlexTrainEngine:
         """One optimizer step over ``batch_size`` samples.  Returns the list of
         per-micro-batch loss results (whatever the ``loss`` callback returned)."""
         cfg = self.config
+        # learn of a failed peer on the host, before anything is launched for this step
+        self.heartbeat.check_peers()
+        self.heartbeat.beat(self.global_steps)
+        self.watchdog.step_started()
+        try:
+            return self._train_iteration(cfg)
+        except PeerFailure:
+            raise
+        except BaseException as exc:
+            self.heartbeat.post_failure(f"{type(exc).__name__}: {exc}")
+            failed = {r: m for r, m in self.heartbeat.failures().items() if r != dist.get_rank()}
+            if failed and not isinstance(exc, KeyboardInterrupt):
+                raise PeerFailure("; ".join(f"rank {r} failed: {m}" for r, m in sorted(failed.items()))) \
+                    from exc
+            raise
+        finally:
+            self.watchdog.step_finished()
+
+    def _train_iteration(self, cfg):
         self.timer.start_step()
         self._reset_context()
         self.opts.prune_pending()
@@ -335,6 +357,12 @@ class FlexTrainEngine:
                    pending_host_updates=len(self.opts._pending),
                    traffic=self.inter.traffic(), opt_d2h_bytes=self.opts.bytes_d2h)
         out.update(self.timer.summary())
+        out["watchdog_tripped"] = self.watchdog.tripped
+        if self.device.type == "cuda":
+            from .ops.native import cuda_lib
+            lib = cuda_lib()
+            out["gemm_error_word"] = lib.ft_gemm_error()
+            out["comm_error_word"] = lib.ft_comm_error() if hasattr(lib, "ft_comm_error") else 0
         return out
 
     # ------------------------------------------------------ save / resume
@@ -388,6 +416,7 @@ class FlexTrainEngine:
         dist.barrier()
 
     def shutdown(self):
+        self.watchdog.close()
         self.opts.shutdown()
         self.para.drain()
         self.para.close()

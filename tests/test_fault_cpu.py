@@ -1,0 +1,90 @@
+"""Failure detection without touching a GPU: a gloo rank raises in the middle of
+a step; the other rank must come back with an error that names the failed peer
+within the (short) process-group timeout instead of hanging, and a slow step
+must trip the watchdog."""
+import os
+import time
+from datetime import timedelta
+
+import torch
+import torch.multiprocessing as mp
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    import flextrain_b200 as ft
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine
+    from flextrain_b200.utils.health import PeerFailure
+    ft.init_distributed("gloo", timeout=timedelta(seconds=8))
+    cfg = preset("tiny", num_layers=2, hidden=64, num_heads=2, ffn=128, vocab=128, seq_len=16)
+    tok = torch.randint(0, 128, (1, 17))
+    calls = {"n": 0}
+
+    def batch_fn():
+        calls["n"] += 1
+        if rank == 1 and calls["n"] == 3:
+            raise RuntimeError("injected failure on rank 1")
+        return tok[:, :-1], tok[:, 1:]
+
+    ft_cfg = {"batch_size": 2, "micro_batch_size": 1, "mixed_precision": {"device_dtype": "fp32"}}
+    model, opt, eng = build_llama_engine(cfg, ft_cfg, batch_fn)
+    t0 = time.time()
+    outcome = "finished"
+    try:
+        for _ in range(5):
+            eng.train_iteration()
+    except PeerFailure as e:
+        outcome = f"peer:{e}"
+    except RuntimeError as e:
+        outcome = f"own:{e}" if "injected" in str(e) else f"runtime:{e}"
+    q.put((rank, outcome, time.time() - t0, eng.global_steps))
+    q.close()
+    q.join_thread()                                   # flush before the hard exit below
+    os._exit(0 if outcome == "finished" else 3)       # no orderly teardown with a dead peer
+
+
+def test_failed_rank_is_reported_not_waited_for():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29800 + os.getpid() % 150
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict()
+    for _ in procs:
+        rank, outcome, secs, steps = q.get(timeout=120)
+        got[rank] = (outcome, secs, steps)
+    for p in procs:
+        p.join(30)
+        assert p.exitcode == 3
+    assert got[1][0].startswith("own:") and got[1][2] == 2
+    assert got[0][0].startswith("peer:") and "rank 1 failed" in got[0][0] and "injected" in got[0][0]
+    assert got[0][1] < 60
+
+
+def test_watchdog_trips_on_a_slow_step(fresh_runtime):
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine
+    cfg = preset("tiny", num_layers=2, hidden=64, num_heads=2, ffn=128, vocab=128, seq_len=16)
+    tok = torch.randint(0, 128, (2, 17))
+    slow = {"on": False}
+
+    def batch_fn():
+        if slow["on"]:
+            time.sleep(1.2)
+        return tok[:, :-1], tok[:, 1:]
+
+    ft_cfg = {"batch_size": 2, "micro_batch_size": 2, "mixed_precision": {"device_dtype": "fp32"},
+              "engine": {"watchdog_seconds": 0.5}}
+    model, opt, eng = build_llama_engine(cfg, ft_cfg, batch_fn, backend="gloo")
+    eng.train_iteration()                     # first step pays one-off costs
+    eng.watchdog.reset()
+    eng.train_iteration()
+    assert not eng.health()["watchdog_tripped"]
+    slow["on"] = True
+    eng.train_iteration()
+    assert eng.health()["watchdog_tripped"]
+    eng.shutdown()
