@@ -36,7 +36,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     configured = true;
   }
   const int num_blk = (P.S + BQ - 1) / BQ;
-  kern<<<P.B * P.Hkv * num_blk, ATTN_THREADS, BwdSmem<D>::BYTES, s>>>(tq, tk, tv, tdo, P);
+  kern<<<P.B * P.Hkv * num_blk, BWD_THREADS, BwdSmem<D>::BYTES, s>>>(tq, tk, tv, tdo, P);
   return 0;
 }
 

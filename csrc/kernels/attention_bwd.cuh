@@ -19,6 +19,11 @@
 namespace ft {
 namespace attn {
 
+// 2 control warps + 8 compute warps: warps 2-5 own S / dP / dQ / dK / dV columns of the
+// first half, warps 6-9 those of the second half (each warp still reads only its own
+// TMEM lane quarter, warp % 4).
+constexpr int BWD_THREADS = 320;
+
 template <int D>
 struct BwdSmem {
   static constexpr int TILE = BQ * D * 2;
@@ -50,7 +55,7 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(ATTN_THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                 const __grid_constant__ BwdParams P) {
@@ -83,9 +88,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars->qdo_full, 1);
     mbar_init(&bars->qdo_empty, 1);
     mbar_init(&bars->sdp_full, 1);
-    mbar_init(&bars->pds_full, 128);
+    mbar_init(&bars->pds_full, 256);
     mbar_init(&bars->dq_full, 1);
-    mbar_init(&bars->s_free, 128);
+    mbar_init(&bars->s_free, 256);
     mbar_init(&bars->acc_full, 1);
     bars->abort = 0;
     fence_barrier_init();
@@ -171,6 +176,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                // which half of the columns this warp owns
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float log2e = 1.4426950408889634f;
@@ -188,7 +194,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_after();
       const bool diag = (m == nb);
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = half * (BKV / 64); c < (half + 1) * (BKV / 64); ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(tm_s + lane_addr + c * 32, sv);
         tmem_ld_32x32(tm_dp + lane_addr + c * 32, dv);
@@ -221,7 +227,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_after();
       float* dq_row = P.dq_acc + ((int64_t)(batch * P.S + q_pos) * P.Hq + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tm_dq + lane_addr + c * 32, v);
         tmem_ld_wait();
@@ -243,7 +249,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         T* dk_row = reinterpret_cast<T*>(P.dk) + (int64_t)(batch * P.S + kv_pos) * P.dk_stride + kv_head * D;
         T* dv_row = reinterpret_cast<T*>(P.dv) + (int64_t)(batch * P.S + kv_pos) * P.dv_stride + kv_head * D;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t a[32], b[32];
           tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
           tmem_ld_32x32(tm_dv + lane_addr + c * 32, b);
@@ -260,7 +266,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       } else {
         // rows past the end of the sequence still have to drain their TMEM loads uniformly
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t a[32];
           tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
           tmem_ld_wait();

@@ -1,0 +1,261 @@
+// tcgen05 GEMM with CTA pairs (cta_group::2): two CTAs of a 2-CTA cluster, on the
+// two SMs of a TPC, compute one 256 x 256 output tile.  Each CTA stages its own
+// 128 rows of A and one 128-row half of B per k-block (32 KB instead of 48 KB), the
+// leader CTA's single MMA thread issues tcgen05.mma.cta_group::2 (M = 256, N = 256,
+// K = 16) that reads both CTAs' shared memory, and each CTA's tensor memory
+// receives the 128 x 256 accumulator of its own rows.  Compared with the
+// single-CTA kernel of gemm_kernel.cuh this cuts shared-memory traffic per FLOP
+// (that kernel is bound by it) and deepens the TMA ring to 6 stages.
+//
+// Barrier protocol per pipeline stage s
+//   full[s]   lives in the leader; the leader's producer arms it with the bytes of
+//             BOTH CTAs, every TMA load (cta_group::2 form, no multicast) signals the
+//             leader's barrier;
+//   empty[s]  one per CTA; the leader's tcgen05.commit multicasts its arrival to both;
+//   tmem_full[a]   one per CTA, arrival multicast by the leader's commit;
+//   tmem_empty[a]  lives in the leader; the epilogue warps of both CTAs arrive on it.
+// All waits are bounded; on expiry an error code is recorded and the CTA leaves
+// through the common exit (cluster barrier, tensor-memory release).
+#pragma once
+#include "gemm_kernel.cuh"
+
+namespace ft {
+namespace gemm {
+
+constexpr int P_BM = 256, P_BN = 256;               // tile of a CTA pair
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = 128 * BK * 2, P_B_BYTES = 128 * BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared::cluster address
+
+struct PairBarriers {
+  uint64_t full[P_STAGES];
+  uint64_t empty[P_STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Warps arrive after divergent role code, so the non-aligned forms are used and every
+// warp reconverges first.
+__device__ __forceinline__ void cluster_sync_all() {
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+
+// TMA tile load of a CTA pair: data lands in this CTA, completion bytes go to the
+// barrier at the same offset in the leader CTA.  Not a multicast load.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerBitMask),
+      "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrival on the barrier at this offset in both CTAs of the pair once all MMAs issued
+// so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask)
+      : "memory");
+}
+
+// Arrive on the barrier at this offset in the leader CTA (from either CTA).
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPeerBitMask) : "memory");
+}
+
+template <typename T, bool A_MN, bool B_MN, int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 void* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(smem + P_STAGES * P_STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();            // 0 = leader
+  const int pair = (int)(blockIdx.x >> 1), num_pairs = (int)(gridDim.x >> 1);
+  const int mt = (M + P_BM - 1) / P_BM, nt = (N + P_BN - 1) / P_BN, kt = (K + BK - 1) / BK;
+  const int num_tiles = mt * nt;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 8);            // 4 epilogue warps in each of the two CTAs
+    }
+    bars->abort = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  volatile uint32_t* abort_flag = &bars->abort;
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
+        int mb, nb;
+        tile_coords(t, mt, nt, mb, nb);
+        const int m0 = mb * P_BM + (int)cta * 128;   // this CTA's rows of A
+        const int n0 = nb * P_BN + (int)cta * 128;   // this CTA's half of B
+        for (int kb = 0; kb < kt; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1)) {
+            *abort_flag = 1;
+            atomicCAS(err, 0, 11);
+            break;
+          }
+          uint8_t* sa = smem + stage * P_STAGE_BYTES;
+          uint8_t* sb = sa + P_A_BYTES;
+          if (cta == 0) mbar_expect_tx(&bars->full[stage], 2 * P_STAGE_BYTES);
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_2d_pair(sa + j * (64 * BK * 2), &tmap_a, &bars->full[stage], m0 + j * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(sa, &tmap_a, &bars->full[stage], kb * BK, m0);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_2d_pair(sb + j * (64 * BK * 2), &tmap_b, &bars->full[stage], n0 + j * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(sb, &tmap_b, &bars->full[stage], kb * BK, n0);
+          }
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && cta == 0) {
+      constexpr uint32_t idesc =
+          make_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, A_MN ? 1 : 0, B_MN ? 1 : 0, P_BM, P_BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1)) {
+          *abort_flag = 1;
+          atomicCAS(err, 0, 12);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * P_BN;
+        bool failed = false;
+        for (int kb = 0; kb < kt; ++kb) {
+          if (!mbar_wait(&bars->full[stage], phase)) {
+            *abort_flag = 1;
+            atomicCAS(err, 0, 13);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * P_STAGE_BYTES);
+          const uint32_t sb = sa + P_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * (UK * 128), 64 * BK * 2, 1024)
+                                     : make_smem_desc(sa + k * (UK * 2), 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * (UK * 128), 64 * BK * 2, 1024)
+                                     : make_smem_desc(sb + k * (UK * 2), 16, 1024);
+            umma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&bars->empty[stage]);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (failed) break;
+        umma_commit_pair(&bars->tmem_full[acc]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;
+    int it = 0;
+    for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++it) {
+      int mb, nb;
+      tile_coords(t, mt, nt, mb, nb);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&bars->tmem_full[acc], acc_phase)) {
+        *abort_flag = 1;
+        atomicCAS(err, 0, 14);
+        break;
+      }
+      tc_fence_after();
+      const int row = mb * P_BM + (int)cta * 128 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * P_BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < P_BN / 32; ++c) {
+        const int col0 = nb * P_BN + c * 32;
+        if (col0 >= N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        store_chunk<T, MODE>(r, C, ldc, row, col0, M, N);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&bars->tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();                                // the peer may still read this CTA's shared memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+}  // namespace gemm
+}  // namespace ft

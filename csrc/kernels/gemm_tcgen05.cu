@@ -26,7 +26,7 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "gemm_kernel.cuh"
+#include "gemm2_kernel.cuh"
 #include "gemm_host.h"
 
 namespace {
@@ -164,6 +164,55 @@ int launch_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
   return 0;
 }
 
+// ---- CTA-pair kernel (cluster of 2)
+template <typename T, bool A_MN, bool B_MN, int MODE>
+int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64_t ldc, int M, int N, int K,
+                    int* err, int grid, cudaStream_t s) {
+  auto kern = gemm_pair_kernel<T, A_MN, B_MN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, ldc, M, N, K, err);
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+template <typename T, bool A_MN, bool B_MN>
+int launch_pair_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64_t ldc, int M,
+                     int N, int K, int* err, int grid, cudaStream_t s) {
+  switch (mode) {
+    case kStore16: return launch_pair_one<T, A_MN, B_MN, kStore16>(ta, tb, C, ldc, M, N, K, err, grid, s);
+    case kStore32: return launch_pair_one<T, A_MN, B_MN, kStore32>(ta, tb, C, ldc, M, N, K, err, grid, s);
+    case kAcc16: return launch_pair_one<T, A_MN, B_MN, kAcc16>(ta, tb, C, ldc, M, N, K, err, grid, s);
+    case kAcc32: return launch_pair_one<T, A_MN, B_MN, kAcc32>(ta, tb, C, ldc, M, N, K, err, grid, s);
+    default: return -3;
+  }
+}
+
+template <typename T>
+int launch_pair(int a_mn, int b_mn, int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
+                int64_t ldc, int M, int N, int K, int* err, int grid, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch_pair_mode<T, false, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
+  if (!a_mn && b_mn) return launch_pair_mode<T, false, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
+  if (a_mn && b_mn) return launch_pair_mode<T, true, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
+  return launch_pair_mode<T, true, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
+}
+
+int g_use_pair = -1;   // -1: read FLEXTRAIN_GEMM_PAIR on first use
+
 template <typename T>
 int launch_layout(int a_mn, int b_mn, int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
                   int64_t ldc, int M, int N, int K, int* err, int grid, cudaStream_t s) {
@@ -194,24 +243,44 @@ int ft_gemm(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64
   int* err = error_word(dev);
   CUtensorMap ta, tb;
   int rc;
+  if (g_use_pair < 0) {
+    const char* e = getenv("FLEXTRAIN_GEMM_PAIR");
+    g_use_pair = e ? atoi(e) : 0;
+  }
+  const bool pair = g_use_pair != 0;
+  const int b_box = pair ? 128 : BN;              // rows of B one CTA stages per k-block
   if (a_mn) rc = make_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK, ab_dtype);
   else rc = make_tmap(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM, ab_dtype);
   if (rc) return rc;
   if (b_mn) rc = make_tmap(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK, ab_dtype);
-  else rc = make_tmap(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN, ab_dtype);
+  else rc = make_tmap(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, b_box, ab_dtype);
   if (rc) return rc;
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
   const int mode = c_dtype == kF32 ? (accumulate ? kAcc32 : kStore32) : (accumulate ? kAcc16 : kStore16);
-  if (ab_dtype == kBF16)
-    rc = launch_layout<__nv_bfloat16>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
-  else
-    rc = launch_layout<__half>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+  if (pair) {
+    const int tiles = ((M + P_BM - 1) / P_BM) * ((N + P_BN - 1) / P_BN);
+    const int pairs = sm_count(dev) / 2;
+    const int grid = 2 * (tiles < pairs ? tiles : pairs);
+    if (ab_dtype == kBF16)
+      rc = launch_pair<__nv_bfloat16>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+    else
+      rc = launch_pair<__half>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+  } else {
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
+    if (ab_dtype == kBF16)
+      rc = launch_layout<__nv_bfloat16>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+    else
+      rc = launch_layout<__half>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+  }
   if (rc) return rc;
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;
 }
+
+// Selects the CTA-pair kernel (1) or the single-CTA kernel (0) for later ft_gemm calls.
+void ft_gemm_set_pair(int on) { g_use_pair = on ? 1 : 0; }
+int ft_gemm_get_pair() { return g_use_pair > 0 ? 1 : 0; }
 
 // Reads (and clears) the device error word: 0 = no bounded wait ever expired.
 // Synchronises the device; meant for tests and health checks.
