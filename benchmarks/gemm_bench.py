@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Times the tcgen05 GEMM against torch.matmul (cuBLAS) on the Llama shapes.
 
-    python benchmarks/gemm_bench.py [--shapes 70b|13b|7b|small] [--iters 10]
+    python benchmarks/gemm_bench.py [--shapes 70b|13b|7b|8k|small] [--iters 10]
 
 CUDA events, 3 warm-up launches, a >L2 buffer is rewritten between timed
 launches.  Prints one line per (shape, layout): ms, TFLOP/s, fraction of the
@@ -20,6 +20,7 @@ from flextrain_b200.ops.cuda_ops import gemm  # noqa: E402
 
 SHAPES = {
     "small": [(4096, 4096, 4096)],
+    "8k": [(8192, 8192, 8192)],
     "7b": [(16384, 12288, 4096), (16384, 4096, 4096), (16384, 22016, 4096), (16384, 4096, 11008)],
     "13b": [(32768, 15360, 5120), (32768, 5120, 5120), (32768, 27648, 5120), (32768, 5120, 13824)],
     "70b": [(8192, 10240, 8192), (8192, 8192, 8192), (8192, 57344, 8192), (8192, 8192, 28672),

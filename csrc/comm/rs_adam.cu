@@ -58,6 +58,8 @@ struct RsAdamParams {
   int param_dtype;
   void* host_grad;                // [og, S) -> host_grad (indexed from og), or nullptr
   int host_grad_dtype;
+  int npush;                      // all-reduce form: updated parameters of [0, og) are also
+  void* push[kMaxRanks];          // stored at [rank*S + i] of every rank's full parameter buffer
   int* finite_flag;               // or nullptr
   int nseg;
   Segment seg[kMaxSeg];
@@ -156,6 +158,7 @@ __global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ Rs
         } else if (P.param_b) {
           store8(P.param_b, P.param_dtype, i - P.a_hi, pv);
         }
+        for (int k = 0; k < P.npush; ++k) store8(P.push[(R + k) % P.npush], P.param_dtype, base + i, pv);
       }
     } else if (P.host_grad) {
       store8(P.host_grad, P.host_grad_dtype, i - P.og, g);
@@ -169,6 +172,7 @@ __global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ Rs
     __threadfence_system();
     const unsigned int done = atomicAdd(P.block_counter, 1u);
     if (done == gridDim.x - 1) {
+      __threadfence_system();     // every CTA's peer stores precede the done words below
       *P.block_counter = 0;
       if (W > 1) {
         for (int p = 0; p < W; ++p)
@@ -205,15 +209,13 @@ struct FtAdamSegment {
   int64_t step;
 };
 
-// See the file comment.  `grads[r]` / `flags[r]` are this process's mappings of
-// rank r's gradient buffer and flag page.  Alignment: shard, og, a_hi and every
-// segment bound must be multiples of 8 elements; returns -2 otherwise.
-int ft_rs_adam(int world, int rank, const void* const* grads, uint32_t* const* flags, int grad_dtype,
-               int64_t shard, float scale, uint32_t seq, int start_slot, int done_slot,
-               void* reduced_out, int64_t og, int do_adam, float* master, float* m, float* v,
-               void* param_a, int64_t a_hi, void* param_b, int param_dtype, void* host_grad,
-               int host_grad_dtype, int* finite_flag, int nseg, const FtAdamSegment* segs,
-               int max_blocks, cudaStream_t stream) {
+static int rs_adam_impl(int world, int rank, const void* const* grads, uint32_t* const* flags,
+                        int grad_dtype, int64_t shard, float scale, uint32_t seq, int start_slot,
+                        int done_slot, void* reduced_out, int64_t og, int do_adam, float* master, float* m,
+                        float* v, void* param_a, int64_t a_hi, void* param_b, int param_dtype,
+                        void* host_grad, int host_grad_dtype, int* finite_flag, int nseg,
+                        const FtAdamSegment* segs, int max_blocks, void* const* pushes,
+                        cudaStream_t stream) {
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -1;
   if (shard % 8 || og % 8 || a_hi % 8 || nseg > kMaxSeg) return -2;
   if (shard <= 0) return 0;
@@ -244,6 +246,8 @@ int ft_rs_adam(int world, int rank, const void* const* grads, uint32_t* const* f
   P.param_a = param_a; P.a_hi = a_hi; P.param_b = param_b; P.param_dtype = param_dtype;
   P.host_grad = host_grad; P.host_grad_dtype = host_grad_dtype;
   P.finite_flag = finite_flag;
+  P.npush = pushes ? world : 0;
+  for (int r = 0; r < P.npush; ++r) P.push[r] = pushes[r];
   P.nseg = nseg;
   for (int s = 0; s < nseg; ++s) {
     const FtAdamSegment& in = segs[s];
@@ -274,6 +278,42 @@ int ft_rs_adam(int world, int rank, const void* const* grads, uint32_t* const* f
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;
+}
+
+// See the file comment.  `grads[r]` / `flags[r]` are this process's mappings of
+// rank r's gradient buffer and flag page.  Alignment: shard, og, a_hi and every
+// segment bound must be multiples of 8 elements; returns -2 otherwise.
+int ft_rs_adam(int world, int rank, const void* const* grads, uint32_t* const* flags, int grad_dtype,
+               int64_t shard, float scale, uint32_t seq, int start_slot, int done_slot,
+               void* reduced_out, int64_t og, int do_adam, float* master, float* m, float* v,
+               void* param_a, int64_t a_hi, void* param_b, int param_dtype, void* host_grad,
+               int host_grad_dtype, int* finite_flag, int nseg, const FtAdamSegment* segs,
+               int max_blocks, cudaStream_t stream) {
+  return rs_adam_impl(world, rank, grads, flags, grad_dtype, shard, scale, seq, start_slot, done_slot,
+                      reduced_out, og, do_adam, master, m, v, param_a, a_hi, param_b, param_dtype,
+                      host_grad, host_grad_dtype, finite_flag, nseg, segs, max_blocks, nullptr, stream);
+}
+
+// All-reduce form for parameters that every rank keeps whole (embedding, final
+// norm, head): the same kernel with og = shard, whose owner of slice r reduces
+// it, applies Adam to its slice of the fp32 state (which is therefore sharded,
+// not replicated) and stores the updated device-dtype parameters into slice r of
+// EVERY rank's parameter buffer `params[p]` over NVLink.  When the kernel has
+// finished on a rank, all slices of its parameter buffer are up to date (the end
+// barrier follows the peers' stores) and its gradient buffer may be zeroed.
+// With `do_adam` = 0 only the reduced, unscaled slice is written to
+// `reduced_out` (two-phase use under dynamic loss scaling).  Replaces the NCCL
+// all-reduce + replicated optimizer step of flextrain/optimizer.py:273-300.
+int ft_ar_adam(int world, int rank, const void* const* grads, uint32_t* const* flags, int grad_dtype,
+               int64_t shard, float scale, uint32_t seq, int start_slot, int done_slot,
+               void* reduced_out, int do_adam, float* master, float* m, float* v, void* const* params,
+               int param_dtype, int* finite_flag, int nseg, const FtAdamSegment* segs, int max_blocks,
+               cudaStream_t stream) {
+  if (do_adam && !params) return -1;
+  return rs_adam_impl(world, rank, grads, flags, grad_dtype, shard, scale, seq, start_slot, done_slot,
+                      reduced_out, shard, do_adam, master, m, v, nullptr, 0, nullptr, param_dtype,
+                      nullptr, -1, finite_flag, nseg, segs, max_blocks, do_adam ? params : nullptr,
+                      stream);
 }
 
 // Clock-cycle budget of every cross-GPU wait (0 restores the default of ~10 s).

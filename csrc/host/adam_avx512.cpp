@@ -286,19 +286,4 @@ int ft_cast_to_f32(const void* src, int src_dtype, float* dst, int64_t n, int th
   return 0;
 }
 
-// Multi-threaded streaming copy for DRAM<->DRAM staging
-// (capability parity: flextrain/ops/csrc/aio/py_lib/deepspeed_py_copy.cpp:25-135).
-int ft_host_memcpy(void* dst, const void* src, int64_t nbytes, int threads) {
-  if (threads <= 0) threads = omp_get_max_threads();
-  const int64_t chunk = 1 << 20;
-  const int64_t blocks = (nbytes + chunk - 1) / chunk;
-  if (blocks < threads) threads = (int)(blocks > 0 ? blocks : 1);
-#pragma omp parallel for num_threads(threads) schedule(static)
-  for (int64_t b = 0; b < blocks; ++b) {
-    int64_t lo = b * chunk, len = lo + chunk < nbytes ? chunk : nbytes - lo;
-    std::memcpy((char*)dst + lo, (const char*)src + lo, (size_t)len);
-  }
-  return 0;
-}
-
 }  // extern "C"

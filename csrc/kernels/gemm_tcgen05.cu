@@ -245,9 +245,10 @@ int ft_gemm(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64
   int rc;
   if (g_use_pair < 0) {
     const char* e = getenv("FLEXTRAIN_GEMM_PAIR");
-    g_use_pair = e ? atoi(e) : 0;
+    g_use_pair = e ? atoi(e) : 1;
   }
-  const bool pair = g_use_pair != 0;
+  // The pair kernel's tile is 256 rows tall: below that half of it would be padding.
+  const bool pair = g_use_pair != 0 && M > 128;
   const int b_box = pair ? 128 : BN;              // rows of B one CTA stages per k-block
   if (a_mn) rc = make_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK, ab_dtype);
   else rc = make_tmap(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM, ab_dtype);

@@ -418,5 +418,6 @@ class FlexTrainEngine:
     def shutdown(self):
         self.watchdog.close()
         self.opts.shutdown()
+        self.optimizer.close()
         self.para.drain()
         self.para.close()

@@ -83,3 +83,84 @@ def allocate_pin_memory_blocks(numel: int, dtype: torch.dtype, shape: Tuple[int,
         return [nest(level + 1, offset + i * stride) for i in range(shape[level])]
 
     return nest(0, 0)
+
+
+# ------------------------------------------------- locked-tensor manager
+# address -> (ctypes buffer, "cuda" | "host"); keeps the mapping alive until freed
+_LOCKED: dict = {}
+
+
+def new_cpu_locked_tensor(numel: int, dtype: torch.dtype) -> torch.Tensor:
+    """Exact-size page-locked CPU tensor owned by the native pool.
+
+    With a CUDA context the memory comes from ``cudaHostAlloc`` (portable, so
+    every stream can DMA from it); without one it is ``posix_memalign`` +
+    ``mlock`` from the host library.  Free it with ``free_cpu_locked_tensor``.
+    Counterpart of ``aio_handle.new_cpu_locked_tensor``
+    (flextrain/ops/csrc/aio/py_lib/deepspeed_pin_tensor.cpp:23-44)."""
+    import ctypes
+    from ..ops import native
+    from ..utils import distributed as dist
+    nbytes = max(1, int(numel) * torch.empty((), dtype=dtype).element_size())
+    if dist.is_cuda():
+        lib = native.cuda_lib()
+        lib.ft_pinned_alloc.restype = ctypes.c_void_p
+        addr, kind = lib.ft_pinned_alloc(ctypes.c_size_t(nbytes)), "cuda"
+    else:
+        lib = native.host_lib()
+        lib.ft_locked_alloc.restype = ctypes.c_void_p
+        lib.ft_locked_alloc.argtypes = [ctypes.c_size_t, ctypes.c_void_p]
+        addr, kind = lib.ft_locked_alloc(nbytes, None), "host"
+    if not addr:
+        raise MemoryError(f"page-locked allocation of {nbytes} bytes failed")
+    buf = (ctypes.c_uint8 * nbytes).from_address(addr)
+    _LOCKED[addr] = (buf, kind)
+    return torch.frombuffer(buf, dtype=torch.uint8, count=nbytes).view(dtype)[:numel]
+
+
+def is_cpu_locked_tensor(t: torch.Tensor) -> bool:
+    return t.data_ptr() in _LOCKED
+
+
+def free_cpu_locked_tensor(t: torch.Tensor) -> None:
+    """Return a tensor from ``new_cpu_locked_tensor`` to the system.  The caller
+    must not touch ``t`` (or views of it) afterwards."""
+    import ctypes
+    from ..ops import native
+    addr = t.data_ptr()
+    entry = _LOCKED.pop(addr, None)
+    if entry is None:
+        raise ValueError("tensor was not allocated by new_cpu_locked_tensor")
+    _buf, kind = entry
+    if kind == "cuda":
+        lib = native.cuda_lib()
+        lib.ft_pinned_free.argtypes = [ctypes.c_void_p]
+        rc = lib.ft_pinned_free(addr)
+    else:
+        lib = native.host_lib()
+        lib.ft_locked_free.argtypes = [ctypes.c_void_p]
+        rc = lib.ft_locked_free(addr)
+    if rc != 0:
+        raise RuntimeError(f"freeing page-locked memory failed with {rc}")
+
+
+def host_memcpy(dst: torch.Tensor, src: torch.Tensor, threads: int = 0) -> torch.Tensor:
+    """``dst.copy_(src)`` for contiguous CPU tensors of equal byte size, done by
+    the native multi-threaded copy with non-temporal stores (``ft_host_memcpy``;
+    the reference's counterpart is ``deepspeed_memcpy``,
+    flextrain/ops/csrc/aio/py_lib/deepspeed_py_copy.cpp:113-135)."""
+    import ctypes
+    from ..ops import native
+    if dst.device.type != "cpu" or src.device.type != "cpu":
+        raise ValueError("host_memcpy copies between CPU tensors")
+    if not (dst.is_contiguous() and src.is_contiguous()):
+        raise ValueError("host_memcpy needs contiguous tensors")
+    nbytes = dst.numel() * dst.element_size()
+    if nbytes != src.numel() * src.element_size():
+        raise ValueError("host_memcpy needs tensors of equal byte size")
+    lib = native.host_lib()
+    lib.ft_host_memcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    rc = lib.ft_host_memcpy(dst.data_ptr(), src.data_ptr(), nbytes, int(threads))
+    if rc != 0:
+        raise RuntimeError("ft_host_memcpy rejected its arguments (overlapping ranges?)")
+    return dst

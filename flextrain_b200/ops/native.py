@@ -50,7 +50,7 @@ def host_lib() -> ctypes.CDLL:
         lib.ft_has_nonfinite.argtypes = [c_void_p, c_int, c_int64, c_int]
         lib.ft_cast_from_f32.argtypes = [c_void_p, c_void_p, c_int, c_int64, c_int]
         lib.ft_cast_to_f32.argtypes = [c_void_p, c_int, c_void_p, c_int64, c_int]
-        lib.ft_host_memcpy.argtypes = [c_void_p, c_void_p, c_int64, c_int]
+        lib.ft_host_memcpy.argtypes = [c_void_p, c_void_p, ctypes.c_size_t, c_int]
         _HOST = lib
     return _HOST
 

@@ -163,26 +163,110 @@ class FlexTrainOptimizer:
         if not params:
             return
         from .memory import allocate_memory, move_into_contiguous
-        dev, mp = self.device, self._cfg.mixed_precision
+        dev = self.device
         where = self._cfg.engine.nonlayer_optimizer_device
         self._nl_on_device = (where == "gpu") or (where == "auto")
-        self._nl_para = allocate_memory(total, self.device_dtype, dev)
-        self._nl_grad = allocate_memory(total, self.device_dtype, dev, zero=True)
-        move_into_contiguous(params, self._nl_para)
+        self._nl_fused = self._nl_want_fused()
+        world, rank = dist.get_world_size(), dist.get_rank()
+        if self._nl_fused:
+            # Peer-mapped flat parameter and gradient buffers, padded so that they
+            # split into `world` slices of a multiple of 8 elements; the fp32 state
+            # exists only for this rank's slice.
+            from .parallel.symm_mem import SymmetricBuffer, get_flag_page
+            from .param_group import merge_segments
+            shard = -(-total // (world * 8)) * 8
+            padded = shard * world
+            if padded > total:
+                last = self._nl_segments[-1].group
+                self._nl_segments = merge_segments(
+                    list(self._nl_segments) + [GroupSegment(last, total, padded)])
+            itemsize = torch.empty((), dtype=self.device_dtype).element_size()
+            self._nl_para_symm = SymmetricBuffer(padded * itemsize)
+            self._nl_grad_symm = SymmetricBuffer(padded * itemsize)
+            self._nl_flag_page = get_flag_page()
+            self._nl_para = self._nl_para_symm.tensor(self.device_dtype)
+            self._nl_grad = self._nl_grad_symm.tensor(self.device_dtype)
+            self._nl_grad.zero_()
+            self._nl_shard, self._nl_lo = shard, rank * shard
+            state_numel = shard
+        else:
+            self._nl_para = allocate_memory(total, self.device_dtype, dev)
+            self._nl_grad = allocate_memory(total, self.device_dtype, dev, zero=True)
+            self._nl_shard, self._nl_lo = total, 0
+            state_numel = total
+        move_into_contiguous(params, self._nl_para[:total])
         off = 0
         for p, n in zip(params, numels):
             p.grad = self._nl_grad[off:off + n].view(p.shape)
             off += n
         state_dev = dev if self._nl_on_device else torch.device("cpu")
         pinned = not self._nl_on_device
-        self._nl_master = allocate_memory(total, self.master_dtype, state_dev, pinned)
-        self._nl_master.copy_(self._nl_para)
-        self._nl_states = [allocate_memory(total, self.master_dtype, state_dev, pinned, zero=True)
+        self._nl_master = allocate_memory(state_numel, self.master_dtype, state_dev, pinned)
+        self._nl_master.copy_(self._nl_para[self._nl_lo:self._nl_lo + state_numel])
+        self._nl_states = [allocate_memory(state_numel, self.master_dtype, state_dev, pinned, zero=True)
                            for _ in range(self.optimizer_state_per_element)]
         if not self._nl_on_device:
             self._nl_host_grad = allocate_memory(total, torch.float32, "cpu", True)
             self._nl_host_para = allocate_memory(total, self.device_dtype, "cpu", True)
         self._nl_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def _nl_want_fused(self) -> bool:
+        """The fused all-reduce + Adam kernel needs CUDA, the update on the
+        device, peer access between all ranks, group boundaries on multiples of
+        8 elements and the built-in Adam (it carries its own arithmetic)."""
+        want = self._cfg.engine.fused_collectives
+        if want is False or self.device.type != "cuda" or not self._nl_on_device:
+            return False
+        from .ops.adam import FlexTrainAdam
+        from .parallel.fused import segments_aligned
+        from .parallel.symm_mem import peer_access_available
+        if not isinstance(self.cpu_optimizer, FlexTrainAdam):
+            return False
+        if self.master_dtype != torch.float32 or self.optimizer_state_per_element != 2:
+            return False
+        return segments_aligned(self._nl_segments) and dist.get_world_size() <= 8 \
+            and peer_access_available()
+
+    def _nl_fused_step(self, grad_scale: float, check_overflow: bool) -> bool:
+        """Non-layerwise update as one kernel: every rank reduces its slice of
+        all ranks' gradients over NVLink, updates its slice of the fp32 state and
+        stores the new parameters into every rank's buffer."""
+        from .ops.adam.gpu_adam import device_adam_update
+        from .parallel import fused
+        from .param_group import slice_segments
+        world, rank = dist.get_world_size(), dist.get_rank()
+        S, lo = self._nl_shard, self._nl_lo
+        segs = slice_segments(self._nl_segments, lo, lo + S, rebase=True)
+        page = self._nl_flag_page
+        step = max(int(self.param_groups[0][STEP_KEY]), 1)
+        arr = fused.make_segments(segs, self.param_groups, self.cpu_optimizer, step)
+        for i, seg in enumerate(segs):          # every group carries its own step counter
+            arr[i].step = max(int(self.param_groups[seg.group][STEP_KEY]), 1)
+        own = self._nl_grad[lo:lo + S]
+        if check_overflow:
+            self._nl_flag.zero_()
+        fused.ar_adam(world, rank, self._nl_grad_symm.ptr_array(), page.ptr_array(), self.device_dtype,
+                      S, grad_scale / world, page.next_seq("nl"),
+                      reduced_out=own if check_overflow else None, do_adam=not check_overflow,
+                      master=self._nl_master, m=self._nl_states[0], v=self._nl_states[1],
+                      param_ptrs=self._nl_para_symm.ptr_array(), param_dtype=self.device_dtype,
+                      finite_flag=self._nl_flag if check_overflow else None, segments=arr,
+                      nseg=len(segs), max_blocks=self._cfg.engine.fused_blocks)
+        overflow = False
+        if check_overflow:
+            overflow = dist.all_reduce_scalar(float(self._nl_flag.item() != 0), dist.ReduceOp.MAX) > 0
+            if not overflow:
+                for seg in segs:
+                    g = self.param_groups[seg.group]
+                    sl = slice(seg.start, seg.end)
+                    device_adam_update(g, max(int(g[STEP_KEY]), 1), self.cpu_optimizer,
+                                       self._nl_master[sl], own[sl], [s[sl] for s in self._nl_states],
+                                       self._nl_para[lo:lo + S][sl], grad_scale=1.0)
+                itemsize = self._nl_para.element_size()
+                fused.peer_gather(world, rank, self._nl_para_symm.ptr_array(), page.ptr_array(),
+                                  page.next_seq("nl_gather"), S * itemsize, start_slot=8, done_slot=9)
+        self._nl_grad.zero_()
+        return overflow
 
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0, check_overflow: bool = False) -> bool:
@@ -192,6 +276,8 @@ class FlexTrainOptimizer:
         if not self.non_layerwise_params:
             return False
         from .ops.adam.gpu_adam import device_adam_update, has_nonfinite
+        if self._nl_fused:
+            return self._nl_fused_step(grad_scale, check_overflow)
         dist.all_reduce(self._nl_grad, dist.ReduceOp.AVG)
         overflow = False
         if check_overflow:
@@ -216,6 +302,24 @@ class FlexTrainOptimizer:
         self._nl_grad.zero_()
         return overflow
 
+    def close(self):
+        """Release the peer-mapped buffers of the fused non-layerwise path (the
+        parameters move to ordinary device memory first).  Collective."""
+        if not self.non_layerwise_params or not getattr(self, "_nl_fused", False):
+            return
+        torch.cuda.synchronize()
+        keep = self._nl_para[:self._nl_numel].clone()
+        off = 0
+        for p in self.non_layerwise_params:
+            n = p.numel()
+            p.data = keep[off:off + n].view(p.shape)
+            p.grad = None
+            off += n
+        self._nl_para, self._nl_grad = keep, None
+        self._nl_para_symm.close()
+        self._nl_grad_symm.close()
+        self._nl_fused = False
+
     def update_states(self):
         """Advance every group's step counter (once per training iteration)."""
         for g in self.param_groups:
@@ -223,18 +327,29 @@ class FlexTrainOptimizer:
 
     # -------------------------------------------------- state (save / load)
     def non_layerwise_state(self):
+        """fp32 master and moments of the non-layerwise parameters: the whole
+        vector when the state is replicated, this rank's slice when the fused
+        all-reduce kernel keeps it sharded."""
         if not self.non_layerwise_params:
             return {}
         return {"master": self._nl_master.detach().cpu().clone(),
-                "states": [s.detach().cpu().clone() for s in self._nl_states]}
+                "states": [s.detach().cpu().clone() for s in self._nl_states],
+                "sharded": bool(self._nl_fused)}
 
     def load_non_layerwise_state(self, state):
         if not state:
             return
+        if bool(state.get("sharded", False)) != bool(self._nl_fused):
+            raise ValueError("non-layerwise optimizer state was saved with a different "
+                             "engine.fused_collectives setting")
         self._nl_master.copy_(state["master"])
         for dst, src in zip(self._nl_states, state["states"]):
             dst.copy_(src)
-        self._nl_para.copy_(self._nl_master)
+        lo, n = self._nl_lo, self._nl_master.numel()
+        self._nl_para[lo:lo + n].copy_(self._nl_master)
+        if self._nl_fused and dist.get_world_size() > 1:
+            import torch.distributed as tdist
+            tdist.all_gather_into_tensor(self._nl_para, self._nl_para[lo:lo + n].clone())
 
     def hyper_state(self):
         return [{k: v for k, v in g.items() if k != PARAMS_KEY} for g in self.param_groups]

@@ -36,6 +36,10 @@ def _lib():
             c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_float, c_uint32, c_int, c_int,
             c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int,
             c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p]
+        lib.ft_ar_adam.argtypes = [
+            c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_float, c_uint32, c_int, c_int,
+            c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+            c_int, c_void_p]
         lib.ft_comm_error.restype = c_int
         _DECLARED = True
     return lib
@@ -77,6 +81,25 @@ def rs_adam(world: int, rank: int, grad_ptrs, flag_ptrs, grad_dtype: torch.dtype
         ctypes.cast(segments, c_void_p), max_blocks, stream_handle())
     if rc != 0:
         raise RuntimeError(f"ft_rs_adam failed (code {rc})")
+
+
+def ar_adam(world: int, rank: int, grad_ptrs, flag_ptrs, grad_dtype: torch.dtype, shard: int,
+            scale: float, seq: int, reduced_out: Optional[torch.Tensor], do_adam: bool,
+            master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, param_ptrs,
+            param_dtype: torch.dtype, finite_flag: Optional[torch.Tensor], segments, nseg: int,
+            max_blocks: int = 64, start_slot: int = 6, done_slot: int = 7):
+    """All-reduce form of the fused kernel for parameters every rank keeps
+    whole (``ft_ar_adam`` in ``csrc/comm/rs_adam.cu``): rank ``r`` reduces slice
+    ``r`` of all ranks' gradient buffers, updates its slice of the fp32 state
+    and stores the new parameters into slice ``r`` of every rank's buffer."""
+    rc = _lib().ft_ar_adam(
+        world, rank, ctypes.cast(grad_ptrs, c_void_p), ctypes.cast(flag_ptrs, c_void_p) if flag_ptrs
+        is not None else None, dtype_code(grad_dtype), shard, float(scale), seq, start_slot, done_slot,
+        ptr(reduced_out), int(do_adam), ptr(master), ptr(m), ptr(v), ctypes.cast(param_ptrs, c_void_p),
+        dtype_code(param_dtype), ptr(finite_flag), nseg, ctypes.cast(segments, c_void_p), max_blocks,
+        stream_handle())
+    if rc != 0:
+        raise RuntimeError(f"ft_ar_adam failed (code {rc})")
 
 
 def comm_error() -> int:

@@ -139,6 +139,53 @@ def ranges_from_plan(plan: Sequence[int]) -> List[Tuple[int, int]]:
     return [(a, b) for a, b in zip(plan[:-1], plan[1:]) if b > a]
 
 
+def create_tensor_split_plans(tensor_numels: Sequence[int], plan: Sequence[int]) -> List[List[int]]:
+    """Distribute one cut-point list over consecutive buffers.
+
+    ``tensor_numels`` are the sizes of buffers laid end to end from ``plan[0]``
+    to ``plan[-1]``; the result gives, per non-empty buffer, the lengths of the
+    pieces the plan cuts it into.  Every buffer boundary must itself be a cut
+    point (merge the boundaries into the plan first).  Counterpart of
+    flextrain/param_group.py:267-310, expressed on offsets instead of lengths."""
+    numels = [int(n) for n in tensor_numels if n > 0]
+    ranges = ranges_from_plan(plan)
+    if not numels:
+        if ranges:
+            raise ValueError("plan covers elements but there is no buffer")
+        return []
+    if sum(numels) != plan[-1] - plan[0]:
+        raise ValueError("buffers and plan cover different numbers of elements")
+    out: List[List[int]] = []
+    it = iter(ranges)
+    for n in numels:
+        left, pieces = n, []
+        while left > 0:
+            a, b = next(it)
+            if b - a > left:
+                raise ValueError("a buffer boundary is not a cut point of the plan")
+            pieces.append(b - a)
+            left -= b - a
+        out.append(pieces)
+    return out
+
+
+def get_sliced_tensors(tensors, split_plans: Sequence[Sequence[int]]) -> List[torch.Tensor]:
+    """Views of flat ``tensors`` (one tensor or a list; empty ones are skipped)
+    cut by the per-buffer piece lengths of ``create_tensor_split_plans``
+    (flextrain/param_group.py:313-329)."""
+    if isinstance(tensors, torch.Tensor):
+        tensors = [tensors]
+    tensors = [t for t in tensors if t.numel() > 0]
+    if len(tensors) != len(split_plans):
+        raise ValueError(f"{len(tensors)} buffers but {len(split_plans)} split plans")
+    out: List[torch.Tensor] = []
+    for t, pieces in zip(tensors, split_plans):
+        if t.numel() != sum(pieces):
+            raise ValueError(f"pieces {list(pieces)} do not cover a buffer of {t.numel()} elements")
+        out.extend(torch.split(t, list(pieces)))
+    return out
+
+
 def create_step_contexts(param_groups: Sequence[Dict], segments: Sequence[GroupSegment],
                          master: torch.Tensor, grad: torch.Tensor,
                          states: Sequence[torch.Tensor],

@@ -169,3 +169,48 @@ def test_peer_gather_emulated_ranks():
     torch.cuda.synchronize()
     assert cuda_lib().ft_gemm_error() == 0
     assert torch.equal(bufs[2], full)
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_ar_adam_emulated_ranks(world):
+    """All-reduce form: every emulated rank reduces its slice, updates its slice
+    of the state and stores the new parameters into all ranks' buffers; after
+    all ranks ran, every buffer holds the whole updated vector."""
+    from flextrain_b200.ops.adam.cpu_adam import cpu_adam_update
+    from flextrain_b200.parallel import fused
+    from flextrain_b200.param_group import GroupSegment, slice_segments
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(10 + world)
+    S = 8 * 1031
+    N = world * S
+    grads = [(torch.randn(N, device=dev) * 4).to(torch.bfloat16) for _ in range(world)]
+    paras = [torch.zeros(N, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.full((128 * 8,), 5, dtype=torch.int32, device=dev) for _ in range(world)]
+    gp = (ctypes.c_void_p * world)(*[g.data_ptr() for g in grads])
+    pp = (ctypes.c_void_p * world)(*[p.data_ptr() for p in paras])
+    fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    groups = [dict(weight_decay=0.01), dict(weight_decay=0.0, lr=5e-4)]
+    cut = 8 * 700
+    global_segs = [GroupSegment(0, 0, cut), GroupSegment(1, cut, N)]
+    master0 = torch.randn(N)
+    ref_master, ref_m, ref_v = master0.clone(), torch.zeros(N), torch.zeros(N)
+    want = (sum(g.float() for g in grads) / (world * 4.0)).cpu()
+    for seg in global_segs:
+        grp = {**_Owner.defaults, **groups[seg.group]}
+        sl = slice(seg.start, seg.end)
+        cpu_adam_update(1, grp["lr"], 0.9, 0.999, 1e-8, grp["weight_decay"], True, True,
+                        ref_master[sl], want[sl].contiguous(), ref_m[sl], ref_v[sl])
+    for rank in range(world):
+        lo = rank * S
+        segs = slice_segments(global_segs, lo, lo + S, rebase=True)
+        master = master0[lo:lo + S].to(dev)
+        m, v = torch.zeros(S, device=dev), torch.zeros(S, device=dev)
+        arr = fused.make_segments(segs, groups, _Owner, step=1)
+        fused.ar_adam(world, rank, gp, fp, torch.bfloat16, S, 1.0 / (world * 4.0), 5, None, True,
+                      master, m, v, pp, torch.bfloat16, None, arr, len(segs), max_blocks=16)
+        torch.cuda.synchronize()
+        assert fused.comm_error() == 0
+        assert torch.allclose(master.cpu(), ref_master[lo:lo + S], rtol=1e-5, atol=1e-6)
+        assert torch.allclose(v.cpu(), ref_v[lo:lo + S], rtol=1e-5, atol=1e-7)
+    for p in paras:
+        assert torch.allclose(p.cpu().float(), ref_master.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-3)

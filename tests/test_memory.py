@@ -105,3 +105,30 @@ def test_data_ids():
     from flextrain_b200.memory import FlexTrainDataID, FlexTrainDataType
     assert str(FlexTrainDataID(FlexTrainDataType.CKPT, "3-1")) == "rank0_CKPT_layer3-1.swp"
     assert str(FlexTrainDataID(FlexTrainDataType.OPTS, 7)) == "rank0_OPTS_layer7.swp"
+
+
+def test_host_memcpy_and_locked_tensors():
+    import pytest
+    import torch
+    from flextrain_b200.memory.pin_memory import (free_cpu_locked_tensor, host_memcpy,
+                                                  is_cpu_locked_tensor, new_cpu_locked_tensor)
+    for n in (0, 1, 63, 4097, (3 << 20) + 17):
+        src = torch.randn(n)
+        dst = torch.zeros(n)
+        host_memcpy(dst, src, threads=3)
+        assert torch.equal(dst, src)
+    big = torch.arange(1 << 20, dtype=torch.int32)
+    out = torch.empty(1 << 22, dtype=torch.uint8)
+    host_memcpy(out[1:1 + 4 * 1000], big[:1000].view(torch.uint8))      # misaligned destination
+    assert torch.equal(out[1:4001].clone().view(torch.int32), big[:1000])
+    with pytest.raises(ValueError):
+        host_memcpy(torch.zeros(4), torch.zeros(5))
+    with pytest.raises(RuntimeError):
+        host_memcpy(big[1:], big[:-1])                                  # overlap
+    t = new_cpu_locked_tensor(1000, torch.float32)
+    assert t.numel() == 1000 and is_cpu_locked_tensor(t)
+    t.fill_(3.0)
+    assert float(t.sum()) == 3000.0
+    free_cpu_locked_tensor(t)
+    with pytest.raises(ValueError):
+        free_cpu_locked_tensor(torch.zeros(3))

@@ -79,3 +79,24 @@ def test_step_contexts_bind_views():
     assert [c.numel for c in ctxs] == [4, 6]
     ctxs[1].master.add_(100)
     assert master[4].item() == 104.0
+
+
+def test_tensor_split_plans_and_sliced_tensors():
+    import pytest
+    import torch
+    from flextrain_b200.param_group import (create_tensor_split_plans, get_sliced_tensors,
+                                            merge_slice_plans)
+    plan = merge_slice_plans([0, 10, 30], [0, 6, 10, 24, 30])
+    plans = create_tensor_split_plans([10, 0, 20], plan)
+    assert plans == [[6, 4], [14, 6]]
+    bufs = [torch.arange(10.), torch.empty(0), torch.arange(10., 30.)]
+    views = get_sliced_tensors(bufs, plans)
+    assert [v.numel() for v in views] == [6, 4, 14, 6]
+    assert torch.equal(torch.cat(views), torch.arange(30.))
+    views[2][0] = -1.0                      # views, not copies
+    assert bufs[2][0] == -1.0
+    assert create_tensor_split_plans([0, 0], [0]) == []
+    with pytest.raises(ValueError):
+        create_tensor_split_plans([12, 18], plan)      # 12 is not a cut point
+    with pytest.raises(ValueError):
+        get_sliced_tensors(bufs[0], plans)
