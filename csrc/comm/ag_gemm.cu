@@ -4,14 +4,16 @@
 //
 // ft_ag_gemm: y[M,N] = x[M,K] * W[N,K]^T where W is row-sharded over `world`
 // ranks (rank r owns rows [r*N/world, (r+1)*N/world) of every rank's peer-mapped
-// [N,K] buffer).  One persistent launch: the first `num_copiers` CTAs pull the
-// remote shards into the local buffer with non-multicast bulk copies (peer HBM
-// -> shared memory -> local HBM), publishing one counter per 256-row block; the
-// other CTAs run the tcgen05 GEMM pipeline of kernels/gemm_kernel.cuh, walking
-// the output tiles from the local shard outwards in arrival order, their TMA
-// producers waiting (bounded) for a block's counter before loading it.  The
-// transfer therefore overlaps the math tile by tile and the weight crosses
-// NVLink exactly once.
+// [N,K] buffer).  One persistent launch.  Default form (M > 128): the CTA-pair
+// tcgen05 pipeline of kernels/gemm2_kernel.cuh on every SM, with one more warp
+// per CTA that pulls its share of the remote shards into the local buffer with
+// non-multicast bulk copies (peer HBM -> shared memory -> local HBM) and
+// publishes one counter per 256-row block.  Fallback form: the first
+// `num_copiers` CTAs only copy and the others run the single-CTA pipeline of
+// kernels/gemm_kernel.cuh.  Either way the output tiles are walked from the
+// local shard outwards in arrival order, the TMA producers waiting (bounded) for
+// a block's counter before loading it, so the transfer overlaps the math tile by
+// tile and the weight crosses NVLink exactly once.
 //
 // ft_peer_gather: the copier role alone, for any flat sharded buffer.
 //
@@ -21,6 +23,7 @@
 #include <cstdio>
 
 #include "../kernels/gemm_host.h"
+#include "../kernels/gemm2_kernel.cuh"
 #include "../kernels/gemm_kernel.cuh"
 
 namespace {
@@ -79,9 +82,42 @@ int fill_gather(GatherArgs& G, int world, int rank, const void* const* w_ptrs, u
   return 0;
 }
 
+// CTA-pair form (kernels/gemm2_kernel.cuh with GATHER): every CTA computes and its
+// seventh warp copies, so no SM is given up to the transfer.
+template <typename T, int MODE>
+int launch_pair_gather(const CUtensorMap& ta, const CUtensorMap& tb, void* y, int64_t ldc, int M, int N,
+                       int K, int* err, int grid, const GatherArgs& G, cudaStream_t stream) {
+  auto kern = gemm_pair_kernel<T, false, false, MODE, true>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES_GATHER);
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(P_THREADS_GATHER, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES_GATHER;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, y, ldc, M, N, K, err, G);
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+int g_ag_pair = -1;   // -1: read FLEXTRAIN_AG_GEMM_PAIR on first use (default on)
+
 }  // namespace
 
 extern "C" {
+
+// Selects the CTA-pair form (1, default) or the single-CTA form with dedicated copy
+// CTAs (0) for later ft_ag_gemm calls.
+void ft_ag_gemm_set_pair(int on) { g_ag_pair = on ? 1 : 0; }
 
 void ft_ag_set_spin_budget(long long cycles) { g_spin_budget = cycles; }
 
@@ -111,12 +147,35 @@ int ft_ag_gemm(int world, int rank, const void* const* w_ptrs, uint32_t* const* 
   G.rows_per_rank = N / world;
   G.shard_bytes = (int64_t)G.rows_per_rank * G.row_bytes;
   G.block_bytes = (int64_t)BN * G.row_bytes;
+  if (g_ag_pair < 0) {
+    const char* e = getenv("FLEXTRAIN_AG_GEMM_PAIR");
+    g_ag_pair = e ? atoi(e) : 1;
+  }
+  const bool pair = g_ag_pair != 0 && M > 128;
   CUtensorMap ta, tb;
   int rc = make_tmap(&ta, x, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM, ab_dtype);
   if (rc) return rc;
-  rc = make_tmap(&tb, w_ptrs[rank], (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN, ab_dtype);
+  rc = make_tmap(&tb, w_ptrs[rank], (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, pair ? 128 : BN, ab_dtype);
   if (rc) return rc;
   cudaMemsetAsync(g_ready[dev], 0, nt * sizeof(uint32_t), stream);
+  if (pair) {
+    const int ptiles = ((M + P_BM - 1) / P_BM) * (N / P_BN);
+    int pgrid = 2 * ptiles < sms ? 2 * ptiles : (sms & ~1);
+    G.num_copiers = pgrid;
+    int* perr = error_word(dev);
+    if (ab_dtype == kBF16)
+      rc = c_dtype == kF32
+               ? launch_pair_gather<__nv_bfloat16, kStore32>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream)
+               : launch_pair_gather<__nv_bfloat16, kStore16>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream);
+    else
+      rc = c_dtype == kF32
+               ? launch_pair_gather<__half, kStore32>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream)
+               : launch_pair_gather<__half, kStore16>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream);
+    if (rc) return rc;
+    FT_LAUNCHED(1);
+    FT_CUDA_RETURN_IF_ERROR();
+    return 0;
+  }
   const int tiles = ((M + BM - 1) / BM) * nt;
   int grid = tiles + num_copiers < sms ? tiles + num_copiers : sms;
   int* err = error_word(dev);

@@ -5,6 +5,7 @@
 #include <cstdlib>
 
 #include "attention_bwd.cuh"
+#include "attention_fwd2.cuh"
 #include "gemm_host.h"
 
 namespace {
@@ -26,6 +27,33 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   return 0;
 }
 
+// Second-generation forward: one CTA per pair of query blocks.
+template <typename T, int D>
+int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
+                cudaStream_t s) {
+  auto kern = attn_fwd2_kernel<T, D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<D>::BYTES);
+    configured = true;
+  }
+  const int num_pairs = ((P.S + BQ - 1) / BQ + 1) / 2;
+  kern<<<P.B * P.Hq * num_pairs, F2_THREADS, Fwd2Smem<D>::BYTES, s>>>(tq, tk, tv, P);
+  return 0;
+}
+
+int g_fwd_version = -1;   // -1: read FLEXTRAIN_ATTN_FWD on first use (2 = default, 1 = first generation)
+
+template <typename T, int D>
+int launch_fwd_any(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
+                   cudaStream_t s) {
+  if (g_fwd_version < 0) {
+    const char* e = getenv("FLEXTRAIN_ATTN_FWD");
+    g_fwd_version = e ? atoi(e) : 2;
+  }
+  return g_fwd_version == 1 ? launch_fwd<T, D>(tq, tk, tv, P, s) : launch_fwd2<T, D>(tq, tk, tv, P, s);
+}
+
 template <typename T, int D>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                const BwdParams& P, cudaStream_t s) {
@@ -43,7 +71,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 template <typename T>
 void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_stride, float* delta,
                      const float* dq_acc, void* dq, int64_t dq_stride, int B, int S, int Hq, int D,
-                     cudaStream_t s) {
+                     float scale, cudaStream_t s) {
   if (!post) {
     const int64_t rows = (int64_t)B * S * Hq;
     attn_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const T*)o, (const T*)d_o, do_stride,
@@ -51,13 +79,16 @@ void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_strid
   } else {
     const int64_t tokens = (int64_t)B * S;
     attn_dq_cast_kernel<T><<<grid_for(tokens * (Hq * D / 8), 256), 256, 0, s>>>(dq_acc, (T*)dq, dq_stride,
-                                                                                tokens, Hq * D);
+                                                                                tokens, Hq * D, scale);
   }
 }
 
 }  // namespace
 
 extern "C" {
+
+// Selects the forward kernel generation for later ft_attn_fwd calls (1 or 2).
+void ft_attn_set_fwd_version(int v) { g_fwd_version = v == 1 ? 1 : 2; }
 
 // o[B,S,Hq,D], lse[B,Hq,S] <- causal attention of q[B,S,Hq,D], k/v[B,S,Hkv,D].
 // *_stride: elements between consecutive tokens of that tensor.  D in {64, 128}.
@@ -83,11 +114,11 @@ int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.q_col0 = P.k_col0 = P.v_col0 = 0;
   P.err = gemm::error_word(dev);
   if (dtype == kBF16) {
-    if (D == 128) launch_fwd<__nv_bfloat16, 128>(tq, tk, tv, P, stream);
-    else launch_fwd<__nv_bfloat16, 64>(tq, tk, tv, P, stream);
+    if (D == 128) launch_fwd_any<__nv_bfloat16, 128>(tq, tk, tv, P, stream);
+    else launch_fwd_any<__nv_bfloat16, 64>(tq, tk, tv, P, stream);
   } else {
-    if (D == 128) launch_fwd<__half, 128>(tq, tk, tv, P, stream);
-    else launch_fwd<__half, 64>(tq, tk, tv, P, stream);
+    if (D == 128) launch_fwd_any<__half, 128>(tq, tk, tv, P, stream);
+    else launch_fwd_any<__half, 64>(tq, tk, tv, P, stream);
   }
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
@@ -126,15 +157,15 @@ int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.err = gemm::error_word(dev);
   P.debug_skip = getenv("FLEXTRAIN_ATTN_DEBUG_SKIP") ? atoi(getenv("FLEXTRAIN_ATTN_DEBUG_SKIP")) : 0;
   if (dtype == kBF16) {
-    launch_pre_post<__nv_bfloat16>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, stream);
+    launch_pre_post<__nv_bfloat16>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
     if (D == 128) launch_bwd<__nv_bfloat16, 128>(tq, tk, tv, tdo, P, stream);
     else launch_bwd<__nv_bfloat16, 64>(tq, tk, tv, tdo, P, stream);
-    launch_pre_post<__nv_bfloat16>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, stream);
+    launch_pre_post<__nv_bfloat16>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, scale, stream);
   } else {
-    launch_pre_post<__half>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, stream);
+    launch_pre_post<__half>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
     if (D == 128) launch_bwd<__half, 128>(tq, tk, tv, tdo, P, stream);
     else launch_bwd<__half, 64>(tq, tk, tv, tdo, P, stream);
-    launch_pre_post<__half>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, stream);
+    launch_pre_post<__half>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, scale, stream);
   }
   FT_LAUNCHED(3);
   FT_CUDA_RETURN_IF_ERROR();

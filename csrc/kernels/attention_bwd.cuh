@@ -4,10 +4,13 @@
 // memory; the CTA walks every query head of the group and every query block
 // m >= n, and per (head, m):
 //   TMA      Q_m, dO_m                      ([64-col chunk][row][64], 128B swizzle)
-//   MMA      S  = Q K^T,  dP = dO V^T       -> TMEM
-//   warps    P  = exp(scale*S - lse),  dS = scale * P * (dP - delta)
-//            written as 16-bit tiles [q][kv] into shared memory
-//   MMA      dV += P^T dO,  dK += dS^T Q    (accumulated in TMEM over the whole walk)
+//   MMA      S  = Q K^T,  dP = dO V^T       -> TMEM (separate completion signals)
+//   warps    P  = exp(scale*S - lse) as soon as S is there (dP is still running),
+//            then dS = P * (dP - delta); both written as 16-bit tiles [q][kv] into
+//            shared memory.  The softmax scale is not applied to dS: dK is scaled
+//            once when it is written and dQ by the conversion pass.
+//   MMA      dV += P^T dO as soon as P is written (dS is still being computed),
+//            dK += dS^T Q (both accumulated in TMEM over the whole walk),
 //            dQ_m = dS K                    -> TMEM, then fp32 vector atomics into dq_acc
 // The same shared-memory bytes serve as K-major operand (reduction over the 64
 // contiguous columns) and as MN-major operand (reduction over the rows), so no
@@ -15,6 +18,7 @@
 // converted to the 16-bit dq by a separate pass.  All waits are bounded.
 #pragma once
 #include "attention_fwd.cuh"
+#include "packed_math.cuh"
 
 namespace ft {
 namespace attn {
@@ -32,7 +36,7 @@ struct BwdSmem {
 };
 
 struct BwdBars {
-  uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_full, dq_full, s_free, acc_full;
+  uint64_t kv_full, qdo_full, qdo_empty, s_full, dp_full, p_full, ds_full, dq_full, s_free, acc_full;
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -87,8 +91,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars->kv_full, 1);
     mbar_init(&bars->qdo_full, 1);
     mbar_init(&bars->qdo_empty, 1);
-    mbar_init(&bars->sdp_full, 1);
-    mbar_init(&bars->pds_full, 256);
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->p_full, 256);
+    mbar_init(&bars->ds_full, 256);
     mbar_init(&bars->dq_full, 1);
     mbar_init(&bars->s_free, 256);
     mbar_init(&bars->acc_full, 1);
@@ -145,20 +151,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_s, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), id_s,
                    kk != 0);
         }
+        umma_commit(&bars->s_full);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
           umma_f16(tm_dp, make_smem_desc(aDO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024), id_s,
                    kk != 0);
         }
-        umma_commit(&bars->sdp_full);
-        if (!mbar_wait(&bars->pds_full, ph)) { atomicCAS(P.err, 0, 405); ok = false; break; }
+        umma_commit(&bars->dp_full);
+        if (!mbar_wait(&bars->p_full, ph)) { atomicCAS(P.err, 0, 405); ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {       // reduction over the 128 query rows
           const uint32_t row_off = kk * 2048;
           umma_f16(tm_dv, make_smem_desc(aP + row_off, CHUNK_BYTES, 1024),
                    make_smem_desc(aDO + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
+        }
+        if (!mbar_wait(&bars->ds_full, ph)) { atomicCAS(P.err, 0, 409); ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) {
+          const uint32_t row_off = kk * 2048;
           umma_f16(tm_dk, make_smem_desc(aDS + row_off, CHUNK_BYTES, 1024),
                    make_smem_desc(aQ + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
         }
@@ -180,6 +193,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float log2e = 1.4426950408889634f;
+    const uint64_t scale2 = pm::pack2(P.scale_log2, P.scale_log2);
+    constexpr int NC = BKV / 64;                     // 32-column chunks per warp
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
       const uint32_t ph = it & 1;
@@ -188,41 +203,76 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const int q_pos = m * BQ + r;
       const bool valid = q_pos < P.S;
       const int64_t stat = ((int64_t)batch * P.Hq + head) * P.S + q_pos;
-      const float lse2 = valid ? P.lse[stat] * log2e : 0.f;
-      const float delta = valid ? P.delta[stat] : 0.f;
-      if (!mbar_wait(&bars->sdp_full, ph)) { atomicCAS(P.err, 0, 406); ok = false; break; }
-      tc_fence_after();
+      // rows past the end of the sequence: lse = +inf makes every P (and dS) of the row zero
+      const float neg_lse2 = valid ? -P.lse[stat] * log2e : -INFINITY;
+      const float neg_delta = valid ? -P.delta[stat] : 0.f;
+      const uint64_t neg_lse22 = pm::pack2(neg_lse2, neg_lse2);
+      const uint64_t neg_delta2 = pm::pack2(neg_delta, neg_delta);
       const bool diag = (m == nb);
-#pragma unroll 1
-      for (int c = half * (BKV / 64); c < (half + 1) * (BKV / 64); ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(tm_s + lane_addr + c * 32, sv);
-        tmem_ld_32x32(tm_dp + lane_addr + c * 32, dv);
-        tmem_ld_wait();
-        float p[32], ds[32];
+      float p[NC][32];
+      // ---- P as soon as S is complete
+      if (!mbar_wait(&bars->s_full, ph)) { atomicCAS(P.err, 0, 406); ok = false; break; }
+      tc_fence_after();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv_pos = nb * BKV + c * 32 + i;
-          float pi = exp2f(__uint_as_float(sv[i]) * P.scale_log2 - lse2);
-          if (!valid || (diag && kv_pos > q_pos)) pi = 0.f;
-          p[i] = pi;
-          ds[i] = pi * (__uint_as_float(dv[i]) - delta) * P.scale;
+      for (int cc = 0; cc < NC; ++cc) {
+        const int c = half * NC + cc;
+        uint32_t sv[32];
+        tmem_ld_32x32(tm_s + lane_addr + c * 32, sv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float a, b;
+          pm::unpack2(pm::fma2(pm::pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, neg_lse22),
+                      a, b);
+          p[cc][i] = (P.debug_skip & 2) ? a : pm::ex2(a);
+          p[cc][i + 1] = (P.debug_skip & 2) ? b : pm::ex2(b);
+        }
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (nb * BKV + c * 32 + i > q_pos) p[cc][i] = 0.f;
         }
         uint8_t* pc = sP + (c / 2) * CHUNK_BYTES;
-        uint8_t* dc = sdS + (c / 2) * CHUNK_BYTES;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          float t[8], d8[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { t[i] = p[u * 8 + i]; d8[i] = ds[u * 8 + i]; }
-          const uint32_t o = swz(r, (c % 2) * 4 + u);
-          *reinterpret_cast<uint4*>(pc + o) = pack8<T>(t);
-          *reinterpret_cast<uint4*>(dc + o) = pack8<T>(d8);
+          uint4 w;
+          w.x = pm::cvt2<T>(p[cc][u * 8 + 0], p[cc][u * 8 + 1]);
+          w.y = pm::cvt2<T>(p[cc][u * 8 + 2], p[cc][u * 8 + 3]);
+          w.z = pm::cvt2<T>(p[cc][u * 8 + 4], p[cc][u * 8 + 5]);
+          w.w = pm::cvt2<T>(p[cc][u * 8 + 6], p[cc][u * 8 + 7]);
+          *reinterpret_cast<uint4*>(pc + swz(r, (c % 2) * 4 + u)) = w;
         }
       }
       tc_fence_before();
       fence_proxy_async();
-      mbar_arrive(&bars->pds_full);
+      mbar_arrive(&bars->p_full);
+      // ---- dS once dP is complete
+      if (!mbar_wait(&bars->dp_full, ph)) { atomicCAS(P.err, 0, 410); ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < NC; ++cc) {
+        const int c = half * NC + cc;
+        uint32_t dv[32];
+        tmem_ld_32x32(tm_dp + lane_addr + c * 32, dv);
+        tmem_ld_wait();
+        uint8_t* dc = sdS + (c / 2) * CHUNK_BYTES;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint32_t w[4];
+#pragma unroll
+          for (int h2 = 0; h2 < 4; ++h2) {
+            const int i = u * 8 + h2 * 2;
+            float a, b;
+            pm::unpack2(pm::mul2(pm::add2(pm::pack2(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), neg_delta2),
+                                 pm::pack2(p[cc][i], p[cc][i + 1])), a, b);
+            w[h2] = pm::cvt2<T>(a, b);
+          }
+          *reinterpret_cast<uint4*>(dc + swz(r, (c % 2) * 4 + u)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      mbar_arrive(&bars->ds_full);
       if (!mbar_wait(&bars->dq_full, ph)) { atomicCAS(P.err, 0, 407); ok = false; break; }
       tc_fence_after();
       float* dq_row = P.dq_acc + ((int64_t)(batch * P.S + q_pos) * P.Hq + head) * D;
@@ -258,7 +308,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           for (int u = 0; u < 4; ++u) {
             float t[8], w[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { t[i] = __uint_as_float(a[u * 8 + i]); w[i] = __uint_as_float(b[u * 8 + i]); }
+            for (int i = 0; i < 8; ++i) {
+              t[i] = __uint_as_float(a[u * 8 + i]) * P.scale;          // dS carried no softmax scale
+              w[i] = __uint_as_float(b[u * 8 + i]);
+            }
             *reinterpret_cast<uint4*>(dk_row + c * 32 + u * 8) = pack8<T>(t);
             *reinterpret_cast<uint4*>(dv_row + c * 32 + u * 8) = pack8<T>(w);
           }
@@ -308,10 +361,11 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const T* __restrict__ o
   }
 }
 
-// dq (16-bit, token stride) <- dq_acc (fp32, contiguous [tokens, W])
+// dq (16-bit, token stride) <- scale * dq_acc (fp32, contiguous [tokens, W])
 template <typename T>
 __global__ void __launch_bounds__(256) attn_dq_cast_kernel(const float* __restrict__ acc, T* __restrict__ dq,
-                                                           int64_t dq_stride, int64_t tokens, int W) {
+                                                           int64_t dq_stride, int64_t tokens, int W,
+                                                           float scale) {
   const int vec = W / 8;
   const int64_t total = tokens * vec;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
@@ -320,7 +374,8 @@ __global__ void __launch_bounds__(256) attn_dq_cast_kernel(const float* __restri
     const int c = (int)(idx % vec) * 8;
     const float4 a = *reinterpret_cast<const float4*>(acc + t * W + c);
     const float4 b = *reinterpret_cast<const float4*>(acc + t * W + c + 4);
-    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[8] = {a.x * scale, a.y * scale, a.z * scale, a.w * scale,
+                  b.x * scale, b.y * scale, b.z * scale, b.w * scale};
     *reinterpret_cast<uint4*>(dq + t * dq_stride + c) = pack8<T>(v);
   }
 }

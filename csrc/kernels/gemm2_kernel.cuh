@@ -27,6 +27,11 @@ constexpr int P_STAGES = 6;
 constexpr int P_A_BYTES = 128 * BK * 2, P_B_BYTES = 128 * BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;       // clears the CTA-rank bit of a shared::cluster address
+// All-gather variant: one more warp per CTA streams remote rows of B through a small
+// ring of its own, so every SM keeps computing while the weight arrives.
+constexpr int G2_CHUNK = 8192, G2_STAGES = 4;
+constexpr int P_SMEM_BYTES_GATHER = P_SMEM_BYTES + G2_STAGES * G2_CHUNK;
+constexpr int P_THREADS_GATHER = NUM_THREADS + 32;
 
 struct PairBarriers {
   uint64_t full[P_STAGES];
@@ -35,7 +40,9 @@ struct PairBarriers {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   uint32_t abort;
+  uint64_t gather_full[G2_STAGES];                   // ring of the copy warp (all-gather variant)
 };
+static_assert(sizeof(PairBarriers) <= 256, "barrier block outgrew its slot");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -98,10 +105,16 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPeerBitMask) : "memory");
 }
 
-template <typename T, bool A_MN, bool B_MN, int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// With GATHER, B is row-sharded over the ranks of `gather.peers` (see GatherArgs): warp 6
+// of every CTA copies its share of the remote rows into the local buffer (peer HBM ->
+// shared memory -> local HBM, bulk copies without multicast) and counts finished
+// chunks per 256-row block; tiles are walked from the local shard outwards and each
+// producer waits (bounded) for the block it is about to load.
+template <typename T, bool A_MN, bool B_MN, int MODE, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? P_THREADS_GATHER : NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 void* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err) {
+                 void* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err,
+                 const __grid_constant__ GatherArgs gather) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -111,12 +124,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int pair = (int)(blockIdx.x >> 1), num_pairs = (int)(gridDim.x >> 1);
   const int mt = (M + P_BM - 1) / P_BM, nt = (N + P_BN - 1) / P_BN, kt = (K + BK - 1) / BK;
   const int num_tiles = mt * nt;
+  const int nt_local = GATHER ? gather.rows_per_rank / P_BN : 0;
+  const int n_rot = GATHER ? gather.peers.rank * nt_local : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
+    if constexpr (GATHER)
+      for (int s = 0; s < G2_STAGES; ++s) mbar_init(&bars->gather_full[s], 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->tmem_full[a], 1);
       mbar_init(&bars->tmem_empty[a], 8);            // 4 epilogue warps in each of the two CTAs
@@ -144,6 +161,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
         int mb, nb;
         tile_coords(t, mt, nt, mb, nb);
+        if constexpr (GATHER) {
+          nb = (nb + n_rot) % nt;
+          if (nb < n_rot || nb >= n_rot + nt_local) {      // rows that come from a peer
+            const uint32_t need = (uint32_t)(gather.block_bytes / G2_CHUNK);
+            const long long t0 = clock64();
+            bool ok = true;
+            while (ld_acquire_gpu(gather.ready + nb) < need) {
+              if (clock64() - t0 > gather.spin_budget) { ok = false; break; }
+              __nanosleep(128);
+            }
+            if (!ok) { *abort_flag = 1; atomicCAS(err, 0, 15); break; }
+            fence_proxy_async_all();
+          }
+        }
         const int m0 = mb * P_BM + (int)cta * 128;   // this CTA's rows of A
         const int n0 = nb * P_BN + (int)cta * 128;   // this CTA's half of B
         for (int kb = 0; kb < kt; ++kb) {
@@ -217,6 +248,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         umma_commit_pair(&bars->tmem_full[acc]);
       }
     }
+  } else if (GATHER && warp == 6) {
+    // ------------------------------------------------------------ copy warp (both CTAs)
+    if (lane == 0) {
+      uint8_t* ring = smem + P_STAGES * P_STAGE_BYTES + 256;
+      gather_role<G2_CHUNK, G2_STAGES, G2_CHUNK>(gather, ring, bars->gather_full, err);
+    }
   } else {
     // ---------------------------------------------------------- epilogue (both CTAs)
     const int quarter = warp & 3;
@@ -224,6 +261,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++it) {
       int mb, nb;
       tile_coords(t, mt, nt, mb, nb);
+      if constexpr (GATHER) nb = (nb + n_rot) % nt;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&bars->tmem_full[acc], acc_phase)) {

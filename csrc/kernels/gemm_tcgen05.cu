@@ -186,7 +186,7 @@ int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, ldc, M, N, K, err);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, ldc, M, N, K, err, GatherArgs{});
   return e == cudaSuccess ? 0 : (int)e;
 }
 
