@@ -6,6 +6,7 @@
 
 #include "attention_bwd.cuh"
 #include "attention_fwd2.cuh"
+#include "attention_fwd3.cuh"
 #include "gemm_host.h"
 
 namespace {
@@ -42,21 +43,45 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   return 0;
 }
 
-int g_fwd_version = -1;   // -1: read FLEXTRAIN_ATTN_FWD on first use (2 = default, 1 = first generation)
+// Third generation: as the second, K/V maps with 64-row boxes.
+template <typename T, int D>
+int launch_fwd3(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
+                cudaStream_t s) {
+  auto kern = attn_fwd3_kernel<T, D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd3Smem<D>::BYTES);
+    configured = true;
+  }
+  const int num_pairs = ((P.S + BQ - 1) / BQ + 1) / 2;
+  kern<<<P.B * P.Hq * num_pairs, F2_THREADS, Fwd3Smem<D>::BYTES, s>>>(tq, tk, tv, P);
+  return 0;
+}
+
+int g_fwd_version = -1;   // -1: read FLEXTRAIN_ATTN_FWD on first use (default 2, the fastest measured)
+
+int fwd_version() {
+  if (g_fwd_version < 0) {
+    const char* e = getenv("FLEXTRAIN_ATTN_FWD");
+    g_fwd_version = e ? atoi(e) : 2;
+    if (g_fwd_version < 1 || g_fwd_version > 3) g_fwd_version = 2;
+  }
+  return g_fwd_version;
+}
 
 template <typename T, int D>
 int launch_fwd_any(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
                    cudaStream_t s) {
-  if (g_fwd_version < 0) {
-    const char* e = getenv("FLEXTRAIN_ATTN_FWD");
-    g_fwd_version = e ? atoi(e) : 2;
+  switch (fwd_version()) {
+    case 1: return launch_fwd<T, D>(tq, tk, tv, P, s);
+    case 2: return launch_fwd2<T, D>(tq, tk, tv, P, s);
+    default: return launch_fwd3<T, D>(tq, tk, tv, P, s);
   }
-  return g_fwd_version == 1 ? launch_fwd<T, D>(tq, tk, tv, P, s) : launch_fwd2<T, D>(tq, tk, tv, P, s);
 }
 
 template <typename T, int D>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-               const BwdParams& P, cudaStream_t s) {
+               const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
   auto kern = attn_bwd_kernel<T, D>;
   static bool configured = false;
   if (!configured) {
@@ -64,7 +89,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     configured = true;
   }
   const int num_blk = (P.S + BQ - 1) / BQ;
-  kern<<<P.B * P.Hkv * num_blk, BWD_THREADS, BwdSmem<D>::BYTES, s>>>(tq, tk, tv, tdo, P);
+  kern<<<P.B * P.Hkv * num_blk, BWD_THREADS, BwdSmem<D>::BYTES, s>>>(tq, tk, tv, tdo, tdq, P);
   return 0;
 }
 
@@ -87,8 +112,8 @@ void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_strid
 
 extern "C" {
 
-// Selects the forward kernel generation for later ft_attn_fwd calls (1 or 2).
-void ft_attn_set_fwd_version(int v) { g_fwd_version = v == 1 ? 1 : 2; }
+// Selects the forward kernel generation for later ft_attn_fwd calls (1, 2 or 3).
+void ft_attn_set_fwd_version(int v) { g_fwd_version = (v >= 1 && v <= 3) ? v : 2; }
 
 // o[B,S,Hq,D], lse[B,Hq,S] <- causal attention of q[B,S,Hq,D], k/v[B,S,Hkv,D].
 // *_stride: elements between consecutive tokens of that tensor.  D in {64, 128}.
@@ -103,9 +128,10 @@ int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   CUtensorMap tq, tk, tv;
   int rc = gemm::make_tmap(&tq, q, (uint64_t)Hq * D, (uint64_t)B * S, (uint64_t)q_stride, 64, BQ, dtype);
   if (rc) return rc;
-  rc = gemm::make_tmap(&tk, k, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)k_stride, 64, BKV, dtype);
+  const uint32_t kv_box = fwd_version() == 3 ? SUB : BKV;
+  rc = gemm::make_tmap(&tk, k, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)k_stride, 64, kv_box, dtype);
   if (rc) return rc;
-  rc = gemm::make_tmap(&tv, v, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)v_stride, 64, BKV, dtype);
+  rc = gemm::make_tmap(&tv, v, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)v_stride, 64, kv_box, dtype);
   if (rc) return rc;
   FwdParams P;
   P.o = o; P.lse = lse; P.B = B; P.S = S; P.Hq = Hq; P.Hkv = Hkv;
@@ -148,6 +174,10 @@ int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   if (rc) return rc;
   rc = gemm::make_tmap(&tdo, d_o, (uint64_t)Hq * D, (uint64_t)B * S, (uint64_t)do_stride, 64, BQ, dtype);
   if (rc) return rc;
+  // dq_acc viewed as [B*S, Hq*D] fp32; the kernel adds 128-row x 32-column slabs into it
+  CUtensorMap tdq;
+  rc = gemm::make_tmap(&tdq, dq_acc, (uint64_t)Hq * D, (uint64_t)B * S, (uint64_t)Hq * D, 32, BQ, kF32);
+  if (rc) return rc;
   cudaMemsetAsync(dq_acc, 0, (size_t)B * S * Hq * D * sizeof(float), stream);
   BwdParams P;
   P.lse = lse; P.delta = delta; P.dq_acc = dq_acc;
@@ -158,13 +188,13 @@ int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.debug_skip = getenv("FLEXTRAIN_ATTN_DEBUG_SKIP") ? atoi(getenv("FLEXTRAIN_ATTN_DEBUG_SKIP")) : 0;
   if (dtype == kBF16) {
     launch_pre_post<__nv_bfloat16>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
-    if (D == 128) launch_bwd<__nv_bfloat16, 128>(tq, tk, tv, tdo, P, stream);
-    else launch_bwd<__nv_bfloat16, 64>(tq, tk, tv, tdo, P, stream);
+    if (D == 128) launch_bwd<__nv_bfloat16, 128>(tq, tk, tv, tdo, tdq, P, stream);
+    else launch_bwd<__nv_bfloat16, 64>(tq, tk, tv, tdo, tdq, P, stream);
     launch_pre_post<__nv_bfloat16>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, scale, stream);
   } else {
     launch_pre_post<__half>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
-    if (D == 128) launch_bwd<__half, 128>(tq, tk, tv, tdo, P, stream);
-    else launch_bwd<__half, 64>(tq, tk, tv, tdo, P, stream);
+    if (D == 128) launch_bwd<__half, 128>(tq, tk, tv, tdo, tdq, P, stream);
+    else launch_bwd<__half, 64>(tq, tk, tv, tdo, tdq, P, stream);
     launch_pre_post<__half>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, scale, stream);
   }
   FT_LAUNCHED(3);

@@ -11,7 +11,9 @@
 //            once when it is written and dQ by the conversion pass.
 //   MMA      dV += P^T dO as soon as P is written (dS is still being computed),
 //            dK += dS^T Q (both accumulated in TMEM over the whole walk),
-//            dQ_m = dS K                    -> TMEM, then fp32 vector atomics into dq_acc
+//            dQ_m = dS K                    -> TMEM -> fp32 staging in shared memory (the P / dS
+//            tiles, idle by then) -> one TMA reduce-add per 32-column slab into dq_acc,
+//            issued by a dedicated warp so it overlaps the next block's S / dP
 // The same shared-memory bytes serve as K-major operand (reduction over the 64
 // contiguous columns) and as MN-major operand (reduction over the rows), so no
 // tile is ever transposed.  dK / dV are written once at the end; dq_acc is
@@ -23,10 +25,10 @@
 namespace ft {
 namespace attn {
 
-// 2 control warps + 8 compute warps: warps 2-5 own S / dP / dQ / dK / dV columns of the
-// first half, warps 6-9 those of the second half (each warp still reads only its own
-// TMEM lane quarter, warp % 4).
-constexpr int BWD_THREADS = 320;
+// 2 control warps + 8 compute warps + the dQ store warp: warps 2-5 own S / dP / dQ / dK /
+// dV columns of the first half, warps 6-9 those of the second half (each warp still reads
+// only its own TMEM lane quarter, warp % 4); warp 10 issues the dQ reduce-adds.
+constexpr int BWD_THREADS = 352;
 
 template <int D>
 struct BwdSmem {
@@ -37,6 +39,7 @@ struct BwdSmem {
 
 struct BwdBars {
   uint64_t kv_full, qdo_full, qdo_empty, s_full, dp_full, p_full, ds_full, dq_full, s_free, acc_full;
+  uint64_t dqs_full, stage_free;
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -53,16 +56,21 @@ struct BwdParams {
   int debug_skip;          // profiling aid: bit 0 skips the dq atomics, bit 1 skips exp
 };
 
-__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
+// fp32 tile in shared memory (128B-swizzled [rows][32] slab) added into global memory
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const void* smem_src, int32_t x,
+                                                  int32_t y) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(m)),
+      "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+      : "memory");
 }
 
 template <typename T, int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                const __grid_constant__ BwdParams P) {
+                const __grid_constant__ CUtensorMap tmap_dq, const __grid_constant__ BwdParams P) {
   constexpr int TILE = BwdSmem<D>::TILE;
   constexpr int CHUNKS = D / 64;
   constexpr int CHUNK_BYTES = BQ * 128;
@@ -98,9 +106,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars->dq_full, 1);
     mbar_init(&bars->s_free, 256);
     mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->dqs_full, 256);
+    mbar_init(&bars->stage_free, 1);
     bars->abort = 0;
     fence_barrier_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
+    prefetch_tmap(&tmap_dq);
   }
   if (warp == 1) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -187,6 +198,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (ok) umma_commit(&bars->acc_full);
       else *abort_flag = 1;
     }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------ dQ store warp
+    if (lane == 0) {
+      for (int it = 0; it < iters && !*abort_flag; ++it) {
+        const int head = kv_head * group + it / q_blocks;
+        const int m = nb + it % q_blocks;
+        if (!mbar_wait(&bars->dqs_full, it & 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 411); break; }
+        if (!(P.debug_skip & 1)) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c)
+            tma_reduce_add_2d(&tmap_dq, sP + c * (BQ * 128), head * D + c * 32, batch * P.S + m * BQ);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        }
+        mbar_arrive(&bars->stage_free);
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
   } else {
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;                // which half of the columns this warp owns
@@ -212,35 +241,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       float p[NC][32];
       // ---- P as soon as S is complete
       if (!mbar_wait(&bars->s_full, ph)) { atomicCAS(P.err, 0, 406); ok = false; break; }
+      // the P / dS tiles double as the dQ staging area: the previous reduce must have read it
+      if (it > 0 && !mbar_wait(&bars->stage_free, (it - 1) & 1)) { atomicCAS(P.err, 0, 412); ok = false; break; }
       tc_fence_after();
+      {
+        uint32_t sv[NC][32];
 #pragma unroll
-      for (int cc = 0; cc < NC; ++cc) {
-        const int c = half * NC + cc;
-        uint32_t sv[32];
-        tmem_ld_32x32(tm_s + lane_addr + c * 32, sv);
+        for (int cc = 0; cc < NC; ++cc) tmem_ld_32x32(tm_s + lane_addr + (half * NC + cc) * 32, sv[cc]);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a, b;
-          pm::unpack2(pm::fma2(pm::pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, neg_lse22),
-                      a, b);
-          p[cc][i] = (P.debug_skip & 2) ? a : pm::ex2(a);
-          p[cc][i + 1] = (P.debug_skip & 2) ? b : pm::ex2(b);
-        }
-        if (diag) {
+        for (int cc = 0; cc < NC; ++cc) {
+          const int c = half * NC + cc;
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (nb * BKV + c * 32 + i > q_pos) p[cc][i] = 0.f;
-        }
-        uint8_t* pc = sP + (c / 2) * CHUNK_BYTES;
+          for (int i = 0; i < 32; i += 2) {
+            float a, b;
+            pm::unpack2(pm::fma2(pm::pack2(__uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1])), scale2,
+                                 neg_lse22), a, b);
+            p[cc][i] = (P.debug_skip & 2) ? a : pm::ex2(a);
+            p[cc][i + 1] = (P.debug_skip & 2) ? b : pm::ex2(b);
+          }
+          if (diag) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 w;
-          w.x = pm::cvt2<T>(p[cc][u * 8 + 0], p[cc][u * 8 + 1]);
-          w.y = pm::cvt2<T>(p[cc][u * 8 + 2], p[cc][u * 8 + 3]);
-          w.z = pm::cvt2<T>(p[cc][u * 8 + 4], p[cc][u * 8 + 5]);
-          w.w = pm::cvt2<T>(p[cc][u * 8 + 6], p[cc][u * 8 + 7]);
-          *reinterpret_cast<uint4*>(pc + swz(r, (c % 2) * 4 + u)) = w;
+            for (int i = 0; i < 32; ++i)
+              if (nb * BKV + c * 32 + i > q_pos) p[cc][i] = 0.f;
+          }
+          uint8_t* pc = sP + (c / 2) * CHUNK_BYTES;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pm::cvt2<T>(p[cc][u * 8 + 0], p[cc][u * 8 + 1]);
+            w.y = pm::cvt2<T>(p[cc][u * 8 + 2], p[cc][u * 8 + 3]);
+            w.z = pm::cvt2<T>(p[cc][u * 8 + 4], p[cc][u * 8 + 5]);
+            w.w = pm::cvt2<T>(p[cc][u * 8 + 6], p[cc][u * 8 + 7]);
+            *reinterpret_cast<uint4*>(pc + swz(r, (c % 2) * 4 + u)) = w;
+          }
         }
       }
       tc_fence_before();
@@ -249,25 +283,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ---- dS once dP is complete
       if (!mbar_wait(&bars->dp_full, ph)) { atomicCAS(P.err, 0, 410); ok = false; break; }
       tc_fence_after();
+      {
+        uint32_t dv[NC][32];
 #pragma unroll
-      for (int cc = 0; cc < NC; ++cc) {
-        const int c = half * NC + cc;
-        uint32_t dv[32];
-        tmem_ld_32x32(tm_dp + lane_addr + c * 32, dv);
+        for (int cc = 0; cc < NC; ++cc) tmem_ld_32x32(tm_dp + lane_addr + (half * NC + cc) * 32, dv[cc]);
         tmem_ld_wait();
-        uint8_t* dc = sdS + (c / 2) * CHUNK_BYTES;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint32_t w[4];
+        for (int cc = 0; cc < NC; ++cc) {
+          const int c = half * NC + cc;
+          uint8_t* dc = sdS + (c / 2) * CHUNK_BYTES;
 #pragma unroll
-          for (int h2 = 0; h2 < 4; ++h2) {
-            const int i = u * 8 + h2 * 2;
-            float a, b;
-            pm::unpack2(pm::mul2(pm::add2(pm::pack2(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), neg_delta2),
-                                 pm::pack2(p[cc][i], p[cc][i + 1])), a, b);
-            w[h2] = pm::cvt2<T>(a, b);
+          for (int u = 0; u < 4; ++u) {
+            uint32_t w[4];
+#pragma unroll
+            for (int h2 = 0; h2 < 4; ++h2) {
+              const int i = u * 8 + h2 * 2;
+              float a, b;
+              pm::unpack2(pm::mul2(pm::add2(pm::pack2(__uint_as_float(dv[cc][i]), __uint_as_float(dv[cc][i + 1])),
+                                            neg_delta2), pm::pack2(p[cc][i], p[cc][i + 1])), a, b);
+              w[h2] = pm::cvt2<T>(a, b);
+            }
+            *reinterpret_cast<uint4*>(dc + swz(r, (c % 2) * 4 + u)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          *reinterpret_cast<uint4*>(dc + swz(r, (c % 2) * 4 + u)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       tc_fence_before();
@@ -275,21 +312,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_arrive(&bars->ds_full);
       if (!mbar_wait(&bars->dq_full, ph)) { atomicCAS(P.err, 0, 407); ok = false; break; }
       tc_fence_after();
-      float* dq_row = P.dq_acc + ((int64_t)(batch * P.S + q_pos) * P.Hq + head) * D;
-#pragma unroll 1
-      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tm_dq + lane_addr + c * 32, v);
+      // dQ tile -> fp32 staging (32-column slabs of [128 rows][128 B], 128B-swizzled); rows
+      // past the end of the sequence hold exact zeros (their P and dS are zero)
+      {
+        uint32_t v[D / 64][32];
+#pragma unroll
+        for (int cc = 0; cc < D / 64; ++cc) tmem_ld_32x32(tm_dq + lane_addr + (half * (D / 64) + cc) * 32, v[cc]);
         tmem_ld_wait();
-        if (valid && !(P.debug_skip & 1)) {
+        tc_fence_before();
+        mbar_arrive(&bars->s_free);                  // the S columns may be overwritten
+#pragma unroll
+        for (int cc = 0; cc < D / 64; ++cc) {
+          uint8_t* slab = sP + (half * (D / 64) + cc) * (BQ * 128);
 #pragma unroll
           for (int u = 0; u < 8; ++u)
-            red_add_v4(dq_row + c * 32 + u * 4, __uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]),
-                       __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3]));
+            *reinterpret_cast<uint4*>(slab + swz(r, u)) =
+                make_uint4(v[cc][u * 4], v[cc][u * 4 + 1], v[cc][u * 4 + 2], v[cc][u * 4 + 3]);
         }
       }
-      tc_fence_before();
-      mbar_arrive(&bars->s_free);
+      fence_proxy_async();
+      mbar_arrive(&bars->dqs_full);
     }
     if (ok && !mbar_wait(&bars->acc_full, 0)) { atomicCAS(P.err, 0, 408); ok = false; }
     if (ok) {

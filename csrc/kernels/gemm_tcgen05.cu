@@ -80,6 +80,7 @@ namespace ft {
 namespace gemm {
 
 // 2-D row-major tensor [outer, inner] with row stride ld (elements), 128B swizzle.
+// dtype: kBF16 / kF16 (2-byte elements) or kF32.
 int make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
               uint32_t box_inner, uint32_t box_outer, int dtype) {
   MapKey key{ptr, inner, outer, ld, box_inner, box_outer, dtype};
@@ -99,13 +100,16 @@ int make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer,
     cudaSetDevice(dev);
     cudaFree(nullptr);
   }
-  if (((uintptr_t)ptr & 15) || ((ld * 2) & 15)) return -101;
+  const uint64_t esize = dtype == kF32 ? 4 : 2;
+  if (((uintptr_t)ptr & 15) || ((ld * esize) & 15)) return -101;
   cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld * 2};
+  cuuint64_t strides[1] = {ld * esize};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                  2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const CUtensorMapDataType dt = dtype == kF32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
