@@ -171,6 +171,7 @@ class EngineConfig:
             raise ValueError("engine.nonlayer_optimizer_device must be auto|gpu|cpu")
         self.gradient_clipping = float(section.get(D.GRAD_CLIP, D.GRAD_CLIP_DEFAULT))
         self.watchdog_seconds = float(section.get(D.WATCHDOG_SECONDS, D.WATCHDOG_SECONDS_DEFAULT))
+        self.nvtx = bool(section.get(D.NVTX, D.NVTX_DEFAULT))
         self.fused_blocks = int(section.get(D.FUSED_BLOCKS, D.FUSED_BLOCKS_DEFAULT))
 
     def to_dict(self):

@@ -110,6 +110,8 @@ NONLAYER_OPTIMIZER_DEVICE_DEFAULT = "auto"
 GRAD_CLIP = "gradient_clipping"            # 0 disables
 GRAD_CLIP_DEFAULT = 0.0
 WATCHDOG_SECONDS = "watchdog_seconds"      # 0 disables the step watchdog
+NVTX = "nvtx"                              # NVTX range per (phase, unit, micro-batch)
+NVTX_DEFAULT = False
 WATCHDOG_SECONDS_DEFAULT = 0.0
 
 PAGE_SIZE = 4096                           # O_DIRECT alignment of every swap piece

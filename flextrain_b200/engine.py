@@ -88,6 +88,7 @@ class FlexTrainEngine:
         self.global_steps = 0
         self.skipped_steps = 0
         self.timer = StepTimer()
+        self._nvtx = bool(cfg.engine.nvtx) and self.device.type == "cuda"
         self._last_overflow = False
         self._status: Dict[str, Any] = {"last_step_seconds": None, "watchdog_tripped": False}
         self.heartbeat = Heartbeat()
@@ -184,7 +185,24 @@ class FlexTrainEngine:
         if backward:
             self.opts.pre_unit_backward(unit)
 
+    # NVTX ranges per (phase, unit, micro-batch) when ``engine.nvtx`` is set; they cost a
+    # Python call each, so they are off by default.
+    def _range_push(self, phase: str, task: LLMTask):
+        if self._nvtx:
+            torch.cuda.nvtx.range_push(f"{phase} u{task.unit} mb{task.micro_batch}")
+
+    def _range_pop(self):
+        if self._nvtx:
+            torch.cuda.nvtx.range_pop()
+
     def _conduct_forward(self, task: LLMTask, nxt: Optional[LLMTask]):
+        self._range_push("fwd", task)
+        try:
+            self._conduct_forward_impl(task, nxt)
+        finally:
+            self._range_pop()
+
+    def _conduct_forward_impl(self, task: LLMTask, nxt: Optional[LLMTask]):
         u, mb = task.unit, task.micro_batch
         ckpt = self.inter.ckpt
         if nxt is not None and nxt.unit > 0 and (nxt.unit, nxt.micro_batch) != (u + 1, mb):
@@ -236,6 +254,13 @@ class FlexTrainEngine:
         return None if x is None else x.grad
 
     def _conduct_backward(self, task: LLMTask, nxt: Optional[LLMTask]):
+        self._range_push("bwd", task)
+        try:
+            self._conduct_backward_impl(task, nxt)
+        finally:
+            self._range_pop()
+
+    def _conduct_backward_impl(self, task: LLMTask, nxt: Optional[LLMTask]):
         u, mb = task.unit, task.micro_batch
         ckpt, grads = self.inter.ckpt, self.inter.grad
         if nxt is not None:
@@ -347,6 +372,15 @@ class FlexTrainEngine:
         """Wait for every queued device and host task of this rank."""
         self.opts.wait_all()
         self.streams.synchronize()
+
+    def stats(self, reset: bool = False) -> Dict[str, Any]:
+        """Observability snapshot: bytes moved between tiers and over the fabric
+        since the last reset (host-side counters), allocation totals per tier,
+        step count and the last step's host wall time."""
+        from .memory import TRAFFIC, allocated_bytes
+        return {"traffic_bytes": TRAFFIC.snapshot(reset=reset), "allocated_bytes": allocated_bytes(),
+                "global_steps": self.global_steps, "skipped_steps": self.skipped_steps,
+                "last_step_seconds": self.timer.last}
 
     def health(self) -> Dict[str, Any]:
         """Status words of the runtime: pending host updates, traffic counters,

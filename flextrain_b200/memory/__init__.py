@@ -248,6 +248,41 @@ def allocate_memory_chunks(numel: int, chunks, dtype: torch.dtype, device,
     return carve(0, 0)
 
 
+class _Traffic:
+    """Bytes moved between tiers since the last ``reset`` (host-side counters:
+    ``h2d``, ``d2h``, ``d2d``, ``h2h`` copies, ``nvme_read`` / ``nvme_write``,
+    ``gather`` / ``reduce`` collective payloads)."""
+
+    KINDS = ("h2d", "d2h", "d2d", "h2h", "nvme_read", "nvme_write", "gather", "reduce")
+
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.bytes: Dict[str, int] = {k: 0 for k in self.KINDS}
+
+    def add(self, kind: str, nbytes: int):
+        with self.lock:
+            self.bytes[kind] = self.bytes.get(kind, 0) + int(nbytes)
+
+    def snapshot(self, reset: bool = False) -> Dict[str, int]:
+        with self.lock:
+            out = dict(self.bytes)
+            if reset:
+                for k in self.bytes:
+                    self.bytes[k] = 0
+        return out
+
+
+TRAFFIC = _Traffic()
+
+
+def tier_copy(dst: torch.Tensor, src: torch.Tensor, non_blocking: bool = True) -> torch.Tensor:
+    """``dst.copy_(src)`` that also books the bytes under the pair of tiers it
+    crosses (the engine's per-tier traffic counters)."""
+    kind = ("d" if src.is_cuda else "h") + "2" + ("d" if dst.is_cuda else "h")
+    TRAFFIC.add(kind, dst.numel() * dst.element_size())
+    return dst.copy_(src, non_blocking=non_blocking)
+
+
 def free_tensor(t: torch.Tensor, record_stream: bool = False):
     """Release ``t``'s storage while the Python object stays alive."""
     if record_stream and t.is_cuda:

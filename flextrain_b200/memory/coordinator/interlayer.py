@@ -26,7 +26,7 @@ import torch
 from ...config import get_flextrain_config
 from ...utils import distributed as dist
 from ...utils.device import DONE, Event, get_streams
-from .. import (FlexTrainDataID, FlexTrainDataType, allocate_memory, get_split_numels)
+from .. import (tier_copy, FlexTrainDataID, FlexTrainDataType, allocate_memory, get_split_numels)
 from ..nvme_swapper import get_nvme_swapper
 
 
@@ -125,27 +125,27 @@ class TieredTensorStore:
                 slot.gpu = slot.gpu if slot.gpu is not None else (
                     self._pool_gpu.pop() if self._pool_gpu else
                     allocate_memory(g, tensor.dtype, self.device))
-                slot.gpu.copy_(flat[:g], non_blocking=True)
+                tier_copy(slot.gpu, flat[:g])
             host_n = c + (n if (pin_to_dram or not n) else 0)
             if pin_to_dram and n:
                 # whole non-HBM part stays in DRAM
                 if slot.cpu is None or slot.cpu.numel() != c + n:
                     slot.cpu = allocate_memory(c + n, tensor.dtype, "cpu", True)
-                slot.cpu.copy_(flat[g:], non_blocking=True)
+                tier_copy(slot.cpu, flat[g:])
                 slot.nvme_id = None
             else:
                 if c:
                     if slot.cpu is None or slot.cpu.numel() != c:
                         slot.cpu = self._pool_cpu.pop() if self._pool_cpu else \
                             allocate_memory(c, tensor.dtype, "cpu", True)
-                    slot.cpu.copy_(flat[g:g + c], non_blocking=True)
+                    tier_copy(slot.cpu, flat[g:g + c])
                 if n:
                     i = self._stage_next
                     self._stage_next = (i + 1) % 2
                     if self._stage_busy[i] is not None:
                         self._stage_busy[i].wait()
                     stage = self._nvme_stage[i]
-                    stage.copy_(flat[g + c:], non_blocking=True)
+                    tier_copy(stage, flat[g + c:])
                     copied = st.d2h.record()
                     copied.synchronize()
                     slot.nvme_id = self._data_id(key)
@@ -188,11 +188,11 @@ class TieredTensorStore:
             st.h2d.wait(free_ev)
             st.h2d.wait(slot.stored)
             if g:
-                land[:g].copy_(slot.gpu, non_blocking=True)
+                tier_copy(land[:g], slot.gpu)
             if slot.cpu is not None:
-                land[g:g + slot.cpu.numel()].copy_(slot.cpu, non_blocking=True)
+                tier_copy(land[g:g + slot.cpu.numel()], slot.cpu)
             if stage is not None:
-                land[g + c:].copy_(stage, non_blocking=True)
+                tier_copy(land[g + c:], stage)
             self.bytes_h2d += (self._numel - g) * land.element_size()
             slot.ready = st.h2d.record()
         if stage is not None:

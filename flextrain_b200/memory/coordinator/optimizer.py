@@ -46,7 +46,7 @@ from ...param_group import GroupSegment, create_step_contexts, slice_segments
 from ...utils import distributed as dist
 from ...utils.device import DONE, Event, get_streams
 from ...utils.logging import rank0_logger
-from .. import (FlexTrainDataID, FlexTrainDataType, FutureHandle, allocate_memory,
+from .. import (tier_copy, FlexTrainDataID, FlexTrainDataType, FutureHandle, allocate_memory,
                 get_split_numels)
 from ..nvme_swapper import get_nvme_swapper
 from .parameter import get_para_coordinator
@@ -283,6 +283,9 @@ class FlexTrainOptsCoordinator:
             st.opt.wait(produced)
             shard = src[lo:hi]
             flag = self._flags[unit:unit + 1] if self.check_overflow else None
+            if self.world > 1:
+                from .. import TRAFFIC
+                TRAFFIC.add("reduce", (self.world - 1) * shard.numel() * shard.element_size())
             if self._fused and self._fused_reduce(unit, i, shard, step, grad_scale, flag, entry):
                 host_scale = 1.0                    # the kernel already unscaled what it handed over
             else:
@@ -293,10 +296,10 @@ class FlexTrainOptsCoordinator:
                 if og:
                     self._device_update(unit, shard, step, grad_scale, flag, i)
                 if entry is not None:
-                    entry.grad.copy_(shard[og:], non_blocking=True)
+                    tier_copy(entry.grad, shard[og:])
             if entry is not None:
                 if flag is not None:
-                    entry.flag.copy_(flag, non_blocking=True)
+                    tier_copy(entry.flag, flag)
                 self.bytes_d2h += self.host_numel * entry.grad.element_size()
             done = st.opt.record()
         self._buf_free[i] = done
@@ -340,9 +343,9 @@ class FlexTrainOptsCoordinator:
             if og:
                 self._device_update(unit, shard, step, 1.0, flag, buf_index)
             if entry is not None:
-                entry.grad.copy_(shard[og:], non_blocking=True)
+                tier_copy(entry.grad, shard[og:])
         elif og > g:
-            self._para.cpu_base(unit)[: og - g].copy_(stage[: og - g], non_blocking=True)
+            tier_copy(self._para.cpu_base(unit)[: og - g], stage[: og - g])
         return True
 
     def _reduce_scatter(self, shard: torch.Tensor, full: torch.Tensor):
@@ -370,7 +373,7 @@ class FlexTrainOptsCoordinator:
                                    grad_scale=grad_scale, skip_flag=flag)
         if og > g:
             # parameters updated on the device but resident in pinned DRAM
-            self._para.cpu_base(unit)[: og - g].copy_(stage[: og - g], non_blocking=True)
+            tier_copy(self._para.cpu_base(unit)[: og - g], stage[: og - g])
 
     # ---------------------------------------------------------- host update
     def _host_update(self, unit, entry: _PoolEntry, grads_ready: Event, step, grad_scale):

@@ -34,7 +34,7 @@ from ...config import get_flextrain_config
 from ...utils import distributed as dist
 from ...utils.device import DONE, Event, get_streams
 from ...utils.logging import rank0_logger
-from .. import (ContiguousParaGroup, FlexTrainDataID, FlexTrainDataType, Waitable,
+from .. import (tier_copy, ContiguousParaGroup, FlexTrainDataID, FlexTrainDataType, Waitable,
                 allocate_memory, get_split_numels, partition_aligned_numel)
 from ..nvme_swapper import get_nvme_swapper
 
@@ -263,11 +263,11 @@ class FlexTrainParaCoordinator:
             shard = buf[lo:hi]
             if g:
                 st.h2d.wait(self._gpu_base_ready.get(unit, DONE))
-                shard[:g].copy_(self._gpu_base[unit], non_blocking=True)
+                tier_copy(shard[:g], self._gpu_base[unit])
             if c:
-                shard[g:g + c].copy_(self._cpu_base[unit], non_blocking=True)
+                tier_copy(shard[g:g + c], self._cpu_base[unit])
             if n:
-                shard[g + c:].copy_(self._nvme_landing[land_idx], non_blocking=True)
+                tier_copy(shard[g + c:], self._nvme_landing[land_idx])
                 self._landing_busy[land_idx] = st.h2d.record()
             if self.world > 1:
                 self._all_gather(buf, shard, idx)
@@ -275,6 +275,9 @@ class FlexTrainParaCoordinator:
         self._inflight[unit] = (idx, ready)
 
     def _all_gather(self, buf: torch.Tensor, shard: torch.Tensor, idx: int = -1):
+        if self.world > 1:
+            from .. import TRAFFIC
+            TRAFFIC.add("gather", (self.world - 1) * self.shard_numel * self.itemsize)
         if self._peer_gather and idx >= 0:
             from ...parallel import fused
             page = self._flag_page

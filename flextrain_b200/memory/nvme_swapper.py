@@ -189,10 +189,18 @@ class AsyncNVMeSwapper:
         handle.wait()
         return handle
 
+    @staticmethod
+    def _count(kind, tensors):
+        from . import TRAFFIC
+        ts = [tensors] if isinstance(tensors, torch.Tensor) else list(tensors)
+        TRAFFIC.add(kind, sum(t.numel() * t.element_size() for t in ts))
+
     def swap_out(self, data_ids, tensors, async_op: bool = False):
+        self._count("nvme_write", tensors)
         return self._swap(data_ids, tensors, True, async_op)
 
     def swap_in(self, data_ids, tensors, async_op: bool = False):
+        self._count("nvme_read", tensors)
         return self._swap(data_ids, tensors, False, async_op)
 
     def synchronize(self):

@@ -57,3 +57,35 @@ def test_engine_shims_and_health(fresh_runtime):
     assert h["global_steps"] == 2 and h["skipped_steps"] == 0 and h["last_step_seconds"] > 0
     assert eng.train() is eng and eng.eval() is eng
     eng.shutdown()
+
+
+def test_engine_stats_counts_tier_traffic():
+    """``engine.stats()`` books the bytes that cross tiers: with parameters and
+    optimizer state split over DRAM and NVMe every step must move both."""
+    import tempfile
+    import torch
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine, reset_runtime
+    reset_runtime()
+    cfg = preset("tiny", num_layers=3, hidden=64, num_heads=4, ffn=128, vocab=128, seq_len=16)
+    data = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1))
+    with tempfile.TemporaryDirectory() as tmp:
+        ft_cfg = {"batch_size": 2, "micro_batch_size": 2,
+                  "mixed_precision": {"device_dtype": "fp32", "dynamic_loss_scaling": False},
+                  "split_ratio": {"parameter": [0.0, 0.5], "optimizer": [0.0, 0.5],
+                                  "checkpoint": [0.0, 1.0], "gradient": [0.0, 1.0]},
+                  "nvme_swap": {"swap_dir": tmp}}
+        model, opt, eng = build_llama_engine(cfg, ft_cfg, lambda: (data[:, :-1], data[:, 1:]),
+                                             init_device="cpu", backend="gloo")
+        eng.stats(reset=True)
+        eng.train_iteration()
+        eng.synchronize()
+        st = eng.stats()
+        tr = st["traffic_bytes"]
+        assert tr["nvme_read"] > 0 and tr["nvme_write"] > 0
+        assert tr["h2h"] > 0                       # CPU run: tier copies are host to host
+        assert st["global_steps"] == 1 and st["last_step_seconds"] > 0
+        assert eng.stats(reset=True)["traffic_bytes"]["nvme_read"] == tr["nvme_read"]
+        assert eng.stats()["traffic_bytes"]["nvme_read"] == 0
+        eng.shutdown()
+    reset_runtime()
