@@ -14,7 +14,7 @@
 // Unlike that kernel the half-precision copy honours bf16 (the reference
 // always emits fp16 bit patterns, simd.h:33-37).
 #include <immintrin.h>
-#include <omp.h>
+#include "omp_compat.h"
 
 #include <cmath>
 #include <cstdint>

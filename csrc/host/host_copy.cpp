@@ -13,7 +13,7 @@
 // (an 8/4/1-way unrolled float copy) and deepspeed_pin_tensor.cpp:23-61
 // (posix_memalign + mlock behind at::from_blob).  Everything returns status codes.
 #include <immintrin.h>
-#include <omp.h>
+#include "omp_compat.h"
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
