@@ -48,6 +48,8 @@ def parse_args():
     p.add_argument("--unit-buffers", type=int, default=3)
     p.add_argument("--alpha", type=float, default=0.25)
     p.add_argument("--split", default="", help="JSON split_ratio override")
+    p.add_argument("--phases", action="store_true",
+                   help="also report the device time of forward / backward / finish of the last step")
     return p.parse_args()
 
 
@@ -144,6 +146,18 @@ def run_ours(args):
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
+    # A run that stops making progress dumps every thread's Python stack and exits instead
+    # of sitting in the launcher until someone kills it (re-armed before every step).
+    import faulthandler
+    stall_init = int(os.environ.get("FLEXTRAIN_BENCH_INIT_LIMIT", "1500"))
+    stall_step = int(os.environ.get("FLEXTRAIN_BENCH_STEP_LIMIT", "600"))
+
+    def arm(seconds):
+        faulthandler.cancel_dump_traceback_later()
+        if seconds > 0:
+            faulthandler.dump_traceback_later(seconds, exit=True)
+
+    arm(stall_init)
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             raise SystemExit(f"--gpus {args.gpus} needs a torch.distributed.run launch with "
@@ -164,7 +178,7 @@ def run_ours(args):
            "mixed_precision": {"device_dtype": "bf16", "gradacc_dtype": "fp32", "master_dtype": "fp32",
                                "dynamic_loss_scaling": False, "loss_scale": 1.0},
            "nvme_swap": {"swap_dir": os.path.join(tempfile.gettempdir(), "ft_b200_swap")},
-           "engine": {"num_unit_buffers": args.unit_buffers}}
+           "engine": {"num_unit_buffers": args.unit_buffers, "phase_timing": bool(args.phases)}}
     init_flextrain_config(cfg, log=rank == 0)
     t_init = time.time()
     torch.manual_seed(0)
@@ -207,6 +221,7 @@ def run_ours(args):
         d2h = 0
         last = None
         for _ in range(steps):
+            arm(stall_step)
             losses = engine.train_iteration()
             if read_loss:
                 last = [float(l.detach().float().item()) for l in losses]
@@ -219,6 +234,7 @@ def run_ours(args):
         return ms / steps, d2h / max(steps, 1), last
 
     for _ in range(args.warmup):
+        arm(stall_step)
         engine.train_iteration()
     engine.synchronize()
 
@@ -242,7 +258,10 @@ def run_ours(args):
     tps = tokens / (ms_dev / 1e3)
     fpt = llama_flops_per_token(mcfg.num_layers, mcfg.hidden, mcfg.ffn, mcfg.vocab, seq,
                                 mcfg.num_heads, mcfg.num_kv_heads, recompute=False)
+    arm(stall_step)
     health = engine.health()
+    phase_ms = engine.stats()["phase_ms"] if args.phases else None
+    traffic = engine.stats()["traffic_bytes"]
     engine.shutdown()
     if rank == 0:
         out = {"metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -258,8 +277,13 @@ def run_ours(args):
                           "flops": "model FLOPs, 6*N*tokens + attention, recompute not counted",
                           "larger_models_skipped": skipped},
                "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
-               "init_seconds": init_s, "skipped_steps": health["skipped_steps"]}
+               "init_seconds": init_s, "skipped_steps": health["skipped_steps"],
+               "error_words": {"gemm": health.get("gemm_error_word"), "comm": health.get("comm_error_word")}}
+        if phase_ms is not None:
+            out["phase_ms_last_step"] = phase_ms
+            out["traffic_bytes_total"] = traffic
         print(json.dumps(out), flush=True)
+    arm(0)
 
 
 # ---------------------------------------------------------- reference arm

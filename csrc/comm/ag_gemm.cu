@@ -32,16 +32,22 @@ using namespace ft;
 using namespace ft::gemm;
 
 constexpr int kReadyWords = 8192;
+// one "copiers finished" counter per call site (indexed by the start slot), so gathers issued
+// from different streams never count each other's CTAs
+constexpr int kCounters = 64;
 
 uint32_t* g_ready[16] = {nullptr};
 unsigned int* g_counter[16] = {nullptr};
 long long g_spin_budget = 0;
+int g_gather_lag = 1;   // see ft_gather_set_lag
 
 int ensure_state(int dev) {
   if (!g_ready[dev]) {
-    if (cudaMalloc(&g_ready[dev], kReadyWords * sizeof(uint32_t)) != cudaSuccess) return -1;
-    if (cudaMalloc(&g_counter[dev], sizeof(unsigned int)) != cudaSuccess) return -1;
-    cudaMemset(g_counter[dev], 0, sizeof(unsigned int));
+    // first half: ft_ag_gemm (reset per call); second half: ft_peer_gather (write-only there)
+    if (cudaMalloc(&g_ready[dev], 2 * kReadyWords * sizeof(uint32_t)) != cudaSuccess) return -1;
+    cudaMemset(g_ready[dev], 0, 2 * kReadyWords * sizeof(uint32_t));
+    if (cudaMalloc(&g_counter[dev], kCounters * sizeof(unsigned int)) != cudaSuccess) return -1;
+    cudaMemset(g_counter[dev], 0, kCounters * sizeof(unsigned int));
   }
   return 0;
 }
@@ -78,7 +84,8 @@ int fill_gather(GatherArgs& G, int world, int rank, const void* const* w_ptrs, u
   G.spin_budget = g_spin_budget > 0 ? g_spin_budget : peer::kSpinCycles;
   G.num_copiers = num_copiers;
   G.ready = g_ready[dev];
-  G.block_counter = g_counter[dev];
+  G.lagged = g_gather_lag;
+  G.block_counter = g_counter[dev] + (start_slot & (kCounters - 1));
   return 0;
 }
 
@@ -120,6 +127,10 @@ extern "C" {
 void ft_ag_gemm_set_pair(int on) { g_ag_pair = on ? 1 : 0; }
 
 void ft_ag_set_spin_budget(long long cycles) { g_spin_budget = cycles; }
+
+// Completion signalling of the copy role for later ft_ag_gemm / ft_peer_gather calls:
+// 1 = lagged by NSTAGE-1 store groups (default), 0 = one store at a time.
+void ft_gather_set_lag(int on) { g_gather_lag = on ? 1 : 0; }
 
 // y[M,N] = x[M,K] * W^T with W gathered from its row shards inside the same launch.
 // w_ptrs[r]: this process's mapping of rank r's [N,K] buffer (16-bit dtype `ab_dtype`).
@@ -215,6 +226,7 @@ int ft_peer_gather(int world, int rank, const void* const* buf_ptrs, uint32_t* c
   if (num_copiers < 1) num_copiers = 1;
   GatherArgs G;
   fill_gather(G, world, rank, buf_ptrs, flags, seq, start_slot, done_slot, num_copiers, dev);
+  G.ready = g_ready[dev] + kReadyWords;
   G.shard_bytes = shard_bytes;
   G.block_bytes = (shard_bytes * world + kReadyWords - 1) / kReadyWords;
   if (G.block_bytes < PG_CHUNK) G.block_bytes = PG_CHUNK;

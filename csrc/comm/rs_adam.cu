@@ -185,13 +185,17 @@ __global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ Rs
 }
 
 long long g_spin_budget = 0;   // 0: default
+// One "CTAs finished" counter per call site (indexed by the call's start slot): the unit
+// reduce-scatter on the optimizer stream and the non-layerwise all-reduce on the compute
+// stream can be in flight at the same time and must not count each other's CTAs.
+constexpr int kCounters = 64;
 unsigned int* g_counter[16] = {nullptr};
 int* g_err[16] = {nullptr};
 
 int ensure_state(int dev) {
   if (!g_counter[dev]) {
-    if (cudaMalloc(&g_counter[dev], sizeof(unsigned int)) != cudaSuccess) return -1;
-    cudaMemset(g_counter[dev], 0, sizeof(unsigned int));
+    if (cudaMalloc(&g_counter[dev], kCounters * sizeof(unsigned int)) != cudaSuccess) return -1;
+    cudaMemset(g_counter[dev], 0, kCounters * sizeof(unsigned int));
     if (cudaMalloc(&g_err[dev], sizeof(int)) != cudaSuccess) return -1;
     cudaMemset(g_err[dev], 0, sizeof(int));
   }
@@ -236,7 +240,7 @@ static int rs_adam_impl(int world, int rank, const void* const* grads, uint32_t*
   P.seq = seq;
   P.start_slot = start_slot;
   P.done_slot = done_slot;
-  P.block_counter = g_counter[dev];
+  P.block_counter = g_counter[dev] + (start_slot & (kCounters - 1));
   P.err = g_err[dev];
   P.spin_budget = g_spin_budget > 0 ? g_spin_budget : kSpinCycles;
   P.reduced_out = reduced_out;

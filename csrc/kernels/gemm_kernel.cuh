@@ -43,6 +43,8 @@ struct GatherArgs {
   int num_copiers;
   uint32_t* ready;
   unsigned int* block_counter;
+  int lagged;              // 1: announce a chunk NSTAGE-1 store groups late (keeps the copy stream
+                           //    full); 0: wait for each store before the next (the first form)
 };
 
 constexpr int COPY_CHUNK = 32768;
@@ -192,43 +194,77 @@ __device__ __forceinline__ void gather_role(const GatherArgs& G, uint8_t* smem, 
       mbar_expect_tx(&full_bars[s], bytes);
       bulk_load(smem + s * STRIDE, src, bytes, &full_bars[s]);
     }
-    // Stage reuse only needs the previous store to have *read* shared memory; a chunk is
-    // announced once its store group has fully completed, which is checked LAG groups late
-    // so that the completion latency never stalls the copy stream.
-    constexpr int LAG = NSTAGE - 1;
-    int pending[NSTAGE];
-    for (int64_t q = 0; q < n; ++q) {
-      const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
-      locate(q, src, dst, nb, bytes);
-      const int s = (int)(q % NSTAGE);
-      if (!mbar_wait(&full_bars[s], phase[s])) { atomicCAS(err, 0, 202); break; }
-      phase[s] ^= 1;
-      bulk_store(dst, smem + s * STRIDE, bytes);
-      bulk_commit();
-      pending[s] = nb;
-      asm volatile("cp.async.bulk.wait_group %0;" ::"n"(LAG) : "memory");
-      if (q >= LAG) {                         // chunk q - LAG is in local memory
+    if (G.lagged) {
+      // Stage reuse only needs the previous store to have *read* shared memory; a chunk is
+      // announced once its store group has fully completed, which is checked LAG groups late
+      // so that the completion latency never stalls the copy stream.
+      constexpr int LAG = NSTAGE - 1;
+      int pending[NSTAGE];
+      for (int64_t q = 0; q < n; ++q) {
+        const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
+        locate(q, src, dst, nb, bytes);
+        const int s = (int)(q % NSTAGE);
+        if (!mbar_wait(&full_bars[s], phase[s])) { atomicCAS(err, 0, 202); break; }
+        phase[s] ^= 1;
+        bulk_store(dst, smem + s * STRIDE, bytes);
+        bulk_commit();
+        pending[s] = nb;
+        asm volatile("cp.async.bulk.wait_group %0;" ::"n"(LAG) : "memory");
+        if (q >= LAG) {                         // chunk q - LAG is in local memory
+          fence_proxy_async_all();
+          __threadfence();
+          red_release_add(G.ready + pending[(int)((q - LAG) % NSTAGE)], 1u);
+        }
+        const int64_t nq = q + NSTAGE - 1;
+        if (nq < n) {
+          const uint8_t* src2; uint8_t* dst2; int nb2; uint32_t bytes2;
+          locate(nq, src2, dst2, nb2, bytes2);
+          const int s2 = (int)(nq % NSTAGE);    // stage of chunk q - 1
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          mbar_expect_tx(&full_bars[s2], bytes2);
+          bulk_load(smem + s2 * STRIDE, src2, bytes2, &full_bars[s2]);
+        }
+      }
+      bulk_wait_all();
+      fence_proxy_async_all();
+      __threadfence();
+      for (int64_t q = (n > LAG ? n - LAG : 0); q < n; ++q) {
+        const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
+        locate(q, src, dst, nb, bytes);
+        red_release_add(G.ready + nb, 1u);
+      }
+    } else {
+      int prev_nb = -1;
+      for (int64_t q = 0; q < n; ++q) {
+        const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
+        locate(q, src, dst, nb, bytes);
+        const int s = (int)(q % NSTAGE);
+        if (!mbar_wait(&full_bars[s], phase[s])) { atomicCAS(err, 0, 202); break; }
+        phase[s] ^= 1;
+        bulk_store(dst, smem + s * STRIDE, bytes);
+        bulk_commit();
+        bulk_wait_all_but_1();                  // every chunk before this one is in local memory
+        if (q >= 1) {
+          fence_proxy_async_all();
+          __threadfence();
+          red_release_add(G.ready + prev_nb, 1u);
+        }
+        prev_nb = nb;
+        const int64_t nq = q + NSTAGE - 1;
+        if (nq < n) {
+          const uint8_t* src2; uint8_t* dst2; int nb2; uint32_t bytes2;
+          locate(nq, src2, dst2, nb2, bytes2);
+          const int s2 = (int)(nq % NSTAGE);    // stage of chunk q - 1, whose store has completed
+          mbar_expect_tx(&full_bars[s2], bytes2);
+          bulk_load(smem + s2 * STRIDE, src2, bytes2, &full_bars[s2]);
+        }
+      }
+      bulk_wait_all();
+      if (prev_nb >= 0) {
         fence_proxy_async_all();
         __threadfence();
-        red_release_add(G.ready + pending[(int)((q - LAG) % NSTAGE)], 1u);
+        red_release_add(G.ready + prev_nb, 1u);
       }
-      const int64_t nq = q + NSTAGE - 1;
-      if (nq < n) {
-        const uint8_t* src2; uint8_t* dst2; int nb2; uint32_t bytes2;
-        locate(nq, src2, dst2, nb2, bytes2);
-        const int s2 = (int)(nq % NSTAGE);    // stage of chunk q - 1
-        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        mbar_expect_tx(&full_bars[s2], bytes2);
-        bulk_load(smem + s2 * STRIDE, src2, bytes2, &full_bars[s2]);
-      }
-    }
-    bulk_wait_all();
-    fence_proxy_async_all();
-    __threadfence();
-    for (int64_t q = (n > LAG ? n - LAG : 0); q < n; ++q) {
-      const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
-      locate(q, src, dst, nb, bytes);
-      red_release_add(G.ready + nb, 1u);
     }
   }
   // end barrier: the last copier tells the peers that this rank reads their shards no more

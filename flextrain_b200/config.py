@@ -172,10 +172,26 @@ class EngineConfig:
         self.gradient_clipping = float(section.get(D.GRAD_CLIP, D.GRAD_CLIP_DEFAULT))
         self.watchdog_seconds = float(section.get(D.WATCHDOG_SECONDS, D.WATCHDOG_SECONDS_DEFAULT))
         self.nvtx = bool(section.get(D.NVTX, D.NVTX_DEFAULT))
-        self.fused_blocks = int(section.get(D.FUSED_BLOCKS, D.FUSED_BLOCKS_DEFAULT))
+        self.phase_timing = bool(section.get(D.PHASE_TIMING, D.PHASE_TIMING_DEFAULT))
+        self.fused_blocks_setting = int(section.get(D.FUSED_BLOCKS, D.FUSED_BLOCKS_DEFAULT))
+        self.fused_nonlayer = section.get(D.FUSED_NONLAYER, D.FUSED_NONLAYER_DEFAULT)
+        self.gather_lag = section.get(D.GATHER_LAG, D.GATHER_LAG_DEFAULT)
+        for key, val in ((D.FUSED_NONLAYER, self.fused_nonlayer), (D.GATHER_LAG, self.gather_lag)):
+            if val not in ("auto", True, False):
+                raise ValueError(f"engine.{key} must be 'auto', true or false")
+
+    @property
+    def fused_blocks(self) -> int:
+        """CTAs of the fused collective kernels.  Unset (0): 148 on up to 2 ranks,
+        64 above - the grid each world size has been run with."""
+        if self.fused_blocks_setting > 0:
+            return self.fused_blocks_setting
+        import os
+        world = int(os.environ.get("WORLD_SIZE", "1") or 1)
+        return 148 if world <= 2 else 64
 
     def to_dict(self):
-        return dict(vars(self))
+        return dict(vars(self), fused_blocks=self.fused_blocks)
 
     def __repr__(self):
         return f"EngineConfig({self.to_dict()})"

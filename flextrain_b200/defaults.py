@@ -97,8 +97,12 @@ TORCH_DISTRIBUTED_INIT_METHOD_DEFAULT = "env://"
 ENGINE = "engine"
 FUSED_COLLECTIVES = "fused_collectives"    # peer-memory kernels instead of NCCL
 FUSED_COLLECTIVES_DEFAULT = "auto"         # "auto" | True | False
+FUSED_NONLAYER = "fused_nonlayer"          # fused all-reduce + sharded Adam for non-layerwise params
+FUSED_NONLAYER_DEFAULT = "auto"            # "auto": on up to 2 ranks (the sizes it was validated on)
+GATHER_LAG = "gather_lag"                  # lagged completion signalling in the peer gather
+GATHER_LAG_DEFAULT = "auto"                # "auto": on up to 2 ranks
 FUSED_BLOCKS = "fused_blocks"              # CTAs of the fused collective kernels
-FUSED_BLOCKS_DEFAULT = 148
+FUSED_BLOCKS_DEFAULT = 0                   # 0: 148 up to 2 ranks, 64 above (the sizes each was run on)
 NUM_UNIT_BUFFERS = "num_unit_buffers"      # HBM unit buffers in the gather ring
 NUM_UNIT_BUFFERS_DEFAULT = 2
 STRICT_OVERFLOW = "strict_overflow"        # hold every update until the step's
@@ -112,6 +116,8 @@ GRAD_CLIP_DEFAULT = 0.0
 WATCHDOG_SECONDS = "watchdog_seconds"      # 0 disables the step watchdog
 NVTX = "nvtx"                              # NVTX range per (phase, unit, micro-batch)
 NVTX_DEFAULT = False
+PHASE_TIMING = "phase_timing"              # CUDA events at the phase boundaries of a step
+PHASE_TIMING_DEFAULT = False
 WATCHDOG_SECONDS_DEFAULT = 0.0
 
 PAGE_SIZE = 4096                           # O_DIRECT alignment of every swap piece

@@ -89,6 +89,8 @@ class FlexTrainEngine:
         self.skipped_steps = 0
         self.timer = StepTimer()
         self._nvtx = bool(cfg.engine.nvtx) and self.device.type == "cuda"
+        self._phase_timing = bool(cfg.engine.phase_timing) and self.device.type == "cuda"
+        self._phase_events = []          # [(name, event)] of the last step
         self._last_overflow = False
         self._status: Dict[str, Any] = {"last_step_seconds": None, "watchdog_tripped": False}
         self.heartbeat = Heartbeat()
@@ -316,6 +318,8 @@ class FlexTrainEngine:
     def _train_iteration(self, cfg):
         self.timer.start_step()
         self._reset_context()
+        self._phase_events = []
+        self._mark_phase("start")
         self.opts.prune_pending()
         fwd, bwd = self.scheduler.forward_tasks, self.scheduler.backward_tasks
         self.para.submit_gather(fwd[0].unit if fwd else bwd[0].unit)
@@ -329,6 +333,7 @@ class FlexTrainEngine:
                 prev_unit = task.unit
             self._conduct_forward(task, nxt)
 
+        self._mark_phase("forward")
         self.optimizer.update_states()
         for i, task in enumerate(bwd):
             nxt = bwd[i + 1] if i + 1 < len(bwd) else None
@@ -340,8 +345,10 @@ class FlexTrainEngine:
             if nxt is None or nxt.unit != task.unit:
                 self.opts.post_unit_backward(task.unit)
         self.para.release(prev_unit)
+        self._mark_phase("backward")
 
         overflow = self._finish_step()
+        self._mark_phase("finish")
         self.global_steps += 1
         if overflow:
             self.skipped_steps += 1
@@ -352,6 +359,26 @@ class FlexTrainEngine:
             from .auto_config import system_auto_config
             system_auto_config(self)
         return list(self._loss_results)
+
+    def _mark_phase(self, name: str):
+        """With ``engine.phase_timing``: record an event on the compute stream at a
+        phase boundary (``stats()`` turns consecutive pairs into milliseconds)."""
+        if self._phase_timing:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream())
+            self._phase_events.append((name, ev))
+
+    def phase_times_ms(self) -> Dict[str, float]:
+        """Device time of the last step's phases on the compute stream: forward,
+        backward (recompute included) and finish (waits for the optimizer stream
+        and the host updates that the step needs, non-layerwise update)."""
+        if len(self._phase_events) < 2:
+            return {}
+        self._phase_events[-1][1].synchronize()
+        out = {}
+        for (_, a), (name, b) in zip(self._phase_events[:-1], self._phase_events[1:]):
+            out[name] = a.elapsed_time(b)
+        return out
 
     def _finish_step(self) -> bool:
         grad_scale = 1.0 / float(self.loss_scale)
@@ -380,7 +407,7 @@ class FlexTrainEngine:
         from .memory import TRAFFIC, allocated_bytes
         return {"traffic_bytes": TRAFFIC.snapshot(reset=reset), "allocated_bytes": allocated_bytes(),
                 "global_steps": self.global_steps, "skipped_steps": self.skipped_steps,
-                "last_step_seconds": self.timer.last}
+                "last_step_seconds": self.timer.last, "phase_ms": self.phase_times_ms()}
 
     def health(self) -> Dict[str, Any]:
         """Status words of the runtime: pending host updates, traffic counters,

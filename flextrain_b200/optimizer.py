@@ -217,6 +217,11 @@ class FlexTrainOptimizer:
         want = self._cfg.engine.fused_collectives
         if want is False or self.device.type != "cuda" or not self._nl_on_device:
             return False
+        nl = self._cfg.engine.fused_nonlayer
+        # "auto": the world sizes this path has been run on (1 and 2 ranks); larger
+        # worlds keep the NCCL all-reduce + replicated device Adam unless asked
+        if nl is False or (nl == "auto" and dist.get_world_size() > 2):
+            return False
         from .ops.adam import FlexTrainAdam
         from .parallel.fused import segments_aligned
         from .parallel.symm_mem import peer_access_available
