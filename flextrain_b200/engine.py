@@ -90,6 +90,8 @@ class FlexTrainEngine:
         self.timer = StepTimer()
         self._nvtx = bool(cfg.engine.nvtx) and self.device.type == "cuda"
         self._phase_timing = bool(cfg.engine.phase_timing) and self.device.type == "cuda"
+        import os as _os
+        self._trace_on = bool(_os.environ.get("FLEXTRAIN_TRACE"))
         self._phase_events = []          # [(name, event)] of the last step
         self._last_overflow = False
         self._status: Dict[str, Any] = {"last_step_seconds": None, "watchdog_tripped": False}
@@ -177,8 +179,20 @@ class FlexTrainEngine:
             return retrieve_tensor(out)
         return other_unit
 
+    def _trace(self, what: str):
+        """With the environment variable FLEXTRAIN_TRACE set: one host-side line per
+        scheduling event (rank, step, seconds since the step began) on stderr, so a run
+        that stops shows where every rank stood.  Costs nothing when unset."""
+        if self._trace_on:
+            import sys
+            import time
+            t0 = getattr(self, "_trace_t0", None) or time.monotonic()
+            print(f"[ft-trace r{dist.get_rank()} s{self.global_steps} +{time.monotonic() - t0:8.3f}] {what}",
+                  file=sys.stderr, flush=True)
+
     def _enter_unit(self, unit: int, prev_unit: Optional[int], next_unit: Optional[int],
                     backward: bool):
+        self._trace(f"enter unit {unit} ({'bwd' if backward else 'fwd'}), prefetch {next_unit}")
         if prev_unit is not None and prev_unit != unit:
             self.para.release(prev_unit, keep=True)
         self.para.acquire(unit)
@@ -319,6 +333,10 @@ class FlexTrainEngine:
         self.timer.start_step()
         self._reset_context()
         self._phase_events = []
+        if self._trace_on:
+            import time
+            self._trace_t0 = time.monotonic()
+            self._trace("step begins")
         self._mark_phase("start")
         self.opts.prune_pending()
         fwd, bwd = self.scheduler.forward_tasks, self.scheduler.backward_tasks
@@ -334,6 +352,7 @@ class FlexTrainEngine:
             self._conduct_forward(task, nxt)
 
         self._mark_phase("forward")
+        self._trace("forward launched")
         self.optimizer.update_states()
         for i, task in enumerate(bwd):
             nxt = bwd[i + 1] if i + 1 < len(bwd) else None
@@ -346,9 +365,11 @@ class FlexTrainEngine:
                 self.opts.post_unit_backward(task.unit)
         self.para.release(prev_unit)
         self._mark_phase("backward")
+        self._trace("backward launched")
 
         overflow = self._finish_step()
         self._mark_phase("finish")
+        self._trace("finish launched")
         self.global_steps += 1
         if overflow:
             self.skipped_steps += 1
