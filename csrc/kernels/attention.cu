@@ -7,6 +7,7 @@
 #include "attention_bwd.cuh"
 #include "attention_fwd2.cuh"
 #include "attention_fwd3.cuh"
+#include "attention_fwd4.cuh"
 #include "gemm_host.h"
 
 namespace {
@@ -58,13 +59,28 @@ int launch_fwd3(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   return 0;
 }
 
+// Fourth generation (two threads per score row); not yet run on a GPU, never the default.
+template <typename T, int D>
+int launch_fwd4(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
+                cudaStream_t s) {
+  auto kern = attn_fwd4_kernel<T, D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd4Smem<D>::BYTES);
+    configured = true;
+  }
+  const int num_pairs = ((P.S + BQ - 1) / BQ + 1) / 2;
+  kern<<<P.B * P.Hq * num_pairs, F4_THREADS, Fwd4Smem<D>::BYTES, s>>>(tq, tk, tv, P);
+  return 0;
+}
+
 int g_fwd_version = -1;   // -1: read FLEXTRAIN_ATTN_FWD on first use (default 2, the fastest measured)
 
 int fwd_version() {
   if (g_fwd_version < 0) {
     const char* e = getenv("FLEXTRAIN_ATTN_FWD");
     g_fwd_version = e ? atoi(e) : 2;
-    if (g_fwd_version < 1 || g_fwd_version > 3) g_fwd_version = 2;
+    if (g_fwd_version < 1 || g_fwd_version > 4) g_fwd_version = 2;
   }
   return g_fwd_version;
 }
@@ -74,8 +90,9 @@ int launch_fwd_any(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorM
                    cudaStream_t s) {
   switch (fwd_version()) {
     case 1: return launch_fwd<T, D>(tq, tk, tv, P, s);
-    case 2: return launch_fwd2<T, D>(tq, tk, tv, P, s);
-    default: return launch_fwd3<T, D>(tq, tk, tv, P, s);
+    case 3: return launch_fwd3<T, D>(tq, tk, tv, P, s);
+    case 4: return launch_fwd4<T, D>(tq, tk, tv, P, s);
+    default: return launch_fwd2<T, D>(tq, tk, tv, P, s);
   }
 }
 
@@ -112,8 +129,8 @@ void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_strid
 
 extern "C" {
 
-// Selects the forward kernel generation for later ft_attn_fwd calls (1, 2 or 3).
-void ft_attn_set_fwd_version(int v) { g_fwd_version = (v >= 1 && v <= 3) ? v : 2; }
+// Selects the forward kernel generation for later ft_attn_fwd calls (1 to 4; 2 is the default).
+void ft_attn_set_fwd_version(int v) { g_fwd_version = (v >= 1 && v <= 4) ? v : 2; }
 
 // o[B,S,Hq,D], lse[B,Hq,S] <- causal attention of q[B,S,Hq,D], k/v[B,S,Hkv,D].
 // *_stride: elements between consecutive tokens of that tensor.  D in {64, 128}.

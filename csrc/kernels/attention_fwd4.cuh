@@ -1,0 +1,302 @@
+// Causal grouped-query flash attention, forward, fourth generation (experimental).
+//
+// attention_fwd2.cuh with TWO threads per score row: each query tile has eight softmax
+// warps instead of four, warps w and w+4 share the same 32 rows and own the score
+// columns [0,64) and [64,128).  Per K/V block the two threads of a row exchange
+// their partial row maximum (and, at the end, their partial row sums) through shared
+// memory and a 64-thread named barrier; everything else (P and O in tensor memory,
+// lazy rescale, packed fp32 math, MMA order) is unchanged.  The point is latency:
+// the softmax of a tile is the longest link of the per-block dependency chain, and
+// halving the work per thread while doubling the warps per scheduler shortens it.
+// Not yet run on a GPU; selected only by ft_attn_set_fwd_version(4).
+#pragma once
+#include "attention_fwd2.cuh"
+
+namespace ft {
+namespace attn {
+
+constexpr int F4_THREADS = 576;                     // TMA, MMA, 2 tiles x 8 softmax warps
+constexpr int F4_XCH_BYTES = 2 * 2 * 2 * BQ * 4;     // [parity][tile][half][row] floats
+
+template <int D>
+struct Fwd4Smem {
+  static constexpr int TILE = BQ * D * 2;
+  static constexpr int BYTES = 2 * TILE + 2 * KV_STAGES * TILE + 1024 + 256 + F4_XCH_BYTES;
+};
+
+// 64-thread named barrier shared by the two warps that own the same rows
+__device__ __forceinline__ void pair_sync(int id) {
+  asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(F4_THREADS, 1)
+attn_fwd4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams P) {
+  constexpr int TILE = Fwd4Smem<D>::TILE;
+  constexpr int CHUNKS = D / 64;
+  constexpr int CHUNK_BYTES = BQ * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;                                // two tiles
+  uint8_t* sK = sQ + 2 * TILE;
+  uint8_t* sV = sK + KV_STAGES * TILE;
+  Fwd2Bars* bars = reinterpret_cast<Fwd2Bars*>(sV + KV_STAGES * TILE);
+  float* xch = reinterpret_cast<float*>(sV + KV_STAGES * TILE + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_qb = (P.S + BQ - 1) / BQ;
+  const int num_pairs = (num_qb + 1) / 2;
+  const int pi = num_pairs - 1 - (int)(blockIdx.x % num_pairs);      // heaviest pairs first
+  const int head = (int)((blockIdx.x / num_pairs) % P.Hq);
+  const int batch = (int)(blockIdx.x / (num_pairs * P.Hq));
+  const int kv_head = head / (P.Hq / P.Hkv);
+  const int qb0 = 2 * pi, qb1 = 2 * pi + 1;
+  const int n0 = qb0 + 1;                            // K/V blocks tile 0 needs (causal)
+  const int n1 = qb1 < num_qb ? qb1 + 1 : 0;         // tile 1 may not exist
+  const int nmax = n0 > n1 ? n0 : n1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 256);
+      mbar_init(&bars->o_full[t], 1);
+    }
+    bars->abort = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  volatile uint32_t* abort_flag = &bars->abort;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA
+    if (lane == 0) {
+      mbar_expect_tx(&bars->q_full, (n1 > 0 ? 2 : 1) * TILE);
+      for (int t = 0; t < (n1 > 0 ? 2 : 1); ++t)
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_2d(sQ + t * TILE + c * CHUNK_BYTES, &tmap_q, &bars->q_full,
+                      P.q_col0 + head * D + c * 64, batch * P.S + (qb0 + t) * BQ);
+      for (int j = 0; j < nmax && !*abort_flag; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        const int kv_row0 = batch * P.S + j * BKV;
+        if (!mbar_wait(&bars->k_empty[s], ph ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 341); break; }
+        mbar_expect_tx(&bars->k_full[s], TILE);
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_2d(sK + s * TILE + c * CHUNK_BYTES, &tmap_k, &bars->k_full[s],
+                      P.k_col0 + kv_head * D + c * 64, kv_row0);
+        if (!mbar_wait(&bars->v_empty[s], ph ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 342); break; }
+        mbar_expect_tx(&bars->v_full[s], TILE);
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_2d(sV + s * TILE + c * CHUNK_BYTES, &tmap_v, &bars->v_full[s],
+                      P.v_col0 + kv_head * D + c * 64, kv_row0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA
+    if (lane == 0) {
+      constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_s = make_idesc_f16(AB, 0, 0, BQ, BKV);      // Q, K both K-major
+      constexpr uint32_t idesc_o = make_idesc_f16(AB, 0, 1, BQ, D);        // P (tmem) K-major, V MN-major
+      const uint32_t q_addr = smem_u32(sQ);
+      bool ok = true;
+      auto qk = [&](int t, int j) {
+        const int s = j % KV_STAGES;
+        if (!mbar_wait(&bars->k_full[s], (j / KV_STAGES) & 1)) { atomicCAS(P.err, 0, 343); ok = false; return; }
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + s * TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
+          umma_f16(tmem + t * 128, make_smem_desc(q_addr + t * TILE + off, 16, 1024),
+                   make_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0);
+        }
+        if (t == 1 || j >= n1) umma_commit(&bars->k_empty[s]);       // last reader of K_j
+        umma_commit(&bars->s_full[t]);
+      };
+      auto pv = [&](int t, int j) {
+        const int s = j % KV_STAGES;
+        if (!mbar_wait(&bars->v_full[s], (j / KV_STAGES) & 1)) { atomicCAS(P.err, 0, 344); ok = false; return; }
+        if (!mbar_wait(&bars->p_full[t], j & 1)) { atomicCAS(P.err, 0, 345); ok = false; return; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + s * TILE);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          umma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
+                      make_smem_desc(v_addr + kk * 2048, CHUNK_BYTES, 1024), idesc_o, (j | kk) != 0);
+        if (t == 1 || j >= n1) umma_commit(&bars->v_empty[s]);       // last reader of V_j
+        umma_commit(&bars->o_full[t]);
+      };
+      if (!mbar_wait(&bars->q_full, 0)) { atomicCAS(P.err, 0, 349); ok = false; }
+      if (ok) qk(0, 0);
+      if (ok && n1 > 0) qk(1, 0);
+      for (int j = 0; j < nmax && ok && !*abort_flag; ++j) {
+        if (j < n0) pv(0, j);
+        if (ok && j + 1 < n0) qk(0, j + 1);
+        if (ok && j < n1) pv(1, j);
+        if (ok && j + 1 < n1) qk(1, j + 1);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    // ------------------------------------------------------------ softmax
+    const int t = (warp - 2) >> 3;                   // query tile
+    const int half = ((warp - 2) >> 2) & 1;          // score columns [64*half, 64*half + 64)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int qb = t ? qb1 : qb0;
+    const int n_t = t ? n1 : n0;
+    const int q_pos = qb * BQ + r;
+    const int bar_id = 1 + t * 4 + quarter;          // named barriers 1..8
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tm_s = tmem + t * 128 + lane_addr;
+    const uint32_t tm_o = tmem + 256 + t * 128 + lane_addr;
+    const uint64_t scale2 = pm::pack2(P.scale_log2, P.scale_log2);
+    auto slot = [&](int parity, int h) -> float* { return xch + ((parity * 2 + t) * 2 + h) * BQ + r; };
+    constexpr int OC = D / 64;                       // 32-column O chunks per thread
+    float m_used = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    // A wait that runs out must not leave the loop: the partner warp would sit in the named
+    // barrier for good.  It raises the abort flag instead; from then on nobody waits and every
+    // warp runs through its remaining steps (on garbage) to the common exit.
+    auto wait_or_abort = [&](uint64_t* bar, uint32_t parity, int code) {
+      if (!ok || *abort_flag) { ok = false; return; }
+      if (!mbar_wait(bar, parity)) { atomicCAS(P.err, 0, code); *abort_flag = 1; ok = false; }
+    };
+    for (int j = 0; j < n_t; ++j) {
+      wait_or_abort(&bars->s_full[t], j & 1, 346);
+      tc_fence_after();
+      const bool diag = (j == qb);
+      const int kv0 = j * BKV + half * 64;
+      uint32_t v[2][32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) tmem_ld_32x32(tm_s + half * 64 + c * 32, v[c]);
+      tmem_ld_wait();
+      if (diag) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kv0 + c * 32 + i > q_pos) v[c][i] = 0xff800000u;     // -inf
+      }
+      float mx[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) mx[h] = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          mx[(c * 2 + (i >> 4)) & 3] = pm::max3(mx[(c * 2 + (i >> 4)) & 3], __uint_as_float(v[c][i]),
+                                                __uint_as_float(v[c][i + 1]));
+      const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      // the row maximum of the block needs the other half; after this barrier both threads
+      // have also finished READING their scores, so P may overwrite the first 64 columns
+      *slot(j & 1, half) = m_half;
+      pair_sync(bar_id);
+      const float m_blk = fmaxf(m_half, *slot(j & 1, half ^ 1));
+      const bool grow = (m_blk - m_used) * P.scale_log2 > kRescaleLog2;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_used, m_blk);
+        if (j > 0) {
+          wait_or_abort(&bars->o_full[t], (j - 1) & 1, 347);
+          tc_fence_after();
+          const float alpha = pm::ex2((m_used - m_new) * P.scale_log2);
+          const uint64_t alpha2 = pm::pack2(alpha, alpha);
+#pragma unroll 1
+          for (int c = 0; c < OC; ++c) {             // this thread's half of the O row
+            uint32_t w[32];
+            tmem_ld_32x32(tm_o + (half * OC + c) * 32, w);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float a, b;
+              pm::unpack2(pm::mul2(pm::pack2(__uint_as_float(w[i]), __uint_as_float(w[i + 1])), alpha2), a, b);
+              w[i] = __float_as_uint(a);
+              w[i + 1] = __float_as_uint(b);
+            }
+            tmem_st_32x32(tm_o + (half * OC + c) * 32, w);
+          }
+          l_run *= alpha;
+        }
+        m_used = m_new;
+      }
+      const float neg_m = -m_used * P.scale_log2;
+      const uint64_t neg_m2 = pm::pack2(neg_m, neg_m);
+      uint64_t ls[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) ls[h] = pm::pack2(0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float a, b;
+          pm::unpack2(pm::fma2(pm::pack2(__uint_as_float(v[c][2 * i]), __uint_as_float(v[c][2 * i + 1])), scale2,
+                               neg_m2), a, b);
+          a = pm::ex2(a);
+          b = pm::ex2(b);
+          ls[i & 3] = pm::add2(ls[i & 3], pm::pack2(a, b));
+          pk[i] = pm::cvt2<T>(a, b);
+        }
+        tmem_st_32x16(tm_s + half * 32 + c * 16, pk);   // P columns [32*half + 16c, +16)
+      }
+      float la, lb;
+      pm::unpack2(pm::add2(pm::add2(ls[0], ls[1]), pm::add2(ls[2], ls[3])), la, lb);
+      l_run += la + lb;
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[t]);
+    }
+    if (n_t > 0) wait_or_abort(&bars->o_full[t], (n_t - 1) & 1, 348);
+    if (n_t > 0) {
+      // whole-row sum = this half + the other half (both scaled by the same history of alphas)
+      *slot(n_t & 1, half) = l_run;
+      pair_sync(bar_id);
+      l_run += *slot(n_t & 1, half ^ 1);
+    }
+    if (ok && n_t > 0) {
+      tc_fence_after();
+      const float inv_l = 1.f / l_run;
+      const bool valid = q_pos < P.S;
+      T* orow = reinterpret_cast<T*>(P.o) + ((int64_t)(batch * P.S + q_pos) * P.Hq + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < OC; ++c) {
+        uint32_t w[32];
+        tmem_ld_32x32(tm_o + (half * OC + c) * 32, w);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 x;
+            x.x = pm::cvt2<T>(__uint_as_float(w[u * 8 + 0]) * inv_l, __uint_as_float(w[u * 8 + 1]) * inv_l);
+            x.y = pm::cvt2<T>(__uint_as_float(w[u * 8 + 2]) * inv_l, __uint_as_float(w[u * 8 + 3]) * inv_l);
+            x.z = pm::cvt2<T>(__uint_as_float(w[u * 8 + 4]) * inv_l, __uint_as_float(w[u * 8 + 5]) * inv_l);
+            x.w = pm::cvt2<T>(__uint_as_float(w[u * 8 + 6]) * inv_l, __uint_as_float(w[u * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + (half * OC + c) * 32 + u * 8) = x;
+          }
+        }
+      }
+      if (valid && half == 0)
+        P.lse[((int64_t)batch * P.Hq + head) * P.S + q_pos] = m_used * P.scale_ln + logf(l_run);
+    } else if (!ok) {
+      *abort_flag = 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+}  // namespace attn
+}  // namespace ft
