@@ -191,3 +191,31 @@ def _run_batch4(ft_config, steps):
         p.join(timeout=120)
         assert p.exitcode == 0
     return losses
+
+
+def _worker_b8(rank, world, port, ft_config, steps, queue):
+    global _data
+    orig = _data
+    _data = lambda steps=STEPS, batch=8, seq=128, vocab=1024: orig(steps, batch, seq, vocab)  # noqa
+    _worker(rank, world, port, ft_config, {}, steps, queue, False, 0.0)
+
+
+def test_world8_host_optimizer_and_deferred_updates():
+    """Eight ranks (the size of the target box) with every tier on the host and
+    alpha-deferred updates: the host-side scheduling (gather order, pinned pool,
+    worker thread, heartbeats) must neither stall nor drift from plain Adam."""
+    steps = 4
+    data = _data(steps, batch=8)
+    ref = _reference_losses(preset("tiny"), data)
+    cfg = _config(batch_size=8)
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = 29500 + (os.getpid() * 13 + 1531) % 2000
+    procs = [ctx.Process(target=_worker_b8, args=(r, 8, port, cfg, steps, queue)) for r in range(8)]
+    for p in procs:
+        p.start()
+    losses = queue.get(timeout=600)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    _check(losses, ref)
