@@ -233,16 +233,26 @@ def run_ours(args):
         ms = ft.distributed.all_reduce_scalar(ms, ft.distributed.ReduceOp.MAX)
         return ms / steps, d2h / max(steps, 1), last
 
-    for _ in range(args.warmup):
+    def note(msg):
+        # progress lines on stderr (rank 0): a run that stalls shows how far it got
+        if rank == 0:
+            print(f"[bench +{time.time() - t_init:7.1f}s] {msg}", file=sys.stderr, flush=True)
+
+    note(f"engine ready, {args.warmup} warm-up steps follow")
+    for i in range(args.warmup):
         arm(stall_step)
+        t_w = time.time()
         engine.train_iteration()
-    engine.synchronize()
+        engine.synchronize()
+        note(f"warm-up step {i + 1} took {time.time() - t_w:.2f} s (host wall, synchronised)")
 
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
     launches0 = lib.ft_launch_count() if hasattr(lib, "ft_launch_count") else 0
     if sampler:
         sampler.start()
+    note("timed steps (device-timed region) begin")
     ms_dev, _, _ = timed(args.steps, read_loss=False)
+    note(f"timed region done: {ms_dev:.1f} ms/step")
     launches = (lib.ft_launch_count() - launches0) if hasattr(lib, "ft_launch_count") else None
     clocks = sampler.stop() if sampler else None
 
