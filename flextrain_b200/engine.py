@@ -97,9 +97,9 @@ class FlexTrainEngine:
         self._status: Dict[str, Any] = {"last_step_seconds": None, "watchdog_tripped": False}
         self.heartbeat = Heartbeat()
         self.watchdog = StepWatchdog(cfg.engine.watchdog_seconds)
-        if cfg.engine.gradient_clipping > 0:
-            rank0_logger.warning("gradient_clipping is ignored: updates are applied unit by unit "
-                                 "while backward is still running, before a global norm exists")
+        if self.opts.deferred:
+            rank0_logger.info("deferred updates: strict overflow handling / gradient clipping hold every "
+                              "update until backward has ended (no overlap of updates with backward)")
 
     def _move_buffers(self):
         for mod in self.model.modules():
@@ -403,6 +403,19 @@ class FlexTrainEngine:
 
     def _finish_step(self) -> bool:
         grad_scale = 1.0 / float(self.loss_scale)
+        if self.opts.deferred:
+            # one verdict and one clip coefficient for the whole step, then every update
+            self.optimizer.reduce_gradients()
+            overflow, coef = self.opts.resolve_deferred(self.optimizer.gradient_sumsq(grad_scale))
+            if overflow:
+                self.optimizer.discard_gradients()
+            else:
+                self.optimizer.apply_update(grad_scale * coef)
+            self.loss_scaler.update_scale(overflow)
+            if self._custom_loss_scale is not None:
+                self._custom_loss_scale = self.loss_scaler.loss_scale
+            self._last_overflow = overflow
+            return overflow
         overflow = self.opts.finish_step()
         overflow |= self.optimizer.step(grad_scale=grad_scale,
                                         check_overflow=self.opts.check_overflow)

@@ -118,6 +118,14 @@ class FlexTrainOptsCoordinator:
             else None
         self.reduce_dtype = self.acc_dtype or self.device_dtype
         self.check_overflow = mp.device_dtype == torch.float16 or loss_scaler.dynamic
+        # Deferred mode: every update waits for the end of backward, when the global gradient
+        # norm and one overflow verdict for the whole step exist (strict overflow handling,
+        # gradient clipping).  The reduced shards are held until then; nothing overlaps backward.
+        self.clip = float(cfg.engine.gradient_clipping)
+        self.deferred = bool(cfg.engine.strict_overflow) or self.clip > 0
+        self._held: Dict[int, torch.Tensor] = {}
+        self._held_scale: Dict[int, float] = {}
+        self.last_grad_norm: Optional[float] = None
         self.num_units = para.num_units
         S = para.shard_numel
         self.S = S
@@ -208,6 +216,7 @@ class FlexTrainOptsCoordinator:
             threads = cfg.engine.cpu_adam_threads or max(1, (os.cpu_count() or 1) // self.world - 1)
             self.cpu_optimizer.threads = threads
         self._flags = torch.zeros(self.num_units + 1, dtype=torch.int32, device=self.device)
+        self._sumsq = torch.zeros(self.num_units, dtype=torch.float32, device=self.device)
         self._host_overflow = False
         self._pending: List[Future] = []
         self.bytes_d2h = 0
@@ -276,6 +285,9 @@ class FlexTrainOptsCoordinator:
         lo, hi = self._para.shard_range()
         step = max(int(self.optimizer.param_groups[0]["step"]), 1)
         grad_scale = 1.0 / float(self.loss_scaler.loss_scale)
+        if self.deferred:
+            self._hold_reduced(unit, i, src, produced, step, grad_scale)
+            return
         entry = self._pool.get() if self.host_numel else None    # back-pressure on the host side
         self._para.invalidate(unit)
         host_scale = grad_scale
@@ -311,7 +323,7 @@ class FlexTrainOptsCoordinator:
             self._para.add_host_update(unit, FutureHandle(fut))
             self._pending.append(fut)
 
-    def _fused_reduce(self, unit, buf_index, shard, step, grad_scale, flag, entry) -> bool:
+    def _fused_reduce(self, unit, buf_index, shard, step, grad_scale, flag, entry, defer=False) -> bool:
         """One kernel: peer reduce-scatter + unscale (+ Adam on the HBM share and the
         host hand-off when no overflow check has to come first).  Returns False when
         this unit's segments cannot be expressed to the kernel."""
@@ -339,6 +351,8 @@ class FlexTrainOptsCoordinator:
             host_grad=None if (two_phase or entry is None) else entry.grad, finite_flag=flag,
             segments=fused.make_segments(segs, self.optimizer.param_groups, self.cpu_optimizer, step),
             nseg=len(segs), max_blocks=self._cfg.engine.fused_blocks)
+        if defer:
+            return True                             # the caller keeps the reduced shard
         if two_phase:
             if og:
                 self._device_update(unit, shard, step, 1.0, flag, buf_index)
@@ -429,6 +443,80 @@ class FlexTrainOptsCoordinator:
                 ev.synchronize()
         finally:
             self._pool.put(entry)
+
+    # ------------------------------------------------------------ deferred mode
+    def _hold_reduced(self, unit, i, src, produced, step, grad_scale):
+        """Deferred mode: reduce-scatter ``unit``'s gradients, keep the reduced
+        shard and its squared norm; no update yet."""
+        st = self.streams
+        lo, hi = self._para.shard_range()
+        with st.opt.use():
+            st.opt.wait(produced)
+            shard = src[lo:hi]
+            flag = self._flags[unit:unit + 1]
+            if self._fused and self._fused_reduce(unit, i, shard, step, grad_scale, flag, None, defer=True):
+                held_scale = 1.0                     # the kernel unscaled and averaged already
+            else:
+                self._reduce_scatter(shard, src)
+                held_scale = grad_scale
+            hold = self._held.get(unit)
+            if hold is None:
+                hold = allocate_memory(self.S, shard.dtype, self.device)
+                self._held[unit] = hold
+            hold.copy_(shard)
+            self._sumsq[unit] = torch.linalg.vector_norm(hold, dtype=torch.float32) ** 2 * (held_scale ** 2)
+            done = st.opt.record()
+        self._buf_free[i] = done
+        self._held_scale[unit] = held_scale
+
+    @torch.no_grad()
+    def resolve_deferred(self, extra_sumsq=0.0):
+        """End of a deferred step: global gradient norm over every unit shard of
+        every rank plus ``extra_sumsq`` (the replicated parameters' share), one
+        overflow verdict, the clip coefficient, then the held updates in
+        ascending unit order (the order the next forward needs them).
+        Returns ``(overflow, clip_coefficient)``."""
+        st = self.streams
+        with st.opt.use():
+            total = self._sumsq.sum()
+            done = st.opt.record()
+        done.synchronize()
+        total = dist.all_reduce_scalar(float(total), dist.ReduceOp.SUM) if self.world > 1 else float(total)
+        total += float(extra_sumsq)
+        overflow = not math.isfinite(total)
+        coef = 1.0
+        if not overflow:
+            norm = math.sqrt(max(total, 0.0))
+            self.last_grad_norm = norm
+            if self.clip > 0:
+                coef = min(1.0, self.clip / (norm + 1e-6))
+            step = max(int(self.optimizer.param_groups[0]["step"]), 1)
+            for unit in sorted(self._held_scale):
+                self._apply_held(unit, step, coef)
+        self._held_scale.clear()
+        return overflow, coef
+
+    def _apply_held(self, unit, step, coef):
+        st = self.streams
+        og = self.opt_tiers[0]
+        hold = self._held[unit]
+        scale = self._held_scale[unit] * coef
+        entry = self._pool.get() if self.host_numel else None
+        self._para.invalidate(unit)
+        with st.opt.use():
+            if og:
+                self._device_update(unit, hold, step, scale, None, unit % 2)
+            if entry is not None:
+                tier_copy(entry.grad, hold[og:])
+                entry.flag.zero_()
+            done = st.opt.record()
+        if og:
+            self._para.note_gpu_base_write(unit, done)
+        if entry is not None:
+            fut = self._worker.submit(
+                unit, lambda u=unit, e=entry, d=done, sc=scale: self._host_update(u, e, d, step, sc))
+            self._para.add_host_update(unit, FutureHandle(fut))
+            self._pending.append(fut)
 
     # -------------------------------------------------------------- end of step
     def finish_step(self) -> bool:

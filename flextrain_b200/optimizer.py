@@ -217,6 +217,8 @@ class FlexTrainOptimizer:
         want = self._cfg.engine.fused_collectives
         if want is False or self.device.type != "cuda" or not self._nl_on_device:
             return False
+        if self._cfg.engine.strict_overflow or self._cfg.engine.gradient_clipping > 0:
+            return False                            # deferred mode splits reduce and update
         nl = self._cfg.engine.fused_nonlayer
         # "auto": the world sizes this path has been run on (1 and 2 ranks); larger
         # worlds keep the NCCL all-reduce + replicated device Adam unless asked
@@ -280,32 +282,60 @@ class FlexTrainOptimizer:
         because of a non-finite gradient."""
         if not self.non_layerwise_params:
             return False
-        from .ops.adam.gpu_adam import device_adam_update, has_nonfinite
+        from .ops.adam.gpu_adam import has_nonfinite
         if self._nl_fused:
             return self._nl_fused_step(grad_scale, check_overflow)
-        dist.all_reduce(self._nl_grad, dist.ReduceOp.AVG)
-        overflow = False
-        if check_overflow:
-            overflow = has_nonfinite(self._nl_grad)
-        if not overflow:
-            if self._nl_on_device:
-                for seg in self._nl_segments:
-                    g = self.param_groups[seg.group]
-                    sl = slice(seg.start, seg.end)
-                    device_adam_update(g, max(int(g[STEP_KEY]), 1), self.cpu_optimizer,
-                                       self._nl_master[sl], self._nl_grad[sl],
-                                       [s[sl] for s in self._nl_states], self._nl_para[sl],
-                                       grad_scale=grad_scale)
-            else:
-                self._nl_host_grad.copy_(self._nl_grad)     # synchronous: pageable semantics
-                if self.device.type == "cuda":
-                    torch.cuda.current_stream().synchronize()
-                ctxs = create_step_contexts(self.param_groups, self._nl_segments, self._nl_master,
-                                            self._nl_host_grad, self._nl_states, self._nl_host_para)
-                self.cpu_optimizer.step(ctxs, grad_scale=grad_scale)
-                self._nl_para.copy_(self._nl_host_para, non_blocking=True)
-        self._nl_grad.zero_()
+        self.reduce_gradients()
+        overflow = has_nonfinite(self._nl_grad) if check_overflow else False
+        if overflow:
+            self.discard_gradients()
+        else:
+            self.apply_update(grad_scale)
         return overflow
+
+    @torch.no_grad()
+    def reduce_gradients(self):
+        """First half of ``step``: average the replicated gradients over ranks."""
+        if self.non_layerwise_params:
+            dist.all_reduce(self._nl_grad, dist.ReduceOp.AVG)
+
+    @torch.no_grad()
+    def gradient_sumsq(self, grad_scale: float = 1.0) -> float:
+        """Squared L2 norm of the (reduced, unscaled) non-layerwise gradients."""
+        if not self.non_layerwise_params:
+            return 0.0
+        n = torch.linalg.vector_norm(self._nl_grad, dtype=torch.float32)
+        return float(n) ** 2 * float(grad_scale) ** 2
+
+    @torch.no_grad()
+    def discard_gradients(self):
+        if self.non_layerwise_params:
+            self._nl_grad.zero_()
+
+    @torch.no_grad()
+    def apply_update(self, grad_scale: float = 1.0):
+        """Second half of ``step``: one update from the already reduced gradients
+        (``grad_scale`` may carry a clip coefficient), then zero them."""
+        if not self.non_layerwise_params:
+            return
+        from .ops.adam.gpu_adam import device_adam_update
+        if self._nl_on_device:
+            for seg in self._nl_segments:
+                g = self.param_groups[seg.group]
+                sl = slice(seg.start, seg.end)
+                device_adam_update(g, max(int(g[STEP_KEY]), 1), self.cpu_optimizer,
+                                   self._nl_master[sl], self._nl_grad[sl],
+                                   [s[sl] for s in self._nl_states], self._nl_para[sl],
+                                   grad_scale=grad_scale)
+        else:
+            self._nl_host_grad.copy_(self._nl_grad)     # synchronous: pageable semantics
+            if self.device.type == "cuda":
+                torch.cuda.current_stream().synchronize()
+            ctxs = create_step_contexts(self.param_groups, self._nl_segments, self._nl_master,
+                                        self._nl_host_grad, self._nl_states, self._nl_host_para)
+            self.cpu_optimizer.step(ctxs, grad_scale=grad_scale)
+            self._nl_para.copy_(self._nl_host_para, non_blocking=True)
+        self._nl_grad.zero_()
 
     def close(self):
         """Release the peer-mapped buffers of the fused non-layerwise path (the

@@ -89,3 +89,52 @@ def test_engine_stats_counts_tier_traffic():
         assert eng.stats()["traffic_bytes"]["nvme_read"] == 0
         eng.shutdown()
     reset_runtime()
+
+
+def test_strict_overflow_skips_the_whole_step():
+    """engine.strict_overflow: a non-finite gradient anywhere skips every update
+    of that step (layer units and replicated parameters alike) and the next
+    clean step proceeds from untouched state."""
+    import torch
+    from flextrain_b200.llm_func import LLMFunc
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine, reset_runtime
+    reset_runtime()
+    cfg = preset("tiny", num_layers=3, hidden=64, num_heads=4, ffn=128, vocab=128, seq_len=16)
+    data = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1))
+    ft_cfg = {"batch_size": 2, "micro_batch_size": 2,
+              "mixed_precision": {"device_dtype": "fp32", "dynamic_loss_scaling": False},
+              "split_ratio": {"parameter": [0.0, 1.0], "optimizer": [0.0, 1.0],
+                              "checkpoint": [0.0, 1.0], "gradient": [0.0, 1.0]},
+              "engine": {"strict_overflow": True}}
+    model, opt, eng = build_llama_engine(cfg, ft_cfg, lambda: (data[:, :-1], data[:, 1:]),
+                                         init_device="cpu", backend="gloo")
+    poison = {"on": False}
+    clean_loss = LLMFunc.loss
+
+    def loss(outputs, inputs):
+        out = clean_loss(outputs, inputs)
+        return out * float("inf") if poison["on"] else out
+
+    LLMFunc.loss = staticmethod(loss)
+    try:
+        eng.train_iteration()
+        eng.synchronize()
+        before = [eng.opts.read_states(u)[0].clone() for u in range(eng.num_units)]
+        nl_before = eng.optimizer.non_layerwise_state()["master"].clone()
+        poison["on"] = True
+        eng.train_iteration()
+        eng.synchronize()
+        assert eng.skipped_steps == 1
+        for u in range(eng.num_units):
+            assert torch.equal(eng.opts.read_states(u)[0], before[u])
+        assert torch.equal(eng.optimizer.non_layerwise_state()["master"], nl_before)
+        poison["on"] = False
+        first = float(eng.train_iteration()[0].detach())
+        eng.synchronize()
+        assert first == first and eng.skipped_steps == 1
+        assert not torch.equal(eng.opts.read_states(0)[0], before[0])
+    finally:
+        LLMFunc.loss = staticmethod(clean_loss)
+        eng.shutdown()
+        reset_runtime()

@@ -219,3 +219,43 @@ def test_world8_host_optimizer_and_deferred_updates():
         p.join(timeout=120)
         assert p.exitcode == 0
     _check(losses, ref)
+
+
+def _reference_losses_clipped(cfg, data, clip, lr=1e-3):
+    torch.manual_seed(0)
+    model = LlamaModel(cfg)
+    decay = [p for p in model.parameters() if p.dim() > 1]
+    no_decay = [p for p in model.parameters() if p.dim() <= 1]
+    opt = torch.optim.Adam([{"params": decay, "weight_decay": 0.0},
+                            {"params": no_decay, "weight_decay": 0.0}], lr=lr, betas=(0.9, 0.999), eps=1e-8)
+    out, norms = [], []
+    for t in data:
+        loss = model(t[:, :-1], t[:, 1:])
+        opt.zero_grad()
+        loss.backward()
+        norms.append(float(torch.nn.utils.clip_grad_norm_(model.parameters(), clip)))
+        opt.step()
+        out.append(loss.item())
+    return out, norms
+
+
+def test_world2_gradient_clipping_by_global_norm():
+    """engine.gradient_clipping: one global norm over layer shards of both ranks
+    and the replicated parameters, updates held until it is known; must equal
+    torch's clip_grad_norm_ + Adam.  The clip value is far below the gradient
+    norm of this model (about 1.5), so every step is clipped."""
+    clip = 0.25
+    ref, norms = _reference_losses_clipped(preset("tiny"), _data(), clip)
+    assert min(norms) > clip
+    cfg = _config(engine={"gradient_clipping": clip},
+                  split_ratio={"optimizer": [0.0, 0.5], "parameter": [0.0, 1.0],
+                               "checkpoint": [0.0, 1.0], "gradient": [0.0, 1.0], "alpha": 0.25})
+    with tempfile.TemporaryDirectory() as tmp:
+        cfg["nvme_swap"] = {"swap_dir": tmp}
+        _check(_run(2, cfg), ref, tol=2e-5)
+
+
+def test_world1_strict_overflow_matches_streaming_updates(ref_losses):
+    """engine.strict_overflow without any overflow: same numbers as the
+    streaming updates, just applied after backward."""
+    _check(_run(1, _config(engine={"strict_overflow": True})), ref_losses)
