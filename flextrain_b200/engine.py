@@ -32,7 +32,7 @@ from .memory.coordinator.parameter import get_para_coordinator
 from .scheduler import GreedySnakeBlockScheduler, LLMTask
 from .utils import distributed as dist
 from .utils.device import get_streams
-from .utils.logging import rank0_logger
+from .utils.logging import logger, rank0_logger
 from .utils.health import Heartbeat, PeerFailure, StepWatchdog
 from .utils.timer import StepTimer
 
@@ -316,7 +316,10 @@ class FlexTrainEngine:
         self.heartbeat.beat(self.global_steps)
         self.watchdog.step_started()
         try:
-            return self._train_iteration(cfg)
+            result = self._train_iteration(cfg)
+            if self.global_steps <= 2:
+                self._fused_health_check()
+            return result
         except PeerFailure:
             raise
         except BaseException as exc:
@@ -442,6 +445,35 @@ class FlexTrainEngine:
         return {"traffic_bytes": TRAFFIC.snapshot(reset=reset), "allocated_bytes": allocated_bytes(),
                 "global_steps": self.global_steps, "skipped_steps": self.skipped_steps,
                 "last_step_seconds": self.timer.last, "phase_ms": self.phase_times_ms()}
+
+    # bounded waits of the peer-memory kernels that ran out: start / end barriers of the
+    # reduce kernels (101, 102) and of the gather (201 .. 204, reported in the GEMM error word)
+    _COMM_TIMEOUTS = (101, 102)
+    _GATHER_TIMEOUTS = (201, 202, 203, 204)
+
+    def _fused_health_check(self):
+        """After each of the first two steps on more than one GPU: if a cross-GPU
+        wait of the fused collective kernels ran out on any rank, all ranks switch
+        to the NCCL collectives for the rest of the run (a step that waited out
+        its budget is wrong anyway, and the next ones would crawl from time-out to
+        time-out).  Costs one device synchronisation and a scalar all-reduce."""
+        if self.device.type != "cuda" or self.world == 1:
+            return
+        if not (self.opts._fused or self.para._peer_gather):
+            return
+        from .ops.native import cuda_lib
+        lib = cuda_lib()
+        gemm_word, comm_word = lib.ft_gemm_error(), lib.ft_comm_error()
+        if gemm_word and gemm_word not in self._GATHER_TIMEOUTS:
+            self._status["gemm_error_word_seen"] = gemm_word     # reading cleared it: keep it visible
+        bad = comm_word in self._COMM_TIMEOUTS or gemm_word in self._GATHER_TIMEOUTS
+        bad = dist.all_reduce_scalar(1.0 if bad else 0.0, dist.ReduceOp.MAX) > 0
+        if bad:
+            logger.error(f"rank {dist.get_rank()}: a bounded wait of the fused collective kernels ran out "
+                         f"(error words: gather {gemm_word}, reduce {comm_word}); switching to NCCL collectives")
+            self.opts._fused = False
+            self.para._peer_gather = False
+            self._status["fused_collectives_disabled"] = True
 
     def health(self) -> Dict[str, Any]:
         """Status words of the runtime: pending host updates, traffic counters,
