@@ -193,6 +193,10 @@ class FlexTrainEngine:
     def _enter_unit(self, unit: int, prev_unit: Optional[int], next_unit: Optional[int],
                     backward: bool):
         self._trace(f"enter unit {unit} ({'bwd' if backward else 'fwd'}), prefetch {next_unit}")
+        if self.global_steps == 0 and unit % 8 == 7:
+            # first step only: look at the fused kernels' error words every few units, so that a
+            # systematic time-out costs a few waits, not one per unit, before NCCL takes over
+            self._fused_health_check()
         if prev_unit is not None and prev_unit != unit:
             self.para.release(prev_unit, keep=True)
         self.para.acquire(unit)
