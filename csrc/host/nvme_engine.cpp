@@ -19,6 +19,7 @@
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <sys/syscall.h>
+#include <sys/uio.h>
 #include <unistd.h>
 
 #include <atomic>
@@ -96,13 +97,20 @@ struct Uring {
     sqes = nullptr; cq_ptr = sq_ptr = nullptr; fd = -1;
   }
 
-  // queue one read/write; caller guarantees in-flight < entries
-  void push(bool write, int file, void* buf, unsigned len, uint64_t off, uint64_t tag) {
+  // queue one read/write; caller guarantees in-flight < entries.  `fixed` >= 0 names a
+  // registered buffer that contains [buf, buf + len): the kernel then skips pinning the
+  // pages for this request.
+  void push(bool write, int file, void* buf, unsigned len, uint64_t off, uint64_t tag, int fixed = -1) {
     unsigned tail = *sq_tail;
     unsigned idx = tail & *sq_mask;
     io_uring_sqe* e = &sqes[idx];
     std::memset(e, 0, sizeof(*e));
-    e->opcode = write ? IORING_OP_WRITE : IORING_OP_READ;
+    if (fixed >= 0) {
+      e->opcode = write ? IORING_OP_WRITE_FIXED : IORING_OP_READ_FIXED;
+      e->buf_index = (uint16_t)fixed;
+    } else {
+      e->opcode = write ? IORING_OP_WRITE : IORING_OP_READ;
+    }
     e->fd = file;
     e->addr = (uint64_t)buf;
     e->len = len;
@@ -119,6 +127,14 @@ struct Uring {
       if (r < 0 && errno == EINTR) continue;
       return r < 0 ? -errno : r;
     }
+  }
+
+  // (Re)register a set of buffers; n == 0 just drops the current set.  0 or -errno.
+  int register_buffers(const iovec* iov, unsigned n) {
+    syscall(__NR_io_uring_register, fd, IORING_UNREGISTER_BUFFERS, nullptr, 0);   // fine if none
+    if (n == 0) return 0;
+    long r = syscall(__NR_io_uring_register, fd, IORING_REGISTER_BUFFERS, iov, n);
+    return r < 0 ? -errno : 0;
   }
 
   bool pop(io_uring_cqe* out) {
@@ -156,6 +172,7 @@ struct Worker {
   bool stop = false;
   Uring ring;
   bool ring_ok = false;
+  std::atomic<bool> ring_registered{false};  // this worker's ring holds Engine::reg
   aio_context_t aio_ctx = 0;
   bool aio_ok = false;
 };
@@ -182,7 +199,22 @@ struct Engine {
   std::atomic<int> fault_kind{0};            // 0 none, 1 EIO, 2 short transfer
   std::atomic<int> fault_countdown{0};
   std::atomic<int64_t> bytes_read{0}, bytes_written{0};
+
+  // registered (page-locked) buffers of the io_uring workers, split into <= 1 GiB pieces
+  std::mutex reg_mu;
+  std::vector<iovec> reg;                    // index == buf_index in every worker's ring
+  std::atomic<int64_t> fixed_ops{0};
 };
+
+// index of the registered piece that contains [p, p + len), or -1
+int find_registered(Engine* e, const char* p, int64_t len) {
+  std::lock_guard<std::mutex> lk(e->reg_mu);
+  for (size_t i = 0; i < e->reg.size(); ++i) {
+    const char* b = (const char*)e->reg[i].iov_base;
+    if (p >= b && p + len <= b + e->reg[i].iov_len) return (int)i;
+  }
+  return -1;
+}
 
 int consume_fault(Engine* e) {
   int k = e->fault_kind.load();
@@ -236,8 +268,10 @@ int run_uring(Engine* e, Worker* w, const SubOp& s) {
       int64_t len = s.nbytes - issued < e->block_size ? s.nbytes - issued : e->block_size;
       int f = consume_fault(e);
       if (f) { err = -EIO; break; }
+      const int fixed = w->ring_registered ? find_registered(e, s.buf + issued, len) : -1;
+      if (fixed >= 0) e->fixed_ops.fetch_add(1);
       w->ring.push(s.write, s.fd, s.buf + issued, (unsigned)len, (uint64_t)(s.file_off + issued),
-                   (uint64_t)len);
+                   (uint64_t)len, fixed);
       issued += len; ++inflight; ++batch;
     }
     if (inflight == 0) break;
@@ -543,6 +577,53 @@ void ft_nvme_inject_fault(void* h, int kind, int count) {
   e->fault_countdown.store(count);
   e->fault_kind.store(kind);
 }
+
+// Registers page-locked buffers with every io_uring worker: block transfers that lie
+// inside one of them are issued as fixed-buffer requests (no per-request page pinning).
+// Replaces any earlier set; n = 0 drops it.  Must be called while no operation is
+// pending (-EBUSY otherwise).  Returns the number of workers that hold the
+// registration - 0 when the engine does not run on io_uring or the kernel refused
+// (memlock limit): transfers then simply stay ordinary requests - or a negative errno.
+// The reference's engine has no counterpart (libaio has no registered buffers).
+int ft_nvme_register_buffers(void* h, void* const* ptrs, const int64_t* lens, int n) {
+  if (!h || n < 0 || (n > 0 && (!ptrs || !lens))) return -EINVAL;
+  auto* e = (Engine*)h;
+  {
+    std::lock_guard<std::mutex> lk(e->op_mu);
+    if (!e->ops.empty()) return -EBUSY;
+  }
+  constexpr int64_t kPiece = 1ll << 30;          // the kernel takes at most 1 GiB per entry
+  std::vector<iovec> pieces;
+  for (int i = 0; i < n; ++i) {
+    if (!ptrs[i] || lens[i] <= 0) return -EINVAL;
+    for (int64_t off = 0; off < lens[i]; off += kPiece) {
+      iovec v;
+      v.iov_base = (char*)ptrs[i] + off;
+      v.iov_len = (size_t)(lens[i] - off < kPiece ? lens[i] - off : kPiece);
+      pieces.push_back(v);
+    }
+  }
+  if (pieces.size() > 1024) return -E2BIG;
+  for (auto& w : e->workers) w->ring_registered.store(false);
+  {
+    std::lock_guard<std::mutex> lk(e->reg_mu);
+    e->reg = pieces;
+  }
+  int holders = 0;
+  if (e->kind == kUring) {
+    for (auto& w : e->workers) {
+      if (!w->ring_ok) continue;
+      if (w->ring.register_buffers(pieces.data(), (unsigned)pieces.size()) == 0 && !pieces.empty()) {
+        w->ring_registered.store(true);
+        ++holders;
+      }
+    }
+  }
+  return holders;
+}
+
+// Block requests issued as fixed-buffer requests so far.
+int64_t ft_nvme_fixed_ops(void* h) { return h ? ((Engine*)h)->fixed_ops.load() : 0; }
 
 void ft_nvme_stats(void* h, int64_t* bytes_read, int64_t* bytes_written) {
   if (!h) return;

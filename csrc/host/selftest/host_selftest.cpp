@@ -37,6 +37,8 @@ int64_t ft_nvme_wait(void* h);
 int ft_nvme_sync_rw(void* h, const char* path, void* buffer, int64_t nbytes, int64_t file_offset, int is_write);
 int ft_nvme_forget(void* h, const char* path);
 void ft_nvme_inject_fault(void* h, int kind, int count);
+int ft_nvme_register_buffers(void* h, void* const* ptrs, const int64_t* lens, int n);
+int64_t ft_nvme_fixed_ops(void* h);
 }
 
 static int g_failed = 0;
@@ -116,6 +118,20 @@ static void test_nvme(const std::string& dir, int kind) {
   int64_t rid = ft_nvme_submit(h, f2.c_str(), in.data(), 4 * 65536, 0, 0);
   CHECK(rid > 0 && ft_nvme_wait_op(h, rid) == 0);
   CHECK(memcmp(in.data(), out.data(), 4 * 65536) == 0);
+  // registered staging buffer: same data path with fixed-buffer requests where the kernel
+  // accepts the registration (io_uring engine only)
+  {
+    void* ptrs[1] = {out.data()};
+    int64_t lens[1] = {n};
+    const int holders = ft_nvme_register_buffers(h, ptrs, lens, 1);
+    CHECK(holders >= 0);
+    CHECK(ft_nvme_sync_rw(h, f1.c_str(), out.data(), n, 0, 1) == 0);
+    std::fill(in.begin(), in.end(), 0);
+    CHECK(ft_nvme_sync_rw(h, f1.c_str(), in.data(), n, 0, 0) == 0);
+    CHECK(memcmp(in.data(), out.data(), n) == 0);
+    if (holders > 0) CHECK(ft_nvme_fixed_ops(h) > 0);
+    CHECK(ft_nvme_register_buffers(h, nullptr, nullptr, 0) == 0);
+  }
   // an injected I/O error surfaces as a status code, and the engine keeps working
   ft_nvme_inject_fault(h, 1, 1);
   CHECK(ft_nvme_sync_rw(h, f1.c_str(), in.data(), 65536, 0, 0) != 0);

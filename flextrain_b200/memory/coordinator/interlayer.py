@@ -82,6 +82,8 @@ class TieredTensorStore:
             if self._tiers[2]:
                 self._nvme_stage = [allocate_memory(self._tiers[2], t.dtype, "cpu", True)
                                     for _ in range(2)]
+                for stage in self._nvme_stage:
+                    get_nvme_swapper().register_staging(stage)
                 self._stage_busy = [None, None]
                 self._stage_next = 0
 

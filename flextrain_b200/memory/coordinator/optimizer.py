@@ -173,6 +173,8 @@ class FlexTrainOptsCoordinator:
         self._nvme_stage = [allocate_memory(on, torch.float32, "cpu", True) for _ in range(self.K)] \
             if on else None
         self._nvme_para_stage = allocate_memory(n, self.device_dtype, "cpu", True) if n else None
+        for stage in (self._nvme_stage or []) + ([self._nvme_para_stage] if n else []):
+            get_nvme_swapper().register_staging(stage)
         lo, hi = para.shard_range()
         self._segments: List[List[GroupSegment]] = [
             slice_segments(optimizer.unit_group_segments[u], lo, hi) for u in range(self.num_units)]

@@ -97,6 +97,8 @@ class FlexTrainParaCoordinator:
         self._host_ready: Dict[int, List[Waitable]] = {}  # host-side updates still running
         self._nvme_landing = [allocate_memory(n, self.device_dtype, "cpu", True) for _ in range(2)] \
             if n else []
+        for landing in self._nvme_landing:
+            get_nvme_swapper().register_staging(landing)
         self._nvme_loads: Dict[int, tuple] = {}    # unit -> (landing index, read handle)
         self._landing_busy = [DONE for _ in self._nvme_landing]
         self._nvme_next = 0

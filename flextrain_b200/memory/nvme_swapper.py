@@ -46,6 +46,9 @@ def _lib():
         lib.ft_nvme_open_fds.argtypes = [c_void_p]
         lib.ft_nvme_inject_fault.argtypes = [c_void_p, c_int, c_int]
         lib.ft_nvme_stats.argtypes = [c_void_p, ctypes.POINTER(c_int64), ctypes.POINTER(c_int64)]
+        lib.ft_nvme_register_buffers.argtypes = [c_void_p, c_void_p, c_void_p, c_int]
+        lib.ft_nvme_fixed_ops.restype = c_int64
+        lib.ft_nvme_fixed_ops.argtypes = [c_void_p]
         lib._nvme_declared = True
     return lib
 
@@ -138,7 +141,23 @@ class NVMeEngine:
     def stats(self):
         r, w = c_int64(0), c_int64(0)
         self._lib.ft_nvme_stats(self._h, ctypes.byref(r), ctypes.byref(w))
-        return {"bytes_read": r.value, "bytes_written": w.value}
+        return {"bytes_read": r.value, "bytes_written": w.value,
+                "fixed_buffer_requests": int(self._lib.ft_nvme_fixed_ops(self._h))}
+
+    def register_buffers(self, tensors: Sequence[torch.Tensor]) -> int:
+        """Register the storage of ``tensors`` (contiguous CPU staging buffers)
+        with the io_uring workers; transfers inside them then run as
+        fixed-buffer requests.  Replaces any earlier set.  Returns how many
+        workers hold the registration (0: not io_uring, or the kernel refused -
+        transfers stay ordinary requests).  No transfer may be pending."""
+        tensors = [t for t in tensors if t.numel() > 0]
+        n = len(tensors)
+        ptrs = (c_void_p * max(n, 1))(*[t.data_ptr() for t in tensors])
+        lens = (c_int64 * max(n, 1))(*[t.numel() * t.element_size() for t in tensors])
+        rc = self._lib.ft_nvme_register_buffers(self._h, ptrs, lens, n)
+        if rc < 0:
+            raise NVMeError(-rc, f"cannot register NVMe staging buffers: {os.strerror(-rc)}")
+        return rc
 
 
 class AsyncNVMeSwapper:
@@ -148,6 +167,8 @@ class AsyncNVMeSwapper:
         self._engine = engine
         self._inflight: List[AsyncIOHandle] = []
         self._ready = False
+        self._staging: List[torch.Tensor] = []      # pinned buffers every transfer goes through
+        self._staging_dirty = False
 
     def _init(self):
         if self._ready:
@@ -173,8 +194,25 @@ class AsyncNVMeSwapper:
     def _filename(self, data_id) -> str:
         return os.path.join(self.swap_dir, str(data_id))
 
+    def register_staging(self, tensor: torch.Tensor):
+        """Tell the swapper that ``tensor`` is a long-lived staging buffer of the
+        NVMe tier.  The set is registered with the engine (io_uring fixed
+        buffers) at the next moment no transfer is pending."""
+        if tensor is not None and tensor.numel() > 0 and tensor.device.type == "cpu":
+            self._staging.append(tensor)
+            self._staging_dirty = True
+
+    def _register_if_idle(self):
+        if self._staging_dirty and self._engine.pending() == 0:
+            self._staging_dirty = False
+            try:
+                self._engine.register_buffers(self._staging)
+            except NVMeError as exc:                 # registration is an optimisation only
+                rank0_logger.warning(f"NVMe staging buffers not registered: {exc}")
+
     def _swap(self, data_ids, tensors, write: bool, async_op: bool):
         self._init()
+        self._register_if_idle()
         if isinstance(data_ids, (FlexTrainDataID, str)):
             data_ids, tensors = [data_ids], [tensors]
         ids = []

@@ -97,3 +97,42 @@ def test_swapper_names_files_like_the_reference(swap_cfg):
         grp.single_offload(oid, torch.randn(5), 0)
     sw.remove(did)
     assert not os.path.exists(os.path.join(swap_cfg, "rank0_PARA_layer3.swp"))
+
+
+def test_registered_buffers_become_fixed_requests(tmp_path):
+    """io_uring only: transfers that lie inside a registered staging buffer are
+    issued as fixed-buffer requests; others stay ordinary; data round-trips in
+    both cases; re-registering and dropping the set works while idle."""
+    import torch
+    from flextrain_b200.memory.nvme_swapper import NVMeEngine
+    eng = NVMeEngine(block_size=1 << 16, queue_depth=4, threads=2, engine="auto")
+    if eng.kind != "io_uring":
+        eng.close()
+        pytest.skip("io_uring is not available here")
+    staged = torch.arange(1 << 18, dtype=torch.int32)            # 1 MiB
+    other = torch.arange(1 << 16, dtype=torch.int32) * 3
+    holders = eng.register_buffers([staged])
+    path_a, path_b = str(tmp_path / "a.swp"), str(tmp_path / "b.swp")
+    eng.write(path_a, staged)
+    eng.write(path_b, other)
+    fixed_after_writes = eng.stats()["fixed_buffer_requests"]
+    if holders:                                                  # the kernel may refuse (memlock limit)
+        assert fixed_after_writes == (staged.numel() * 4) // (1 << 16)
+    else:
+        assert fixed_after_writes == 0
+    back = torch.zeros_like(staged)
+    eng.read(path_a, back)                                       # not registered: ordinary requests
+    assert torch.equal(back, staged)
+    assert eng.stats()["fixed_buffer_requests"] == fixed_after_writes
+    # a view inside the registered buffer is covered as well
+    staged.zero_()
+    eng.read(path_a, staged[: 1 << 17])
+    assert torch.equal(staged[: 1 << 17], back[: 1 << 17])
+    if holders:
+        assert eng.stats()["fixed_buffer_requests"] > fixed_after_writes
+    assert eng.register_buffers([staged, other]) in (0, 2)       # replace the set
+    assert eng.register_buffers([]) == 0                         # drop it
+    check = torch.zeros_like(other)
+    eng.read(path_b, check)
+    assert torch.equal(check, other)
+    eng.close()
