@@ -590,7 +590,8 @@ int ft_nvme_register_buffers(void* h, void* const* ptrs, const int64_t* lens, in
   auto* e = (Engine*)h;
   {
     std::lock_guard<std::mutex> lk(e->op_mu);
-    if (!e->ops.empty()) return -EBUSY;
+    for (auto& kv : e->ops)
+      if (kv.second->remaining.load() != 0) return -EBUSY;   // a ring is in use
   }
   constexpr int64_t kPiece = 1ll << 30;          // the kernel takes at most 1 GiB per entry
   std::vector<iovec> pieces;

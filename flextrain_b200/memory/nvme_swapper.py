@@ -208,7 +208,10 @@ class AsyncNVMeSwapper:
             try:
                 self._engine.register_buffers(self._staging)
             except NVMeError as exc:                 # registration is an optimisation only
-                rank0_logger.warning(f"NVMe staging buffers not registered: {exc}")
+                if exc.errno == 16:                  # EBUSY: a transfer started meanwhile, try later
+                    self._staging_dirty = True
+                else:
+                    rank0_logger.warning(f"NVMe staging buffers not registered: {exc}")
 
     def _swap(self, data_ids, tensors, write: bool, async_op: bool):
         self._init()
