@@ -259,3 +259,17 @@ def test_world1_strict_overflow_matches_streaming_updates(ref_losses):
     """engine.strict_overflow without any overflow: same numbers as the
     streaming updates, just applied after backward."""
     _check(_run(1, _config(engine={"strict_overflow": True})), ref_losses)
+
+
+def test_world2_clipping_with_device_and_nvme_tiers():
+    """Deferred updates through every tier at once: device share of the optimizer
+    ahead of the device share of the parameters (staged output), host share and
+    NVMe share, two ranks, clipping active."""
+    clip = 0.25
+    ref, _ = _reference_losses_clipped(preset("tiny"), _data(), clip)
+    with tempfile.TemporaryDirectory() as tmp:
+        cfg = _config(engine={"gradient_clipping": clip},
+                      split_ratio={"optimizer": [0.5, 0.3], "parameter": [0.3, 0.5],
+                                   "checkpoint": [0.5, 0.5], "gradient": [1.0, 0.0], "alpha": 0.25},
+                      nvme_swap={"swap_dir": tmp})
+        _check(_run(2, cfg), ref, tol=2e-5)
