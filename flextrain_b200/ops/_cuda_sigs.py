@@ -14,6 +14,16 @@ def declare(lib):
     lib.ft_rmsnorm_fwd.argtypes = [P, P, P, P, L, I, F, I, P]
     lib.ft_rmsnorm_bwd_parts.restype = I
     lib.ft_rmsnorm_bwd.argtypes = [P, P, P, P, P, P, P, L, I, I, P]
+    lib.ft_norm_max_hidden.argtypes = [I]
+    lib.ft_norm_max_hidden.restype = I
+    lib.ft_norm_bwd_parts.argtypes = [L, I]
+    lib.ft_norm_bwd_parts.restype = I
+    lib.ft_norm_fwd.argtypes = [P, P, P, P, P, P, L, I, F, I, I, P]
+    lib.ft_norm_bwd.argtypes = [P, P, P, P, P, P, P, P, P, P, L, I, I, I, P]
+    lib.ft_bias_act_fwd.argtypes = [P, P, P, L, I, I, I, P]
+    lib.ft_bias_act_bwd_parts.argtypes = [L, I]
+    lib.ft_bias_act_bwd_parts.restype = I
+    lib.ft_bias_act_bwd.argtypes = [P, P, P, P, P, P, L, I, I, I, I, P]
     lib.ft_rope.argtypes = [P, L, P, L, P, P, L, I, I, I, F, I, P]
     lib.ft_swiglu_fwd.argtypes = [P, P, L, I, I, P]
     lib.ft_swiglu_bwd.argtypes = [P, P, P, L, I, I, P]

@@ -113,6 +113,115 @@ def rmsnorm(x, w, eps):
     return _RMSNorm.apply(x, w, eps)
 
 
+class _Norm(torch.autograd.Function):
+    """LayerNorm (``b`` given) or RMSNorm (``b`` None) through the register-resident
+    row kernels (``ft_norm_fwd`` / ``ft_norm_bwd``)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        h = x.shape[-1]
+        x2 = x.reshape(-1, h).contiguous()
+        rows = x2.shape[0]
+        ln = b is not None
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device) if ln else None
+        _check(cuda_lib().ft_norm_fwd(ptr(x2), ptr(w), ptr(b) if ln else None, ptr(y),
+                                      ptr(mean) if ln else None, ptr(rstd), rows, h, float(eps), int(ln),
+                                      dtype_code(x.dtype), stream_handle()), "ft_norm_fwd")
+        ctx.save_for_backward(x2, w, mean, rstd)
+        ctx.ln = ln
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, mean, rstd = ctx.saved_tensors
+        rows, h = x2.shape
+        ln = ctx.ln
+        dy2 = dy.reshape(rows, h).contiguous()
+        dx = torch.empty_like(x2)
+        dw = torch.empty_like(w)
+        db = torch.empty_like(w) if ln else None
+        lib = cuda_lib()
+        parts = lib.ft_norm_bwd_parts(rows, h)
+        part = torch.empty((2 if ln else 1) * parts * h, dtype=torch.float32, device=x2.device)
+        db_part = part[parts * h:] if ln else None
+        _check(lib.ft_norm_bwd(ptr(x2), ptr(w), ptr(dy2), ptr(mean) if ln else None, ptr(rstd), ptr(dx),
+                               ptr(dw), ptr(db) if ln else None, ptr(part),
+                               ptr(db_part) if ln else None, rows, h, int(ln), dtype_code(x2.dtype),
+                               stream_handle()), "ft_norm_bwd")
+        return dx.view(dy.shape), dw, db, None
+
+
+def layernorm(x, w, b, eps):
+    return _Norm.apply(x, w, b, eps)
+
+
+def rmsnorm_rows(x, w, eps):
+    """RMSNorm through the same row kernels as ``layernorm`` (each row read once)."""
+    return _Norm.apply(x, w, None, eps)
+
+
+class _BiasAct(torch.autograd.Function):
+    """``act(x + bias)`` over the last dimension; act 0 adds the bias in place,
+    act 1 is the tanh GELU.  The backward produces dx and the bias gradient (column
+    sums of dx) in one pass."""
+
+    @staticmethod
+    def forward(ctx, x, bias, act):
+        n = x.shape[-1]
+        x2 = x.reshape(-1, n)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        in_place = act == 0 and x2.data_ptr() == x.data_ptr()
+        y = x2 if in_place else torch.empty_like(x2)
+        _check(cuda_lib().ft_bias_act_fwd(ptr(x2), ptr(bias), ptr(y), rows, n, int(act),
+                                          dtype_code(x.dtype), stream_handle()), "ft_bias_act_fwd")
+        ctx.act = act
+        if act == 0:
+            ctx.save_for_backward(bias)
+        else:
+            ctx.save_for_backward(bias, x2)
+        if in_place:
+            ctx.mark_dirty(x)
+            return x
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        act = ctx.act
+        bias = ctx.saved_tensors[0]
+        n = bias.shape[0]
+        dy2 = dy.reshape(-1, n)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        rows = dy2.shape[0]
+        lib = cuda_lib()
+        parts = lib.ft_bias_act_bwd_parts(rows, n)
+        part = torch.empty(parts * n, dtype=torch.float32, device=dy.device)
+        dbias = torch.empty_like(bias)
+        if act == 0:
+            dx2 = dy2
+            x_ptr = dx_ptr = None
+        else:
+            x2 = ctx.saved_tensors[1]
+            dx2 = torch.empty_like(dy2)
+            x_ptr, dx_ptr = ptr(x2), ptr(dx2)
+        _check(lib.ft_bias_act_bwd(ptr(dy2), x_ptr, ptr(bias) if act else None, dx_ptr, ptr(dbias),
+                                   ptr(part), rows, n, int(act), 0, dtype_code(dy.dtype),
+                                   stream_handle()), "ft_bias_act_bwd")
+        return dx2.view(dy.shape), dbias, None
+
+
+def bias_add(x, bias):
+    return _BiasAct.apply(x, bias, 0)
+
+
+def bias_gelu(x, bias):
+    return _BiasAct.apply(x, bias, 1)
+
+
 # --------------------------------------------------------------------- RoPE
 def _rope_launch(x, y, cos, sin, heads, d, seq_len, sign):
     tokens = x.numel() // x.shape[-1] if x.dim() > 1 else 1

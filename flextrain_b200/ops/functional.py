@@ -1,10 +1,12 @@
-"""Model ops as the Llama blocks call them.
+"""Model ops as the Llama and GPT blocks call them.
 
 CUDA tensors are routed to the hand-written sm_100a kernels (``cuda_ops``);
 a missing CUDA library raises instead of silently running eager PyTorch.  CPU
 tensors use the plain PyTorch statements in ``reference`` (gloo backend).
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -25,8 +27,45 @@ def linear(x, w):
 def rmsnorm(x, weight, eps):
     if _cuda(x):
         from . import cuda_ops
+        if os.environ.get("FLEXTRAIN_RMSNORM", "") == "rows":
+            return cuda_ops.rmsnorm_rows(x, weight, eps)
         return cuda_ops.rmsnorm(x, weight, eps)
     return ref.rmsnorm(x, weight, eps)
+
+
+def gpt_native_elementwise() -> bool:
+    """Whether CUDA tensors take the package's LayerNorm / bias / GELU kernels
+    (``FLEXTRAIN_GPT_ELEMENTWISE=native``) or the ATen ones (default until the
+    kernels have been checked on hardware).  GEMMs and attention are native either way."""
+    return os.environ.get("FLEXTRAIN_GPT_ELEMENTWISE", "aten") == "native"
+
+
+def layernorm(x, weight, bias, eps):
+    if _cuda(x):
+        if gpt_native_elementwise():
+            from . import cuda_ops
+            return cuda_ops.layernorm(x, weight, bias, eps)
+        return torch.nn.functional.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+    return ref.layernorm(x, weight, bias, eps)
+
+
+def bias_add(x, bias):
+    """``x + bias`` over the last dimension (in place on CUDA with the native kernels)."""
+    if _cuda(x):
+        if gpt_native_elementwise():
+            from . import cuda_ops
+            return cuda_ops.bias_add(x, bias)
+        return x + bias
+    return ref.bias_add(x, bias)
+
+
+def bias_gelu(x, bias):
+    if _cuda(x):
+        if gpt_native_elementwise():
+            from . import cuda_ops
+            return cuda_ops.bias_gelu(x, bias)
+        return torch.nn.functional.gelu(x + bias, approximate="tanh")
+    return ref.bias_gelu(x, bias)
 
 
 def rope(x, cos, sin):

@@ -24,6 +24,22 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return (xf * inv * weight.float()).to(x.dtype)
 
 
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    mean = xf.mean(-1, keepdim=True)
+    var = (xf - mean).pow(2).mean(-1, keepdim=True)
+    return ((xf - mean) * torch.rsqrt(var + eps) * weight.float() + bias.float()).to(x.dtype)
+
+
+def bias_add(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    return (x.float() + bias.float()).to(x.dtype)
+
+
+def bias_gelu(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """tanh-approximated GELU of ``x + bias`` (the GPT-2 / Megatron form)."""
+    return F.gelu(x.float() + bias.float(), approximate="tanh").to(x.dtype)
+
+
 def rope_tables(seq_len: int, head_dim: int, theta: float, device=None,
                 dtype=torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
     """cos/sin tables of shape ``[seq_len, head_dim // 2]``."""

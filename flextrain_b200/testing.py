@@ -53,3 +53,27 @@ def build_llama_engine(model_cfg, ft_config: Dict, batch_fn, lr=1e-3, weight_dec
     ft.set_llm_func(*make_llm_funcs(model, batch_fn))
     engine = ft.initialize(model, opt, dist_init_required=False)
     return model, opt, engine
+
+
+def build_gpt_engine(model_cfg, ft_config: Dict, batch_fn, lr=1e-3, weight_decay=0.0,
+                     betas=(0.9, 0.999), eps=1e-8, adamw_mode=True, seed=0,
+                     init_device=None, dtype=torch.float32, backend: Optional[str] = None):
+    """Config -> Init -> model -> optimizer -> engine for a GPT-style model."""
+    import flextrain_b200 as ft
+    from .config import init_flextrain_config
+    from .models.gpt import GPTBlock, GPTModel, make_llm_funcs, make_param_groups, param_grouping
+    from .ops.adam import FlexTrainAdam
+    if backend is not None:
+        ft.init_distributed(dist_backend=backend, force_init=False)
+    else:
+        ft.init_distributed(force_init=False)
+    init_flextrain_config(ft_config, log=False)
+    torch.manual_seed(seed)
+    with ft.Init(layer_class=GPTBlock, num_layers=model_cfg.num_layers,
+                 param_grouping_func=param_grouping, init_device=init_device):
+        model = GPTModel(model_cfg, dtype=dtype, device=init_device)
+    opt = FlexTrainAdam(make_param_groups(model, weight_decay), lr=lr, betas=betas, eps=eps,
+                        weight_decay=weight_decay, adamw_mode=adamw_mode)
+    ft.set_llm_func(*make_llm_funcs(model, batch_fn))
+    engine = ft.initialize(model, opt, dist_init_required=False)
+    return model, opt, engine
