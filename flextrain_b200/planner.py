@@ -40,9 +40,13 @@ class ModelShape:
 
 
 def shape_of(cfg, micro_batch_size: int) -> ModelShape:
-    return ModelShape(cfg.num_layers, cfg.layer_numel, 2 * cfg.vocab * cfg.hidden + cfg.hidden,
+    """Shape of a model config of ``models.llama`` or ``models.gpt`` (anything with
+    ``num_layers``, ``layer_numel``, ``total_numel``, ``hidden``, ``ffn``, ``vocab``,
+    ``seq_len``, ``num_heads`` and optionally ``num_kv_heads``)."""
+    kv_heads = getattr(cfg, "num_kv_heads", None) or cfg.num_heads
+    return ModelShape(cfg.num_layers, cfg.layer_numel, cfg.total_numel - cfg.num_layers * cfg.layer_numel,
                       cfg.hidden, cfg.ffn, cfg.vocab, micro_batch_size * cfg.seq_len,
-                      cfg.num_kv_heads * cfg.head_dim)
+                      kv_heads * cfg.head_dim)
 
 
 def activation_bytes(s: ModelShape, interval: int = 1) -> float:
