@@ -33,6 +33,7 @@ class GPTConfig:
     eps: float = 1e-5
     init_std: float = 0.02
     tie_embeddings: bool = True
+    dropout: float = 0.0                 # embedding and residual-branch dropout (GPT-2: 0.1)
     name: str = "tiny"
 
     def __post_init__(self):
@@ -40,6 +41,8 @@ class GPTConfig:
             self.ffn = 4 * self.hidden
         if self.hidden % self.num_heads:
             raise ValueError("hidden must divide by heads")
+        if not 0.0 <= self.dropout < 1.0:
+            raise ValueError("dropout must lie in [0, 1)")
 
     @property
     def head_dim(self) -> int:
@@ -93,6 +96,12 @@ class GPTBlock(nn.Module):
         for w in (self.wo, self.w_proj):
             nn.init.normal_(w, mean=0.0, std=cfg.init_std / (2.0 * cfg.num_layers) ** 0.5)
 
+    def _drop(self, t: torch.Tensor) -> torch.Tensor:
+        # masks come from the default generator: the engine's checkpointing saves and
+        # replays its state, so the recomputed forward draws the same masks
+        p = self.cfg.dropout
+        return torch.nn.functional.dropout(t, p, True) if p > 0.0 and self.training else t
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         B, S, H = x.shape
@@ -103,10 +112,10 @@ class GPTBlock(nn.Module):
         if a is None:
             q, k, v = (t.unflatten(-1, (nh, d)) for t in qkv.split(H, dim=-1))
             a = F.causal_attention(q, k, v).reshape(B, S, H)
-        x = x + F.bias_add(F.linear(a, self.wo), self.bo)
+        x = x + self._drop(F.bias_add(F.linear(a, self.wo), self.bo))
         h = F.layernorm(x, self.ln2_w, self.ln2_b, cfg.eps)
         h = F.bias_gelu(F.linear(h, self.w_fc), self.b_fc)
-        return x + F.bias_add(F.linear(h, self.w_proj), self.b_proj)
+        return x + self._drop(F.bias_add(F.linear(h, self.w_proj), self.b_proj))
 
 
 class GPTModel(nn.Module):
@@ -137,7 +146,9 @@ class GPTModel(nn.Module):
         S = tokens.shape[1]
         if S > self.cfg.seq_len:
             raise ValueError(f"sequence of {S} tokens exceeds the position table ({self.cfg.seq_len})")
-        return torch.nn.functional.embedding(tokens, self.wte) + self.wpe[:S]
+        x = torch.nn.functional.embedding(tokens, self.wte) + self.wpe[:S]
+        p = self.cfg.dropout
+        return torch.nn.functional.dropout(x, p, True) if p > 0.0 and self.training else x
 
     def post_process(self, x: torch.Tensor) -> torch.Tensor:
         return F.layernorm(x, self.lnf_w, self.lnf_b, self.cfg.eps)

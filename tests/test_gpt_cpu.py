@@ -67,6 +67,7 @@ def _data(steps=STEPS, batch=2, seq=128, vocab=1024):
 def _reference_losses(cfg, data, lr=1e-3):
     torch.manual_seed(0)
     model = GPTModel(cfg)
+    model.train()
     decay = [p for p in model.parameters() if p.dim() > 1]
     no_decay = [p for p in model.parameters() if p.dim() <= 1]
     opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.01},
@@ -89,7 +90,7 @@ def _worker(rank, world, port, ft_config, model_kwargs, steps, queue):
     import flextrain_b200 as ft
     ft.init_distributed(dist_backend="gloo")
     cfg = preset("tiny", **model_kwargs)
-    data = _data(steps)
+    data = _data(steps, batch=ft_config["batch_size"])
     mbs = ft_config["micro_batch_size"]
     per_rank = ft_config["batch_size"] // world
     cursor = {"step": 0, "mb": 0}
@@ -159,3 +160,12 @@ def test_untied_gpt_world1_device_tier_interval2():
                                "checkpoint": [1.0, 0.0], "gradient": [1.0, 0.0], "alpha": 0.0})
     _check(_run(1, cfg, {"tie_embeddings": False}),
            _reference_losses(preset("tiny", tie_embeddings=False), _data()))
+
+
+def test_dropout_masks_are_replayed_in_the_recomputation():
+    """One micro-batch per step on one rank draws its dropout masks in the order of a
+    plain forward pass; the engine recomputes every unit in backward, so it only
+    reproduces plain AdamW if each recomputation sees the masks of its first pass."""
+    cfg = _config(batch_size=1)
+    data = _data(batch=1)
+    _check(_run(1, cfg, {"dropout": 0.1}), _reference_losses(preset("tiny", dropout=0.1), data))
