@@ -99,6 +99,8 @@ def main():
     ap.add_argument("--weight-decay", type=float, default=0.1)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--log-every", type=int, default=1)
+    ap.add_argument("--eval-every", type=int, default=0, help="validation pass every N steps (0: never)")
+    ap.add_argument("--eval-data", default=None, help="token file of the validation pass (default: --data)")
     ap.add_argument("--save-dir", default=None)
     ap.add_argument("--save-every", type=int, default=0, help="0: only at the end")
     ap.add_argument("--resume", default=None, help="directory written by --save-dir")
@@ -133,7 +135,12 @@ def main():
     mbs = ft_cfg["micro_batch_size"]
     feeder = MicroBatchFeeder(source, mbs, cfg.seq_len, device=device, rank=rank, world=world,
                               seed=args.seed)
-    flextrain.set_llm_func(*fam.make_llm_funcs(model, feeder))
+    # validation draws from its own stream through the same callback
+    eval_source = TokenFile(args.eval_data) if args.eval_data else source
+    eval_feeder = MicroBatchFeeder(eval_source, mbs, cfg.seq_len, device=device, rank=rank, world=world,
+                                   seed=args.seed + 1) if args.eval_every else None
+    active = {"feeder": feeder}
+    flextrain.set_llm_func(*fam.make_llm_funcs(model, lambda: active["feeder"]()))
     engine = flextrain.initialize(model, opt, dist_init_required=False)
 
     start_step = 0
@@ -168,6 +175,13 @@ def main():
             flextrain.distributed.print_rank0(
                 f"step {step + 1:6d}  loss {loss:8.4f}  {rep['tokens_per_s']:10.0f} tok/s  "
                 f"{rep['tflops_per_gpu']:7.1f} TFLOPS/GPU  scale {engine.loss_scale:g}")
+        if eval_feeder is not None and (step + 1) % args.eval_every == 0:
+            active["feeder"] = eval_feeder
+            val = engine.eval_iteration()
+            active["feeder"] = feeder
+            val_loss = flextrain.distributed.all_reduce_scalar(sum(float(v) for v in val) / len(val)) / world
+            flextrain.distributed.print_rank0(f"step {step + 1:6d}  validation loss {val_loss:8.4f}")
+            t_last = time.time()
         if args.save_dir and args.save_every and (step + 1) % args.save_every == 0:
             save(args.save_dir)
     engine.synchronize()
@@ -177,6 +191,8 @@ def main():
         print(json.dumps({"final_loss": losses[-1] if losses else None, "first_loss": losses[0] if losses else None,
                           "steps_done": start_step + args.steps, "losses": losses}), flush=True)
     feeder.close()
+    if eval_feeder is not None:
+        eval_feeder.close()
     engine.shutdown()
 
 

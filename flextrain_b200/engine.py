@@ -140,8 +140,8 @@ class FlexTrainEngine:
         return self.loss_scaler.dynamic
 
     # ------------------------------------------------------- per-step state
-    def _reset_context(self):
-        n = self.micro_batch_per_rank
+    def _reset_context(self, n: Optional[int] = None):
+        n = n or self.micro_batch_per_rank
         self._pre_inputs: List[Any] = [None] * n
         self._post_inputs: List[Any] = [None] * n
         self._loss_inputs: List[Any] = [None] * n
@@ -387,6 +387,47 @@ class FlexTrainEngine:
             from .auto_config import system_auto_config
             system_auto_config(self)
         return list(self._loss_results)
+
+    @torch.no_grad()
+    def eval_iteration(self, micro_batches: Optional[int] = None):
+        """Forward-only pass (validation): ``micro_batches`` micro-batches per rank
+        (default: as many as a training step) are drawn from ``get_batch`` and run
+        through every unit with the model in eval mode; returns the list of loss
+        results.  Nothing is checkpointed, no gradient exists and no state changes:
+        each unit is gathered once, all micro-batches pass through it, and the
+        activations between units stay on the compute device.  All ranks call it
+        together (the gathers are collective).  The reference has ``eval()`` but
+        no forward-only iteration (flextrain/engine.py:362-366)."""
+        n = micro_batches or self.micro_batch_per_rank
+        was_training = self._training
+        self.eval()
+        try:
+            self.opts.prune_pending()
+            self._reset_context(n)
+            acts: List[Any] = [None] * n
+            last = self.num_units - 1
+            self.para.submit_gather(0)
+            prev_unit = None
+            for u in range(self.num_units):
+                self._enter_unit(u, prev_unit, u + 1 if u < last else None, backward=False)
+                prev_unit = u
+                for mb in range(n):
+                    if u == 0:
+                        pre, post, loss_in = LLMFunc.get_batch()
+                        self._pre_inputs[mb], self._post_inputs[mb], self._loss_inputs[mb] = pre, post, loss_in
+                        acts[mb] = self._unit_function(0, mb)()
+                    else:
+                        acts[mb] = self._unit_function(u, mb)(acts[mb])
+                    if u == last:
+                        passed = _join_passed_down(self._pd_template[mb], self._pd_pos[mb], acts[mb])
+                        outputs = LLMFunc.post_process(passed, self._post_inputs[mb])
+                        self._loss_results[mb] = LLMFunc.loss(outputs, self._loss_inputs[mb])
+                        acts[mb] = None
+            self.para.release(prev_unit)
+            return list(self._loss_results)
+        finally:
+            if was_training:
+                self.train()
 
     def _mark_phase(self, name: str):
         """With ``engine.phase_timing``: record an event on the compute stream at a

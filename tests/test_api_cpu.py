@@ -138,3 +138,45 @@ def test_strict_overflow_skips_the_whole_step():
         LLMFunc.loss = staticmethod(clean_loss)
         eng.shutdown()
         reset_runtime()
+
+
+def test_eval_iteration_is_forward_only_and_matches_the_plain_model(fresh_runtime):
+    """Validation pass: the losses equal a plain forward of the same weights, the
+    model is in eval mode meanwhile (dropout off) and training resumes unchanged."""
+    from flextrain_b200.models.gpt import GPTModel, preset
+    from flextrain_b200.testing import build_gpt_engine
+    cfg = preset("tiny", num_layers=3, hidden=64, num_heads=2, vocab=128, seq_len=16, dropout=0.2)
+    gen = torch.Generator().manual_seed(5)
+    batches = [torch.randint(0, 128, (2, 17), generator=gen) for _ in range(32)]
+    served = []
+
+    def batch_fn():
+        t = batches[len(served)]
+        served.append(t)
+        return t[:, :-1], t[:, 1:]
+
+    ft_cfg = {"batch_size": 4, "micro_batch_size": 2, "checkpoint_interval": 2,
+              "mixed_precision": {"device_dtype": "fp32"},
+              "split_ratio": {"parameter": [0.5, 0.5], "optimizer": [0.0, 1.0],
+                              "checkpoint": [0.0, 1.0], "gradient": [0.0, 1.0], "alpha": 0.5}}
+    model, opt, eng = build_gpt_engine(cfg, ft_cfg, batch_fn, backend="gloo")
+    # a plain copy with the same initial weights (same seed, same construction order)
+    torch.manual_seed(0)
+    plain = GPTModel(cfg).eval()
+    got = [float(l) for l in eng.eval_iteration()]
+    assert len(got) == 2 and len(served) == 2
+    with torch.no_grad():
+        want = [float(plain(t[:, :-1], t[:, 1:])) for t in served]
+    assert max(abs(a - b) for a, b in zip(got, want)) < 1e-5
+    assert model.training                               # mode restored
+    three = eng.eval_iteration(micro_batches=3)
+    assert len(three) == 3 and len(served) == 5
+    # training after a validation pass behaves like training without it
+    l_after_eval = [float(l.detach()) for l in eng.train_iteration()]
+    assert eng.global_steps == 1 and len(l_after_eval) == 2
+    # a pass after the update sees the new weights: the same batch scores differently
+    eng.synchronize()
+    batches[len(served)] = served[0]
+    e2 = float(eng.eval_iteration(micro_batches=1)[0])
+    assert e2 == e2 and e2 != got[0] and abs(e2 - got[0]) < 1.0
+    eng.shutdown()
