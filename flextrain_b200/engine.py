@@ -551,7 +551,7 @@ class FlexTrainEngine:
         state = {
             "world_size": self.world, "rank": dist.get_rank(), "global_steps": self.global_steps,
             "skipped_steps": self.skipped_steps, "num_units": self.num_units,
-            "shard_numel": self.para.shard_numel,
+            "shard_numel": self.para.shard_numel, "unit_numel": self.para.unit_numel,
             "units": [self.opts.read_states(u) for u in range(self.num_units)],
             "non_layerwise": self.optimizer.non_layerwise_state(),
             "param_groups": self.optimizer.hyper_state(),
@@ -565,27 +565,84 @@ class FlexTrainEngine:
         return path
 
     def load(self, directory: str):
-        """Restore what ``save`` wrote (same world size and partition geometry)."""
+        """Restore what ``save`` wrote.  With the world size and partition geometry
+        of the checkpoint this rank reads its own file; otherwise (a run restarted
+        on fewer or more GPUs, e.g. after losing one) the shards are re-cut: every
+        rank assembles its new shard of each unit from the old ranks' files that
+        overlap it (read through ``mmap``, so only those pieces are touched).  RNG
+        states belong to the old ranks and are then left alone."""
         import os
         self.synchronize()
-        path = os.path.join(directory, f"rank{dist.get_rank()}_state.pt")
-        state = torch.load(path, map_location="cpu", weights_only=False)
-        if state["world_size"] != self.world or state["num_units"] != self.num_units \
-                or state["shard_numel"] != self.para.shard_numel:
-            raise ValueError("checkpoint was written with a different world size or model partition")
-        for u, states in enumerate(state["units"]):
-            self.opts.write_states(u, states)
-        self.optimizer.load_non_layerwise_state(state["non_layerwise"])
+        own = os.path.join(directory, f"rank{dist.get_rank()}_state.pt")
+        first = os.path.join(directory, "rank0_state.pt")
+        head = torch.load(first, map_location="cpu", weights_only=False, mmap=True)
+        if head["num_units"] != self.num_units:
+            raise ValueError("checkpoint was written for a different model partition "
+                             f"({head['num_units']} units, this run has {self.num_units})")
+        same = head["world_size"] == self.world and head["shard_numel"] == self.para.shard_numel
+        if same:
+            state = torch.load(own, map_location="cpu", weights_only=False)
+            for u, states in enumerate(state["units"]):
+                self.opts.write_states(u, states)
+            self.optimizer.load_non_layerwise_state(state["non_layerwise"])
+        else:
+            state = head
+            self._load_resharded(directory, head)
         self.optimizer.load_hyper_state(state["param_groups"])
         self.loss_scaler.load_state_dict(state["loss_scaler"])
         self.global_steps = state["global_steps"]
         self.skipped_steps = state["skipped_steps"]
-        torch.set_rng_state(state["rng_cpu"])
-        if state.get("rng_cuda") is not None and self.device.type == "cuda":
-            torch.cuda.set_rng_state(state["rng_cuda"])
+        if same:
+            torch.set_rng_state(state["rng_cpu"])
+            if state.get("rng_cuda") is not None and self.device.type == "cuda":
+                torch.cuda.set_rng_state(state["rng_cuda"])
         self.para.drain()
         self.synchronize()
         dist.barrier()
+
+    def _load_resharded(self, directory: str, head: Dict[str, Any]):
+        import os
+        old_world, old_shard = head["world_size"], head["shard_numel"]
+        new_shard = self.para.shard_numel
+        unit_numel = self.para.unit_numel
+        if head.get("unit_numel", unit_numel) != unit_numel or old_world * old_shard < unit_numel:
+            raise ValueError("checkpoint was written for a different model (unit size differs)")
+        files: Dict[int, Any] = {0: head}
+
+        def old(rank: int):
+            if rank not in files:
+                path = os.path.join(directory, f"rank{rank}_state.pt")
+                if not os.path.exists(path):
+                    raise FileNotFoundError(f"{path}: the checkpoint of {old_world} ranks is incomplete")
+                files[rank] = torch.load(path, map_location="cpu", weights_only=False, mmap=True)
+            return files[rank]
+
+        lo, hi = dist.get_rank() * new_shard, (dist.get_rank() + 1) * new_shard
+        kinds = len(head["units"][0])
+        for u in range(self.num_units):
+            states = [torch.zeros(new_shard, dtype=torch.float32) for _ in range(kinds)]
+            for r in range(lo // old_shard, min(old_world, (hi - 1) // old_shard + 1)):
+                a, b = max(lo, r * old_shard), min(hi, (r + 1) * old_shard)
+                src = old(r)["units"][u]
+                for k in range(kinds):
+                    states[k][a - lo:b - lo].copy_(src[k][a - r * old_shard:b - r * old_shard])
+            # what lies past the unit's true size is padding in either layout
+            if hi > unit_numel:
+                for k in range(kinds):
+                    states[k][max(0, unit_numel - lo):].zero_()
+            self.opts.write_states(u, states)
+        nl = head["non_layerwise"]
+        if nl:
+            if nl.get("sharded", False):
+                total = nl["total"]
+                pieces = [old(r)["non_layerwise"] for r in range(old_world)]
+                master = torch.cat([p["master"] for p in pieces])[:total]
+                moments = [torch.cat([p["states"][k] for p in pieces])[:total]
+                           for k in range(len(nl["states"]))]
+            else:
+                master, moments = nl["master"], nl["states"]
+            self.optimizer.load_non_layerwise_full(master, moments)
+        rank0_logger.info(f"checkpoint of {old_world} rank(s) re-cut for {self.world} rank(s)")
 
     def shutdown(self):
         self.watchdog.close()

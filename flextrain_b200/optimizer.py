@@ -369,7 +369,26 @@ class FlexTrainOptimizer:
             return {}
         return {"master": self._nl_master.detach().cpu().clone(),
                 "states": [s.detach().cpu().clone() for s in self._nl_states],
-                "sharded": bool(self._nl_fused)}
+                "sharded": bool(self._nl_fused), "total": self._nl_numel, "lo": self._nl_lo}
+
+    def load_non_layerwise_full(self, master: torch.Tensor, states):
+        """Install the state from whole vectors (``total`` elements each, any
+        rank layout it was saved under): the resharding path of ``engine.load``."""
+        if not self.non_layerwise_params:
+            return
+        total = self._nl_numel
+        if master.numel() != total or any(s.numel() != total for s in states):
+            raise ValueError("non-layerwise state of the checkpoint does not match this model")
+        lo, n = self._nl_lo, self._nl_master.numel()
+        hi = min(lo + n, total)
+
+        def piece(full):
+            out = torch.zeros(n, dtype=full.dtype)
+            if hi > lo:
+                out[:hi - lo].copy_(full[lo:hi])
+            return out
+        self.load_non_layerwise_state({"master": piece(master), "states": [piece(s) for s in states],
+                                       "sharded": bool(self._nl_fused)})
 
     def load_non_layerwise_state(self, state):
         if not state:

@@ -54,3 +54,83 @@ def test_resume_matches_uninterrupted_run():
     reset_runtime()
     assert first == straight[:3]
     assert max(abs(a - b) for a, b in zip(rest, straight[3:])) < 1e-5
+
+
+# ------------------------------------------------- resume on another world size
+def _elastic_worker(rank, world, port, directory, action, steps_before, steps_after, queue):
+    import os
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(2)
+    import flextrain_b200 as ft
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine, reset_runtime
+    ft.init_distributed(dist_backend="gloo")
+    cfg = preset("tiny", num_layers=3, hidden=64, num_heads=2, ffn=136, vocab=128, seq_len=32)
+    g = torch.Generator().manual_seed(11)
+    data = [torch.randint(0, 128, (4, 33), generator=g) for _ in range(steps_before + steps_after)]
+    per_rank = 4 // world
+    mbs = min(2, per_rank)
+    cursor = {"step": steps_before if action == "load" else 0, "mb": 0}
+
+    def batch_fn():
+        t = data[cursor["step"]]
+        lo = rank * per_rank + cursor["mb"] * mbs
+        cursor["mb"] += 1
+        if cursor["mb"] * mbs >= per_rank:
+            cursor["mb"], cursor["step"] = 0, cursor["step"] + 1
+        return t[lo:lo + mbs, :-1].contiguous(), t[lo:lo + mbs, 1:].contiguous()
+
+    ft_cfg = {"batch_size": 4, "micro_batch_size": mbs, "mixed_precision": {"device_dtype": "fp32"},
+              "split_ratio": {"parameter": [0.5, 0.5], "optimizer": [0.25, 0.75],
+                              "checkpoint": [1.0, 0.0], "gradient": [1.0, 0.0]}}
+    model, opt, eng = build_llama_engine(cfg, ft_cfg, batch_fn, lr=1e-2, weight_decay=0.01)
+
+    def loss():
+        r = eng.train_iteration()
+        local = sum(float(x.detach()) for x in r) / len(r)
+        return ft.distributed.all_reduce_scalar(local) / world
+
+    out = []
+    if action == "save":
+        for _ in range(steps_before):
+            loss()
+        eng.save(directory)
+    else:
+        eng.load(directory)
+        assert eng.global_steps == steps_before
+    out = [loss() for _ in range(steps_after)]
+    eng.synchronize()
+    eng.shutdown()
+    if rank == 0:
+        queue.put(out)
+    reset_runtime()
+
+
+def _elastic(world, directory, action, steps_before=3, steps_after=3):
+    import os
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = 27000 + (os.getpid() * 3 + world * 17 + len(action)) % 2000
+    procs = [ctx.Process(target=_elastic_worker,
+                         args=(r, world, port, directory, action, steps_before, steps_after, queue))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    out = queue.get(timeout=600)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    return out
+
+
+def test_checkpoint_of_two_ranks_resumes_on_one_and_on_four():
+    """Shards are re-cut when the world size changed: the continuation on 1 or 4
+    ranks follows the continuation of the 2 ranks that wrote the checkpoint."""
+    with tempfile.TemporaryDirectory() as d:
+        straight = _elastic(2, d, "save")            # 3 steps, save, 3 more steps
+        on_one = _elastic(1, d, "load")
+        on_four = _elastic(4, d, "load")
+    assert max(abs(a - b) for a, b in zip(on_one, straight)) < 1e-5, (on_one, straight)
+    assert max(abs(a - b) for a, b in zip(on_four, straight)) < 1e-5, (on_four, straight)
