@@ -644,6 +644,103 @@ class FlexTrainEngine:
             self.optimizer.load_non_layerwise_full(master, moments)
         rank0_logger.info(f"checkpoint of {old_world} rank(s) re-cut for {self.world} rank(s)")
 
+    # ------------------------------------------------ whole-model weights
+    def _param_names(self) -> Dict[int, str]:
+        return {id(p): name for name, p in self.model.named_parameters()}
+
+    @torch.no_grad()
+    def export_state_dict(self, dtype: torch.dtype = torch.float32) -> Optional[Dict[str, torch.Tensor]]:
+        """The model's weights by parameter name, taken from the fp32 master copies
+        of every tier and rank (what a user needs to evaluate or publish a trained
+        model; the reference offers no way to get weights out).  Collective: all
+        ranks call it, rank 0 receives the dict (CPU tensors of ``dtype``), the
+        others None.  Memory on rank 0: the whole model in ``dtype``."""
+        self.synchronize()
+        names = self._param_names()
+        rank0 = dist.get_rank() == 0
+        out: Dict[str, torch.Tensor] = {}
+        comm_dev = self.device if dist.get_backend() == "nccl" else torch.device("cpu")
+        S = self.para.shard_numel
+        for u in range(self.num_units):
+            shard = self.opts.read_states(u)[0].to(comm_dev)
+            full = torch.empty(S * self.world, dtype=torch.float32, device=comm_dev)
+            dist.all_gather(full, shard)
+            if rank0:
+                flat = full.cpu()
+                grp = self.para.unit_group(u)
+                for p, off, n, shape in zip(grp.paras, grp.offsets, grp.numels, grp.shapes):
+                    out[names[id(p)]] = flat[off:off + n].view(shape).to(dtype).clone()
+        nl = self.optimizer.non_layerwise_master_full()
+        if rank0 and nl is not None:
+            off = 0
+            for p in self.optimizer.non_layerwise_params:
+                n = p.numel()
+                out[names[id(p)]] = nl[off:off + n].view(p.shape).to(dtype).clone()
+                off += n
+        dist.barrier()
+        return out if rank0 else None
+
+    @torch.no_grad()
+    def import_state_dict(self, state_dict: Dict[str, torch.Tensor], strict: bool = True,
+                          reset_moments: bool = True):
+        """Overwrite the weights from named tensors (start from pre-trained weights):
+        fp32 masters and 16-bit copies of every tier are rewritten; Adam moments are
+        zeroed unless ``reset_moments`` is off.  Every rank passes the same dict (for
+        large models load it with ``torch.load(..., mmap=True)``) and takes its own
+        shard of each unit.  With ``strict`` every parameter must be present with its
+        shape; otherwise missing ones keep their value."""
+        self.synchronize()
+        names = self._param_names()
+        known = set(names.values())
+        if strict:
+            missing = sorted(known - set(state_dict))
+            extra = sorted(set(state_dict) - known)
+            if missing or extra:
+                raise KeyError(f"state dict does not match the model: missing {missing[:5]}, "
+                               f"unexpected {extra[:5]}")
+
+        def fill(dst: torch.Tensor, p, shape):
+            t = state_dict.get(names[id(p)])
+            if t is None:
+                return False
+            if tuple(t.shape) != tuple(shape):
+                raise ValueError(f"{names[id(p)]}: shape {tuple(t.shape)} in the state dict, "
+                                 f"{tuple(shape)} in the model")
+            dst.copy_(t.reshape(-1).to(torch.float32))
+            return True
+
+        S = self.para.shard_numel
+        lo, hi = dist.get_rank() * S, (dist.get_rank() + 1) * S
+        for u in range(self.num_units):
+            states = self.opts.read_states(u)
+            grp = self.para.unit_group(u)
+            for p, off, n, shape in zip(grp.paras, grp.offsets, grp.numels, grp.shapes):
+                a, b = max(lo, off), min(hi, off + n)
+                if a >= b:
+                    continue
+                t = state_dict.get(names[id(p)])
+                if t is None:
+                    continue
+                if tuple(t.shape) != tuple(shape):
+                    raise ValueError(f"{names[id(p)]}: shape {tuple(t.shape)} in the state dict, "
+                                     f"{tuple(shape)} in the model")
+                states[0][a - lo:b - lo].copy_(t.reshape(-1)[a - off:b - off].to(torch.float32))
+            if reset_moments:
+                for s in states[1:]:
+                    s.zero_()
+            self.opts.write_states(u, states)
+        if self.optimizer.non_layerwise_params:
+            full = self.optimizer.non_layerwise_master_full()
+            off = 0
+            for p in self.optimizer.non_layerwise_params:
+                n = p.numel()
+                fill(full[off:off + n], p, p.shape)
+                off += n
+            self.optimizer.set_non_layerwise_master(full, reset_moments)
+        self.para.drain()
+        self.synchronize()
+        dist.barrier()
+
     def shutdown(self):
         self.watchdog.close()
         self.opts.shutdown()

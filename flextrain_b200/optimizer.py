@@ -405,6 +405,35 @@ class FlexTrainOptimizer:
             import torch.distributed as tdist
             tdist.all_gather_into_tensor(self._nl_para, self._nl_para[lo:lo + n].clone())
 
+    def non_layerwise_master_full(self) -> Optional[torch.Tensor]:
+        """The fp32 master vector of all non-layerwise parameters on the CPU
+        (gathered over ranks when the state is sharded).  Collective."""
+        if not self.non_layerwise_params:
+            return None
+        local = self._nl_master.detach()
+        if self._nl_fused and dist.get_world_size() > 1:
+            import torch.distributed as tdist
+            full = torch.empty(local.numel() * dist.get_world_size(), dtype=local.dtype, device=local.device)
+            tdist.all_gather_into_tensor(full, local.contiguous())
+            return full[:self._nl_numel].cpu()
+        return local[:self._nl_numel].cpu().clone()
+
+    def set_non_layerwise_master(self, full: torch.Tensor, reset_moments: bool = True):
+        """Overwrite the master weights (and the 16-bit copies) of the non-layerwise
+        parameters from a whole vector; the moments are zeroed or kept."""
+        if not self.non_layerwise_params:
+            return
+        if full.numel() != self._nl_numel:
+            raise ValueError("non-layerwise vector does not match this model")
+        lo, n = self._nl_lo, self._nl_master.numel()
+        hi = min(lo + n, self._nl_numel)
+        piece = torch.zeros(n, dtype=torch.float32)
+        if hi > lo:
+            piece[:hi - lo].copy_(full[lo:hi])
+        states = [torch.zeros(n, dtype=torch.float32) if reset_moments else s.detach().cpu()
+                  for s in self._nl_states]
+        self.load_non_layerwise_state({"master": piece, "states": states, "sharded": bool(self._nl_fused)})
+
     def hyper_state(self):
         return [{k: v for k, v in g.items() if k != PARAMS_KEY} for g in self.param_groups]
 
