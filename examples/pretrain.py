@@ -104,6 +104,9 @@ def main():
     ap.add_argument("--save-dir", default=None)
     ap.add_argument("--save-every", type=int, default=0, help="0: only at the end")
     ap.add_argument("--resume", default=None, help="directory written by --save-dir")
+    ap.add_argument("--init-weights", default=None,
+                    help="torch file of named tensors (this package's names) to start from")
+    ap.add_argument("--export", default=None, help="write the final weights (named fp32 tensors) here")
     args = ap.parse_args()
 
     flextrain.init_distributed(dist_backend="nccl" if torch.cuda.is_available() else "gloo",
@@ -144,6 +147,8 @@ def main():
     engine = flextrain.initialize(model, opt, dist_init_required=False)
 
     start_step = 0
+    if args.init_weights:
+        engine.import_state_dict(torch.load(args.init_weights, map_location="cpu", mmap=True))
     if args.resume:
         engine.load(args.resume)
         with open(os.path.join(args.resume, f"rank{rank}_data.json")) as f:
@@ -187,6 +192,10 @@ def main():
     engine.synchronize()
     if args.save_dir:
         save(args.save_dir)
+    if args.export:
+        weights = engine.export_state_dict()           # collective; rank 0 gets the dict
+        if rank == 0:
+            torch.save(weights, args.export)
     if rank == 0:
         print(json.dumps({"final_loss": losses[-1] if losses else None, "first_loss": losses[0] if losses else None,
                           "steps_done": start_step + args.steps, "losses": losses}), flush=True)
