@@ -2,7 +2,7 @@
 """Times the native causal attention kernels against PyTorch SDPA.
 
     python benchmarks/attn_bench.py [--shapes 7b 13b 70b small] [--iters 5] [--no-sdpa]
-                                    [--pass fwd bwd]
+                                    [--pass fwd bwd] [--fwd-version N] [--bwd-version N]
 
 Shapes are (batch, seq, q heads, kv heads, head dim).  CUDA events, 3 warm-up
 launches; q/k/v/o/do of the named shapes are larger than L2 except for
@@ -47,8 +47,15 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--no-sdpa", action="store_true")
     ap.add_argument("--pass", dest="passes", nargs="+", default=["fwd", "bwd"])
+    ap.add_argument("--fwd-version", type=int, default=0, help="forward kernel generation (0: default)")
+    ap.add_argument("--bwd-version", type=int, default=0, help="backward kernel generation (0: default)")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
+    from flextrain_b200.ops.native import cuda_lib
+    if args.fwd_version:
+        cuda_lib().ft_attn_set_fwd_version(args.fwd_version)
+    if args.bwd_version:
+        cuda_lib().ft_attn_set_bwd_version(args.bwd_version)
     for name in args.shapes:
         B, S, Hq, Hkv, D = SHAPES[name]
         torch.manual_seed(0)
@@ -79,7 +86,6 @@ def main():
                 ms = timed(lambda: torch.autograd.grad(o2, (q, k, v), doh, retain_graph=True), args.iters)
                 line.append(f"sdpa {ms:.3f} ms {2.5 * fwd_flops / ms / 1e9:.0f} TF/s")
         print(" ".join(line), flush=True)
-    from flextrain_b200.ops.native import cuda_lib
     print("error word", cuda_lib().ft_gemm_error())
 
 

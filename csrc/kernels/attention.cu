@@ -1,10 +1,11 @@
-// Host launchers of the causal flash-attention kernels (attention_fwd.cuh,
-// attention_bwd.cuh).  q / k / v may be views into one packed QKV tensor: each is
+// Host launchers of the causal flash-attention kernels (attention_fwd*.cuh,
+// attention_bwd*.cuh).  q / k / v may be views into one packed QKV tensor: each is
 // described by its own base pointer and token stride, rows of H*D columns.
 // Replaces the scaled-dot-product attention library call a PyTorch model makes.
 #include <cstdlib>
 
 #include "attention_bwd.cuh"
+#include "attention_bwd2.cuh"
 #include "attention_fwd2.cuh"
 #include "attention_fwd3.cuh"
 #include "attention_fwd4.cuh"
@@ -110,6 +111,40 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   return 0;
 }
 
+// Second-generation backward (Q double-buffered, dQ on the dP columns); not yet run on a GPU,
+// never the default.
+template <typename T, int D>
+int launch_bwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
+  auto kern = attn_bwd2_kernel<T, D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd2Smem<D>::BYTES);
+    configured = true;
+  }
+  const int num_blk = (P.S + BQ - 1) / BQ;
+  kern<<<P.B * P.Hkv * num_blk, BWD_THREADS, Bwd2Smem<D>::BYTES, s>>>(tq, tk, tv, tdo, tdq, P);
+  return 0;
+}
+
+int g_bwd_version = -1;   // -1: read FLEXTRAIN_ATTN_BWD on first use (default 1)
+
+int bwd_version() {
+  if (g_bwd_version < 0) {
+    const char* e = getenv("FLEXTRAIN_ATTN_BWD");
+    g_bwd_version = e ? atoi(e) : 1;
+    if (g_bwd_version < 1 || g_bwd_version > 2) g_bwd_version = 1;
+  }
+  return g_bwd_version;
+}
+
+template <typename T, int D>
+int launch_bwd_any(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                   const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
+  return bwd_version() == 2 ? launch_bwd2<T, D>(tq, tk, tv, tdo, tdq, P, s)
+                            : launch_bwd<T, D>(tq, tk, tv, tdo, tdq, P, s);
+}
+
 template <typename T>
 void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_stride, float* delta,
                      const float* dq_acc, void* dq, int64_t dq_stride, int B, int S, int Hq, int D,
@@ -128,6 +163,9 @@ void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_strid
 }  // namespace
 
 extern "C" {
+
+// Selects the backward kernel generation for later ft_attn_bwd calls (1: default, 2).
+void ft_attn_set_bwd_version(int v) { g_bwd_version = (v == 2) ? 2 : 1; }
 
 // Selects the forward kernel generation for later ft_attn_fwd calls (1 to 4; 2 is the default).
 void ft_attn_set_fwd_version(int v) { g_fwd_version = (v >= 1 && v <= 4) ? v : 2; }
@@ -206,13 +244,13 @@ int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.split_qdo = getenv("FLEXTRAIN_ATTN_BWD_SPLIT") ? atoi(getenv("FLEXTRAIN_ATTN_BWD_SPLIT")) : 0;
   if (dtype == kBF16) {
     launch_pre_post<__nv_bfloat16>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
-    if (D == 128) launch_bwd<__nv_bfloat16, 128>(tq, tk, tv, tdo, tdq, P, stream);
-    else launch_bwd<__nv_bfloat16, 64>(tq, tk, tv, tdo, tdq, P, stream);
+    if (D == 128) launch_bwd_any<__nv_bfloat16, 128>(tq, tk, tv, tdo, tdq, P, stream);
+    else launch_bwd_any<__nv_bfloat16, 64>(tq, tk, tv, tdo, tdq, P, stream);
     launch_pre_post<__nv_bfloat16>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, scale, stream);
   } else {
     launch_pre_post<__half>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
-    if (D == 128) launch_bwd<__half, 128>(tq, tk, tv, tdo, tdq, P, stream);
-    else launch_bwd<__half, 64>(tq, tk, tv, tdo, tdq, P, stream);
+    if (D == 128) launch_bwd_any<__half, 128>(tq, tk, tv, tdo, tdq, P, stream);
+    else launch_bwd_any<__half, 64>(tq, tk, tv, tdo, tdq, P, stream);
     launch_pre_post<__half>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, scale, stream);
   }
   FT_LAUNCHED(3);

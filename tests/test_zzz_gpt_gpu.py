@@ -1,4 +1,4 @@
-"""GPT family on one B200.
+"""GPT family on one B200, and kernels that have not yet run on hardware.
 
 The engine test runs a bf16 tiny GPT with the native GEMM, attention and head
 kernels and the ATen LayerNorm / GELU (the default).  The tests of the package's
@@ -6,6 +6,8 @@ own LayerNorm / bias / GELU / row-RMSNorm kernels, and of the engine on top of
 them, run when ``FLEXTRAIN_TEST_NEW_KERNELS=1``: those kernels are newer than
 the last hardware session of this file and are switched on by that variable
 (tests) or ``FLEXTRAIN_GPT_ELEMENTWISE=native`` / ``FLEXTRAIN_RMSNORM=rows`` (use).
+The same variable runs the second-generation attention backward
+(``FLEXTRAIN_ATTN_BWD=2``) and the fourth-generation forward (``FLEXTRAIN_ATTN_FWD=4``).
 """
 import math
 import os
@@ -136,3 +138,68 @@ def test_gpt_engine_with_native_elementwise(monkeypatch):
     native = _run_engine(ALL_HBM)
     assert max(abs(a - b) for a, b in zip(aten, native)) < 3e-2, (aten, native)
     assert native[-1] < native[0] - 0.05
+
+
+def _attention_grads(q, k, v, do, scale):
+    from flextrain_b200.ops.attention_native import attention_native
+    o = attention_native(q, k, v, scale)
+    return (o,) + torch.autograd.grad(o, (q, k, v), do)
+
+
+@new_kernels
+@pytest.mark.parametrize("shape", [
+    (1, 128, 2, 2, 128), (2, 384, 8, 2, 128), (1, 1000, 2, 2, 128), (2, 640, 4, 4, 64), (1, 2048, 4, 1, 128),
+])
+def test_attention_backward_second_generation(shape):
+    """Backward with the double-buffered Q and dQ on the dP columns against the
+    first generation (validated) and against the fp32 oracle."""
+    from flextrain_b200.ops import reference as ref
+    from flextrain_b200.ops.native import cuda_lib
+    B, S, Hq, Hkv, D = shape
+    lib = cuda_lib()
+    torch.manual_seed(S + D + Hq)
+    mk = lambda h: torch.randn(B, S, h, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)  # noqa: E731
+    q, k, v = mk(Hq), mk(Hkv), mk(Hkv)
+    do = torch.randn(B, S, Hq, D, device=_dev(), dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    base = _attention_grads(q, k, v, do, scale)
+    lib.ft_attn_set_bwd_version(2)
+    try:
+        for _ in range(3):                              # repeated: ordering bugs are timing dependent
+            got = _attention_grads(q, k, v, do, scale)
+            torch.cuda.synchronize()
+            assert lib.ft_gemm_error() == 0
+            for g, b in zip(got[1:], base[1:]):
+                assert _rel_err(g, b) < 5e-3
+    finally:
+        lib.ft_attn_set_bwd_version(1)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    of = ref.causal_attention(qf, kf, vf, scale)
+    want = torch.autograd.grad(of, (qf, kf, vf), do.float())
+    for g, w in zip(got[1:], want):
+        assert _rel_err(g, w) < 3e-2
+
+
+@new_kernels
+@pytest.mark.parametrize("shape", [(1, 128, 2, 2, 128), (2, 384, 8, 2, 128), (1, 1000, 2, 2, 128), (2, 640, 4, 4, 64)])
+def test_attention_forward_fourth_generation(shape):
+    """Forward with two threads per score row against the default forward."""
+    from flextrain_b200.ops.attention_native import attention_forward
+    from flextrain_b200.ops.native import cuda_lib
+    B, S, Hq, Hkv, D = shape
+    lib = cuda_lib()
+    torch.manual_seed(S + D)
+    q = torch.randn(B, S, Hq, D, device=_dev(), dtype=torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, device=_dev(), dtype=torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, device=_dev(), dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    o2, lse2, _ = attention_forward(q, k, v, scale)
+    lib.ft_attn_set_fwd_version(4)
+    try:
+        for _ in range(3):
+            o4, lse4, _ = attention_forward(q, k, v, scale)
+            torch.cuda.synchronize()
+            assert lib.ft_gemm_error() == 0
+            assert _rel_err(o4, o2) < 1e-2 and float((lse4 - lse2).abs().max()) < 1e-2
+    finally:
+        lib.ft_attn_set_fwd_version(2)
