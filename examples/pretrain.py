@@ -32,6 +32,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import flextrain_b200 as flextrain  # noqa: E402
 from flextrain_b200.config import init_flextrain_config  # noqa: E402
 from flextrain_b200.data import MicroBatchFeeder, SyntheticTokens, TokenFile  # noqa: E402
+from flextrain_b200.lr_schedule import LRSchedule  # noqa: E402
 from flextrain_b200.ops.adam import FlexTrainAdam  # noqa: E402
 from flextrain_b200.utils.timer import ThroughputReporter, llama_flops_per_token  # noqa: E402
 
@@ -96,6 +97,9 @@ def main():
     ap.add_argument("--micro-batches-per-rank", type=int, default=2, help="without --flextrain-config")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--warmup-steps", type=int, default=0)
+    ap.add_argument("--lr-decay", default="constant", choices=["constant", "cosine", "linear"])
+    ap.add_argument("--total-steps", type=int, default=0, help="length of the decay (default: --steps)")
     ap.add_argument("--weight-decay", type=float, default=0.1)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--log-every", type=int, default=1)
@@ -146,20 +150,26 @@ def main():
     flextrain.set_llm_func(*fam.make_llm_funcs(model, lambda: active["feeder"]()))
     engine = flextrain.initialize(model, opt, dist_init_required=False)
 
+    sched = LRSchedule(opt, peak_lr=args.lr, warmup_steps=args.warmup_steps,
+                       total_steps=(args.total_steps or args.steps) if args.lr_decay != "constant" else None,
+                       decay=args.lr_decay)
+    engine.register_post_step_function(sched.step)
     start_step = 0
     if args.init_weights:
         engine.import_state_dict(torch.load(args.init_weights, map_location="cpu", mmap=True))
     if args.resume:
         engine.load(args.resume)
         with open(os.path.join(args.resume, f"rank{rank}_data.json")) as f:
-            feeder.load_state_dict(json.load(f))
+            extra = json.load(f)
+        feeder.load_state_dict(extra["data"])
+        sched.load_state_dict(extra["lr_schedule"])
         start_step = engine.global_steps + engine.skipped_steps
         flextrain.rank0_logger.info(f"resumed from {args.resume} at step {start_step}")
 
     def save(directory):
         engine.save(directory)
         with open(os.path.join(directory, f"rank{rank}_data.json"), "w") as f:
-            json.dump(feeder.state_dict(), f)
+            json.dump({"data": feeder.state_dict(), "lr_schedule": sched.state_dict()}, f)
 
     tokens_per_step = ft_cfg["batch_size"] * cfg.seq_len
     fpt = llama_flops_per_token(cfg.num_layers, cfg.hidden, cfg.ffn, cfg.vocab, cfg.seq_len,
@@ -169,6 +179,7 @@ def main():
                                 f"{tokens_per_step} tokens per step on {world} rank(s), device {device}")
     t_last, losses = time.time(), []
     for step in range(start_step, start_step + args.steps):
+        lr_used = sched.current_lrs[0]
         out = engine.train_iteration()
         local = sum(float(l.detach().float()) for l in out) / len(out)       # reads the loss back
         loss = flextrain.distributed.all_reduce_scalar(local) / world
@@ -179,7 +190,7 @@ def main():
             t_last = now
             flextrain.distributed.print_rank0(
                 f"step {step + 1:6d}  loss {loss:8.4f}  {rep['tokens_per_s']:10.0f} tok/s  "
-                f"{rep['tflops_per_gpu']:7.1f} TFLOPS/GPU  scale {engine.loss_scale:g}")
+                f"{rep['tflops_per_gpu']:7.1f} TFLOPS/GPU  lr {lr_used:.3g}  scale {engine.loss_scale:g}")
         if eval_feeder is not None and (step + 1) % args.eval_every == 0:
             active["feeder"] = eval_feeder
             val = engine.eval_iteration()
