@@ -50,12 +50,17 @@ def main(args, metric, micro_batch_table):
         dev = torch.device("cuda", torch.cuda.current_device())
         name = args.model
         if name == "auto":
-            name = _auto_model(world, torch, psutil, SHAPES)
+            name = _auto_model(world, torch, psutil, SHAPES, micro_batch_table, args)
         shape = dict(SHAPES[name])
         if args.seq_len:
             shape["seq_len"] = args.seq_len
         if args.layers:
             shape["num_layers"] = args.layers
+        short = _host_capacity_shortfall(shape, psutil)
+        if short is not None:
+            if rank == 0:
+                _unavailable(f"{name} on {world} GPU(s): {short}")
+            return
         mbs = micro_batch_table.get(name, 2)
         mbpr = args.micro_batches_per_rank or 1
         seq = shape["seq_len"]
@@ -184,17 +189,58 @@ def main(args, metric, micro_batch_table):
             _unavailable(f"reference run failed: {type(exc).__name__}: {str(exc)[:300]}")
 
 
-def _auto_model(world, torch, psutil, shapes):
-    """Same rule as the other arm: the largest model whose 14 bytes/parameter of
-    state fit the HBM + host DRAM of the ranks."""
+def _numel(s):
+    kv = s["num_kv_heads"] * (s["hidden"] // s["num_heads"])
+    layer = 2 * s["hidden"] + s["hidden"] * (s["hidden"] + 2 * kv) + s["hidden"] ** 2 \
+        + 3 * s["hidden"] * s["ffn"]
+    return layer, s["num_layers"] * layer + 2 * s["vocab"] * s["hidden"] + s["hidden"]
+
+
+def _auto_model(world, torch, psutil, shapes, micro_batch_table=None, args=None):
+    """The model the other arm trains on this many ranks: the largest of the three
+    shapes for which that arm's capacity planner finds a tier split (HBM first, then
+    host DRAM).  The planner is a stand-alone pure-Python file; it is loaded by path so
+    that nothing else of that package enters this process."""
+    import importlib.util
+    import types
+    path = os.path.join(os.path.dirname(HERE), "flextrain_b200", "planner.py")
+    spec = importlib.util.spec_from_file_location("_ft_capacity_planner", path)
+    planner = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = planner          # dataclasses looks the module up by name
+    spec.loader.exec_module(planner)
     hbm, _ = torch.cuda.mem_get_info()
-    dram = psutil.virtual_memory().available * 0.85
+    dram = psutil.virtual_memory().available
+    table = micro_batch_table or {}
+    mbpr = (getattr(args, "micro_batches_per_rank", 0) or 1) if args is not None else 1
+    buffers = getattr(args, "unit_buffers", 3) if args is not None else 3
+    alpha = getattr(args, "alpha", 0.25) if args is not None else 0.25
     for name in ("llama3-70b", "llama2-13b", "llama2-7b"):
-        s = shapes[name]
-        kv = s["num_kv_heads"] * (s["hidden"] // s["num_heads"])
-        layer = 2 * s["hidden"] + s["hidden"] * (s["hidden"] + 2 * kv) + s["hidden"] ** 2 \
-            + 3 * s["hidden"] * s["ffn"]
-        total = s["num_layers"] * layer + 2 * s["vocab"] * s["hidden"] + s["hidden"]
-        if total * 14 < world * hbm * 0.8 + dram:
+        s = dict(shapes[name])
+        if args is not None and getattr(args, "seq_len", 0):
+            s["seq_len"] = args.seq_len
+        if args is not None and getattr(args, "layers", 0):
+            s["num_layers"] = args.layers
+        layer, total = _numel(s)
+        cfg = types.SimpleNamespace(num_layers=s["num_layers"], layer_numel=layer, total_numel=total,
+                                    hidden=s["hidden"], ffn=s["ffn"], vocab=s["vocab"], seq_len=s["seq_len"],
+                                    num_heads=s["num_heads"], num_kv_heads=s["num_kv_heads"],
+                                    head_dim=s["hidden"] // s["num_heads"])
+        shape = planner.shape_of(cfg, table.get(name, 2))
+        budget = planner.MemoryBudget(hbm, dram / world * 0.85, 0.0)
+        if planner.plan(shape, world, mbpr, budget, unit_buffers=buffers, alpha=alpha) is not None:
             return name
     return "llama2-7b"
+
+
+def _host_capacity_shortfall(shape, psutil):
+    """The reference keeps every parameter (2 B), its fp32 master copy and both Adam
+    moments (12 B) in pinned host DRAM, whatever the number of GPUs.  Returns a one-line
+    reason when that exceeds 92 % of what the box has available, else None: building the
+    model anyway would pin (or exhaust) nearly all memory of a shared machine."""
+    _, total = _numel(shape)
+    need = total * 14
+    have = psutil.virtual_memory().available
+    if need > 0.92 * have:
+        return (f"the reference keeps all parameters and optimizer state in host DRAM "
+                f"({need / 1e9:.0f} GB for this model) and the box offers {have / 1e9:.0f} GB")
+    return None
