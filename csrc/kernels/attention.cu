@@ -240,8 +240,6 @@ int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.B = B; P.S = S; P.Hq = Hq; P.Hkv = Hkv;
   P.scale = scale; P.scale_log2 = scale * 1.4426950408889634f;
   P.err = gemm::error_word(dev);
-  P.debug_skip = getenv("FLEXTRAIN_ATTN_DEBUG_SKIP") ? atoi(getenv("FLEXTRAIN_ATTN_DEBUG_SKIP")) : 0;
-  P.split_qdo = getenv("FLEXTRAIN_ATTN_BWD_SPLIT") ? atoi(getenv("FLEXTRAIN_ATTN_BWD_SPLIT")) : 0;
   if (dtype == kBF16) {
     launch_pre_post<__nv_bfloat16>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
     if (D == 128) launch_bwd_any<__nv_bfloat16, 128>(tq, tk, tv, tdo, tdq, P, stream);

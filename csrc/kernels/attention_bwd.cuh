@@ -40,7 +40,6 @@ struct BwdSmem {
 struct BwdBars {
   uint64_t kv_full, qdo_full, qdo_empty, s_full, dp_full, p_full, ds_full, dq_full, s_free, acc_full;
   uint64_t dqs_full, stage_free;
-  uint64_t do_full, do_empty;          // used with BwdParams::split_qdo
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -54,9 +53,6 @@ struct BwdParams {
   int B, S, Hq, Hkv;
   float scale, scale_log2;
   int* err;
-  int debug_skip;          // profiling aid: bit 0 skips the dq atomics, bit 1 skips exp
-  int split_qdo;           // 1: dO_m is released right after dV and Q_m after dK (separate barriers), so
-                           //    the next block's loads overlap the tail of this block; 0: one barrier pair
 };
 
 // fp32 tile in shared memory (128B-swizzled [rows][32] slab) added into global memory
@@ -111,8 +107,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->dqs_full, 256);
     mbar_init(&bars->stage_free, 1);
-    mbar_init(&bars->do_full, 1);
-    mbar_init(&bars->do_empty, 1);
     bars->abort = 0;
     fence_barrier_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
@@ -138,17 +132,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int head = kv_head * group + it / q_blocks;
         const int m = nb + it % q_blocks;
         const int q_row0 = batch * P.S + m * BQ;
-        if (P.split_qdo) {
-          if (!mbar_wait(&bars->do_empty, (it & 1) ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 413); break; }
-          mbar_expect_tx(&bars->do_full, TILE);
-          for (int c = 0; c < CHUNKS; ++c)
-            tma_load_2d(sdO + c * CHUNK_BYTES, &tmap_do, &bars->do_full, head * D + c * 64, q_row0);
-          if (!mbar_wait(&bars->qdo_empty, (it & 1) ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 401); break; }
-          mbar_expect_tx(&bars->qdo_full, TILE);
-          for (int c = 0; c < CHUNKS; ++c)
-            tma_load_2d(sQ + c * CHUNK_BYTES, &tmap_q, &bars->qdo_full, head * D + c * 64, q_row0);
-          continue;
-        }
         if (!mbar_wait(&bars->qdo_empty, (it & 1) ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 401); break; }
         mbar_expect_tx(&bars->qdo_full, 2 * TILE);
         for (int c = 0; c < CHUNKS; ++c) {
@@ -179,10 +162,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                    kk != 0);
         }
         umma_commit(&bars->s_full);
-        if (P.split_qdo) {
-          if (!mbar_wait(&bars->do_full, ph)) { atomicCAS(P.err, 0, 414); ok = false; break; }
-          tc_fence_after();
-        }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
@@ -198,7 +177,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dv, make_smem_desc(aP + row_off, CHUNK_BYTES, 1024),
                    make_smem_desc(aDO + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
         }
-        if (P.split_qdo) umma_commit(&bars->do_empty);
         if (!mbar_wait(&bars->ds_full, ph)) { atomicCAS(P.err, 0, 409); ok = false; break; }
         tc_fence_after();
 #pragma unroll
@@ -207,14 +185,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dk, make_smem_desc(aDS + row_off, CHUNK_BYTES, 1024),
                    make_smem_desc(aQ + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
         }
-        if (P.split_qdo) umma_commit(&bars->qdo_empty);
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {      // reduction over the 128 kv rows
           const uint32_t a_off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
           umma_f16(tm_dq, make_smem_desc(aDS + a_off, 16, 1024),
                    make_smem_desc(aK + kk * 2048, CHUNK_BYTES, 1024), id_q, kk != 0);
         }
-        if (!P.split_qdo) umma_commit(&bars->qdo_empty);
+        umma_commit(&bars->qdo_empty);
         umma_commit(&bars->dq_full);
       }
       if (ok) umma_commit(&bars->acc_full);
@@ -227,13 +204,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int head = kv_head * group + it / q_blocks;
         const int m = nb + it % q_blocks;
         if (!mbar_wait(&bars->dqs_full, it & 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 411); break; }
-        if (!(P.debug_skip & 1)) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c)
-            tma_reduce_add_2d(&tmap_dq, sP + c * (BQ * 128), head * D + c * 32, batch * P.S + m * BQ);
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        }
+        for (int c = 0; c < D / 32; ++c)
+          tma_reduce_add_2d(&tmap_dq, sP + c * (BQ * 128), head * D + c * 32, batch * P.S + m * BQ);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         mbar_arrive(&bars->stage_free);
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -279,8 +254,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             float a, b;
             pm::unpack2(pm::fma2(pm::pack2(__uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1])), scale2,
                                  neg_lse22), a, b);
-            p[cc][i] = (P.debug_skip & 2) ? a : pm::ex2(a);
-            p[cc][i + 1] = (P.debug_skip & 2) ? b : pm::ex2(b);
+            p[cc][i] = pm::ex2(a);
+            p[cc][i + 1] = pm::ex2(b);
           }
           if (diag) {
 #pragma unroll
