@@ -27,6 +27,7 @@
 #include <unordered_map>
 
 #include "gemm2_kernel.cuh"
+#include "gemm2_swiglu.cuh"
 #include "gemm_host.h"
 
 namespace {
@@ -218,6 +219,31 @@ int launch_pair(int a_mn, int b_mn, int mode, const CUtensorMap& ta, const CUten
 int g_use_pair = -1;   // -1: read FLEXTRAIN_GEMM_PAIR on first use
 
 template <typename T>
+int launch_pair_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, void* act, int64_t ld_act, void* gu,
+                       int64_t ld_gu, int M, int F, int K, int* err, int grid, cudaStream_t s) {
+  auto kern = gemm_pair_swiglu_kernel<T>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, act, ld_act, gu, ld_gu, M, F, K, err);
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+template <typename T>
 int launch_layout(int a_mn, int b_mn, int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
                   int64_t ldc, int M, int N, int K, int* err, int grid, cudaStream_t s) {
   if (!a_mn && !b_mn) return launch_mode<T, false, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
@@ -277,6 +303,36 @@ int ft_gemm(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64
     else
       rc = launch_layout<__half>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
   }
+  if (rc) return rc;
+  FT_LAUNCHED(1);
+  FT_CUDA_RETURN_IF_ERROR();
+  return 0;
+}
+
+// act[M,F] = silu(X Wg^T) * (X Wu^T) with W = [Wg ; Wu] stored [2F, K] (row stride ldw), X stored
+// [M, K] (row stride ldx); gu (optional, [M, 2F], row stride ld_gu) receives the two projections
+// as the unfused path would have stored them.  Returns -4 when the shape is not covered (F not a
+// multiple of 128, fewer than 129 rows): the caller then runs ft_gemm + the activation kernel.
+int ft_gemm_swiglu(const void* X, int64_t ldx, const void* W, int64_t ldw, void* act, int64_t ld_act,
+                   void* gu, int64_t ld_gu, int M, int F, int K, int dtype, cudaStream_t stream) {
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if (dtype != kBF16 && dtype != kF16) return -1;
+  if (F % 128 || M <= 128) return -4;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* err = error_word(dev);
+  CUtensorMap ta, tb;
+  int rc = make_tmap(&ta, X, (uint64_t)K, (uint64_t)M, (uint64_t)ldx, BK, BM, dtype);
+  if (rc) return rc;
+  rc = make_tmap(&tb, W, (uint64_t)K, (uint64_t)(2 * F), (uint64_t)ldw, BK, 128, dtype);
+  if (rc) return rc;
+  const int tiles = ((M + P_BM - 1) / P_BM) * (F / 128);
+  const int pairs = sm_count(dev) / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  if (dtype == kBF16)
+    rc = launch_pair_swiglu<__nv_bfloat16>(ta, tb, act, ld_act, gu, ld_gu, M, F, K, err, grid, stream);
+  else
+    rc = launch_pair_swiglu<__half>(ta, tb, act, ld_act, gu, ld_gu, M, F, K, err, grid, stream);
   if (rc) return rc;
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();

@@ -99,7 +99,7 @@ class LlamaBlock(nn.Module):
             if packed is not None:
                 x = x + F.linear(packed, self.wo)
                 h = F.rmsnorm(x, self.ffn_norm, cfg.eps)
-                return x + F.linear(F.swiglu(F.linear(h, self.w_gate_up)), self.w_down)
+                return x + F.linear(F.linear_swiglu(h, self.w_gate_up), self.w_down)
         q = qkv[..., : nh * d].unflatten(-1, (nh, d))
         k = qkv[..., nh * d: (nh + nkv) * d].unflatten(-1, (nkv, d))
         v = qkv[..., (nh + nkv) * d:].unflatten(-1, (nkv, d))
@@ -108,7 +108,7 @@ class LlamaBlock(nn.Module):
         a = F.causal_attention(q, k, v).reshape(B, S, H)
         x = x + F.linear(a, self.wo)
         h = F.rmsnorm(x, self.ffn_norm, cfg.eps)
-        x = x + F.linear(F.swiglu(F.linear(h, self.w_gate_up)), self.w_down)
+        x = x + F.linear(F.linear_swiglu(h, self.w_gate_up), self.w_down)
         return x
 
 

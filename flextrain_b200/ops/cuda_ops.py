@@ -319,6 +319,63 @@ def swiglu(gate_up):
     return _SwiGLU.apply(gate_up)
 
 
+class _LinearSwiGLU(torch.autograd.Function):
+    """``swiglu(x @ w.T)`` for ``w = [w_gate ; w_up]`` with the activation in the
+    GEMM's epilogue.  The ``[rows, 2F]`` projection is materialised only when a
+    backward pass will need it (it is stored from the epilogue's registers, never
+    read back in the forward)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        k = x.shape[-1]
+        x2 = x.reshape(-1, k)
+        if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
+            x2 = x2.contiguous()
+        rows, f = x2.shape[0], w.shape[0] // 2
+        need_gu = any(ctx.needs_input_grad[:2])
+        act = torch.empty(rows, f, dtype=x.dtype, device=x.device)
+        gu = torch.empty(rows, 2 * f, dtype=x.dtype, device=x.device) if need_gu else None
+        lib = cuda_lib()
+        rc = lib.ft_gemm_swiglu(ptr(x2), x2.stride(0), ptr(w), w.stride(0), ptr(act), f, ptr(gu), 2 * f,
+                                rows, f, k, dtype_code(x.dtype), stream_handle())
+        if rc == -4:                                   # shape outside the fused kernel: two steps
+            gu = torch.empty(rows, 2 * f, dtype=x.dtype, device=x.device)
+            gemm(x2, False, w, False, rows, 2 * f, k, out=gu)
+            _check(lib.ft_swiglu_fwd(ptr(gu), ptr(act), rows, f, dtype_code(x.dtype), stream_handle()),
+                   "ft_swiglu_fwd")
+            if not need_gu:
+                gu = None
+        else:
+            _check(rc, "ft_gemm_swiglu")
+        ctx.save_for_backward(x2, w, gu)
+        ctx.x_shape = x.shape
+        return act.view(*x.shape[:-1], f)
+
+    @staticmethod
+    def backward(ctx, dact):
+        x2, w, gu = ctx.saved_tensors
+        rows, f2 = gu.shape
+        k = w.shape[1]
+        d2 = dact.reshape(rows, f2 // 2).contiguous()
+        dgu = torch.empty_like(gu)
+        _check(cuda_lib().ft_swiglu_bwd(ptr(gu), ptr(d2), ptr(dgu), rows, f2 // 2, dtype_code(gu.dtype),
+                                        stream_handle()), "ft_swiglu_bwd")
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dgu, False, w, True, rows, k, f2).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            g = w.grad
+            if g is not None and g.shape == w.shape and g.is_contiguous() and g.dtype == w.dtype:
+                gemm(dgu, True, x2, True, f2, k, rows, out=g, accumulate=True)
+            else:
+                dw = gemm(dgu, True, x2, True, f2, k, rows)
+        return dx, dw
+
+
+def linear_swiglu(x, w_gate_up):
+    return _LinearSwiGLU.apply(x, w_gate_up)
+
+
 # ---------------------------------------------------------------- attention
 def _attn_impl() -> str:
     return os.environ.get("FLEXTRAIN_ATTN", "native")

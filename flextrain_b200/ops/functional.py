@@ -100,6 +100,16 @@ def swiglu(gate_up):
     return ref.swiglu(gate_up)
 
 
+def linear_swiglu(x, w_gate_up):
+    """``swiglu(linear(x, w_gate_up))``; with ``FLEXTRAIN_SWIGLU=epilogue`` on CUDA the
+    activation runs in the epilogue of the projection GEMM (default: two kernels, until
+    the fused one has been checked on hardware)."""
+    if _cuda(x) and os.environ.get("FLEXTRAIN_SWIGLU", "") == "epilogue":
+        from . import cuda_ops
+        return cuda_ops.linear_swiglu(x, w_gate_up)
+    return swiglu(linear(x, w_gate_up))
+
+
 def causal_attention(q, k, v, scale=None):
     if _cuda(q):
         from . import cuda_ops

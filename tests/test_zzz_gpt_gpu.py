@@ -203,3 +203,26 @@ def test_attention_forward_fourth_generation(shape):
             assert _rel_err(o4, o2) < 1e-2 and float((lse4 - lse2).abs().max()) < 1e-2
     finally:
         lib.ft_attn_set_fwd_version(2)
+
+
+@new_kernels
+@pytest.mark.parametrize("rows,k,f", [(256, 256, 128), (520, 320, 384), (4096, 1024, 2816), (200, 256, 136)])
+def test_swiglu_in_the_gemm_epilogue(rows, k, f):
+    """Projection GEMM with the activation in its epilogue against the two-kernel path
+    (values and all gradients); the last shape is outside the fused kernel and must take
+    the fallback inside the same op."""
+    from flextrain_b200.ops import cuda_ops
+    from flextrain_b200.ops.native import cuda_lib
+    torch.manual_seed(rows + k + f)
+    x = (torch.randn(rows, k, device=_dev()) * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(2 * f, k, device=_dev()) * 0.05).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(rows, f, device=_dev(), dtype=torch.bfloat16)
+    want = cuda_ops.swiglu(cuda_ops.linear(x, w))
+    wx, ww = torch.autograd.grad(want, (x, w), dy)
+    got = cuda_ops.linear_swiglu(x, w)
+    gx, gw = torch.autograd.grad(got, (x, w), dy)
+    torch.cuda.synchronize()
+    assert cuda_lib().ft_gemm_error() == 0
+    assert _rel_err(got, want) < 1e-2 and _rel_err(gx, wx) < 1e-2 and _rel_err(gw, ww) < 1e-2
+    with torch.no_grad():                                  # no backward ahead: nothing but the activation is written
+        assert _rel_err(cuda_ops.linear_swiglu(x, w), want) < 1e-2
