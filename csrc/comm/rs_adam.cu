@@ -17,7 +17,10 @@
 // waits for the same from them, so kernel completion means the local gradient
 // buffer may be overwritten).  CTAs never wait for each other, only for other
 // GPUs, so no co-residency is assumed.  All spins are bounded; on expiry an
-// error word is set and the kernel returns.
+// error word is set, the CTA skips its share of the work and still goes through the
+// end barrier (counter and done words), so one late rank costs one wrong step on the
+// fused path (the engine then switches to NCCL) instead of desynchronising every
+// later call.
 //
 // Replaces, on the reference's path, the NCCL reduce-scatter of
 // flextrain/memory/coordinator/optimizer.py:550-552, the D2H scatter :554-580 and
@@ -109,12 +112,15 @@ __global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ Rs
     s_ok = ok;
   }
   __syncthreads();
-  if (!s_ok) return;
+  // A CTA whose start wait ran out skips the work but still takes part in the end barrier
+  // below: leaving here would keep the CTA counter short and the peers without this rank's
+  // done word, and every later call on this slot would then wait out its budget as well.
+  const bool run = s_ok != 0;
 
   // ---- reduce + update
   const int64_t base = (int64_t)R * P.shard;
   bool bad = false;
-  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < P.shard;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; run && i < P.shard;
        i += (int64_t)gridDim.x * blockDim.x * 8) {
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < W; ++k) {
@@ -177,7 +183,9 @@ __global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ Rs
       if (W > 1) {
         for (int p = 0; p < W; ++p)
           if (p != R) st_release_sys(P.peers.flags[p] + P.done_slot * kMaxRanks + R, P.seq);
-        for (int p = 0; p < W; ++p)
+        // a rank that gave up at the start has read nothing: it owes the peers its done word
+        // (sent above) but has no reason to wait for theirs
+        for (int p = 0; p < W && run; ++p)
           if (p != R && !wait_seq(mine + P.done_slot * kMaxRanks + p, P.seq, P.spin_budget)) atomicCAS(P.err, 0, 102);
       }
     }
