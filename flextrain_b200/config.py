@@ -174,6 +174,12 @@ class EngineConfig:
         self.nvtx = bool(section.get(D.NVTX, D.NVTX_DEFAULT))
         self.phase_timing = bool(section.get(D.PHASE_TIMING, D.PHASE_TIMING_DEFAULT))
         self.fused_blocks_setting = int(section.get(D.FUSED_BLOCKS, D.FUSED_BLOCKS_DEFAULT))
+        waits = section.get(D.FUSED_WAIT_SECONDS, D.FUSED_WAIT_SECONDS_DEFAULT)
+        if isinstance(waits, (int, float)):
+            waits = (waits, waits)
+        if len(waits) != 2 or min(waits) <= 0:
+            raise ValueError("engine.fused_wait_seconds must be a positive number or [steady, first step]")
+        self.fused_wait_seconds = (float(waits[0]), float(waits[1]))
         self.fused_nonlayer = section.get(D.FUSED_NONLAYER, D.FUSED_NONLAYER_DEFAULT)
         self.gather_lag = section.get(D.GATHER_LAG, D.GATHER_LAG_DEFAULT)
         for key, val in ((D.FUSED_NONLAYER, self.fused_nonlayer), (D.GATHER_LAG, self.gather_lag)):

@@ -103,6 +103,8 @@ GATHER_LAG = "gather_lag"                  # lagged completion signalling in the
 GATHER_LAG_DEFAULT = "auto"                # "auto": on up to 2 ranks
 FUSED_BLOCKS = "fused_blocks"              # CTAs of the fused collective kernels
 FUSED_BLOCKS_DEFAULT = 0                   # 0: 148 up to 2 ranks, 64 above (the sizes each was run on)
+FUSED_WAIT_SECONDS = "fused_wait_seconds"  # [steady state, first step]: limit of every cross-GPU wait of
+FUSED_WAIT_SECONDS_DEFAULT = (10.0, 30.0)  # the fused kernels (first-step allocations make ranks drift more)
 NUM_UNIT_BUFFERS = "num_unit_buffers"      # HBM unit buffers in the gather ring
 NUM_UNIT_BUFFERS_DEFAULT = 2
 STRICT_OVERFLOW = "strict_overflow"        # hold every update until the step's

@@ -193,8 +193,8 @@ class FlexTrainEngine:
     def _enter_unit(self, unit: int, prev_unit: Optional[int], next_unit: Optional[int],
                     backward: bool):
         self._trace(f"enter unit {unit} ({'bwd' if backward else 'fwd'}), prefetch {next_unit}")
-        if self.global_steps == 0 and unit % 8 == 7:
-            # first step only: look at the fused kernels' error words every few units, so that a
+        if self.global_steps == 0 and unit % 2 == 1:
+            # first step only: look at the fused kernels' error words every other unit, so that a
             # systematic time-out costs a few waits, not one per unit, before NCCL takes over
             self._fused_health_check()
         if prev_unit is not None and prev_unit != unit:
@@ -320,7 +320,11 @@ class FlexTrainEngine:
         self.heartbeat.beat(self.global_steps)
         self.watchdog.step_started()
         try:
+            if self.global_steps == 0:
+                self._set_fused_wait(first_step=True)
             result = self._train_iteration(cfg)
+            if self.global_steps == 1:
+                self._set_fused_wait(first_step=False)
             if self.global_steps <= 2:
                 self._fused_health_check()
             return result
@@ -495,6 +499,15 @@ class FlexTrainEngine:
     # reduce kernels (101, 102) and of the gather (201 .. 204, reported in the GEMM error word)
     _COMM_TIMEOUTS = (101, 102)
     _GATHER_TIMEOUTS = (201, 202, 203, 204)
+
+    def _set_fused_wait(self, first_step: bool):
+        """Wait limit of the fused kernels: longer during the first step, whose one-off
+        allocations and module loads let ranks drift apart further than they ever do later."""
+        if self.device.type != "cuda" or self.world == 1 or not (self.opts._fused or self.para._peer_gather):
+            return
+        from .parallel import fused
+        steady, first = self.config.engine.fused_wait_seconds
+        fused.set_wait_seconds(first if first_step else steady, self.device)
 
     def _fused_health_check(self):
         """After each of the first two steps on more than one GPU: if a cross-GPU

@@ -143,6 +143,23 @@ def ag_gemm(world: int, rank: int, w_ptrs, flag_ptrs, seq: int, x: torch.Tensor,
     return out
 
 
+def set_wait_seconds(seconds: float, device=None):
+    """Limit of every cross-GPU wait inside the fused kernels (start / end barriers of the
+    reduce kernels, start / end / per-block waits of the gather), converted to SM clock
+    cycles at the device's maximum clock.  Applies to kernels launched afterwards."""
+    try:
+        props = torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device())
+        khz = int(getattr(props, "clock_rate", 0)) or 1_965_000
+    except Exception:                                              # the limit matters, its exact length does not
+        khz = 1_965_000
+    cycles = int(float(seconds) * khz * 1e3)
+    lib = _ag_lib()
+    lib.ft_comm_set_spin_budget.argtypes = [ctypes.c_longlong]
+    lib.ft_comm_set_spin_budget(cycles)
+    lib.ft_ag_set_spin_budget(cycles)
+    return cycles
+
+
 def set_gather_lag(on: bool):
     """Completion signalling of the copy role in ``ag_gemm`` / ``peer_gather``:
     lagged by the ring depth (keeps the copy stream full) or one store at a time."""

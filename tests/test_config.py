@@ -66,3 +66,12 @@ def test_singleton_and_json_path(tmp_path):
     assert get_flextrain_config() is c
     assert json.loads(json.dumps(c.to_dict(), default=str))["batch_size"] == 2
     reset_flextrain_config()
+
+
+def test_fused_wait_limits():
+    base = {"batch_size": 4, "micro_batch_size": 1}
+    assert FlexTrainConfig(base).engine.fused_wait_seconds == (10.0, 30.0)
+    assert FlexTrainConfig({**base, "engine": {"fused_wait_seconds": 5}}).engine.fused_wait_seconds == (5.0, 5.0)
+    assert FlexTrainConfig({**base, "engine": {"fused_wait_seconds": [8, 20]}}).engine.fused_wait_seconds == (8.0, 20.0)
+    with pytest.raises(ValueError):
+        FlexTrainConfig({**base, "engine": {"fused_wait_seconds": [1, 0]}})
