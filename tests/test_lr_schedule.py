@@ -69,6 +69,6 @@ def test_engine_applies_the_rate_of_each_step(fresh_runtime):
         loss.backward()
         topt.step()
         ref.step()
-        want.append(float(loss))
+        want.append(float(loss.detach()))
     assert max(abs(a - b) for a, b in zip(got, want)) < 2e-5, (got, want)
     assert not math.isclose(want[-1], want[0])
