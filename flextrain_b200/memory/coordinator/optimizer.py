@@ -320,8 +320,9 @@ class FlexTrainOptsCoordinator:
         if og:
             self._para.note_gpu_base_write(unit, done)
         if entry is not None:
+            groups = self._hyper_snapshot()
             fut = self._worker.submit(
-                unit, lambda: self._host_update(unit, entry, done, step, host_scale))
+                unit, lambda: self._host_update(unit, entry, done, step, host_scale, groups))
             self._para.add_host_update(unit, FutureHandle(fut))
             self._pending.append(fut)
 
@@ -392,7 +393,13 @@ class FlexTrainOptsCoordinator:
             tier_copy(self._para.cpu_base(unit)[: og - g], stage[: og - g])
 
     # ---------------------------------------------------------- host update
-    def _host_update(self, unit, entry: _PoolEntry, grads_ready: Event, step, grad_scale):
+    def _hyper_snapshot(self):
+        """Hyper-parameters of every param group as they are now.  A host update runs later,
+        possibly during the next step's forward: it must use the rates of the step whose
+        gradients it applies, not whatever a scheduler has written since."""
+        return [{k: v for k, v in g.items() if k != "params"} for g in self.optimizer.param_groups]
+
+    def _host_update(self, unit, entry: _PoolEntry, grads_ready: Event, step, grad_scale, groups=None):
         try:
             grads_ready.synchronize()
             if self.check_overflow and int(entry.flag.item()) != 0:
@@ -401,7 +408,8 @@ class FlexTrainOptsCoordinator:
             og, oc, on = self.opt_tiers
             g, c, n = self.para_tiers
             para = self._para
-            groups = self.optimizer.param_groups
+            if groups is None:
+                groups = self.optimizer.param_groups
             segs = self._segments[unit]
             # device-dtype destinations, in shard coordinates
             out_hbm_hi = max(og, min(g, self.S))     # [og, out_hbm_hi) -> entry.out -> gpu_base
@@ -515,8 +523,9 @@ class FlexTrainOptsCoordinator:
         if og:
             self._para.note_gpu_base_write(unit, done)
         if entry is not None:
+            groups = self._hyper_snapshot()
             fut = self._worker.submit(
-                unit, lambda u=unit, e=entry, d=done, sc=scale: self._host_update(u, e, d, step, sc))
+                unit, lambda u=unit, e=entry, d=done, sc=scale, g=groups: self._host_update(u, e, d, step, sc, g))
             self._para.add_host_update(unit, FutureHandle(fut))
             self._pending.append(fut)
 
