@@ -245,7 +245,10 @@ class FlexTrainParaCoordinator:
         if unit in self._inflight or unit in self._held or not 0 <= unit < self.num_units:
             return
         if self._direct:
-            self._inflight[unit] = (-1, self._gpu_base_ready.get(unit, DONE))
+            # nothing to copy; what has to be awaited (host updates that still write into the
+            # base copy) is awaited when the unit is taken, not here, so that a prefetch of the
+            # next unit never blocks the launch of the current one
+            self._inflight[unit] = (-1, None)
             return
         if unit in self._cached:
             self._inflight[unit] = self._cached.pop(unit)
@@ -302,6 +305,11 @@ class FlexTrainParaCoordinator:
         if unit not in self._inflight:
             self.submit_gather(unit)
         idx, ready = self._inflight.pop(unit)
+        if idx < 0:
+            # computing straight from the base copy: the host share of the last update must have
+            # landed in it (the worker records the event of its copy before it reports done)
+            self.wait_host_updates(unit)
+            ready = self._gpu_base_ready.get(unit, DONE)
         self.streams.compute.wait(ready)
         self._unit_groups[unit].link_para_to(self._gpu_base[unit] if idx < 0 else self._buffers[idx])
         self._held[unit] = idx

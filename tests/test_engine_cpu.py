@@ -273,3 +273,16 @@ def test_world2_clipping_with_device_and_nvme_tiers():
                                    "checkpoint": [0.5, 0.5], "gradient": [1.0, 0.0], "alpha": 0.25},
                       nvme_swap={"swap_dir": tmp})
         _check(_run(2, cfg), ref, tol=2e-5)
+
+
+def test_world1_parameters_in_place_with_host_optimizer(ref_losses):
+    """All parameters on the compute device at world size 1 (the engine then computes
+    straight from the base copy, no gather) while the optimizer state lives on the host:
+    the next step's forward of a unit must wait for that unit's host update to have
+    landed in the base copy.  Three buffers and host checkpoints make the forward reach
+    the unit early enough to lose the race if it does not."""
+    cfg = _config(engine={"num_unit_buffers": 3}, checkpoint_interval=2,
+                  split_ratio={"optimizer": [0.0, 1.0], "parameter": [1.0, 0.0],
+                               "checkpoint": [0.5, 0.5], "gradient": [1.0, 0.0], "alpha": 0.0})
+    for _ in range(2):
+        _check(_run(1, cfg), ref_losses)
