@@ -509,19 +509,22 @@ class FlexTrainEngine:
         steady, first = self.config.engine.fused_wait_seconds
         fused.set_wait_seconds(first if first_step else steady, self.device)
 
-    def _fused_health_check(self):
+    def _fused_health_check(self, read_words=None):
         """After each of the first two steps on more than one GPU: if a cross-GPU
         wait of the fused collective kernels ran out on any rank, all ranks switch
         to the NCCL collectives for the rest of the run (a step that waited out
         its budget is wrong anyway, and the next ones would crawl from time-out to
-        time-out).  Costs one device synchronisation and a scalar all-reduce."""
-        if self.device.type != "cuda" or self.world == 1:
-            return
-        if not (self.opts._fused or self.para._peer_gather):
-            return
-        from .ops.native import cuda_lib
-        lib = cuda_lib()
-        gemm_word, comm_word = lib.ft_gemm_error(), lib.ft_comm_error()
+        time-out).  Costs one device synchronisation and a scalar all-reduce.
+        ``read_words`` (tests) replaces the device error words by ``() -> (gather, reduce)``."""
+        if read_words is None:
+            if self.device.type != "cuda" or self.world == 1:
+                return
+            if not (self.opts._fused or self.para._peer_gather):
+                return
+            from .ops.native import cuda_lib
+            lib = cuda_lib()
+            read_words = lambda: (lib.ft_gemm_error(), lib.ft_comm_error())     # noqa: E731
+        gemm_word, comm_word = read_words()
         if gemm_word and gemm_word not in self._GATHER_TIMEOUTS:
             self._status["gemm_error_word_seen"] = gemm_word     # reading cleared it: keep it visible
         bad = comm_word in self._COMM_TIMEOUTS or gemm_word in self._GATHER_TIMEOUTS

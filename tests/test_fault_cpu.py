@@ -88,3 +88,52 @@ def test_watchdog_trips_on_a_slow_step(fresh_runtime):
     eng.train_iteration()
     assert eng.health()["watchdog_tripped"]
     eng.shutdown()
+
+
+def _fallback_worker(rank, world, port, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    import flextrain_b200 as ft
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine, reset_runtime
+    ft.init_distributed("gloo")
+    cfg = preset("tiny", num_layers=2, hidden=64, num_heads=2, ffn=128, vocab=128, seq_len=16)
+    tok = torch.randint(0, 128, (1, 17))
+    ft_cfg = {"batch_size": 2, "micro_batch_size": 1, "mixed_precision": {"device_dtype": "fp32"}}
+    model, opt, eng = build_llama_engine(cfg, ft_cfg, lambda: (tok[:, :-1], tok[:, 1:]))
+    # pretend the peer-memory kernels are in use, then report a wait that ran out on ONE rank only
+    eng.opts._fused = True
+    eng.para._peer_gather = True
+    eng._fused_health_check(read_words=lambda: (0, 0))
+    clean = (eng.opts._fused, eng.para._peer_gather)
+    eng._fused_health_check(read_words=lambda: (7, 0))          # a GEMM-internal code is kept, not a time-out
+    kept = eng.health().get("gemm_error_word_seen")
+    eng._fused_health_check(read_words=lambda: (0, 101) if rank == 1 else (0, 0))
+    after = (eng.opts._fused, eng.para._peer_gather, eng.health().get("fused_collectives_disabled"))
+    loss = float(eng.train_iteration()[0].detach())             # and the run goes on, on the library collectives
+    eng.shutdown()
+    q.put((rank, clean, kept, after, loss))
+    reset_runtime()
+
+
+def test_timeout_on_one_rank_switches_every_rank_to_library_collectives():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29950 + os.getpid() % 40
+    procs = [ctx.Process(target=_fallback_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in procs:
+        rank, clean, kept, after, loss = q.get(timeout=120)
+        got[rank] = (clean, kept, after, loss)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank in (0, 1):
+        clean, kept, after, loss = got[rank]
+        assert clean == (True, True)                    # no time-out: nothing changes
+        assert kept == 7
+        assert after == (False, False, True), f"rank {rank} did not switch: {after}"
+        assert loss == loss
