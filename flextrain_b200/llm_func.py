@@ -54,6 +54,12 @@ def set_llm_func(get_layer: Callable[[int], Module],
     LLMFunc.loss = staticmethod(loss)
 
 
+def reset_llm_func():
+    """Forget the registered callbacks (and with them the model they close over)."""
+    for name in ("get_layer", "get_batch", "pre_process", "layer_forward", "post_process", "loss"):
+        setattr(LLMFunc, name, _unset(name))
+
+
 def retrieve_llm_loss(loss_rsts) -> Tensor:
     """The numerical loss inside whatever the user's loss callback returned."""
     if isinstance(loss_rsts, Tensor):

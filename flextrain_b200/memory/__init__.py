@@ -163,6 +163,8 @@ def get_split_numels(total: int, ratios: Sequence[float], itemsize: int,
     for r in ratios:
         acc += r
         cut = min(total, int(round(acc * total / per_page)) * per_page)
+        if acc >= 1.0 - 1e-9:
+            cut = total            # a full share is a full share, also for tensors smaller than a page
         cut = max(cut, used)
         out.append(cut - used)
         used = cut

@@ -8,14 +8,16 @@ import torch
 
 
 def reset_runtime():
-    """Forget config, coordinators, streams, swapper and the process group."""
+    """Forget config, coordinators, streams, swapper, callbacks and the process group."""
     from .config import reset_flextrain_config
+    from .llm_func import reset_llm_func
     from .memory.coordinator.interlayer import reset_interlayer_coordinator
     from .memory.coordinator.optimizer import reset_opts_coordinator
     from .memory.coordinator.parameter import reset_para_coordinator
     from .memory.nvme_swapper import reset_nvme_swapper
     from .utils import distributed as dist
     from .utils.device import reset_streams
+    reset_llm_func()
     reset_opts_coordinator()
     try:
         from .parallel.symm_mem import reset_flag_page

@@ -15,6 +15,8 @@ def test_config_arguments():
 
 
 def test_llm_func_registry_and_loss_retrieval():
+    from flextrain_b200.llm_func import reset_llm_func
+    reset_llm_func()
     with pytest.raises(NotImplementedError):
         LLMFunc.get_batch()
     set_llm_func(lambda i: i, lambda: ((1,), (), ()), lambda x: (x, ()), lambda s, e: (lambda *a: a),
