@@ -285,7 +285,9 @@ def run_ours(args):
                           "parallelism": f"zero3-dp{world}", "split_ratio": split,
                           "l2": "inputs and weights per step exceed L2 (126 MB) many times over",
                           "flops": "model FLOPs, 6*N*tokens + attention, recompute not counted",
-                          "larger_models_skipped": skipped},
+                          "larger_models_skipped": skipped,
+                          "across_n": "the model is the largest that fits N ranks, so tokens/s at different N "
+                                      "may refer to different models: compare tflops_per_gpu"},
                "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
                "init_seconds": init_s, "skipped_steps": health["skipped_steps"],
                "error_words": {"gemm": health.get("gemm_error_word"), "comm": health.get("comm_error_word")}}
