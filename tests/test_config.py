@@ -75,3 +75,20 @@ def test_fused_wait_limits():
     assert FlexTrainConfig({**base, "engine": {"fused_wait_seconds": [8, 20]}}).engine.fused_wait_seconds == (8.0, 20.0)
     with pytest.raises(ValueError):
         FlexTrainConfig({**base, "engine": {"fused_wait_seconds": [1, 0]}})
+
+
+def test_wait_limit_reaches_the_native_library():
+    """The setter converts seconds to clock cycles and hands them to both kernel families
+    (no GPU needed: the library only stores the number)."""
+    import ctypes
+    from flextrain_b200.ops.native import cuda_lib
+    from flextrain_b200.parallel import fused
+    lib = cuda_lib()
+    lib.ft_comm_spin_budget.restype = ctypes.c_longlong
+    try:
+        cycles = fused.set_wait_seconds(30.0)
+        assert 30 * 1.0e9 < cycles < 30 * 3.0e9 and lib.ft_comm_spin_budget() == cycles
+        assert fused.set_wait_seconds(10.0) * 3 == cycles
+    finally:
+        lib.ft_comm_set_spin_budget(0)
+        lib.ft_ag_set_spin_budget(0)
