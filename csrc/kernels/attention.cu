@@ -16,6 +16,13 @@ namespace {
 using namespace ft;
 using namespace ft::attn;
 
+// dynamic shared memory a CTA may ask for on sm_100 (227 KB)
+constexpr int kMaxDynamicSmem = 232448;
+static_assert(FwdSmem<128>::BYTES <= kMaxDynamicSmem && Fwd2Smem<128>::BYTES <= kMaxDynamicSmem &&
+                  Fwd3Smem<128>::BYTES <= kMaxDynamicSmem && Fwd4Smem<128>::BYTES <= kMaxDynamicSmem &&
+                  BwdSmem<128>::BYTES <= kMaxDynamicSmem && Bwd2Smem<128>::BYTES <= kMaxDynamicSmem,
+              "an attention kernel outgrew the shared memory of an SM");
+
 template <typename T, int D>
 int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
                cudaStream_t s) {

@@ -145,6 +145,9 @@ int sm_count(int dev) {
 
 namespace {
 
+static_assert(SMEM_BYTES <= 232448 && P_SMEM_BYTES <= 232448 && P_SMEM_BYTES_GATHER <= 232448,
+              "a GEMM kernel outgrew the 227 KB of dynamic shared memory of an SM");
+
 template <typename T, bool A_MN, bool B_MN>
 int launch_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64_t ldc, int M, int N,
                 int K, int* err, int grid, cudaStream_t s) {
