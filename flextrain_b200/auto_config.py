@@ -19,7 +19,6 @@ What differs, on purpose
 from __future__ import annotations
 
 import os
-import tempfile
 import time
 from dataclasses import asdict, dataclass, field
 from typing import Dict, List, Optional
@@ -352,7 +351,6 @@ def measure_machine(engine, iters: int = 10, swap_dir: Optional[str] = None) -> 
     itemsize = lambda dt: torch.empty((), dtype=dt).element_size()  # noqa: E731
     if dev.type == "cuda":
         free, _total = torch.cuda.mem_get_info()
-        from .memory import allocated_bytes
         vram = (free + torch.cuda.memory_reserved() - torch.cuda.memory_allocated()
                 + _tier_bytes(engine, "hbm")) * D.ACCESSIBLE_GPU_MEMORY_RATIO
     else:

@@ -21,8 +21,8 @@ from typing import Any, Callable, Dict, List, Optional, Tuple
 
 import torch
 
-from .checkpointing import (FWDContext, RNGStatePack, checkpointed_backward, checkpointed_forward,
-                            detach_variable, retrieve_tensor)
+from .checkpointing import (FWDContext, RNGStatePack, checkpointed_backward, detach_variable,
+                            retrieve_tensor)
 from .config import get_flextrain_config
 from .llm_func import LLMFunc, retrieve_llm_loss
 from .loss_scaler import create_loss_scaler

@@ -9,7 +9,7 @@ requirements (flextrain/auto_config.py:3, flextrain/engine.py:7).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 

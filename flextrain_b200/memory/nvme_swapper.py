@@ -12,9 +12,8 @@ from __future__ import annotations
 
 import ctypes
 import os
-import shutil
 from ctypes import c_char_p, c_int, c_int64, c_void_p
-from typing import Dict, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 

@@ -11,7 +11,6 @@ a power of two) has to be used.
 """
 from __future__ import annotations
 
-from functools import lru_cache
 from typing import List, Sequence, Tuple
 
 import torch

@@ -7,7 +7,7 @@ two fp32 states per element; ``_step`` -> ``adam_update[_copy]``).
 from __future__ import annotations
 
 import itertools
-from typing import Dict, List, Optional, Sequence
+from typing import Optional
 
 import torch
 

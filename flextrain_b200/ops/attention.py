@@ -11,7 +11,6 @@ from __future__ import annotations
 import math
 import os
 
-import torch
 import torch.nn.functional as F
 
 from .native import cuda_lib

@@ -6,7 +6,6 @@ fallback here: if the CUDA library is missing these raise.
 """
 from __future__ import annotations
 
-import math
 import os
 from typing import Optional
 

@@ -10,13 +10,12 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_int64, c_uint32, c_void_p
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import torch
 
 from ..ops.native import cuda_lib, dtype_code, ptr, stream_handle
 from ..param_group import GroupSegment
-from .symm_mem import FlagPage, SymmetricBuffer
 
 
 class _AdamSegment(ctypes.Structure):
