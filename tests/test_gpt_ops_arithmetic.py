@@ -145,3 +145,33 @@ def test_bias_backward_tiling(rows, N):
     assert (touched == 1).all()
     assert not np.isnan(db_part).any()
     assert np.allclose(db_part.sum(0), dy.sum(0), atol=1e-9)
+
+
+@pytest.mark.parametrize("M,F", [(256, 128), (520, 384), (4096, 11008), (32768, 13824), (8192, 28672)])
+def test_swiglu_gemm_tile_mapping(M, F):
+    """Tile walk of ``gemm_pair_swiglu_kernel`` (csrc/kernels/gemm2_swiglu.cuh): per output
+    tile the leader CTA stages gate rows and its partner the up rows of the SAME output
+    columns; accumulator columns [0,128) / [128,256) of a row therefore pair up element by
+    element.  Every output element must be produced exactly once."""
+    assert F % 128 == 0
+    mt, nt = (M + 255) // 256, F // 128
+    pairs = 74
+    out_cols = np.zeros(F, np.int64)
+    out_rows = np.zeros(M, np.int64)
+    for pair in range(min(pairs, mt * nt)):
+        for t in range(pair, mt * nt, pairs):
+            mb, nb = t // nt, t % nt                      # any bijection works for the check
+            w_rows = {cta: nb * 128 + cta * F for cta in (0, 1)}
+            assert 0 <= w_rows[0] and w_rows[0] + 128 <= F            # gate block
+            assert F <= w_rows[1] and w_rows[1] + 128 <= 2 * F        # up block of the same columns
+            assert w_rows[1] - F == w_rows[0]
+            for c in range(4):                            # epilogue chunks of 32 columns
+                col0 = nb * 128 + c * 32
+                assert col0 + 32 <= F
+                if mb == 0:
+                    out_cols[col0:col0 + 32] += 1
+            if nb == 0:
+                for cta in (0, 1):
+                    lo = mb * 256 + cta * 128
+                    out_rows[lo:min(lo + 128, M)] += 1
+    assert (out_cols == 1).all() and (out_rows == 1).all()
