@@ -43,7 +43,7 @@ import torch
 
 from ...config import get_flextrain_config
 from ...param_group import GroupSegment, create_step_contexts, slice_segments
-from ...utils import distributed as dist
+from ...utils import chaos, distributed as dist
 from ...utils.device import DONE, Event, get_streams
 from ...utils.logging import rank0_logger
 from .. import (tier_copy, FlexTrainDataID, FlexTrainDataType, FutureHandle, allocate_memory,
@@ -81,6 +81,7 @@ class _HostWorker:
                 fut.set_result(None)
                 return
             try:
+                chaos.perturb("host worker picks up a task")
                 fut.set_result(fn())
             except BaseException as exc:      # surfaced by whoever waits on the future
                 fut.set_exception(exc)
@@ -402,6 +403,7 @@ class FlexTrainOptsCoordinator:
     def _host_update(self, unit, entry: _PoolEntry, grads_ready: Event, step, grad_scale, groups=None):
         try:
             grads_ready.synchronize()
+            chaos.perturb("host update has its gradients")
             if self.check_overflow and int(entry.flag.item()) != 0:
                 self._host_overflow = True
                 return
@@ -449,6 +451,7 @@ class FlexTrainOptsCoordinator:
                     para.gpu_base(unit)[og:out_hbm_hi].copy_(entry.out[: out_hbm_hi - og],
                                                              non_blocking=True)
                     ev = st.h2d.record()
+                chaos.perturb("host update copied back, not yet announced")
                 para.note_gpu_base_write(unit, ev)
                 ev.synchronize()
         finally:

@@ -107,3 +107,13 @@ def test_drawn_configuration_matches_adamw(seed, fresh_runtime):
     want = _reference(cfg, data, mbs, 1e-3, 0.01, clip)
     worst = max(abs(a - b) for a, b in zip(got, want))
     assert worst < TOL, f"{what}: loss differs from AdamW by {worst}"
+
+
+@pytest.mark.parametrize("seed", [34, 39, 257])
+def test_drawn_configuration_under_timing_perturbation(seed, fresh_runtime, monkeypatch):
+    """The same check with the background threads slowed down at random at their hand-over
+    points (``utils/chaos.py``): a consumer that does not wait for its producer shows."""
+    from flextrain_b200.utils import chaos
+    monkeypatch.setattr(chaos, "_MAX_MS", 12.0)
+    assert chaos.enabled()
+    test_drawn_configuration_matches_adamw(seed, fresh_runtime)
