@@ -152,3 +152,18 @@ def test_pointer_and_wide_return_types_are_declared():
             if got != want:
                 bad.append(f"{name}: returns {want} in C, restype is {fn.restype}")
     assert not bad, "\n".join(bad)
+
+
+def test_every_entry_point_named_in_python_exists_in_a_library():
+    libs = _declared()
+    named = set()
+    for base in ("flextrain_b200", "benchmarks", "tests"):
+        for root, dirs, files in os.walk(os.path.join(ROOT, base)):
+            dirs[:] = [d for d in dirs if d != "__pycache__"]
+            for f in files:
+                if f.endswith(".py"):
+                    named.update(re.findall(r"\b(?:lib|_lib\(\)|cuda_lib\(\)|host_lib\(\)|_ag_lib\(\))\.(ft_\w+)",
+                                            open(os.path.join(root, f)).read()))
+    assert len(named) > 50
+    missing = [n for n in sorted(named) if not any(hasattr(lib, n) for lib in libs)]
+    assert not missing, f"not exported by libft_cuda / libft_host: {missing}"
