@@ -167,3 +167,30 @@ def test_every_entry_point_named_in_python_exists_in_a_library():
     assert len(named) > 50
     missing = [n for n in sorted(named) if not any(hasattr(lib, n) for lib in libs)]
     assert not missing, f"not exported by libft_cuda / libft_host: {missing}"
+
+
+def test_call_sites_pass_as_many_arguments_as_the_c_function_takes():
+    import ast
+    c = _c_signatures()
+    checked, bad = 0, []
+    for base in ("flextrain_b200", "benchmarks"):
+        for root, dirs, files in os.walk(os.path.join(ROOT, base)):
+            dirs[:] = [d for d in dirs if d != "__pycache__"]
+            for f in files:
+                if not f.endswith(".py"):
+                    continue
+                path = os.path.join(root, f)
+                for node in ast.walk(ast.parse(open(path).read())):
+                    if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute)):
+                        continue
+                    name = node.func.attr
+                    if not name.startswith("ft_") or name not in c:
+                        continue
+                    if node.keywords or any(isinstance(a, ast.Starred) for a in node.args):
+                        continue
+                    checked += 1
+                    if len(node.args) != len(c[name]):
+                        bad.append(f"{os.path.relpath(path, ROOT)}:{node.lineno} {name}: {len(node.args)} arguments, "
+                                   f"C takes {len(c[name])}")
+    assert not bad, "\n".join(bad)
+    assert checked > 60, f"only {checked} call sites were found"
