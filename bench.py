@@ -48,6 +48,7 @@ def parse_args():
     p.add_argument("--unit-buffers", type=int, default=3)
     p.add_argument("--alpha", type=float, default=0.25)
     p.add_argument("--split", default="", help="JSON split_ratio override")
+    p.add_argument("--engine", default="", help="JSON object merged into the config's engine section")
     p.add_argument("--phases", action="store_true",
                    help="also report the device time of forward / backward / finish of the last step")
     return p.parse_args()
@@ -179,6 +180,8 @@ def run_ours(args):
                                "dynamic_loss_scaling": False, "loss_scale": 1.0},
            "nvme_swap": {"swap_dir": os.path.join(tempfile.gettempdir(), "ft_b200_swap")},
            "engine": {"num_unit_buffers": args.unit_buffers, "phase_timing": bool(args.phases)}}
+    if args.engine:
+        cfg["engine"].update(json.loads(args.engine))
     init_flextrain_config(cfg, log=rank == 0)
     t_init = time.time()
     torch.manual_seed(0)
@@ -285,6 +288,7 @@ def run_ours(args):
                           "parallelism": f"zero3-dp{world}", "split_ratio": split,
                           "l2": "inputs and weights per step exceed L2 (126 MB) many times over",
                           "flops": "model FLOPs, 6*N*tokens + attention, recompute not counted",
+                          "engine_overrides": json.loads(args.engine) if args.engine else None,
                           "larger_models_skipped": skipped,
                           "across_n": "the model is the largest that fits N ranks, so tokens/s at different N "
                                       "may refer to different models: compare tflops_per_gpu"},
