@@ -81,15 +81,3 @@ def test_fp16_dynamic_loss_scale_runs():
     losses, health = _run(ALL_HBM, steps=5, dtype="fp16")
     assert all(l == l for l in losses)
     assert losses[-1] < losses[0]
-
-
-def test_parameters_in_place_with_host_optimizer_share():
-    """The single-GPU benchmark layout: every parameter in HBM (units are computed straight
-    from the base copy, nothing is gathered) while part of the optimizer state is updated
-    on the host and copied back asynchronously."""
-    base, _ = _run(ALL_HBM, steps=5)
-    split = {"parameter": [1.0, 0.0], "optimizer": [0.5, 0.5], "checkpoint": [1.0, 0.0],
-             "gradient": [1.0, 0.0], "alpha": 0.25}
-    got, health = _run(split, steps=5, buffers=3)
-    assert max(abs(a - b) for a, b in zip(base, got)) < 2e-3, (base, got)
-    assert health["skipped_steps"] == 0

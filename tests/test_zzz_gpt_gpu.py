@@ -1,4 +1,6 @@
-"""GPT family on one B200, and kernels that have not yet run on hardware.
+"""GPT family on one B200, the in-place parameter layout with a host optimizer share, and
+kernels that have not yet run on hardware.  The file sorts last on purpose: what is new
+here runs after the established GPU tests.
 
 The engine test runs a bf16 tiny GPT with the native GEMM, attention and head
 kernels and the ATen LayerNorm / GELU (the default).  The tests of the package's
@@ -73,6 +75,48 @@ def test_gpt_trains_through_the_engine():
     assert base[-1] < base[0] - 0.05
     tiered = _run_engine(TIERED)
     assert max(abs(a - b) for a, b in zip(base, tiered)) < 2e-3, (base, tiered)
+
+
+def test_parameters_in_place_with_host_optimizer_share():
+    """The single-GPU benchmark layout on a tiny Llama: every parameter in HBM (units are
+    computed straight from the base copy, nothing is gathered) while part of the optimizer
+    state is updated on the host and copied back asynchronously."""
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine, reset_runtime
+
+    def run(split, buffers):
+        reset_runtime()
+        dev = _dev()
+        cfg = preset("tiny", num_layers=4, hidden=256, num_heads=4, ffn=768, vocab=1024, seq_len=256)
+        gen = torch.Generator().manual_seed(1)
+        data = [torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=gen).to(dev) for _ in range(2)]
+        it = {"i": 0}
+
+        def batch_fn():
+            t = data[it["i"] % 2]
+            it["i"] += 1
+            return t[:, :-1], t[:, 1:]
+
+        ft_cfg = {"batch_size": 4, "micro_batch_size": 2, "mixed_precision": {"device_dtype": "bf16"},
+                  "split_ratio": split, "engine": {"num_unit_buffers": buffers}}
+        model, opt, eng = build_llama_engine(cfg, ft_cfg, batch_fn, lr=1e-3, init_device=dev,
+                                             dtype=torch.bfloat16)
+        losses = []
+        for _ in range(5):
+            r = eng.train_iteration()
+            losses.append(sum(float(x) for x in r) / len(r))
+        eng.synchronize()
+        health = eng.health()
+        eng.shutdown()
+        reset_runtime()
+        return losses, health
+
+    base, _ = run(ALL_HBM, 2)
+    split = {"parameter": [1.0, 0.0], "optimizer": [0.5, 0.5], "checkpoint": [1.0, 0.0],
+             "gradient": [1.0, 0.0], "alpha": 0.25}
+    got, health = run(split, 3)
+    assert max(abs(a - b) for a, b in zip(base, got)) < 2e-3, (base, got)
+    assert health["skipped_steps"] == 0
 
 
 @new_kernels
