@@ -92,6 +92,8 @@ class FlexTrainEngine:
         self._phase_timing = bool(cfg.engine.phase_timing) and self.device.type == "cuda"
         import os as _os
         self._trace_on = bool(_os.environ.get("FLEXTRAIN_TRACE"))
+        from .memory import guard_mode
+        self._guard_mode = guard_mode()
         self._phase_events = []          # [(name, event)] of the last step
         self._last_overflow = False
         self._status: Dict[str, Any] = {"last_step_seconds": None, "watchdog_tripped": False}
@@ -327,6 +329,8 @@ class FlexTrainEngine:
                 self._set_fused_wait(first_step=False)
             if self.global_steps <= 2:
                 self._fused_health_check()
+            if self._guard_mode:
+                self.check_guards()
             return result
         except PeerFailure:
             raise
@@ -535,6 +539,14 @@ class FlexTrainEngine:
             self.opts._fused = False
             self.para._peer_gather = False
             self._status["fused_collectives_disabled"] = True
+
+    def check_guards(self) -> None:
+        """Guard mode (FLEXTRAIN_GUARD=1): wait for all work in flight, then raise if anything
+        was written next to one of the runtime's buffers (``memory.check_guards``).  Runs after
+        every step in that mode; a no-op otherwise."""
+        from .memory import check_guards
+        self.synchronize()
+        check_guards()
 
     def health(self) -> Dict[str, Any]:
         """Status words of the runtime: pending host updates, traffic counters,

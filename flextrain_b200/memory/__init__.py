@@ -11,6 +11,7 @@ of ``utils/device.py``; ``get_data_stream`` returns that set.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from dataclasses import dataclass
 from enum import Enum
@@ -206,25 +207,87 @@ def _pinned_exact(nbytes: int) -> torch.Tensor:
     return t[:nbytes]
 
 
+# Guard mode (environment variable FLEXTRAIN_GUARD=1, a debugging aid): every buffer from
+# ``allocate_memory`` gets a band of pattern bytes on both sides, ``check_guards()`` reports
+# every band that no longer holds the pattern.  A copy, kernel or host routine that runs past
+# the end of a tier buffer, a staging buffer or a ring slot is then seen at the end of the
+# step that did it instead of as wrong numbers many steps later.  The bands keep the
+# alignment of the payload (one page on the host, 512 bytes on the device).
+_GUARD_BYTE = 0xA5
+_GUARDS: List[tuple] = []          # (whole uint8 view, band bytes, payload bytes, where allocated)
+
+
+def guard_mode() -> bool:
+    return os.environ.get("FLEXTRAIN_GUARD", "0") not in ("", "0")
+
+
+def _guarded(numel: int, dtype: torch.dtype, device, pinned: bool, zero: bool, itemsize: int) -> torch.Tensor:
+    import sys
+    band = 512 if torch.device(device).type == "cuda" else PAGE_SIZE
+    nbytes = numel * itemsize
+    padded = (nbytes + band - 1) // band * band
+    whole = _allocate(2 * band + padded, torch.uint8, device, pinned, False, account=nbytes)
+    whole[:band].fill_(_GUARD_BYTE)
+    whole[band + nbytes:].fill_(_GUARD_BYTE)
+    frame = sys._getframe(2)
+    where = f"{os.path.basename(frame.f_code.co_filename)}:{frame.f_lineno} ({frame.f_code.co_name})"
+    _GUARDS.append((whole, band, nbytes, where))
+    t = whole[band:band + nbytes].view(dtype)
+    return t.zero_() if zero else t
+
+
+def check_guards(raise_on_damage: bool = True) -> List[str]:
+    """Guard mode: the buffers whose bands were written to, as ``where allocated: which side,
+    first damaged byte``.  Synchronises the device first.  Empty list when all is well (and
+    always outside guard mode)."""
+    if not _GUARDS:
+        return []
+    if torch.cuda.is_available() and any(w.is_cuda for w, _, _, _ in _GUARDS):
+        torch.cuda.synchronize()
+    damaged = []
+    for whole, band, nbytes, where in _GUARDS:
+        for side, piece, base in (("before", whole[:band], -band), ("after", whole[band + nbytes:], nbytes)):
+            bad = (piece != _GUARD_BYTE).nonzero()
+            if bad.numel():
+                damaged.append(f"{where}: {nbytes} bytes, band {side} the buffer written at byte offset "
+                               f"{base + int(bad[0])} ({int(bad.numel())} bytes differ)")
+    if damaged and raise_on_damage:
+        raise RuntimeError("buffer overrun: " + "; ".join(damaged))
+    return damaged
+
+
+def clear_guards():
+    _GUARDS.clear()
+
+
 def allocate_memory(numel: int, dtype: torch.dtype, device, pinned: bool = True,
                     zero: bool = False) -> torch.Tensor:
     """Accounted flat allocation.  ``device`` cpu + ``pinned`` gives exact-size
     page-locked memory when CUDA is in use, plain memory otherwise."""
+    itemsize = torch.empty((), dtype=dtype).element_size()
+    if guard_mode() and numel > 0:
+        return _guarded(numel, dtype, device, pinned, zero, itemsize)
+    return _allocate(numel, dtype, device, pinned, zero)
+
+
+def _allocate(numel: int, dtype: torch.dtype, device, pinned: bool, zero: bool,
+              account: Optional[int] = None) -> torch.Tensor:
     device = torch.device(device)
     itemsize = torch.empty((), dtype=dtype).element_size()
     nbytes = numel * itemsize
+    booked = nbytes if account is None else account     # guard bands are not booked
     if device.type == "cuda":
-        _ACCOUNT.add("hbm", nbytes)
+        _ACCOUNT.add("hbm", booked)
         t = torch.empty(numel, dtype=dtype, device=device)
         return t.zero_() if zero else t
     if pinned and dist.is_cuda() and numel > 0:
-        _ACCOUNT.add("pinned", nbytes)
+        _ACCOUNT.add("pinned", booked)
         try:
             t = _pinned_exact(nbytes).view(dtype)
         except Exception:
             t = torch.empty(numel, dtype=dtype).pin_memory()
         return t.zero_() if zero else t
-    _ACCOUNT.add("dram", nbytes)
+    _ACCOUNT.add("dram", booked)
     return torch.zeros(numel, dtype=dtype) if zero else torch.empty(numel, dtype=dtype)
 
 

@@ -29,6 +29,8 @@ def reset_runtime():
     reset_nvme_swapper()
     reset_streams()
     reset_flextrain_config()
+    from .memory import clear_guards
+    clear_guards()
     dist.shutdown()
 
 
