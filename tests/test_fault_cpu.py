@@ -6,6 +6,8 @@ import os
 import time
 from datetime import timedelta
 
+import pytest
+
 import torch
 import torch.multiprocessing as mp
 
@@ -137,3 +139,37 @@ def test_timeout_on_one_rank_switches_every_rank_to_library_collectives():
         assert kept == 7
         assert after == (False, False, True), f"rank {rank} did not switch: {after}"
         assert loss == loss
+
+
+@pytest.mark.parametrize("kind", ["eio", "short"])
+def test_nvme_fault_during_a_step_surfaces_and_leaves_nothing_in_flight(kind, fresh_runtime, tmp_path):
+    """A block transfer that fails while the engine trains over NVMe tiers: the step ends
+    with an exception that names the I/O error (whether the main thread or a background
+    update met it), no request stays in flight and the engine shuts down without waiting
+    for anything."""
+    import torch
+    from flextrain_b200.memory.nvme_swapper import NVMeError, get_nvme_swapper
+    from flextrain_b200.models.llama import preset
+    from flextrain_b200.testing import build_llama_engine
+    cfg = preset("tiny", num_layers=4, hidden=64, num_heads=2, ffn=136, vocab=128, seq_len=16)
+    gen = torch.Generator().manual_seed(5)
+    data = torch.randint(0, 128, (2, 17), generator=gen)
+    split = {"parameter": [0.0, 0.5], "optimizer": [0.0, 0.5], "checkpoint": [0.0, 0.5], "gradient": [0.0, 1.0]}
+    ft_cfg = {"batch_size": 2, "micro_batch_size": 2, "mixed_precision": {"device_dtype": "fp32"},
+              "split_ratio": split, "nvme_swap": {"swap_dir": str(tmp_path), "aio_thread_count": 1}}
+    model, opt, eng = build_llama_engine(cfg, ft_cfg, lambda: (data[:, :-1].contiguous(), data[:, 1:].contiguous()),
+                                         lr=1e-3, backend="gloo")
+    eng.train_iteration()                                   # a clean step first
+    eng.synchronize()
+    swapper = get_nvme_swapper()
+    swapper.engine.inject_fault(kind, 1)
+    with pytest.raises(Exception) as info:
+        eng.train_iteration()
+        eng.synchronize()
+    chain, exc = [], info.value
+    while exc is not None:
+        chain.append(exc)
+        exc = exc.__cause__ or exc.__context__
+    assert any(isinstance(e, NVMeError) for e in chain), [repr(e) for e in chain]
+    assert swapper.engine.pending() == 0
+    eng.shutdown()
