@@ -103,6 +103,11 @@ def _bind_device(local_rank: int):
     if _BACKEND != "gloo" and torch.cuda.is_available():
         torch.cuda.set_device(local_rank)
         _DEVICE = torch.device("cuda", local_rank)
+        if os.getenv("FLEXTRAIN_NUMA", "0") == "1":
+            # threads started from here on (host Adam, NVMe workers, the update worker) and the
+            # pages they touch first stay on the socket of this rank's GPU
+            from .numa import bind_to_gpu_node
+            bind_to_gpu_node(local_rank, int(os.getenv("LOCAL_WORLD_SIZE", os.getenv("WORLD_SIZE", "1"))))
     else:
         _DEVICE = torch.device("cpu")
 
