@@ -111,6 +111,7 @@ def main():
     ap.add_argument("--init-weights", default=None,
                     help="torch file of named tensors (this package's names) to start from")
     ap.add_argument("--export", default=None, help="write the final weights (named fp32 tensors) here")
+    ap.add_argument("--metrics-file", default=None, help="append one JSON record per step (rank 0)")
     args = ap.parse_args()
 
     flextrain.init_distributed(dist_backend="nccl" if torch.cuda.is_available() else "gloo",
@@ -177,6 +178,8 @@ def main():
     reporter = ThroughputReporter(tokens_per_step, fpt, world)
     flextrain.rank0_logger.info(f"{args.model}: {cfg.total_numel / 1e6:.1f} M parameters, "
                                 f"{tokens_per_step} tokens per step on {world} rank(s), device {device}")
+    from flextrain_b200.utils.metrics import MetricsLog
+    metrics = MetricsLog(args.metrics_file, engine, tokens_per_step, fpt, world) if args.metrics_file else None
     t_last, losses = time.time(), []
     for step in range(start_step, start_step + args.steps):
         lr_used = sched.current_lrs[0]
@@ -184,6 +187,8 @@ def main():
         local = sum(float(l.detach().float()) for l in out) / len(out)       # reads the loss back
         loss = flextrain.distributed.all_reduce_scalar(local) / world
         losses.append(loss)
+        if metrics is not None:
+            metrics.step(None, loss=loss, lr=lr_used)
         if (step + 1) % args.log_every == 0:
             now = time.time()
             rep = reporter.report((now - t_last) / args.log_every)
@@ -210,6 +215,8 @@ def main():
     if rank == 0:
         print(json.dumps({"final_loss": losses[-1] if losses else None, "first_loss": losses[0] if losses else None,
                           "steps_done": start_step + args.steps, "losses": losses}), flush=True)
+    if metrics is not None:
+        metrics.close()
     feeder.close()
     if eval_feeder is not None:
         eval_feeder.close()

@@ -30,7 +30,11 @@ def test_save_resume_matches_uninterrupted_run(tmp_path):
     data = str(tmp_path / "tokens.u16")
     TokenFile.write(data, rng.integers(0, 1024, size=20000))
     common = ["--model", "llama:tiny", "--data", data, "--micro-batch-size", "1"]
-    whole = _run(common + ["--steps", "5"], str(tmp_path))
+    mfile = str(tmp_path / "metrics.jsonl")
+    whole = _run(common + ["--steps", "5", "--metrics-file", mfile], str(tmp_path))
+    rows = [json.loads(l) for l in open(mfile)]
+    assert [r["step"] for r in rows] == [1, 2, 3, 4, 5] and [r["loss"] for r in rows] == whole["losses"]
+    assert all(r["tokens_per_s"] > 0 for r in rows)
     ck = str(tmp_path / "ck")
     first = _run(common + ["--steps", "3", "--save-dir", ck], str(tmp_path))
     assert sorted(os.listdir(ck)) == ["rank0_data.json", "rank0_state.pt"]
