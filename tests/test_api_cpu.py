@@ -182,3 +182,18 @@ def test_eval_iteration_is_forward_only_and_matches_the_plain_model(fresh_runtim
     e2 = float(eng.eval_iteration(micro_batches=1)[0])
     assert e2 == e2 and e2 != got[0] and abs(e2 - got[0]) < 1.0
     eng.shutdown()
+
+
+def test_optimizer_accepts_bare_tensors_and_single_tensor_groups():
+    """The reference iterates its argument as a list of dicts only
+    (flextrain/optimizer.py:113-129); here a bare iterable of tensors and a group whose
+    ``params`` is one tensor are normalised the way torch.optim does."""
+    from flextrain_b200.optimizer import _normalise_param_groups
+    a, b = torch.nn.Parameter(torch.zeros(3)), torch.nn.Parameter(torch.zeros(2))
+    defaults = {"lr": 1e-3, "weight_decay": 0.01}
+    bare = _normalise_param_groups(iter([a, b]), defaults)
+    assert len(bare) == 1 and bare[0]["params"] == [a, b] and bare[0]["lr"] == 1e-3
+    single = _normalise_param_groups([{"params": a, "lr": 0.5}, {"params": [b]}], defaults)
+    assert single[0]["params"] == [a] and single[0]["lr"] == 0.5 and single[1]["weight_decay"] == 0.01
+    with pytest.raises(ValueError):
+        _normalise_param_groups([], defaults)
