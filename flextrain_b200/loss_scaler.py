@@ -21,6 +21,21 @@ import torch
 from .utils.logging import rank0_logger
 
 
+# keyword names of the dynamic scaler's arguments (flextrain/loss_scaler.py:15-19)
+INITIAL_LOSS_SCALE = "init_scale"
+SCALE_WINDOW = "scale_window"
+DELAYED_SHIFT = "delayed_shift"
+CONSECUTIVE_HYSTERESIS = "consecutive_hysteresis"
+MIN_LOSS_SCALE = "min_scale"
+
+
+def to_python_float(value) -> float:
+    """One-element tensor (or number) -> Python float (flextrain/loss_scaler.py:23-27)."""
+    if hasattr(value, "item"):
+        return float(value.item())
+    return float(value)
+
+
 class LossScalerBase:
     def __init__(self, cur_scale: float):
         self.cur_scale = float(cur_scale)

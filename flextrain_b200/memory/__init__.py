@@ -432,3 +432,29 @@ class ContiguousParaGroup:
 def get_data_stream() -> StreamSet:
     """The rank's stream set (compute / h2d / d2h / opt)."""
     return get_streams()
+
+
+# ------------------------------------------------- names of the reference module
+# flextrain/memory/__init__.py spells these helpers with a ``get_`` prefix and keeps two
+# module-level byte counters; scripts written against it find the same names here.
+get_page_aligned_numel = page_aligned_numel
+get_partition_aligned_numel = partition_aligned_numel
+FlexTrainDataStream = StreamSet
+
+
+def get_allocated_dram_size() -> int:
+    """Bytes of host memory handed out so far, pinned and pageable (flextrain/memory/__init__.py:307-308)."""
+    return _ACCOUNT.bytes["pinned"] + _ACCOUNT.bytes["dram"]
+
+
+def get_allocated_vram_size() -> int:
+    """Bytes of device memory handed out so far (flextrain/memory/__init__.py:311-312)."""
+    return _ACCOUNT.bytes["hbm"]
+
+
+def __getattr__(name):
+    # AsyncIOHandle lives with the NVMe engine, which itself imports this module
+    if name == "AsyncIOHandle":
+        from .nvme_swapper import AsyncIOHandle
+        return AsyncIOHandle
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

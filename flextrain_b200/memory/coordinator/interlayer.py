@@ -19,6 +19,7 @@ unit (the snake turn) never go to NVMe.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Dict, Hashable, Optional, Tuple
 
 import torch
@@ -28,6 +29,16 @@ from ...utils import distributed as dist
 from ...utils.device import DONE, Event, get_streams
 from .. import (tier_copy, FlexTrainDataID, FlexTrainDataType, allocate_memory, get_split_numels)
 from ..nvme_swapper import get_nvme_swapper
+from ...scheduler import LLMTask
+
+
+@dataclass(frozen=True)
+class InterLayerTask(LLMTask):
+    """A scheduler task together with the inter-unit tensor it carries
+    (flextrain/memory/coordinator/interlayer.py:27-28).  The stores below are keyed by
+    ``(unit, micro_batch)`` directly; the class is kept for code that builds such tasks."""
+    tensor: Optional[torch.Tensor] = None
+
 
 
 class _Slot:

@@ -322,3 +322,18 @@ def reset_nvme_swapper():
     if _SWAPPER is not None and _SWAPPER._engine is not None:
         _SWAPPER._engine.close()
     _SWAPPER = None
+
+
+def swap_in_tensors(swap_handle, tensor_buffers, swap_paths):
+    """Queue one asynchronous read per (buffer, path) pair on an ``aio_handle``-like object
+    (flextrain/memory/nvme_swapper.py:12-14); the caller ``wait()``s on the handle."""
+    for buffer, path in zip(tensor_buffers, swap_paths):
+        if swap_handle.async_pread(buffer, path, 0) != 0:
+            raise NVMeError(f"cannot queue the read of {path}")
+
+
+def swap_out_tensors(swap_handle, tensor_buffers, swap_paths):
+    """Queue one asynchronous write per (buffer, path) pair (flextrain/memory/nvme_swapper.py:17-19)."""
+    for buffer, path in zip(tensor_buffers, swap_paths):
+        if swap_handle.async_pwrite(buffer, path, 0) != 0:
+            raise NVMeError(f"cannot queue the write of {path}")

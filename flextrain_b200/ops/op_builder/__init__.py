@@ -8,7 +8,7 @@ peer-memory plumbing.
 import glob
 import os
 
-from .builder import (BuildError, CSRC, CUDAOpBuilder, NATIVE_DIR, OpBuilder, cuda_home,
+from .builder import (BuildError, CPUOpBuilder, CSRC, CUDAOpBuilder, NATIVE_DIR, OpBuilder, cuda_home,
                       nvcc_path)
 
 
@@ -16,7 +16,7 @@ def _rel(pattern):
     return sorted(os.path.relpath(p, CSRC) for p in glob.glob(os.path.join(CSRC, pattern)))
 
 
-class HostOpsBuilder(OpBuilder):
+class HostOpsBuilder(CPUOpBuilder):
     def __init__(self):
         super().__init__("ft_host", _rel("host/*.cpp"), headers=_rel("host/*.h"))
 

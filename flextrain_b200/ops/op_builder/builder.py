@@ -67,6 +67,48 @@ def cuda_home() -> Optional[str]:
     return os.path.dirname(os.path.dirname(os.path.realpath(n))) if n else None
 
 
+class MissingCUDAException(BuildError):
+    pass
+
+
+class CUDAMismatchException(BuildError):
+    pass
+
+
+DEFAULT_COMPUTE_CAPABILITIES = "10.0a"
+MIN_CUDA_FOR_SM100A = (12, 8)
+
+
+def installed_cuda_version():
+    """(major, minor) of the nvcc that would build the kernels
+    (flextrain/ops/op_builder/builder.py:50-64)."""
+    nvcc = nvcc_path()
+    if not nvcc:
+        raise MissingCUDAException("nvcc not found: the CUDA kernels cannot be compiled")
+    words = subprocess.check_output([nvcc, "-V"], universal_newlines=True).split()
+    release = words[words.index("release") + 1].rstrip(",").split(".")
+    return int(release[0]), int(release[1])
+
+
+def get_default_compute_capabilities() -> str:
+    """The reference builds for a list of architectures (6.0 ... 8.6,
+    flextrain/ops/op_builder/builder.py:67-78); this package has exactly one target."""
+    return DEFAULT_COMPUTE_CAPABILITIES
+
+
+def assert_no_cuda_mismatch(name: str = "") -> bool:
+    """The reference refuses an nvcc whose version differs from the CUDA PyTorch was built
+    with, because its ops link against PyTorch (flextrain/ops/op_builder/builder.py:92-126).
+    The libraries here have a C ABI and link neither PyTorch nor its CUDA runtime, so the only
+    hard requirement is an nvcc that knows sm_100a."""
+    have = installed_cuda_version()
+    if have < MIN_CUDA_FOR_SM100A:
+        raise CUDAMismatchException(
+            f"{name or 'flextrain_b200'}: nvcc {have[0]}.{have[1]} cannot compile for sm_100a "
+            f"(needs {MIN_CUDA_FOR_SM100A[0]}.{MIN_CUDA_FOR_SM100A[1]} or newer)")
+    return True
+
+
 class OpBuilder:
     """Compiles ``sources`` (relative to ``csrc/``) into ``_native/lib<name>.so``."""
 
@@ -169,6 +211,11 @@ class OpBuilder:
         lib = ctypes.CDLL(self.lib_path, mode=ctypes.RTLD_GLOBAL)
         _LOADED[self.name] = lib
         return lib
+
+
+class CPUOpBuilder(OpBuilder):
+    """Host-only library: g++ with OpenMP, no CUDA toolchain needed
+    (flextrain/ops/op_builder/builder.py:620-642)."""
 
 
 class CUDAOpBuilder(OpBuilder):

@@ -290,3 +290,30 @@ class StepContextContainer:
         for i in range(self.chunks):
             out.extend(self[i])
         return out
+
+
+# ------------------------------------------------------- nested-list helpers
+def reshape_list(items: Sequence, shape: Sequence[int]):
+    """Flat sequence -> numpy object array of ``shape`` (flextrain/param_group.py:9-10); used
+    to address buffers by (unit, micro-batch, ...) index tuples."""
+    import numpy as np
+    out = np.empty(len(items), dtype=object)
+    for i, item in enumerate(items):
+        out[i] = item                                   # element-wise: tensors must not be unpacked
+    return out.reshape(tuple(shape))
+
+
+def flatten_list(nested) -> List:
+    """Arbitrarily nested lists -> one flat list, depth first (flextrain/param_group.py:13-19)."""
+    if not isinstance(nested, list):
+        return [nested]
+    flat: List = []
+    for item in nested:
+        flat.extend(flatten_list(item))
+    return flat
+
+
+def is_same_param_group(a, b) -> bool:
+    """Param groups are compared by identity, not by value: two groups with equal
+    hyper-parameters are still stepped separately (flextrain/param_group.py:38-39)."""
+    return a is b

@@ -117,6 +117,12 @@ def _ensure():
         init_distributed(force_init=False)
 
 
+def is_single_process() -> bool:
+    """True when this run has one rank (flextrain/utils/distributed.py:134-136)."""
+    _ensure()
+    return _WORLD_SIZE == 1
+
+
 def shutdown():
     """Destroy the process group and forget all state (tests)."""
     global _INITIALIZED, _RANK, _WORLD_SIZE, _BACKEND, _DEVICE

@@ -63,3 +63,56 @@ def test_aio_handle_speaks_the_reference_dialect(tmp_path):
     assert aio_read(dst, c, 1 << 16, 4, False, True, False) == 0 and torch.equal(src, dst)
     dst.zero_()
     assert deepspeed_memcpy(dst, src) == 0 and torch.equal(src, dst)
+
+
+def test_helper_names_of_the_reference_modules():
+    import numpy as np
+    from flextrain_b200 import memory as M
+    from flextrain_b200.loss_scaler import INITIAL_LOSS_SCALE, MIN_LOSS_SCALE, DynamicLossScaler, to_python_float
+    from flextrain_b200.memory.coordinator.interlayer import InterLayerTask
+    from flextrain_b200.memory.nvme_swapper import AsyncIOHandle
+    from flextrain_b200.param_group import flatten_list, is_same_param_group, reshape_list
+    from flextrain_b200.utils.distributed import is_single_process
+    grid = reshape_list([torch.zeros(2), torch.ones(2), torch.zeros(3), torch.ones(3)], [2, 2])
+    assert isinstance(grid, np.ndarray) and grid.shape == (2, 2) and grid[1, 0].numel() == 3
+    assert flatten_list([1, [2, [3, 4]], 5]) == [1, 2, 3, 4, 5] and flatten_list(7) == [7]
+    g = {"lr": 1.0}
+    assert is_same_param_group(g, g) and not is_same_param_group(g, dict(g))
+    assert to_python_float(torch.tensor([2.5])) == 2.5 and to_python_float(3) == 3.0
+    scaler = DynamicLossScaler(**{INITIAL_LOSS_SCALE: 2.0 ** 8, MIN_LOSS_SCALE: 1.0})
+    assert scaler.loss_scale == 256.0
+    assert M.get_page_aligned_numel(5, 4) == 1024 and M.get_partition_aligned_numel(5, 3, 2) == 6144
+    before = M.get_allocated_dram_size()
+    M.allocate_memory(100, torch.float32, "cpu", pinned=False)
+    assert M.get_allocated_dram_size() - before == 400 and M.get_allocated_vram_size() >= 0
+    assert M.AsyncIOHandle is AsyncIOHandle and M.FlexTrainDataStream is not None
+    task = InterLayerTask(True, 2, 1, torch.ones(1))
+    assert (task.unit, task.micro_batch) == (2, 1) and task.tensor.item() == 1.0
+    assert isinstance(is_single_process(), bool)
+
+
+def test_swap_helpers_on_an_aio_handle(tmp_path):
+    from flextrain_b200.memory.nvme_swapper import swap_in_tensors, swap_out_tensors
+    from flextrain_b200.ops.aio import aio_handle
+    h = aio_handle(intra_op_parallelism=2)
+    xs = [torch.randn(4096), torch.randn(8192)]
+    paths = [str(tmp_path / "x0.swp"), str(tmp_path / "x1.swp")]
+    swap_out_tensors(h, xs, paths)
+    assert h.wait() == 2
+    ys = [torch.empty_like(x) for x in xs]
+    swap_in_tensors(h, ys, paths)
+    assert h.wait() == 2 and all(torch.equal(a, b) for a, b in zip(xs, ys))
+    h.close()
+
+
+def test_builder_version_helpers():
+    from flextrain_b200.ops.op_builder import CPUAdamBuilder
+    from flextrain_b200.ops.op_builder import builder as B
+    assert issubclass(CPUAdamBuilder, B.CPUOpBuilder)
+    assert B.get_default_compute_capabilities() == "10.0a"
+    if B.nvcc_path():
+        major, minor = B.installed_cuda_version()
+        assert (major, minor) >= (12, 8) and B.assert_no_cuda_mismatch("test")
+    else:
+        with pytest.raises(B.MissingCUDAException):
+            B.installed_cuda_version()
