@@ -56,7 +56,18 @@ def _ratio_pair(value, name: str, default: Tuple[float, float]) -> Tuple[float, 
     return (gpu, cpu)
 
 
-class SplitRatioConfig:
+class _Section:
+    """``to_log(indent)``: the section as the reference prints it inside its configuration
+    dump (flextrain/config.py:88-98,161-174,285-303): ``"name": {...}`` with tab indentation."""
+    _SECTION_NAME = ""
+
+    def to_log(self, indent: int = 0) -> str:
+        tabs = "\t" * indent
+        body = json.dumps(self.to_dict(), indent="\t", default=str).replace("\n", "\n" + tabs)
+        return f'{tabs}"{self._SECTION_NAME}": {body}'
+
+
+class SplitRatioConfig(_Section):
     """Where each kind of state lives.  Every entry is ``(GPU, CPU)``; NVMe
     gets ``1 - GPU - CPU``.  ``alpha`` is the fraction of every unit's
     host-side optimizer work that may be finished lazily during the next
@@ -94,7 +105,7 @@ class SplitRatioConfig:
         return f"SplitRatioConfig({self.to_dict()})"
 
 
-class NVMeSwapConfig:
+class NVMeSwapConfig(_Section):
     def __init__(self, section: Optional[Dict[str, Any]] = None):
         section = dict(section or {})
         self.swap_dir = section.get(D.SWAP_DIR, D.SWAP_DIR_DEFAULT)
@@ -118,7 +129,7 @@ class NVMeSwapConfig:
         return f"NVMeSwapConfig({self.to_dict()})"
 
 
-class MixedPrecisionConfig:
+class MixedPrecisionConfig(_Section):
     def __init__(self, section: Optional[Dict[str, Any]] = None):
         section = dict(section or {})
         self.device_dtype = parse_dtype(section.get(D.DEVICE_DTYPE, D.DEVICE_DTYPE_DEFAULT))
@@ -152,7 +163,7 @@ class MixedPrecisionConfig:
 MixedPercisionConfig = MixedPrecisionConfig
 
 
-class EngineConfig:
+class EngineConfig(_Section):
     """Knobs of the B200 runtime that have no counterpart in the reference."""
 
     def __init__(self, section: Optional[Dict[str, Any]] = None):
@@ -201,6 +212,12 @@ class EngineConfig:
 
     def __repr__(self):
         return f"EngineConfig({self.to_dict()})"
+
+
+SplitRatioConfig._SECTION_NAME = D.SPLIT_RATIO
+NVMeSwapConfig._SECTION_NAME = D.NVME_SWAP
+MixedPrecisionConfig._SECTION_NAME = D.MIXED_PRECISION
+EngineConfig._SECTION_NAME = D.ENGINE
 
 
 class FlexTrainConfig:

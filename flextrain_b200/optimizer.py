@@ -337,6 +337,12 @@ class FlexTrainOptimizer:
             self._nl_para.copy_(self._nl_host_para, non_blocking=True)
         self._nl_grad.zero_()
 
+    @property
+    def non_layerwise_numel(self) -> int:
+        """Elements of the parameters outside the layer stack (embeddings, final norm, head;
+        flextrain/optimizer.py:240-242)."""
+        return self._nl_numel
+
     def close(self):
         """Release the peer-mapped buffers of the fused non-layerwise path (the
         parameters move to ordinary device memory first).  Collective."""

@@ -92,3 +92,12 @@ def test_wait_limit_reaches_the_native_library():
     finally:
         lib.ft_comm_set_spin_budget(0)
         lib.ft_ag_set_spin_budget(0)
+
+
+def test_sections_print_like_the_reference_dump():
+    from flextrain_b200.config import FlexTrainConfig
+    cfg = FlexTrainConfig({"batch_size": 4, "micro_batch_size": 2})
+    text = cfg.split_ratio.to_log(indent=1)
+    assert text.startswith('\t"split_ratio": {') and '\n\t\t"alpha": 0.25' in text and text.endswith("\n\t}")
+    assert cfg.mixed_precision.to_log().startswith('"mixed_precision": {')
+    assert '"aio_queue_depth": 8' in cfg.nvme_swap.to_log()
