@@ -75,7 +75,9 @@ class DynamicLossScaler(LossScalerBase):
     def __init__(self, init_scale: float = 2.0 ** 16, scale_factor: float = 2.0,
                  scale_window: int = 1000, min_scale: float = 1.0,
                  delayed_shift: int = 1, consecutive_hysteresis: bool = False,
-                 raise_error_at_min_scale: bool = False):
+                 raise_error_at_min_scale: bool = False, dtype=None):
+        # ``dtype`` is accepted for call compatibility (flextrain/loss_scaler.py:104-113 stores it
+        # and never reads it); the scale itself is a Python float here
         super().__init__(init_scale)
         self.dynamic = True
         self.cur_iter = 0

@@ -164,10 +164,10 @@ def _native_avg() -> bool:
     return _BACKEND == "nccl"
 
 
-def barrier():
+def barrier(group=None):
     _ensure()
     if _WORLD_SIZE > 1:
-        tdist.barrier()
+        tdist.barrier(group=group)
 
 
 def print_rank0(*args, **kwargs):
@@ -182,21 +182,24 @@ def print_rank_by_rank(*args, **kwargs):
         barrier()
 
 
-def broadcast(tensor: torch.Tensor, src: int = 0, async_op: bool = False):
+# The collectives below take their arguments in the order of the reference's wrappers
+# (flextrain/utils/distributed.py:171-199): ``group`` before ``async_op``.  The engine only
+# ever uses the default group; a caller's own group is passed through to torch.distributed.
+def broadcast(tensor: torch.Tensor, src: int = 0, group=None, async_op: bool = False):
     _ensure()
     if _WORLD_SIZE == 1:
         return DummyHandle()
-    return tdist.broadcast(tensor, src, async_op=async_op) or DummyHandle()
+    return tdist.broadcast(tensor, src, group=group, async_op=async_op) or DummyHandle()
 
 
-def all_gather(output: torch.Tensor, shard: torch.Tensor, async_op: bool = False):
+def all_gather(output: torch.Tensor, shard: torch.Tensor, group=None, async_op: bool = False):
     """``output`` (W * n elements) receives every rank's ``shard`` (n) in rank order."""
     _ensure()
     if _WORLD_SIZE == 1:
         if output.data_ptr() != shard.data_ptr():
             output.view(-1)[: shard.numel()].copy_(shard.view(-1), non_blocking=True)
         return DummyHandle()
-    return tdist.all_gather_into_tensor(output, shard, async_op=async_op) or DummyHandle()
+    return tdist.all_gather_into_tensor(output, shard, group=group, async_op=async_op) or DummyHandle()
 
 
 class _PostOp:
@@ -217,21 +220,21 @@ class _PostOp:
         return self._work is None and self._fn is None
 
 
-def all_reduce(tensor: torch.Tensor, op=ReduceOp.SUM, async_op: bool = False):
+def all_reduce(tensor: torch.Tensor, op=ReduceOp.SUM, group=None, async_op: bool = False):
     _ensure()
     if _WORLD_SIZE == 1:
         return DummyHandle()
     if op == ReduceOp.AVG and not _native_avg():
-        work = tdist.all_reduce(tensor, ReduceOp.SUM, async_op=async_op)
-        post = _PostOp(work if async_op else None, lambda: tensor.div_(_WORLD_SIZE))
+        work = tdist.all_reduce(tensor, ReduceOp.SUM, group=group, async_op=async_op)
+        post = _PostOp(work if async_op else None, lambda: tensor.div_(tdist.get_world_size(group)))
         if not async_op:
             post.wait()
             return DummyHandle()
         return post
-    return tdist.all_reduce(tensor, op, async_op=async_op) or DummyHandle()
+    return tdist.all_reduce(tensor, op, group=group, async_op=async_op) or DummyHandle()
 
 
-def reduce_scatter(output: torch.Tensor, full: torch.Tensor, op=ReduceOp.SUM,
+def reduce_scatter(output: torch.Tensor, full: torch.Tensor, op=ReduceOp.SUM, group=None,
                    async_op: bool = False):
     """``output`` (n) receives this rank's slice of the reduction of ``full`` (W * n).
     ``output`` may alias ``full``'s own slice (the reference reduces in place:
@@ -242,16 +245,17 @@ def reduce_scatter(output: torch.Tensor, full: torch.Tensor, op=ReduceOp.SUM,
             output.view(-1).copy_(full.view(-1)[: output.numel()], non_blocking=True)
         return DummyHandle()
     if _BACKEND == "nccl":
-        return tdist.reduce_scatter_tensor(output, full, op, async_op=async_op) or DummyHandle()
+        return tdist.reduce_scatter_tensor(output, full, op, group=group, async_op=async_op) or DummyHandle()
     # gloo: all-reduce a scratch copy, keep the local slice
     scratch = full.detach().clone()
-    work = tdist.all_reduce(scratch, ReduceOp.SUM, async_op=async_op)
+    work = tdist.all_reduce(scratch, ReduceOp.SUM, group=group, async_op=async_op)
     n = output.numel()
+    g_rank, g_world = tdist.get_rank(group), tdist.get_world_size(group)
 
     def finish():
-        piece = scratch.view(-1)[_RANK * n:(_RANK + 1) * n]
+        piece = scratch.view(-1)[g_rank * n:(g_rank + 1) * n]
         if op == ReduceOp.AVG:
-            piece = piece / _WORLD_SIZE
+            piece = piece / g_world
         output.view(-1).copy_(piece)
 
     post = _PostOp(work if async_op else None, finish)

@@ -61,3 +61,38 @@ def test_world_size_one_needs_no_process_group():
     assert dist.all_reduce(x).is_completed()
     dist.barrier()
     dist.shutdown()
+
+
+def _sub_group_worker(rank, world, port, q):
+    import os
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as tdist
+    from flextrain_b200.utils import distributed as dist
+    dist.init_distributed(dist_backend="gloo")
+    pair = tdist.new_group([0, 1])                       # every rank creates it, ranks 0 and 1 use it
+    out = None
+    if rank < 2:
+        t = torch.full((4,), float(rank + 1))
+        dist.all_reduce(t, dist.ReduceOp.AVG, pair)       # the reference's order: (tensor, op, group, async_op)
+        full = torch.arange(4.0) + rank
+        piece = torch.empty(2)
+        dist.reduce_scatter(piece, full, dist.ReduceOp.SUM, group=pair)
+        out = (t.tolist(), piece.tolist())
+    dist.barrier()
+    q.put((rank, out))
+    dist.shutdown()
+
+
+def test_collectives_accept_a_group_in_the_reference_position():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 400) + 17
+    procs = [ctx.Process(target=_sub_group_worker, args=(r, 3, port, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(3))
+    for p in procs:
+        p.join(timeout=60)
+    assert got[0][0] == [1.5] * 4 and got[1][0] == [1.5] * 4 and got[2] is None
+    assert got[0][1] == [1.0, 3.0] and got[1][1] == [5.0, 7.0]
