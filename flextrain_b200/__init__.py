@@ -68,6 +68,23 @@ def initialize(model=None, optimizer=None, config=None, dist_init_required: Opti
     return FlexTrainEngine(model, optimizer)
 
 
+_LAZY = {"FlexTrainEngine": ("engine", "FlexTrainEngine"), "FlexTrainOptimizer": ("optimizer", "FlexTrainOptimizer"),
+         "op_builder": ("ops.op_builder", None), "checkpointing": ("checkpointing", None)}
+
+
+def __getattr__(name):
+    # names the reference package also exposes at its root (flextrain/__init__.py:5-18); resolved
+    # on first use so that ``import flextrain_b200`` stays light
+    if name in _LAZY:
+        import importlib
+        module, attr = _LAZY[name]
+        mod = importlib.import_module(f"{__name__}.{module}")
+        value = getattr(mod, attr) if attr else mod
+        globals()[name] = value
+        return value
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
 __all__ = ["Init", "LLMFunc", "add_config_arguments", "distributed", "get_flextrain_config",
            "init_distributed", "init_flextrain_config", "initialize", "logger", "rank0_logger",
            "restore_init_context", "set_llm_func", "shutdown_init_context"]

@@ -31,8 +31,11 @@ def test_llm_func_registry_and_loss_retrieval():
 
 def test_public_names():
     for name in ("Init", "LLMFunc", "set_llm_func", "initialize", "init_distributed", "distributed",
-                 "add_config_arguments", "shutdown_init_context", "restore_init_context"):
+                 "add_config_arguments", "shutdown_init_context", "restore_init_context",
+                 "FlexTrainEngine", "FlexTrainOptimizer", "op_builder", "init_flextrain_config"):
         assert hasattr(ft, name)
+    with pytest.raises(AttributeError):
+        ft.no_such_name
     from flextrain_b200.checkpointing import (checkpointed_backward, checkpointed_forward,  # noqa
                                               detach_variable, get_cuda_rng_tracker,
                                               model_parallel_cuda_manual_seed)
