@@ -132,3 +132,41 @@ def test_host_memcpy_and_locked_tensors():
     free_cpu_locked_tensor(t)
     with pytest.raises(ValueError):
         free_cpu_locked_tensor(torch.zeros(3))
+
+
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+
+@settings(max_examples=300, deadline=None)
+@given(total=st.integers(0, 5_000_000), g=st.floats(0, 1), c=st.floats(0, 1),
+       itemsize=st.sampled_from([1, 2, 4]))
+def test_tier_split_properties(total, g, c, itemsize):
+    """For any size and any pair of shares: the three tiers are non-negative and sum to the
+    total, interior cuts sit on page boundaries (or at the end), a share of zero is empty,
+    shares that sum to one leave nothing for the last tier, and every tier is within one
+    page of its nominal share."""
+    c = min(c, 1.0 - g)
+    parts = M.get_split_numels(total, (g, c), itemsize)
+    per_page = 4096 // itemsize
+    assert len(parts) == 3 and all(p >= 0 for p in parts) and sum(parts) == total
+    first_cut, second_cut = parts[0], parts[0] + parts[1]
+    for cut in (first_cut, second_cut):
+        assert cut % per_page == 0 or cut == total
+    if g == 0.0:
+        assert parts[0] == 0
+    if g + c >= 1.0 - 1e-9:
+        assert parts[2] == 0
+    assert abs(parts[0] - g * total) <= per_page
+    assert abs(second_cut - (g + c) * total) <= per_page
+
+
+@settings(max_examples=200, deadline=None)
+@given(numel=st.integers(1, 10_000_000), parts=st.integers(1, 64), itemsize=st.sampled_from([2, 4]))
+def test_partition_alignment_properties(numel, parts, itemsize):
+    """The padded unit size splits into ``parts`` whole pages each and adds less than one
+    page per part."""
+    aligned = M.partition_aligned_numel(numel, parts, itemsize)
+    per_page = 4096 // itemsize
+    assert aligned >= numel and aligned % (parts * per_page) == 0
+    assert aligned - numel < parts * per_page
+    assert M.page_aligned_numel(numel, itemsize) - numel == M.get_page_aligned_padding_numel(numel, itemsize)
