@@ -59,3 +59,23 @@ def test_sample_config_parses(fresh_runtime):
     cfg = get_flextrain_config()
     assert cfg.batch_size == 16 and cfg.micro_batch_size == 2
     assert cfg.split_ratio.optimizer[0] == 0.92
+
+
+def test_custom_model_example_learns_and_offload_changes_nothing(tmp_path):
+    script = os.path.join(ROOT, "examples", "custom_model.py")
+    env = dict(os.environ)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    env["OMP_NUM_THREADS"] = "2"
+
+    def last_line(extra):
+        proc = subprocess.run([sys.executable, script, "--device", "cpu", "--steps", "30"] + extra,
+                              cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+        return [l for l in proc.stdout.splitlines() if l.startswith("first loss")][-1]
+
+    resident = last_line([])
+    offloaded = last_line(["--offload"])
+    first, last = float(resident.split()[2]), float(resident.split()[5])
+    assert last < 0.3 * first
+    assert resident == offloaded                       # same numbers to the printed precision
