@@ -5,8 +5,8 @@ here runs after the established GPU tests.
 The engine test runs a bf16 tiny GPT with the native GEMM, attention and head
 kernels and the ATen LayerNorm / GELU (the default).  The tests of the package's
 own LayerNorm / bias / GELU / row-RMSNorm kernels, and of the engine on top of
-them, run when ``FLEXTRAIN_TEST_NEW_KERNELS=1``: those kernels are newer than
-the last hardware session of this file and are switched on by that variable
+them, run when ``FLEXTRAIN_TEST_NEW_KERNELS=1``: those kernels have not yet run
+on hardware and are switched on by that variable
 (tests) or ``FLEXTRAIN_GPT_ELEMENTWISE=native`` / ``FLEXTRAIN_RMSNORM=rows`` (use).
 The same variable runs the second-generation attention backward
 (``FLEXTRAIN_ATTN_BWD=2``) and the fourth-generation forward (``FLEXTRAIN_ATTN_FWD=4``).
