@@ -18,13 +18,17 @@ import sys
 import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+T_START = time.time()
 
 
 def _unavailable(why: str):
     print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
 
-def main(args, metric, micro_batch_table):
+def main(args, metric, micro_batch_table, policy=None):
+    """``policy``: the model-choice constants of the other arm (``dram_share_use``,
+    ``dram_per_rank_cap``), so that both arms pick the same model on the same box."""
+    policy = policy or {"dram_share_use": 0.85, "dram_per_rank_cap": 96 * 2 ** 30}
     ref_root = os.path.join(HERE, "_ref")
     if not os.path.isdir(os.path.join(ref_root, "flextrain")):
         return _unavailable("reference is not installed under baseline/_ref")
@@ -50,13 +54,14 @@ def main(args, metric, micro_batch_table):
         dev = torch.device("cuda", torch.cuda.current_device())
         name = args.model
         if name == "auto":
-            name = _auto_model(world, torch, psutil, SHAPES, micro_batch_table, args)
+            name = _auto_model(torch.cuda.device_count(), torch, psutil, SHAPES, micro_batch_table, args,
+                               policy)
         shape = dict(SHAPES[name])
         if args.seq_len:
             shape["seq_len"] = args.seq_len
         if args.layers:
             shape["num_layers"] = args.layers
-        short = _host_capacity_shortfall(shape, psutil)
+        short = _host_capacity_shortfall(shape, psutil, whole_box=world >= torch.cuda.device_count())
         if short is not None:
             if rank == 0:
                 _unavailable(f"{name} on {world} GPU(s): {short}")
@@ -64,12 +69,13 @@ def main(args, metric, micro_batch_table):
         mbs = micro_batch_table.get(name, 2)
         mbpr = args.micro_batches_per_rank or 1
         seq = shape["seq_len"]
+        alpha = _feasible_alpha(shape, world, mbs, mbpr, getattr(args, "alpha", 0.25))
         cfg = {"max_dram_usage": psutil.virtual_memory().available / 2 ** 30,
                "batch_size": mbs * mbpr * world, "micro_batch_size": mbs, "checkpoint_interval": 1,
                # checkpoints stay in host DRAM (the reference's default): its alpha split
                # borrows that buffer for the deferred gradients and refuses alpha > 0 without it
                "split_ratio": {"checkpoint": [0.0, 1.0], "gradient": [1.0, 0.0],
-                               "parameter": [0.0, 1.0], "optimizer": [0.0, 1.0], "alpha": 0.25},
+                               "parameter": [0.0, 1.0], "optimizer": [0.0, 1.0], "alpha": alpha},
                "mixed_precision": {"device_dtype": "fp16", "gradacc_dtype": "fp32",
                                    "master_dtype": "fp32"}}
         init_flextrain_config(cfg)
@@ -85,7 +91,7 @@ def main(args, metric, micro_batch_table):
 
         gen = torch.Generator().manual_seed(1 + rank)
         pool = [torch.randint(0, shape["vocab"], (mbs, seq + 1), generator=gen).pin_memory()
-                for _ in range(max(2, mbpr))]
+                for _ in range(max(64, mbpr))]
         dev_pool = [t.to(dev) for t in pool]
         state = {"i": 0, "host": False, "h2d": 0}
 
@@ -161,12 +167,19 @@ def main(args, metric, micro_batch_table):
         ms_dev, _, _ = timed(args.steps, False)
         e2e = None
         if not args.no_e2e:
+            # as many steps as the device-timed pass when the command's time limit allows it
+            room = getattr(args, "wall_limit", 780.0) - (time.time() - T_START) - 20.0
+            n_e2e = max(3, min(args.steps, int(room / (ms_dev / 1e3 * 1.05)) if room > 0 else 0))
+            if world > 1:
+                t = torch.tensor([n_e2e], device=dev)
+                torch.distributed.all_reduce(t, torch.distributed.ReduceOp.MIN)
+                n_e2e = int(t.item())
             state["host"], state["h2d"] = True, 0
-            ms_e2e, d2h, last = timed(args.steps, True)
+            ms_e2e, d2h, last = timed(n_e2e, True)
             tokens = mbs * mbpr * world * seq
             e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                   "h2d_bytes_per_step": state["h2d"] // args.steps, "d2h_bytes_per_step": int(d2h),
-                   "last_loss": last}
+                   "steps": n_e2e, "h2d_bytes_per_step": state["h2d"] // n_e2e,
+                   "d2h_bytes_per_step": int(d2h), "last_loss": last}
         tokens = mbs * mbpr * world * seq
         if rank == 0:
             print(json.dumps({
@@ -196,13 +209,29 @@ def _numel(s):
     return layer, s["num_layers"] * layer + 2 * s["vocab"] * s["hidden"] + s["hidden"]
 
 
-def _auto_model(world, torch, psutil, shapes, micro_batch_table=None, args=None):
-    """The model the other arm trains on this many ranks: the largest of the three
-    shapes for which that arm's capacity planner finds a tier split (HBM first, then
-    host DRAM).  The planner is a stand-alone pure-Python file; it is loaded by path so
-    that nothing else of that package enters this process."""
+def _feasible_alpha(shape, world, mbs, mbpr, wanted):
+    """The reference borrows its host checkpoint buffer for the gradients whose update it
+    defers into the next forward pass and refuses an ``alpha`` for which those do not fit
+    (``flextrain/memory/coordinator/optimizer.py:385-404``: alpha * parameters per rank and
+    micro-batch must fit the checkpoint buffer of one micro-batch, in units of the fp32
+    accumulation type).  Returns ``wanted`` where that holds and the largest safe value below
+    it otherwise."""
+    layer, _ = _numel(shape)
+    ckpt = mbs * shape["seq_len"] * shape["hidden"]
+    para = layer / (world * mbpr)
+    bound = 0.95 * ckpt / (2.0 * para)
+    return round(min(wanted, bound), 4)
+
+
+def _auto_model(gpus_in_node, torch, psutil, shapes, micro_batch_table=None, args=None, policy=None):
+    """The model the other arm trains on this node: the largest of the three shapes for
+    which that arm's capacity planner finds a tier split on ONE GPU with its share of the
+    node's host memory (the same model at every N).  The planner is a stand-alone
+    pure-Python file; it is loaded by path so that nothing else of that package enters
+    this process."""
     import importlib.util
     import types
+    policy = policy or {"dram_share_use": 0.85, "dram_per_rank_cap": 96 * 2 ** 30}
     path = os.path.join(os.path.dirname(HERE), "flextrain_b200", "planner.py")
     spec = importlib.util.spec_from_file_location("_ft_capacity_planner", path)
     planner = importlib.util.module_from_spec(spec)
@@ -210,6 +239,7 @@ def _auto_model(world, torch, psutil, shapes, micro_batch_table=None, args=None)
     spec.loader.exec_module(planner)
     hbm, _ = torch.cuda.mem_get_info()
     dram = psutil.virtual_memory().available
+    share = min(dram / max(gpus_in_node, 1) * policy["dram_share_use"], policy["dram_per_rank_cap"])
     table = micro_batch_table or {}
     mbpr = (getattr(args, "micro_batches_per_rank", 0) or 1) if args is not None else 1
     buffers = getattr(args, "unit_buffers", 3) if args is not None else 3
@@ -226,21 +256,26 @@ def _auto_model(world, torch, psutil, shapes, micro_batch_table=None, args=None)
                                     num_heads=s["num_heads"], num_kv_heads=s["num_kv_heads"],
                                     head_dim=s["hidden"] // s["num_heads"])
         shape = planner.shape_of(cfg, table.get(name, 2))
-        budget = planner.MemoryBudget(hbm, dram / world * 0.85, 0.0)
-        if planner.plan(shape, world, mbpr, budget, unit_buffers=buffers, alpha=alpha) is not None:
+        budget = planner.MemoryBudget(hbm, share, 0.0)
+        if planner.plan(shape, 1, mbpr, budget, unit_buffers=buffers, alpha=alpha) is not None:
             return name
     return "llama2-7b"
 
 
-def _host_capacity_shortfall(shape, psutil):
+def _host_capacity_shortfall(shape, psutil, whole_box=True):
     """The reference keeps every parameter (2 B), its fp32 master copy and both Adam
     moments (12 B) in pinned host DRAM, whatever the number of GPUs.  Returns a one-line
-    reason when that exceeds 92 % of what the box has available, else None: building the
-    model anyway would pin (or exhaust) nearly all memory of a shared machine."""
+    reason when that exceeds what the run may take of the box's available memory - 92 %
+    when the run has every GPU of the box, 60 % when others share it - else None: building
+    the model anyway would pin (or exhaust) nearly all memory of a shared machine and fail
+    minutes later."""
     _, total = _numel(shape)
     need = total * 14
     have = psutil.virtual_memory().available
     if need > 0.92 * have:
+        whole_box = True
+    if need > (0.92 if whole_box else 0.60) * have:
         return (f"the reference keeps all parameters and optimizer state in host DRAM "
-                f"({need / 1e9:.0f} GB for this model) and the box offers {have / 1e9:.0f} GB")
+                f"({need / 1e9:.0f} GB for this model) and the box offers {have / 1e9:.0f} GB"
+                + ("" if whole_box else ", shared with the other GPUs' users"))
     return None

@@ -21,6 +21,7 @@
 // flextrain/memory/coordinator/parameter.py:516 (and, for ft_ag_gemm, the cuBLAS
 // GEMM that follows it).
 #include <cstdio>
+#include <cstring>
 
 #include "../kernels/gemm_host.h"
 #include "../kernels/gemm2_kernel.cuh"
@@ -67,6 +68,74 @@ peer_gather_kernel(const __grid_constant__ GatherArgs gather, int* __restrict__ 
     gather_role<PG_CHUNK, PG_STAGES, PG_CHUNK>(gather, ring, full_bars, err);
   }
 }
+
+// The same gather with plain 16-byte peer loads and local stores issued by every thread
+// (four loads in flight per thread), no shared memory: one CTA per SM keeps ~4.8 MB of
+// requests in flight, more than the link's bandwidth-delay product, and the CTAs fit beside
+// any resident kernel.  Start / end barriers as in gather_role; CTAs never wait for each other.
+constexpr int LS_THREADS = 512;
+constexpr int LS_UNROLL = 4;
+
+__global__ void __launch_bounds__(LS_THREADS)
+peer_gather_ldst_kernel(const __grid_constant__ GatherArgs G, int* __restrict__ err) {
+  __shared__ int s_ok;
+  const int W = G.peers.world, R = G.peers.rank;
+  uint32_t* mine = G.peers.flags[R];
+  if (blockIdx.x == 0 && threadIdx.x < W && (int)threadIdx.x != R) {
+    __threadfence_system();
+    peer::st_release_sys(G.peers.flags[threadIdx.x] + G.start_slot * peer::kMaxRanks + R, G.seq);
+  }
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int p = 0; p < W && ok; ++p)
+      if (p != R && !peer::wait_seq(mine + G.start_slot * peer::kMaxRanks + p, G.seq, G.spin_budget)) ok = 0;
+    if (!ok) atomicCAS(err, 0, 201);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (s_ok) {
+    // 16-byte vectors; vector q of the call: peer (R + 1 + q_chunk % (W-1)) so that consecutive
+    // chunks of LS_THREADS vectors go to different links
+    const int64_t vec_per_shard = G.shard_bytes / 16;
+    const int64_t chunks_per_shard = (vec_per_shard + LS_THREADS - 1) / LS_THREADS;
+    const int64_t total_chunks = chunks_per_shard * (W - 1);
+    for (int64_t c0 = (int64_t)blockIdx.x * LS_UNROLL; c0 < total_chunks; c0 += (int64_t)gridDim.x * LS_UNROLL) {
+      uint4 v[LS_UNROLL];
+      int64_t off[LS_UNROLL];
+#pragma unroll
+      for (int u = 0; u < LS_UNROLL; ++u) {
+        const int64_t c = c0 + u;
+        off[u] = -1;
+        if (c < total_chunks) {
+          const int p = (R + 1 + (int)(c % (W - 1))) % W;
+          const int64_t iv = (c / (W - 1)) * LS_THREADS + threadIdx.x;
+          if (iv < vec_per_shard) {
+            off[u] = (int64_t)p * vec_per_shard + iv;
+            v[u] = __ldcg(reinterpret_cast<const uint4*>(G.w_peer[p]) + off[u]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < LS_UNROLL; ++u)
+        if (off[u] >= 0) reinterpret_cast<uint4*>(G.w_local)[off[u]] = v[u];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int done = atomicAdd(G.block_counter, 1u);
+    if (done == gridDim.x - 1) {
+      *G.block_counter = 0;
+      for (int p = 0; p < W; ++p)
+        if (p != R) peer::st_release_sys(G.peers.flags[p] + G.done_slot * peer::kMaxRanks + R, G.seq);
+      for (int p = 0; p < W && s_ok; ++p)
+        if (p != R && !peer::wait_seq(mine + G.done_slot * peer::kMaxRanks + p, G.seq, G.spin_budget))
+          atomicCAS(err, 0, 203);
+    }
+  }
+}
+
+int g_gather_mode = -1;   // -1: read FLEXTRAIN_PEER_GATHER on first use; 0 bulk copies, 1 loads / stores
 
 int fill_gather(GatherArgs& G, int world, int rank, const void* const* w_ptrs, uint32_t* const* flags,
                 uint32_t seq, int start_slot, int done_slot, int num_copiers, int dev) {
@@ -127,6 +196,10 @@ extern "C" {
 void ft_ag_gemm_set_pair(int on) { g_ag_pair = on ? 1 : 0; }
 
 void ft_ag_set_spin_budget(long long cycles) { g_spin_budget = cycles; }
+
+// Form of ft_peer_gather: 1 = loads / stores by every thread (default), 0 = bulk copies through
+// shared memory by one thread per CTA.
+void ft_gather_set_mode(int mode) { g_gather_mode = mode ? 1 : 0; }
 
 // Completion signalling of the copy role for later ft_ag_gemm / ft_peer_gather calls:
 // 1 = lagged by NSTAGE-1 store groups (default), 0 = one store at a time.
@@ -230,7 +303,18 @@ int ft_peer_gather(int world, int rank, const void* const* buf_ptrs, uint32_t* c
   G.shard_bytes = shard_bytes;
   G.block_bytes = (shard_bytes * world + kReadyWords - 1) / kReadyWords;
   if (G.block_bytes < PG_CHUNK) G.block_bytes = PG_CHUNK;
-  peer_gather_kernel<<<num_copiers, 32, 0, stream>>>(G, error_word(dev));
+  if (g_gather_mode < 0) {
+    const char* e = getenv("FLEXTRAIN_PEER_GATHER");
+    g_gather_mode = (e && !strcmp(e, "bulk")) ? 0 : 1;
+  }
+  if (g_gather_mode == 1) {
+    const int64_t chunks = ((shard_bytes / 16 + LS_THREADS - 1) / LS_THREADS) * (world - 1);
+    const int64_t want = (chunks + LS_UNROLL - 1) / LS_UNROLL;
+    const int grid = (int)(want < (int64_t)num_copiers ? want : num_copiers);
+    peer_gather_ldst_kernel<<<grid, LS_THREADS, 0, stream>>>(G, error_word(dev));
+  } else {
+    peer_gather_kernel<<<num_copiers, 32, 0, stream>>>(G, error_word(dev));
+  }
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;

@@ -64,20 +64,46 @@ struct RsAdamParams {
   int npush;                      // all-reduce form: updated parameters of [0, og) are also
   void* push[kMaxRanks];          // stored at [rank*S + i] of every rank's full parameter buffer
   int* finite_flag;               // or nullptr
+  int* status;                    // or nullptr: receives 101 when this rank gave up at the start barrier
   int nseg;
   Segment seg[kMaxSeg];
 };
 
+// Raw 8-element loads of one chunk from every rank's buffer, issued back to back so that all
+// `W` peer requests of a thread are in flight together (the reduction is latency-bound on the
+// NVLink round trip: with one request per thread in flight a grid of one CTA per SM reaches a
+// quarter of the link rate, with eight it saturates the link).
 template <typename G>
-__device__ __forceinline__ void load8(const void* base, int64_t idx, float (&out)[8]) {
+struct Raw8 {
+  uint4 lo;
+  uint4 hi;   // second half of an fp32 chunk; unused for 16-bit gradients
+};
+
+template <typename G>
+__device__ __forceinline__ Raw8<G> load_raw8(const void* base, int64_t idx) {
+  Raw8<G> r;
   if constexpr (sizeof(G) == 4) {
-    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
-    float4 a = __ldcg(p), b = __ldcg(p + 1);
-    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
-    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(base) + idx);
+    r.lo = __ldcg(p);
+    r.hi = __ldcg(p + 1);
   } else {
-    uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const G*>(base) + idx));
-    unpack8<G>(raw, out);
+    r.lo = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const G*>(base) + idx));
+  }
+  return r;
+}
+
+template <typename G>
+__device__ __forceinline__ void add_raw8(const Raw8<G>& r, float (&g)[8]) {
+  if constexpr (sizeof(G) == 4) {
+    g[0] += __uint_as_float(r.lo.x); g[1] += __uint_as_float(r.lo.y);
+    g[2] += __uint_as_float(r.lo.z); g[3] += __uint_as_float(r.lo.w);
+    g[4] += __uint_as_float(r.hi.x); g[5] += __uint_as_float(r.hi.y);
+    g[6] += __uint_as_float(r.hi.z); g[7] += __uint_as_float(r.hi.w);
+  } else {
+    float t[8];
+    unpack8<G>(r.lo, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] += t[j];
   }
 }
 
@@ -94,7 +120,8 @@ __device__ __forceinline__ void store8(void* base, int dtype, int64_t idx, const
 }
 
 template <typename G>
-__global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ RsAdamParams P) {
+// 80 registers x 512 threads: a CTA fits on an SM beside a resident GEMM CTA
+__global__ void __maxnreg__(80) rs_adam_kernel(const __grid_constant__ RsAdamParams P) {
   __shared__ int s_ok;
   const int W = P.peers.world, R = P.peers.rank;
   uint32_t* mine = P.peers.flags[R];
@@ -108,7 +135,12 @@ __global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ Rs
     int ok = 1;
     for (int p = 0; p < W && ok && W > 1; ++p)
       if (p != R && !wait_seq(mine + P.start_slot * kMaxRanks + p, P.seq, P.spin_budget)) ok = 0;
-    if (!ok) atomicCAS(P.err, 0, 101);
+    if (!ok) {
+      atomicCAS(P.err, 0, 101);
+      // the caller's status word (pinned host or device memory): whoever consumes this call's
+      // outputs on the host learns that nothing was written
+      if (P.status) { *reinterpret_cast<volatile int*>(P.status) = 101; __threadfence_system(); }
+    }
     s_ok = ok;
   }
   __syncthreads();
@@ -123,12 +155,19 @@ __global__ void __launch_bounds__(512) rs_adam_kernel(const __grid_constant__ Rs
   for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; run && i < P.shard;
        i += (int64_t)gridDim.x * blockDim.x * 8) {
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < W; ++k) {
-      const int p = (R + k) % W;             // start with the local copy, spread peers over links
-      float t[8];
-      load8<G>(P.grads[p], base + i, t);
+    // four ranks per batch (16 or 32 raw registers): four requests per thread in flight
+    constexpr int PB = 4;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] += t[j];
+    for (int k0 = 0; k0 < kMaxRanks; k0 += PB) {
+      Raw8<G> raw[PB];
+#pragma unroll
+      for (int k = 0; k < PB; ++k) {         // local copy first, peers spread over the links
+        if (k0 + k < W) raw[k] = load_raw8<G>(P.grads[(R + k0 + k) % W], base + i);
+      }
+#pragma unroll
+      for (int k = 0; k < PB; ++k) {         // fixed summation order: the result does not depend on timing
+        if (k0 + k < W) add_raw8<G>(raw[k], g);
+      }
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -225,7 +264,7 @@ static int rs_adam_impl(int world, int rank, const void* const* grads, uint32_t*
                         int grad_dtype, int64_t shard, float scale, uint32_t seq, int start_slot,
                         int done_slot, void* reduced_out, int64_t og, int do_adam, float* master, float* m,
                         float* v, void* param_a, int64_t a_hi, void* param_b, int param_dtype,
-                        void* host_grad, int host_grad_dtype, int* finite_flag, int nseg,
+                        void* host_grad, int host_grad_dtype, int* finite_flag, int* status, int nseg,
                         const FtAdamSegment* segs, int max_blocks, void* const* pushes,
                         cudaStream_t stream) {
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -1;
@@ -258,6 +297,7 @@ static int rs_adam_impl(int world, int rank, const void* const* grads, uint32_t*
   P.param_a = param_a; P.a_hi = a_hi; P.param_b = param_b; P.param_dtype = param_dtype;
   P.host_grad = host_grad; P.host_grad_dtype = host_grad_dtype;
   P.finite_flag = finite_flag;
+  P.status = status;
   P.npush = pushes ? world : 0;
   for (int r = 0; r < P.npush; ++r) P.push[r] = pushes[r];
   P.nseg = nseg;
@@ -299,11 +339,12 @@ int ft_rs_adam(int world, int rank, const void* const* grads, uint32_t* const* f
                int64_t shard, float scale, uint32_t seq, int start_slot, int done_slot,
                void* reduced_out, int64_t og, int do_adam, float* master, float* m, float* v,
                void* param_a, int64_t a_hi, void* param_b, int param_dtype, void* host_grad,
-               int host_grad_dtype, int* finite_flag, int nseg, const FtAdamSegment* segs,
+               int host_grad_dtype, int* finite_flag, int* status, int nseg, const FtAdamSegment* segs,
                int max_blocks, cudaStream_t stream) {
   return rs_adam_impl(world, rank, grads, flags, grad_dtype, shard, scale, seq, start_slot, done_slot,
                       reduced_out, og, do_adam, master, m, v, param_a, a_hi, param_b, param_dtype,
-                      host_grad, host_grad_dtype, finite_flag, nseg, segs, max_blocks, nullptr, stream);
+                      host_grad, host_grad_dtype, finite_flag, status, nseg, segs, max_blocks, nullptr,
+                      stream);
 }
 
 // All-reduce form for parameters that every rank keeps whole (embedding, final
@@ -324,7 +365,7 @@ int ft_ar_adam(int world, int rank, const void* const* grads, uint32_t* const* f
   if (do_adam && !params) return -1;
   return rs_adam_impl(world, rank, grads, flags, grad_dtype, shard, scale, seq, start_slot, done_slot,
                       reduced_out, shard, do_adam, master, m, v, nullptr, 0, nullptr, param_dtype,
-                      nullptr, -1, finite_flag, nseg, segs, max_blocks, do_adam ? params : nullptr,
+                      nullptr, -1, finite_flag, nullptr, nseg, segs, max_blocks, do_adam ? params : nullptr,
                       stream);
 }
 

@@ -5,9 +5,7 @@
 #include <cstdlib>
 
 #include "attention_bwd.cuh"
-#include "attention_bwd2.cuh"
 #include "attention_fwd2.cuh"
-#include "attention_fwd3.cuh"
 #include "attention_fwd4.cuh"
 #include "gemm_host.h"
 
@@ -18,26 +16,11 @@ using namespace ft::attn;
 
 // dynamic shared memory a CTA may ask for on sm_100 (227 KB)
 constexpr int kMaxDynamicSmem = 232448;
-static_assert(FwdSmem<128>::BYTES <= kMaxDynamicSmem && Fwd2Smem<128>::BYTES <= kMaxDynamicSmem &&
-                  Fwd3Smem<128>::BYTES <= kMaxDynamicSmem && Fwd4Smem<128>::BYTES <= kMaxDynamicSmem &&
-                  BwdSmem<128>::BYTES <= kMaxDynamicSmem && Bwd2Smem<128>::BYTES <= kMaxDynamicSmem,
+static_assert(Fwd2Smem<128>::BYTES <= kMaxDynamicSmem && Fwd4Smem<128>::BYTES <= kMaxDynamicSmem &&
+                  BwdSmem<128>::BYTES <= kMaxDynamicSmem,
               "an attention kernel outgrew the shared memory of an SM");
 
-template <typename T, int D>
-int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
-               cudaStream_t s) {
-  auto kern = attn_fwd_kernel<T, D>;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<D>::BYTES);
-    configured = true;
-  }
-  const int num_qb = (P.S + BQ - 1) / BQ;
-  kern<<<P.B * P.Hq * num_qb, ATTN_THREADS, FwdSmem<D>::BYTES, s>>>(tq, tk, tv, P);
-  return 0;
-}
-
-// Second-generation forward: one CTA per pair of query blocks.
+// Forward, one CTA per pair of query blocks, one thread per score row.
 template <typename T, int D>
 int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
                 cudaStream_t s) {
@@ -52,22 +35,7 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   return 0;
 }
 
-// Third generation: as the second, K/V maps with 64-row boxes.
-template <typename T, int D>
-int launch_fwd3(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
-                cudaStream_t s) {
-  auto kern = attn_fwd3_kernel<T, D>;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd3Smem<D>::BYTES);
-    configured = true;
-  }
-  const int num_pairs = ((P.S + BQ - 1) / BQ + 1) / 2;
-  kern<<<P.B * P.Hq * num_pairs, F2_THREADS, Fwd3Smem<D>::BYTES, s>>>(tq, tk, tv, P);
-  return 0;
-}
-
-// Fourth generation (two threads per score row); not yet run on a GPU, never the default.
+// Forward with two threads per score row.
 template <typename T, int D>
 int launch_fwd4(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
                 cudaStream_t s) {
@@ -82,13 +50,13 @@ int launch_fwd4(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   return 0;
 }
 
-int g_fwd_version = -1;   // -1: read FLEXTRAIN_ATTN_FWD on first use (default 2, the fastest measured)
+int g_fwd_version = -1;   // -1: read FLEXTRAIN_ATTN_FWD on first use (2 or 4)
 
 int fwd_version() {
   if (g_fwd_version < 0) {
     const char* e = getenv("FLEXTRAIN_ATTN_FWD");
     g_fwd_version = e ? atoi(e) : 2;
-    if (g_fwd_version < 1 || g_fwd_version > 4) g_fwd_version = 2;
+    if (g_fwd_version != 2 && g_fwd_version != 4) g_fwd_version = 2;
   }
   return g_fwd_version;
 }
@@ -96,12 +64,7 @@ int fwd_version() {
 template <typename T, int D>
 int launch_fwd_any(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
                    cudaStream_t s) {
-  switch (fwd_version()) {
-    case 1: return launch_fwd<T, D>(tq, tk, tv, P, s);
-    case 3: return launch_fwd3<T, D>(tq, tk, tv, P, s);
-    case 4: return launch_fwd4<T, D>(tq, tk, tv, P, s);
-    default: return launch_fwd2<T, D>(tq, tk, tv, P, s);
-  }
+  return fwd_version() == 4 ? launch_fwd4<T, D>(tq, tk, tv, P, s) : launch_fwd2<T, D>(tq, tk, tv, P, s);
 }
 
 template <typename T, int D>
@@ -116,40 +79,6 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   const int num_blk = (P.S + BQ - 1) / BQ;
   kern<<<P.B * P.Hkv * num_blk, BWD_THREADS, BwdSmem<D>::BYTES, s>>>(tq, tk, tv, tdo, tdq, P);
   return 0;
-}
-
-// Second-generation backward (Q double-buffered, dQ on the dP columns); not yet run on a GPU,
-// never the default.
-template <typename T, int D>
-int launch_bwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-                const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
-  auto kern = attn_bwd2_kernel<T, D>;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd2Smem<D>::BYTES);
-    configured = true;
-  }
-  const int num_blk = (P.S + BQ - 1) / BQ;
-  kern<<<P.B * P.Hkv * num_blk, BWD_THREADS, Bwd2Smem<D>::BYTES, s>>>(tq, tk, tv, tdo, tdq, P);
-  return 0;
-}
-
-int g_bwd_version = -1;   // -1: read FLEXTRAIN_ATTN_BWD on first use (default 1)
-
-int bwd_version() {
-  if (g_bwd_version < 0) {
-    const char* e = getenv("FLEXTRAIN_ATTN_BWD");
-    g_bwd_version = e ? atoi(e) : 1;
-    if (g_bwd_version < 1 || g_bwd_version > 2) g_bwd_version = 1;
-  }
-  return g_bwd_version;
-}
-
-template <typename T, int D>
-int launch_bwd_any(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-                   const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
-  return bwd_version() == 2 ? launch_bwd2<T, D>(tq, tk, tv, tdo, tdq, P, s)
-                            : launch_bwd<T, D>(tq, tk, tv, tdo, tdq, P, s);
 }
 
 template <typename T>
@@ -171,11 +100,8 @@ void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_strid
 
 extern "C" {
 
-// Selects the backward kernel generation for later ft_attn_bwd calls (1: default, 2).
-void ft_attn_set_bwd_version(int v) { g_bwd_version = (v == 2) ? 2 : 1; }
-
-// Selects the forward kernel generation for later ft_attn_fwd calls (1 to 4; 2 is the default).
-void ft_attn_set_fwd_version(int v) { g_fwd_version = (v >= 1 && v <= 4) ? v : 2; }
+// Selects the forward kernel for later ft_attn_fwd calls: 2 (one thread per score row) or 4 (two).
+void ft_attn_set_fwd_version(int v) { g_fwd_version = (v == 4) ? 4 : 2; }
 
 // o[B,S,Hq,D], lse[B,Hq,S] <- causal attention of q[B,S,Hq,D], k/v[B,S,Hkv,D].
 // *_stride: elements between consecutive tokens of that tensor.  D in {64, 128}.
@@ -190,7 +116,7 @@ int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   CUtensorMap tq, tk, tv;
   int rc = gemm::make_tmap(&tq, q, (uint64_t)Hq * D, (uint64_t)B * S, (uint64_t)q_stride, 64, BQ, dtype);
   if (rc) return rc;
-  const uint32_t kv_box = fwd_version() == 3 ? SUB : BKV;
+  const uint32_t kv_box = BKV;
   rc = gemm::make_tmap(&tk, k, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)k_stride, 64, kv_box, dtype);
   if (rc) return rc;
   rc = gemm::make_tmap(&tv, v, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)v_stride, 64, kv_box, dtype);
@@ -249,13 +175,13 @@ int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.err = gemm::error_word(dev);
   if (dtype == kBF16) {
     launch_pre_post<__nv_bfloat16>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
-    if (D == 128) launch_bwd_any<__nv_bfloat16, 128>(tq, tk, tv, tdo, tdq, P, stream);
-    else launch_bwd_any<__nv_bfloat16, 64>(tq, tk, tv, tdo, tdq, P, stream);
+    if (D == 128) launch_bwd<__nv_bfloat16, 128>(tq, tk, tv, tdo, tdq, P, stream);
+    else launch_bwd<__nv_bfloat16, 64>(tq, tk, tv, tdo, tdq, P, stream);
     launch_pre_post<__nv_bfloat16>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, scale, stream);
   } else {
     launch_pre_post<__half>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
-    if (D == 128) launch_bwd_any<__half, 128>(tq, tk, tv, tdo, tdq, P, stream);
-    else launch_bwd_any<__half, 64>(tq, tk, tv, tdo, tdq, P, stream);
+    if (D == 128) launch_bwd<__half, 128>(tq, tk, tv, tdo, tdq, P, stream);
+    else launch_bwd<__half, 64>(tq, tk, tv, tdo, tdq, P, stream);
     launch_pre_post<__half>(true, nullptr, nullptr, 0, nullptr, dq_acc, dq, dq_stride, B, S, Hq, D, scale, stream);
   }
   FT_LAUNCHED(3);

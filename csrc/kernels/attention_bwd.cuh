@@ -19,7 +19,7 @@
 // tile is ever transposed.  dK / dV are written once at the end; dq_acc is
 // converted to the 16-bit dq by a separate pass.  All waits are bounded.
 #pragma once
-#include "attention_fwd.cuh"
+#include "attention_common.cuh"
 #include "packed_math.cuh"
 
 namespace ft {

@@ -14,10 +14,10 @@
 // maximum is used consistently for P, the row sum and the final log-sum-exp, so
 // the result is exact).  The softmax arithmetic uses the two-wide fp32
 // instructions and the bare ex2 approximation (packed_math.cuh).
-// Outputs as in attention_fwd.cuh: O [B,S,Hq,D] and lse [B,Hq,S].  All waits
+// Outputs: O [B,S,Hq,D] (16-bit) and lse [B,Hq,S] (fp32, natural log of the row sums).  All waits
 // are bounded.
 #pragma once
-#include "attention_fwd.cuh"
+#include "attention_common.cuh"
 #include "packed_math.cuh"
 
 namespace ft {

@@ -44,7 +44,8 @@ template <typename T, bool LN, int THREADS>
 __global__ void __launch_bounds__(THREADS) norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                                            const T* __restrict__ b, T* __restrict__ y,
                                                            float* __restrict__ mean_out,
-                                                           float* __restrict__ rstd_out, int H, float eps) {
+                                                           float* __restrict__ rstd_out, int H, float eps,
+                                                           const T* __restrict__ res, T* __restrict__ sum_out) {
   __shared__ float red[32];
   const int64_t row = blockIdx.x;
   const int nvec = H / 8;
@@ -54,6 +55,29 @@ __global__ void __launch_bounds__(THREADS) norm_fwd_kernel(const T* __restrict__
   for (int j = 0; j < kNV; ++j) {
     const int i = threadIdx.x + j * THREADS;
     raw[j] = i < nvec ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (res != nullptr) {
+    // fused residual add: the row that is normalised (and written to sum_out) is x + res,
+    // rounded to T first so that the statistics are those of the stored sum
+    const uint4* rr = reinterpret_cast<const uint4*>(res + row * H);
+    uint4* sr = reinterpret_cast<uint4*>(sum_out + row * H);
+    uint4 rraw[kNV];
+#pragma unroll
+    for (int j = 0; j < kNV; ++j) {
+      const int i = threadIdx.x + j * THREADS;
+      rraw[j] = i < nvec ? rr[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < kNV; ++j) {
+      const int i = threadIdx.x + j * THREADS;
+      float a[8], c[8];
+      unpack8<T>(raw[j], a);
+      unpack8<T>(rraw[j], c);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) a[k] += c[k];
+      raw[j] = pack8<T>(a);
+      if (i < nvec) sr[i] = raw[j];
+    }
   }
   float mean = 0.f;
   if constexpr (LN) {
@@ -137,7 +161,8 @@ __global__ void __launch_bounds__(MAXT, 1) norm_bwd_kernel(const T* __restrict__
                                                            const float* __restrict__ mean_in,
                                                            const float* __restrict__ rstd_in,
                                                            T* __restrict__ dx, float* __restrict__ dw_part,
-                                                           float* __restrict__ db_part, int64_t rows, int H) {
+                                                           float* __restrict__ db_part, int64_t rows, int H,
+                                                           const T* __restrict__ dres) {
   __shared__ float red[2 * R * 32];
   const int nvec = H / 8;
   const int nthr = blockDim.x;
@@ -220,6 +245,13 @@ __global__ void __launch_bounds__(MAXT, 1) norm_bwd_kernel(const T* __restrict__
             for (int k = 0; k < 8; ++k) {
               const float xh = (xv[k] - mean[r]) * rstd[r];
               o[k] = rstd[r] * (gv[k] * wv[k] - c1 - xh * c2);
+            }
+            if (dres != nullptr) {
+              // the gradient that reaches the normalised tensor along the residual branch
+              float e[8];
+              unpack8<T>(reinterpret_cast<const uint4*>(dres + row * H)[i], e);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) o[k] += e[k];
             }
             dr[i] = pack8<T>(o);
           }
@@ -350,17 +382,15 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <typename T, bool LN>
 void launch_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
-                     int64_t rows, int H, float eps, cudaStream_t s) {
+                     int64_t rows, int H, float eps, const void* res, void* sum_out, cudaStream_t s) {
   const int nvec = H / 8;
-  if (nvec <= kNV * 256)
-    norm_fwd_kernel<T, LN, 256><<<(unsigned)rows, 256, 0, s>>>((const T*)x, (const T*)w, (const T*)b, (T*)y,
-                                                                mean, rstd, H, eps);
-  else if (nvec <= kNV * 512)
-    norm_fwd_kernel<T, LN, 512><<<(unsigned)rows, 512, 0, s>>>((const T*)x, (const T*)w, (const T*)b, (T*)y,
-                                                                mean, rstd, H, eps);
-  else
-    norm_fwd_kernel<T, LN, 1024><<<(unsigned)rows, 1024, 0, s>>>((const T*)x, (const T*)w, (const T*)b,
-                                                                  (T*)y, mean, rstd, H, eps);
+#define FT_NORM_FWD(THREADS)                                                                           \
+  norm_fwd_kernel<T, LN, THREADS><<<(unsigned)rows, THREADS, 0, s>>>(                                 \
+      (const T*)x, (const T*)w, (const T*)b, (T*)y, mean, rstd, H, eps, (const T*)res, (T*)sum_out)
+  if (nvec <= kNV * 256) FT_NORM_FWD(256);
+  else if (nvec <= kNV * 512) FT_NORM_FWD(512);
+  else FT_NORM_FWD(1024);
+#undef FT_NORM_FWD
 }
 
 inline int round_up32(int v) { return (v + 31) / 32 * 32; }
@@ -377,11 +407,11 @@ inline BwdShape norm_bwd_shape(int H) {
 template <typename T, bool LN>
 void launch_norm_bwd(const void* x, const void* w, const void* dy, const float* mean, const float* rstd,
                      void* dx, float* dw_part, float* db_part, int64_t rows, int H, int parts,
-                     cudaStream_t s) {
+                     const void* dres, cudaStream_t s) {
   const BwdShape sh = norm_bwd_shape(H);
 #define FT_NORM_BWD(NV, R, MAXT)                                                                      \
   norm_bwd_kernel<T, LN, NV, R, MAXT><<<parts, sh.threads, 0, s>>>(                                   \
-      (const T*)x, (const T*)w, (const T*)dy, mean, rstd, (T*)dx, dw_part, db_part, rows, H)
+      (const T*)x, (const T*)w, (const T*)dy, mean, rstd, (T*)dx, dw_part, db_part, rows, H, (const T*)dres)
   if (sh.nv == 1 && sh.threads <= 512) FT_NORM_BWD(1, 4, 512);
   else if (sh.nv == 1) FT_NORM_BWD(1, 4, 640);
   else if (sh.nv == 2) FT_NORM_BWD(2, 2, 512);
@@ -405,41 +435,60 @@ int ft_norm_bwd_parts(int64_t rows, int H) {
 
 // layernorm != 0: y = (x - mean) * rstd * w + b, mean and rstd saved per row.
 // layernorm == 0: y = x * rstd * w (b, mean unused; may be null).
-int ft_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
-                int64_t rows, int H, float eps, int layernorm, int dt, cudaStream_t s) {
+// With `res` (and `sum_out`) the row that is normalised is x + res, which is also written to
+// sum_out in the tensors' dtype: the residual add before a norm costs no pass of its own.
+int ft_add_norm_fwd(const void* x, const void* res, void* sum_out, const void* w, const void* b, void* y,
+                    float* mean, float* rstd, int64_t rows, int H, float eps, int layernorm, int dt,
+                    cudaStream_t s) {
   if (rows <= 0) return 0;
   if (H % 8 || H > ft_norm_max_hidden(0)) return -2;
   if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (layernorm && !aligned16(b))) return -2;
+  if ((res == nullptr) != (sum_out == nullptr)) return -2;
+  if (res && (!aligned16(res) || !aligned16(sum_out))) return -2;
   if (rows > 0x7fffffffLL) return -2;
   FT_DISPATCH_16(dt, T, {
-    if (layernorm) launch_norm_fwd<T, true>(x, w, b, y, mean, rstd, rows, H, eps, s);
-    else launch_norm_fwd<T, false>(x, w, nullptr, y, nullptr, rstd, rows, H, eps, s);
+    if (layernorm) launch_norm_fwd<T, true>(x, w, b, y, mean, rstd, rows, H, eps, res, sum_out, s);
+    else launch_norm_fwd<T, false>(x, w, nullptr, y, nullptr, rstd, rows, H, eps, res, sum_out, s);
   });
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;
 }
 
+int ft_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                int64_t rows, int H, float eps, int layernorm, int dt, cudaStream_t s) {
+  return ft_add_norm_fwd(x, nullptr, nullptr, w, b, y, mean, rstd, rows, H, eps, layernorm, dt, s);
+}
+
 // dw_part (and db_part for LayerNorm): ft_norm_bwd_parts(rows, H) * H floats of scratch.
 // dw / db receive the column sums in the parameters' dtype `dt`.
-int ft_norm_bwd(const void* x, const void* w, const void* dy, const float* mean, const float* rstd,
-                void* dx, void* dw, void* db, float* dw_part, float* db_part, int64_t rows, int H,
-                int layernorm, int dt, cudaStream_t s) {
+// With `dres` ([rows, H], same dtype) dx = dres + (gradient through the norm): the sum of the two
+// gradient branches that meet at the norm's input is formed here (dx and dres are distinct buffers).
+int ft_add_norm_bwd(const void* x, const void* w, const void* dy, const void* dres, const float* mean,
+                    const float* rstd, void* dx, void* dw, void* db, float* dw_part, float* db_part,
+                    int64_t rows, int H, int layernorm, int dt, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (H % 8 || H > ft_norm_max_hidden(1)) return -2;
   if (!aligned16(x) || !aligned16(w) || !aligned16(dy) || !aligned16(dx) || !aligned16(dw_part) ||
-      (layernorm && !aligned16(db_part)))
+      (layernorm && !aligned16(db_part)) || (dres && !aligned16(dres)))
     return -2;
   const int parts = ft_norm_bwd_parts(rows, H);
   FT_DISPATCH_16(dt, T, {
-    if (layernorm) launch_norm_bwd<T, true>(x, w, dy, mean, rstd, dx, dw_part, db_part, rows, H, parts, s);
-    else launch_norm_bwd<T, false>(x, w, dy, nullptr, rstd, dx, dw_part, nullptr, rows, H, parts, s);
+    if (layernorm) launch_norm_bwd<T, true>(x, w, dy, mean, rstd, dx, dw_part, db_part, rows, H, parts, dres, s);
+    else launch_norm_bwd<T, false>(x, w, dy, nullptr, rstd, dx, dw_part, nullptr, rows, H, parts, dres, s);
     parts_reduce_kernel<T><<<(H + 255) / 256, 256, 0, s>>>(dw_part, (T*)dw, parts, H, 0);
     if (layernorm) parts_reduce_kernel<T><<<(H + 255) / 256, 256, 0, s>>>(db_part, (T*)db, parts, H, 0);
   });
   FT_LAUNCHED(layernorm ? 3 : 2);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;
+}
+
+int ft_norm_bwd(const void* x, const void* w, const void* dy, const float* mean, const float* rstd,
+                void* dx, void* dw, void* db, float* dw_part, float* db_part, int64_t rows, int H,
+                int layernorm, int dt, cudaStream_t s) {
+  return ft_add_norm_bwd(x, w, dy, nullptr, mean, rstd, dx, dw, db, dw_part, db_part, rows, H, layernorm,
+                         dt, s);
 }
 
 // y = act(x + bias) over [rows, N]; y may be x.  act 0: identity, 1: tanh GELU.

@@ -66,6 +66,8 @@ class MachinePerfParams:
     cpu_adam_throughput: float      # elements/s per rank
     gpu_adam_throughput: float      # elements/s per rank
     nvlink_bandwidth: float         # B/s per rank, one direction
+    pcie_h2d_bandwidth: float = 0.0  # B/s per rank, host to device (0: take pcie_bandwidth)
+    nvme_backend: str = ""          # which backend the NVMe engine was granted (io_uring, ...)
 
 
 @dataclass
@@ -132,14 +134,15 @@ class FlexTrainConfigSolver:
         lp.add_le({"gpu_opts": P, "T_b": -p.gpu_adam_throughput}, 0.0)
         # ---- PCIe, per direction
         bw = p.pcie_bandwidth
+        bw_in = p.pcie_h2d_bandwidth if p.pcie_h2d_bandwidth > 0 else bw
         h2d_f = {"cpu_para": P * d, "nvme_para": P * d}
         d2h_f = {"cpu_ckpt": mbpr * A * d, "nvme_ckpt": mbpr * A * d}
-        lp.add_le({**h2d_f, "T_f": -bw}, 0.0)
+        lp.add_le({**h2d_f, "T_f": -bw_in}, 0.0)
         lp.add_le({**d2h_f, "T_f": -bw}, 0.0)
         h2d_b = {"cpu_para": P * d, "nvme_para": P * d, "cpu_ckpt": mbpr * A * d,
                  "nvme_ckpt": mbpr * A * d, "cpu_grad": mbpr * A * d}
         d2h_b = {"cpu_opts": P * g, "nvme_opts": P * g, "cpu_grad": mbpr * A * d}
-        lp.add_le({**h2d_b, "T_b": -bw}, 0.0)
+        lp.add_le({**h2d_b, "T_b": -bw_in}, 0.0)
         lp.add_le({**d2h_b, "T_b": -bw}, 0.0)
         # ---- NVMe (read + write share the device)
         rd, wr = p.nvme_read_bandwidth, p.nvme_write_bandwidth
@@ -231,8 +234,8 @@ def _time_host(fn, iters: int) -> float:
     return trimmed_mean(samples)
 
 
-def benchmark_pcie(device, nbytes: int = 1 << 28, iters: int = 20) -> float:
-    """Device-to-host bandwidth of a pinned copy, B/s."""
+def benchmark_pcie(device, nbytes: int = 1 << 28, iters: int = 20, h2d: bool = False) -> float:
+    """Bandwidth of a pinned copy, B/s: device to host, or host to device with ``h2d``."""
     if device.type != "cuda":
         return 50e9
     from .memory import allocate_memory
@@ -240,7 +243,10 @@ def benchmark_pcie(device, nbytes: int = 1 << 28, iters: int = 20) -> float:
     dev = torch.empty(nbytes, dtype=torch.uint8, device=device)
     host.copy_(dev)
     torch.cuda.synchronize()
-    t = _time_cuda(lambda: host.copy_(dev, non_blocking=True), iters)
+    if h2d:
+        t = _time_cuda(lambda: dev.copy_(host, non_blocking=True), iters)
+    else:
+        t = _time_cuda(lambda: host.copy_(dev, non_blocking=True), iters)
     return nbytes / t
 
 
@@ -379,8 +385,21 @@ def measure_machine(engine, iters: int = 10, swap_dir: Optional[str] = None) -> 
         cpu_adam_throughput=world_mean(benchmark_cpu_adam(engine.optimizer.cpu_optimizer, mp.device_dtype)),
         gpu_adam_throughput=world_mean(benchmark_gpu_adam(dev, mp.device_dtype,
                                                           engine.optimizer.cpu_optimizer)),
-        nvlink_bandwidth=world_mean(benchmark_nvlink(dev)))
+        nvlink_bandwidth=world_mean(benchmark_nvlink(dev)),
+        pcie_h2d_bandwidth=world_mean(benchmark_pcie(dev, h2d=True)),
+        nvme_backend=_nvme_backend_name())
     return perf
+
+
+def _nvme_backend_name() -> str:
+    try:
+        from .memory.nvme_swapper import NVMeEngine
+        eng = NVMeEngine()
+        name = str(eng.kind)
+        eng.close()
+        return name
+    except Exception:
+        return "unknown"
 
 
 def _tier_bytes(engine, kind: str) -> float:
@@ -405,4 +424,11 @@ def system_auto_config(engine, iters: int = 10) -> List[ConfigResult]:
     if dist.get_rank() == 0:
         rank0_logger.info(format_results(results))
     engine.last_auto_config = results
-    return sorted(results, key=lambda r: -r.throughput)
+    results = sorted(results, key=lambda r: -r.throughput)
+    engine.auto_config_report = {
+        "measurements": asdict(perf),
+        "candidates": [{"micro_batches_per_rank": r.micro_batches_per_rank, "alpha": r.alpha,
+                        "predicted_micro_batches_per_s": r.throughput,
+                        "predicted_iteration_ms": r.iteration_time * 1e3,
+                        "split_ratio": {**r.split_ratio, "alpha": r.alpha}} for r in results[:6]]}
+    return results

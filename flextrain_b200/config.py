@@ -193,19 +193,18 @@ class EngineConfig(_Section):
         self.fused_wait_seconds = (float(waits[0]), float(waits[1]))
         self.fused_nonlayer = section.get(D.FUSED_NONLAYER, D.FUSED_NONLAYER_DEFAULT)
         self.gather_lag = section.get(D.GATHER_LAG, D.GATHER_LAG_DEFAULT)
+        self.fused_timeout_action = str(section.get(D.FUSED_TIMEOUT_ACTION, D.FUSED_TIMEOUT_ACTION_DEFAULT))
+        if self.fused_timeout_action not in ("raise", "fallback"):
+            raise ValueError("engine.fused_timeout_action must be 'raise' or 'fallback'")
         for key, val in ((D.FUSED_NONLAYER, self.fused_nonlayer), (D.GATHER_LAG, self.gather_lag)):
             if val not in ("auto", True, False):
                 raise ValueError(f"engine.{key} must be 'auto', true or false")
 
     @property
     def fused_blocks(self) -> int:
-        """CTAs of the fused collective kernels.  Unset (0): 148 on up to 2 ranks,
-        64 above - the grid each world size has been run with."""
-        if self.fused_blocks_setting > 0:
-            return self.fused_blocks_setting
-        import os
-        world = int(os.environ.get("WORLD_SIZE", "1") or 1)
-        return 148 if world <= 2 else 64
+        """CTAs of the fused collective kernels.  Unset (0): one per SM (148), which fits
+        beside a resident GEMM CTA and keeps enough peer requests in flight to fill the link."""
+        return self.fused_blocks_setting if self.fused_blocks_setting > 0 else 148
 
     def to_dict(self):
         return dict(vars(self), fused_blocks=self.fused_blocks)

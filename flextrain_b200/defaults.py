@@ -98,11 +98,13 @@ ENGINE = "engine"
 FUSED_COLLECTIVES = "fused_collectives"    # peer-memory kernels instead of NCCL
 FUSED_COLLECTIVES_DEFAULT = "auto"         # "auto" | True | False
 FUSED_NONLAYER = "fused_nonlayer"          # fused all-reduce + sharded Adam for non-layerwise params
-FUSED_NONLAYER_DEFAULT = "auto"            # "auto": on up to 2 ranks (the sizes it was validated on)
+FUSED_NONLAYER_DEFAULT = "auto"            # "auto": on wherever the fused collectives are
 GATHER_LAG = "gather_lag"                  # lagged completion signalling in the peer gather
-GATHER_LAG_DEFAULT = "auto"                # "auto": on up to 2 ranks
+GATHER_LAG_DEFAULT = "auto"                # "auto": on
 FUSED_BLOCKS = "fused_blocks"              # CTAs of the fused collective kernels
-FUSED_BLOCKS_DEFAULT = 0                   # 0: 148 up to 2 ranks, 64 above (the sizes each was run on)
+FUSED_BLOCKS_DEFAULT = 0                   # 0: one CTA per SM (148)
+FUSED_TIMEOUT_ACTION = "fused_timeout_action"   # a cross-GPU wait of a fused kernel ran out:
+FUSED_TIMEOUT_ACTION_DEFAULT = "raise"          # "raise" FusedCollectiveTimeout | "fallback" to NCCL silently
 FUSED_WAIT_SECONDS = "fused_wait_seconds"  # [steady state, first step]: limit of every cross-GPU wait of
 FUSED_WAIT_SECONDS_DEFAULT = (10.0, 30.0)  # the fused kernels (first-step allocations make ranks drift more)
 NUM_UNIT_BUFFERS = "num_unit_buffers"      # HBM unit buffers in the gather ring

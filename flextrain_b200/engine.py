@@ -33,7 +33,7 @@ from .scheduler import GreedySnakeBlockScheduler, LLMTask
 from .utils import distributed as dist
 from .utils.device import get_streams
 from .utils.logging import logger, rank0_logger
-from .utils.health import Heartbeat, PeerFailure, StepWatchdog
+from .utils.health import FusedCollectiveTimeout, Heartbeat, PeerFailure, StepWatchdog
 from .utils.timer import StepTimer
 
 
@@ -327,12 +327,10 @@ class FlexTrainEngine:
             result = self._train_iteration(cfg)
             if self.global_steps == 1:
                 self._set_fused_wait(first_step=False)
-            if self.global_steps <= 2:
-                self._fused_health_check()
             if self._guard_mode:
                 self.check_guards()
             return result
-        except PeerFailure:
+        except (PeerFailure, FusedCollectiveTimeout):
             raise
         except BaseException as exc:
             self.heartbeat.post_failure(f"{type(exc).__name__}: {exc}")
@@ -383,6 +381,8 @@ class FlexTrainEngine:
         self._trace("backward launched")
 
         overflow = self._finish_step()
+        # every step: a cross-GPU wait of the fused kernels that ran out must never pass unnoticed
+        self._fused_health_check(end_of_step=True)
         self._mark_phase("finish")
         self._trace("finish launched")
         self.global_steps += 1
@@ -513,20 +513,25 @@ class FlexTrainEngine:
         steady, first = self.config.engine.fused_wait_seconds
         fused.set_wait_seconds(first if first_step else steady, self.device)
 
-    def _fused_health_check(self, read_words=None):
-        """After each of the first two steps on more than one GPU: if a cross-GPU
-        wait of the fused collective kernels ran out on any rank, all ranks switch
-        to the NCCL collectives for the rest of the run (a step that waited out
-        its budget is wrong anyway, and the next ones would crawl from time-out to
-        time-out).  Costs one device synchronisation and a scalar all-reduce.
+    def _fused_health_check(self, read_words=None, end_of_step: bool = False):
+        """On more than one GPU, at the end of every step (and every other unit of the first
+        one): if a cross-GPU wait of the fused collective kernels ran out on any rank, all
+        ranks switch to the NCCL collectives for the rest of the run, the step counts as
+        skipped, and - unless ``engine.fused_timeout_action`` is ``"fallback"`` -
+        ``FusedCollectiveTimeout`` is raised: the kernels of a rank that gave up wrote nothing
+        (its shard of the unit was not updated, a gather left the previous contents in place),
+        so what the step computed cannot be trusted and the caller should reload a checkpoint.
+        Costs one wait for the optimizer stream and a scalar all-reduce per step.
         ``read_words`` (tests) replaces the device error words by ``() -> (gather, reduce)``."""
         if read_words is None:
             if self.device.type != "cuda" or self.world == 1:
                 return
-            if not (self.opts._fused or self.para._peer_gather):
+            if not (self.opts._fused or self.para._peer_gather or self.optimizer.fused_nonlayer_in_use()):
                 return
             from .ops.native import cuda_lib
             lib = cuda_lib()
+            if end_of_step:
+                self.streams.opt.synchronize()      # the last units' reductions have ended
             read_words = lambda: (lib.ft_gemm_error(), lib.ft_comm_error())     # noqa: E731
         gemm_word, comm_word = read_words()
         if gemm_word and gemm_word not in self._GATHER_TIMEOUTS:
@@ -538,7 +543,35 @@ class FlexTrainEngine:
                          f"(error words: gather {gemm_word}, reduce {comm_word}); switching to NCCL collectives")
             self.opts._fused = False
             self.para._peer_gather = False
+            self.optimizer.disable_fused_nonlayer()
             self._status["fused_collectives_disabled"] = True
+            self._status["fused_timeout_words"] = {"gather": gemm_word, "reduce": comm_word,
+                                                   "step": self.global_steps}
+            if end_of_step:
+                self.skipped_steps += 1
+                if self.config.engine.fused_timeout_action == "raise":
+                    self.global_steps += 1
+                    raise FusedCollectiveTimeout(
+                        f"step {self.global_steps - 1}: a rank waited longer than its limit for a peer inside a "
+                        f"fused collective kernel (error words: gather {gemm_word}, reduce {comm_word}); "
+                        "that rank's share of the step was not applied.  The run continues on the NCCL "
+                        "collectives if this exception is caught; reload a checkpoint to discard the step.")
+
+    def collectives_in_use(self) -> Dict[str, Any]:
+        """Which implementation currently serves each collective of a step."""
+        fused_on = self.world > 1 and self.device.type == "cuda"
+        return {
+            "unit_gather": "ft_peer_gather (peer loads over NVLink)" if fused_on and self.para._peer_gather
+            else ("none (single rank)" if self.world == 1 else "all_gather_into_tensor"),
+            "unit_reduce": "ft_rs_adam (peer reduce-scatter + unscale + Adam)" if fused_on and self.opts._fused
+            else ("none (single rank)" if self.world == 1 else "reduce_scatter_tensor"),
+            "non_layerwise": "ft_ar_adam (peer all-reduce + sharded Adam)"
+            if fused_on and self.optimizer.fused_nonlayer_in_use()
+            else ("none (single rank)" if self.world == 1 else "all_reduce"),
+            "first_gemm": self.para.fused_first_gemm_state() if hasattr(self.para, "fused_first_gemm_state")
+            else "separate",
+            "fused_blocks": self.config.engine.fused_blocks if fused_on else None,
+        }
 
     def check_guards(self) -> None:
         """Guard mode (FLEXTRAIN_GUARD=1): wait for all work in flight, then raise if anything

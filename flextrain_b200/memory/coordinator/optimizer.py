@@ -221,6 +221,7 @@ class FlexTrainOptsCoordinator:
         self._flags = torch.zeros(self.num_units + 1, dtype=torch.int32, device=self.device)
         self._sumsq = torch.zeros(self.num_units, dtype=torch.float32, device=self.device)
         self._host_overflow = False
+        self.fused_timeouts = 0            # host updates dropped because their reduction timed out
         self._pending: List[Future] = []
         self.bytes_d2h = 0
         self._initialized = True
@@ -345,6 +346,12 @@ class FlexTrainOptsCoordinator:
         two_phase = flag is not None
         if flag is not None:
             flag.zero_()
+        # where a rank that gave up waiting for its peers says so: the unit's skip flag when the
+        # update waits for it anyway, else the pinned word the host worker reads before it
+        # touches any state (nothing was reduced or handed over in that case)
+        status = flag if two_phase else (entry.flag if entry is not None else None)
+        if entry is not None and not two_phase:
+            entry.flag.zero_()
         opts = self._gpu_opts.get(unit)
         stage = self._dev_out_stage[buf_index] if self._dev_out_stage is not None else None
         fused.rs_adam(
@@ -354,7 +361,7 @@ class FlexTrainOptsCoordinator:
             param_a=self._para.gpu_base(unit), a_hi=a_hi, param_b=stage, param_dtype=self.device_dtype,
             host_grad=None if (two_phase or entry is None) else entry.grad, finite_flag=flag,
             segments=fused.make_segments(segs, self.optimizer.param_groups, self.cpu_optimizer, step),
-            nseg=len(segs), max_blocks=self._cfg.engine.fused_blocks)
+            nseg=len(segs), max_blocks=self._cfg.engine.fused_blocks, status=status)
         if defer:
             return True                             # the caller keeps the reduced shard
         if two_phase:
@@ -404,8 +411,14 @@ class FlexTrainOptsCoordinator:
         try:
             grads_ready.synchronize()
             chaos.perturb("host update has its gradients")
-            if self.check_overflow and int(entry.flag.item()) != 0:
-                self._host_overflow = True
+            word = int(entry.flag.item())
+            if word != 0:
+                # non-finite gradient (1) or a fused reduction that gave up at its start barrier
+                # (101): the pool entry holds no gradient of this unit, no state may change
+                if word == 101:
+                    self.fused_timeouts += 1
+                else:
+                    self._host_overflow = True
                 return
             og, oc, on = self.opt_tiers
             g, c, n = self.para_tiers
@@ -538,10 +551,13 @@ class FlexTrainOptsCoordinator:
         met a non-finite gradient (its update was skipped)."""
         overflow = False
         if self.check_overflow:
-            overflow = bool(self._flags.any().item())
-            if not overflow and self._pending and self.host_numel:
-                # host flags are only known once the host updates ran
-                pass
+            # the flags are raised on the optimizer stream (reduce kernel / finite check of the
+            # last units are still running when backward has been launched): read them there
+            with self.streams.opt.use():
+                any_flag = self._flags.any()
+                read = self.streams.opt.record()
+            read.synchronize()
+            overflow = bool(any_flag.item())
         return overflow
 
     def collect_host_overflow(self) -> bool:

@@ -117,11 +117,9 @@ class FlexTrainParaCoordinator:
         if want is True and not ok:
             raise RuntimeError("engine.fused_collectives=true needs peer access between all ranks")
         if ok:
-            # lagged completion signalling has been run on up to 2 ranks; larger worlds use the
-            # one-store-at-a-time form unless asked ("auto")
             lag = cfg.engine.gather_lag
             from ...parallel import fused
-            fused.set_gather_lag(lag is True or (lag == "auto" and self.world <= 2))
+            fused.set_gather_lag(lag is not False)
         return bool(ok)
 
     def shard_range(self):

@@ -97,8 +97,7 @@ class LlamaBlock(nn.Module):
             qkv = F.rope_heads_inplace(qkv, cos, sin, nh + nkv, d)
             packed = F.attention_packed(qkv, nh, nkv, d)
             if packed is not None:
-                x = x + F.linear(packed, self.wo)
-                h = F.rmsnorm(x, self.ffn_norm, cfg.eps)
+                x, h = F.add_rmsnorm(x, F.linear(packed, self.wo), self.ffn_norm, cfg.eps)
                 return x + F.linear(F.linear_swiglu(h, self.w_gate_up), self.w_down)
         q = qkv[..., : nh * d].unflatten(-1, (nh, d))
         k = qkv[..., nh * d: (nh + nkv) * d].unflatten(-1, (nkv, d))
@@ -106,8 +105,7 @@ class LlamaBlock(nn.Module):
         if not qkv.is_cuda:
             q, k = F.rope(q, cos, sin), F.rope(k, cos, sin)
         a = F.causal_attention(q, k, v).reshape(B, S, H)
-        x = x + F.linear(a, self.wo)
-        h = F.rmsnorm(x, self.ffn_norm, cfg.eps)
+        x, h = F.add_rmsnorm(x, F.linear(a, self.wo), self.ffn_norm, cfg.eps)
         x = x + F.linear(F.linear_swiglu(h, self.w_gate_up), self.w_down)
         return x
 

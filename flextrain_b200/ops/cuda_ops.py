@@ -161,6 +161,62 @@ def rmsnorm_rows(x, w, eps):
     return _Norm.apply(x, w, None, eps)
 
 
+_NORM_MAX_HIDDEN = None
+
+
+def norm_rows_supported(hidden: int) -> bool:
+    """Whether the row-resident norm kernels cover this hidden size (forward and backward)."""
+    global _NORM_MAX_HIDDEN
+    if _NORM_MAX_HIDDEN is None:
+        lib = cuda_lib()
+        _NORM_MAX_HIDDEN = min(lib.ft_norm_max_hidden(0), lib.ft_norm_max_hidden(1))
+    return hidden % 8 == 0 and 0 < hidden <= _NORM_MAX_HIDDEN
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    """``s = x + r`` and ``y = rmsnorm(s) * w`` in one kernel; the backward adds the gradient
+    that arrives at ``s`` from its other consumer (the next residual add) to the gradient through
+    the norm inside the norm's backward kernel, so neither direction has an add pass."""
+
+    @staticmethod
+    def forward(ctx, x, r, w, eps):
+        h = x.shape[-1]
+        x2 = x.reshape(-1, h).contiguous()
+        r2 = r.reshape(-1, h).contiguous()
+        rows = x2.shape[0]
+        s = torch.empty_like(x2)
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(cuda_lib().ft_add_norm_fwd(ptr(x2), ptr(r2), ptr(s), ptr(w), None, ptr(y), None, ptr(rstd),
+                                          rows, h, float(eps), 0, dtype_code(x.dtype), stream_handle()),
+               "ft_add_norm_fwd")
+        ctx.save_for_backward(s, w, rstd)
+        return s.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, ds, dy):
+        s, w, rstd = ctx.saved_tensors
+        rows, h = s.shape
+        if dy is None:
+            return ds, ds, None, None
+        dy2 = dy.reshape(rows, h).contiguous()
+        ds2 = ds.reshape(rows, h).contiguous() if ds is not None else None
+        dx = torch.empty_like(s)
+        dw = torch.empty_like(w)
+        lib = cuda_lib()
+        parts = lib.ft_norm_bwd_parts(rows, h)
+        part = torch.empty(parts * h, dtype=torch.float32, device=s.device)
+        _check(lib.ft_add_norm_bwd(ptr(s), ptr(w), ptr(dy2), ptr(ds2), None, ptr(rstd), ptr(dx), ptr(dw),
+                                   None, ptr(part), None, rows, h, 0, dtype_code(s.dtype), stream_handle()),
+               "ft_add_norm_bwd")
+        dx = dx.view(dy.shape)
+        return dx, dx, dw, None
+
+
+def add_rmsnorm(x, r, w, eps):
+    return _AddRMSNorm.apply(x, r, w, eps)
+
+
 class _BiasAct(torch.autograd.Function):
     """``act(x + bias)`` over the last dimension; act 0 adds the bias in place,
     act 1 is the tanh GELU.  The backward produces dx and the bias gradient (column

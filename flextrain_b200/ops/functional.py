@@ -27,17 +27,34 @@ def linear(x, w):
 def rmsnorm(x, weight, eps):
     if _cuda(x):
         from . import cuda_ops
-        if os.environ.get("FLEXTRAIN_RMSNORM", "") == "rows":
+        # row-resident kernels (each row read once): 0.70-0.72 of the HBM copy rate forward,
+        # 0.54-0.60 backward at hidden 5120 / 8192, against 0.37 / 0.25 for the two-pass
+        # kernels, which remain for hidden sizes the row kernels do not cover
+        if cuda_ops.norm_rows_supported(x.shape[-1]) and os.environ.get("FLEXTRAIN_RMSNORM", "rows") == "rows":
             return cuda_ops.rmsnorm_rows(x, weight, eps)
         return cuda_ops.rmsnorm(x, weight, eps)
     return ref.rmsnorm(x, weight, eps)
 
 
+def add_rmsnorm(x, r, weight, eps):
+    """``s = x + r`` and ``rmsnorm(s) * weight`` in one pass over the rows; returns ``(s, y)``.
+    The residual add of a transformer block and the norm that follows it (forward), and the
+    sum of the two gradient branches that meet at ``s`` (backward), cost no pass of their own."""
+    if _cuda(x):
+        from . import cuda_ops
+        if cuda_ops.norm_rows_supported(x.shape[-1]) and os.environ.get("FLEXTRAIN_RMSNORM", "rows") == "rows":
+            return cuda_ops.add_rmsnorm(x, r, weight, eps)
+        s = x + r
+        return s, cuda_ops.rmsnorm(s, weight, eps)
+    s = x + r
+    return s, ref.rmsnorm(s, weight, eps)
+
+
 def gpt_native_elementwise() -> bool:
-    """Whether CUDA tensors take the package's LayerNorm / bias / GELU kernels
-    (``FLEXTRAIN_GPT_ELEMENTWISE=native``) or the ATen ones (default until the
-    kernels have been checked on hardware).  GEMMs and attention are native either way."""
-    return os.environ.get("FLEXTRAIN_GPT_ELEMENTWISE", "aten") == "native"
+    """Whether CUDA tensors take the package's LayerNorm / bias / GELU kernels (default) or
+    the ATen ones (``FLEXTRAIN_GPT_ELEMENTWISE=aten``, the comparison arm of
+    ``benchmarks/elementwise_bench.py``).  GEMMs and attention are native either way."""
+    return os.environ.get("FLEXTRAIN_GPT_ELEMENTWISE", "native") == "native"
 
 
 def layernorm(x, weight, bias, eps):

@@ -220,9 +220,7 @@ class FlexTrainOptimizer:
         if self._cfg.engine.strict_overflow or self._cfg.engine.gradient_clipping > 0:
             return False                            # deferred mode splits reduce and update
         nl = self._cfg.engine.fused_nonlayer
-        # "auto": the world sizes this path has been run on (1 and 2 ranks); larger
-        # worlds keep the NCCL all-reduce + replicated device Adam unless asked
-        if nl is False or (nl == "auto" and dist.get_world_size() > 2):
+        if nl is False:
             return False
         from .ops.adam import FlexTrainAdam
         from .parallel.fused import segments_aligned
@@ -275,6 +273,35 @@ class FlexTrainOptimizer:
         self._nl_grad.zero_()
         return overflow
 
+    def fused_nonlayer_in_use(self) -> bool:
+        return bool(getattr(self, "_nl_fused", False)) and not getattr(self, "_nl_fused_off", False)
+
+    def disable_fused_nonlayer(self):
+        """Stop using the fused all-reduce + Adam kernel (after one of its waits ran out).  The
+        fp32 state stays sharded over the ranks; the reduction and the hand-out of the updated
+        parameters go through the library collectives from now on."""
+        self._nl_fused_off = True
+
+    def _nl_sharded_library_step(self, grad_scale: float, check_overflow: bool) -> bool:
+        """The sharded non-layerwise update without the fused kernel: all-reduce (AVG) of the
+        gradients, Adam on this rank's slice of the fp32 state, all-gather of the slices."""
+        from .ops.adam.gpu_adam import device_adam_update, has_nonfinite
+        from .param_group import slice_segments
+        S, lo = self._nl_shard, self._nl_lo
+        dist.all_reduce(self._nl_grad, dist.ReduceOp.AVG)
+        overflow = has_nonfinite(self._nl_grad) if check_overflow else False
+        if not overflow:
+            own = self._nl_grad[lo:lo + S]
+            for seg in slice_segments(self._nl_segments, lo, lo + S, rebase=True):
+                g = self.param_groups[seg.group]
+                sl = slice(seg.start, seg.end)
+                device_adam_update(g, max(int(g[STEP_KEY]), 1), self.cpu_optimizer,
+                                   self._nl_master[sl], own[sl], [s[sl] for s in self._nl_states],
+                                   self._nl_para[lo:lo + S][sl], grad_scale=grad_scale)
+            dist.all_gather(self._nl_para, self._nl_para[lo:lo + S])
+        self._nl_grad.zero_()
+        return overflow
+
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0, check_overflow: bool = False) -> bool:
         """Average the replicated gradients over ranks and apply one update to
@@ -284,6 +311,8 @@ class FlexTrainOptimizer:
             return False
         from .ops.adam.gpu_adam import has_nonfinite
         if self._nl_fused:
+            if getattr(self, "_nl_fused_off", False):
+                return self._nl_sharded_library_step(grad_scale, check_overflow)
             return self._nl_fused_step(grad_scale, check_overflow)
         self.reduce_gradients()
         overflow = has_nonfinite(self._nl_grad) if check_overflow else False

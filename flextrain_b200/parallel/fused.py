@@ -34,7 +34,7 @@ def _lib():
         lib.ft_rs_adam.argtypes = [
             c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_float, c_uint32, c_int, c_int,
             c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int,
-            c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p]
+            c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]
         lib.ft_ar_adam.argtypes = [
             c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_float, c_uint32, c_int, c_int,
             c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
@@ -68,15 +68,17 @@ def rs_adam(world: int, rank: int, grad_ptrs, flag_ptrs, grad_dtype: torch.dtype
             master: Optional[torch.Tensor], m: Optional[torch.Tensor], v: Optional[torch.Tensor],
             param_a: Optional[torch.Tensor], a_hi: int, param_b: Optional[torch.Tensor],
             param_dtype: torch.dtype, host_grad: Optional[torch.Tensor],
-            finite_flag: Optional[torch.Tensor], segments, nseg: int, max_blocks: int = 64,
-            start_slot: int = 0, done_slot: int = 1):
-    """Thin wrapper over ``ft_rs_adam``; see ``csrc/comm/rs_adam.cu``."""
+            finite_flag: Optional[torch.Tensor], segments, nseg: int, max_blocks: int = 148,
+            start_slot: int = 0, done_slot: int = 1, status: Optional[torch.Tensor] = None):
+    """Thin wrapper over ``ft_rs_adam``; see ``csrc/comm/rs_adam.cu``.  ``status`` (one int32,
+    pinned host or device memory) receives 101 when this rank gave up waiting for its peers
+    at the start of the call, in which case none of the outputs was written."""
     rc = _lib().ft_rs_adam(
         world, rank, ctypes.cast(grad_ptrs, c_void_p), ctypes.cast(flag_ptrs, c_void_p) if flag_ptrs
         is not None else None, dtype_code(grad_dtype), shard, float(scale), seq, start_slot, done_slot,
         ptr(reduced_out), og, int(do_adam), ptr(master), ptr(m), ptr(v), ptr(param_a), a_hi,
         ptr(param_b), dtype_code(param_dtype), ptr(host_grad),
-        -1 if host_grad is None else dtype_code(host_grad.dtype), ptr(finite_flag), nseg,
+        -1 if host_grad is None else dtype_code(host_grad.dtype), ptr(finite_flag), ptr(status), nseg,
         ctypes.cast(segments, c_void_p), max_blocks, stream_handle())
     if rc != 0:
         raise RuntimeError(f"ft_rs_adam failed (code {rc})")

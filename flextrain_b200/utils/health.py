@@ -25,6 +25,13 @@ class PeerFailure(RuntimeError):
     """Another rank reported a failure or stopped sending heartbeats."""
 
 
+class FusedCollectiveTimeout(RuntimeError):
+    """A rank waited longer than its limit for a peer inside a fused collective kernel; the
+    kernels of that rank wrote nothing for the call in question, so the step it belongs to is
+    incomplete.  Raised on every rank at the end of that step, after all ranks have switched
+    to the library collectives."""
+
+
 class Heartbeat:
     def __init__(self, prefix: str = "ft/health"):
         self.prefix = prefix

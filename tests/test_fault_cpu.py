@@ -113,9 +113,24 @@ def _fallback_worker(rank, world, port, q):
     kept = eng.health().get("gemm_error_word_seen")
     eng._fused_health_check(read_words=lambda: (0, 101) if rank == 1 else (0, 0))
     after = (eng.opts._fused, eng.para._peer_gather, eng.health().get("fused_collectives_disabled"))
+    # at the end of a step the same finding is an error on EVERY rank (the step is incomplete) ...
+    from flextrain_b200.utils.health import FusedCollectiveTimeout
+    eng.opts._fused = True
+    skipped = eng.skipped_steps
+    try:
+        eng._fused_health_check(read_words=lambda: (0, 101) if rank == 1 else (0, 0), end_of_step=True)
+        raised = False
+    except FusedCollectiveTimeout:
+        raised = True
+    counted = eng.skipped_steps == skipped + 1 and not eng.opts._fused
+    # ... unless the configuration asks for a silent switch
+    eng.config.engine.fused_timeout_action = "fallback"
+    eng.opts._fused = True
+    eng._fused_health_check(read_words=lambda: (201, 0) if rank == 0 else (0, 0), end_of_step=True)
+    quiet = not eng.opts._fused
     loss = float(eng.train_iteration()[0].detach())             # and the run goes on, on the library collectives
     eng.shutdown()
-    q.put((rank, clean, kept, after, loss))
+    q.put((rank, clean, kept, after + (raised, counted, quiet), loss))
     reset_runtime()
 
 
@@ -137,7 +152,7 @@ def test_timeout_on_one_rank_switches_every_rank_to_library_collectives():
         clean, kept, after, loss = got[rank]
         assert clean == (True, True)                    # no time-out: nothing changes
         assert kept == 7
-        assert after == (False, False, True), f"rank {rank} did not switch: {after}"
+        assert after == (False, False, True, True, True, True), f"rank {rank} did not switch: {after}"
         assert loss == loss
 
 

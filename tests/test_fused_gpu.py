@@ -92,29 +92,43 @@ def test_rs_adam_two_phase_and_overflow_flag():
 
 def test_bounded_wait_reports_instead_of_hanging():
     """A start flag that nobody sets: the kernel must give up, raise the error
-    word and leave the context usable (checked by running another kernel)."""
+    word, report through the caller's status word, leave every output (fp32
+    state, parameters, host gradient) untouched and leave the context usable
+    (checked by running another kernel)."""
     import os
     from flextrain_b200.parallel import fused
+    from flextrain_b200.param_group import GroupSegment
     dev = torch.device("cuda", 0)
     if os.environ.get("FLEXTRAIN_SKIP_TIMEOUT_TEST"):
         pytest.skip("disabled by environment")
-    world, S = 2, 8 * 64
+    world, S, og = 2, 8 * 64, 8 * 32
     grads = [torch.randn(world * S, device=dev).to(torch.bfloat16) for _ in range(world)]
     flags = [torch.zeros(128 * 8, dtype=torch.int32, device=dev) for _ in range(world)]
     gp = (ctypes.c_void_p * world)(*[g.data_ptr() for g in grads])
     fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    master = torch.randn(og, device=dev)
+    m, v = torch.rand(og, device=dev), torch.rand(og, device=dev)
+    param = torch.full((og,), 3.0, device=dev, dtype=torch.bfloat16)
+    host_grad = torch.full((S - og,), 7.0, dtype=torch.bfloat16).pin_memory()
+    status = torch.zeros(1, dtype=torch.int32).pin_memory()
+    before = [t.clone() for t in (master, m, v, param)]
+    arr = fused.make_segments([GroupSegment(0, 0, og)], [dict()], _Owner, step=1)
     from flextrain_b200.ops.native import cuda_lib
     lib = cuda_lib()
     lib.ft_comm_set_spin_budget.argtypes = [ctypes.c_longlong]
     lib.ft_comm_set_spin_budget(20_000_000)          # ~10 ms
     try:
-        fused.rs_adam(world, 0, gp, fp, torch.bfloat16, S, 0.5, 7, None, 0, False, None, None, None,
-                      None, 0, None, torch.bfloat16, None, None, (fused._AdamSegment * 1)(), 0,
-                      max_blocks=1)
+        fused.rs_adam(world, 0, gp, fp, torch.bfloat16, S, 0.5, 7, None, og, True, master, m, v,
+                      param, og, None, torch.bfloat16, host_grad, None, arr, 1, max_blocks=2,
+                      status=status)
         torch.cuda.synchronize()
         assert fused.comm_error() == 101
     finally:
         lib.ft_comm_set_spin_budget(0)
+    assert int(status.item()) == 101
+    for now, was in zip((master, m, v, param), before):
+        assert torch.equal(now, was)
+    assert torch.equal(host_grad, torch.full_like(host_grad, 7.0))
     x = torch.ones(1024, device=dev)
     assert float((x * 2).sum()) == 2048.0
 
@@ -150,11 +164,15 @@ def test_ag_gemm_emulated_ranks(world):
         # put the buffer back to 'own shard only' for the next emulated rank's peers
     
 
-def test_peer_gather_emulated_ranks():
+@pytest.mark.parametrize("mode", [1, 0])
+def test_peer_gather_emulated_ranks(mode):
+    """Both forms of the stand-alone gather: loads / stores by every thread (1) and bulk
+    copies through shared memory (0)."""
     from flextrain_b200.ops.native import cuda_lib
     from flextrain_b200.parallel import fused
     dev = torch.device("cuda", 0)
     world = 4
+    cuda_lib().ft_gather_set_mode(mode)
     shard = 4096 * 37 + 4096                      # bytes, page aligned, not a multiple of 32 KiB
     full = torch.randint(0, 255, (world * shard,), dtype=torch.uint8, device=dev)
     bufs = []
@@ -165,8 +183,11 @@ def test_peer_gather_emulated_ranks():
     flags = [torch.full((128 * 8,), 9, dtype=torch.int32, device=dev) for _ in range(world)]
     bp = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
     fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
-    fused.peer_gather(world, 2, bp, fp, 9, shard, num_copiers=3)
-    torch.cuda.synchronize()
+    try:
+        fused.peer_gather(world, 2, bp, fp, 9, shard, num_copiers=3)
+        torch.cuda.synchronize()
+    finally:
+        cuda_lib().ft_gather_set_mode(1)
     assert cuda_lib().ft_gemm_error() == 0
     assert torch.equal(bufs[2], full)
 

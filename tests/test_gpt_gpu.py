@@ -1,16 +1,6 @@
 """GPT family on one B200, the in-place parameter layout with a host optimizer share, and
-kernels that have not yet run on hardware.  The file sorts last on purpose: what is new
-here runs after the established GPU tests.
-
-The engine test runs a bf16 tiny GPT with the native GEMM, attention and head
-kernels and the ATen LayerNorm / GELU (the default).  The tests of the package's
-own LayerNorm / bias / GELU / row-RMSNorm kernels, and of the engine on top of
-them, run when ``FLEXTRAIN_TEST_NEW_KERNELS=1``: those kernels have not yet run
-on hardware and are switched on by that variable
-(tests) or ``FLEXTRAIN_GPT_ELEMENTWISE=native`` / ``FLEXTRAIN_RMSNORM=rows`` (use).
-The same variable runs the second-generation attention backward
-(``FLEXTRAIN_ATTN_BWD=2``) and the fourth-generation forward (``FLEXTRAIN_ATTN_FWD=4``).
-"""
+the row-resident norm / bias / GELU kernels and the SwiGLU GEMM epilogue against fp32
+PyTorch."""
 import math
 import os
 
@@ -19,10 +9,6 @@ import torch
 import torch.nn.functional as TF
 
 pytestmark = pytest.mark.gpu
-
-new_kernels = pytest.mark.skipif(os.environ.get("FLEXTRAIN_TEST_NEW_KERNELS", "0") != "1",
-                                 reason="set FLEXTRAIN_TEST_NEW_KERNELS=1 to run")
-
 
 def _dev():
     return torch.device("cuda", 0)
@@ -119,7 +105,6 @@ def test_parameters_in_place_with_host_optimizer_share():
     assert health["skipped_steps"] == 0
 
 
-@new_kernels
 @pytest.mark.parametrize("rows,h", [(5, 256), (64, 1024), (33, 5120), (17, 8192), (9, 12288)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_layernorm_kernels(rows, h, dtype):
@@ -138,7 +123,6 @@ def test_layernorm_kernels(rows, h, dtype):
     assert _rel_err(gx, fx) < 1e-2 and _rel_err(gw, fw) < 1e-2 and _rel_err(gb, fb) < 1e-2
 
 
-@new_kernels
 @pytest.mark.parametrize("rows,h", [(7, 256), (130, 4096), (33, 5120), (10, 8192)])
 def test_rmsnorm_row_kernels(rows, h):
     from flextrain_b200.ops import cuda_ops, reference as ref
@@ -154,7 +138,6 @@ def test_rmsnorm_row_kernels(rows, h):
     assert _rel_err(y, yf) < 1e-2 and _rel_err(gx, fx) < 1e-2 and _rel_err(gw, fw) < 1e-2
 
 
-@new_kernels
 @pytest.mark.parametrize("rows,n", [(3, 8), (100, 264), (513, 1024), (64, 20480)])
 @pytest.mark.parametrize("act", [0, 1])
 def test_bias_activation_kernels(rows, n, act):
@@ -175,81 +158,14 @@ def test_bias_activation_kernels(rows, n, act):
     assert _rel_err(gx, fx) < 1e-2 and _rel_err(gb, fb) < 2e-2
 
 
-@new_kernels
-def test_gpt_engine_with_native_elementwise(monkeypatch):
-    aten = _run_engine(ALL_HBM)
-    monkeypatch.setenv("FLEXTRAIN_GPT_ELEMENTWISE", "native")
+def test_gpt_engine_native_elementwise_against_aten(monkeypatch):
     native = _run_engine(ALL_HBM)
+    monkeypatch.setenv("FLEXTRAIN_GPT_ELEMENTWISE", "aten")
+    aten = _run_engine(ALL_HBM)
     assert max(abs(a - b) for a, b in zip(aten, native)) < 3e-2, (aten, native)
     assert native[-1] < native[0] - 0.05
 
 
-def _attention_grads(q, k, v, do, scale):
-    from flextrain_b200.ops.attention_native import attention_native
-    o = attention_native(q, k, v, scale)
-    return (o,) + torch.autograd.grad(o, (q, k, v), do)
-
-
-@new_kernels
-@pytest.mark.parametrize("shape", [
-    (1, 128, 2, 2, 128), (2, 384, 8, 2, 128), (1, 1000, 2, 2, 128), (2, 640, 4, 4, 64), (1, 2048, 4, 1, 128),
-])
-def test_attention_backward_second_generation(shape):
-    """Backward with the double-buffered Q and dQ on the dP columns against the
-    first generation (validated) and against the fp32 oracle."""
-    from flextrain_b200.ops import reference as ref
-    from flextrain_b200.ops.native import cuda_lib
-    B, S, Hq, Hkv, D = shape
-    lib = cuda_lib()
-    torch.manual_seed(S + D + Hq)
-    mk = lambda h: torch.randn(B, S, h, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)  # noqa: E731
-    q, k, v = mk(Hq), mk(Hkv), mk(Hkv)
-    do = torch.randn(B, S, Hq, D, device=_dev(), dtype=torch.bfloat16)
-    scale = 1.0 / math.sqrt(D)
-    base = _attention_grads(q, k, v, do, scale)
-    lib.ft_attn_set_bwd_version(2)
-    try:
-        for _ in range(3):                              # repeated: ordering bugs are timing dependent
-            got = _attention_grads(q, k, v, do, scale)
-            torch.cuda.synchronize()
-            assert lib.ft_gemm_error() == 0
-            for g, b in zip(got[1:], base[1:]):
-                assert _rel_err(g, b) < 5e-3
-    finally:
-        lib.ft_attn_set_bwd_version(1)
-    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
-    of = ref.causal_attention(qf, kf, vf, scale)
-    want = torch.autograd.grad(of, (qf, kf, vf), do.float())
-    for g, w in zip(got[1:], want):
-        assert _rel_err(g, w) < 3e-2
-
-
-@new_kernels
-@pytest.mark.parametrize("shape", [(1, 128, 2, 2, 128), (2, 384, 8, 2, 128), (1, 1000, 2, 2, 128), (2, 640, 4, 4, 64)])
-def test_attention_forward_fourth_generation(shape):
-    """Forward with two threads per score row against the default forward."""
-    from flextrain_b200.ops.attention_native import attention_forward
-    from flextrain_b200.ops.native import cuda_lib
-    B, S, Hq, Hkv, D = shape
-    lib = cuda_lib()
-    torch.manual_seed(S + D)
-    q = torch.randn(B, S, Hq, D, device=_dev(), dtype=torch.bfloat16)
-    k = torch.randn(B, S, Hkv, D, device=_dev(), dtype=torch.bfloat16)
-    v = torch.randn(B, S, Hkv, D, device=_dev(), dtype=torch.bfloat16)
-    scale = 1.0 / math.sqrt(D)
-    o2, lse2, _ = attention_forward(q, k, v, scale)
-    lib.ft_attn_set_fwd_version(4)
-    try:
-        for _ in range(3):
-            o4, lse4, _ = attention_forward(q, k, v, scale)
-            torch.cuda.synchronize()
-            assert lib.ft_gemm_error() == 0
-            assert _rel_err(o4, o2) < 1e-2 and float((lse4 - lse2).abs().max()) < 1e-2
-    finally:
-        lib.ft_attn_set_fwd_version(2)
-
-
-@new_kernels
 @pytest.mark.parametrize("rows,k,f", [(256, 256, 128), (520, 320, 384), (4096, 1024, 2816), (200, 256, 136)])
 def test_swiglu_in_the_gemm_epilogue(rows, k, f):
     """Projection GEMM with the activation in its epilogue against the two-kernel path
