@@ -78,6 +78,7 @@ def parse_args(argv=None):
     p.add_argument("--auto-config", action="store_true",
                    help="let the engine's profiling planner (system_auto_config) choose the split after "
                         "the first warm-up step; its measurements are added to the JSON line")
+    p.add_argument("--extra-model", default=EXTRA_MODEL, help=argparse.SUPPRESS)
     p.add_argument("--as-extra", action="store_true", help=argparse.SUPPRESS)
     return p.parse_args(argv)
 
@@ -412,7 +413,7 @@ def run_extra(args, world, rank, elapsed):
     env = dict(os.environ)
     env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 23)
     env.pop("TORCHELASTIC_USE_AGENT_STORE", None)     # the children rendezvous among themselves
-    cmd = [sys.executable, os.path.abspath(__file__), "--as-extra", "--model", EXTRA_MODEL,
+    cmd = [sys.executable, os.path.abspath(__file__), "--as-extra", "--model", args.extra_model,
            "--gpus", str(world), "--steps", "4", "--warmup", "3", "--no-e2e", "--extra", "off",
            "--unit-buffers", str(args.unit_buffers), "--wall-limit", str(room)]
     if args.phases:
@@ -458,7 +459,7 @@ def main_ours(args):
         torch.cuda.empty_cache()
         extra = run_extra(args, world, rank, elapsed)
         if out is not None:
-            out["extra"] = {"llama3_70b": extra}
+            out["extra"] = {args.extra_model.replace("-", "_"): extra}
     if out is not None:
         print(json.dumps(out), flush=True)
 

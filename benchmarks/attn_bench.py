@@ -2,7 +2,7 @@
 """Times the native causal attention kernels against PyTorch SDPA.
 
     python benchmarks/attn_bench.py [--shapes 7b 13b 70b small] [--iters 5] [--no-sdpa]
-                                    [--pass fwd bwd] [--fwd-version 2|4]
+                                    [--pass fwd bwd]
 
 Shapes are (batch, seq, q heads, kv heads, head dim).  CUDA events, 3 warm-up
 launches; q/k/v/o/do of the named shapes are larger than L2 except for
@@ -47,12 +47,9 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--no-sdpa", action="store_true")
     ap.add_argument("--pass", dest="passes", nargs="+", default=["fwd", "bwd"])
-    ap.add_argument("--fwd-version", type=int, default=0, help="forward kernel: 2 (one thread per score row) or 4 (two); 0 keeps the default")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     from flextrain_b200.ops.native import cuda_lib
-    if args.fwd_version:
-        cuda_lib().ft_attn_set_fwd_version(args.fwd_version)
     for name in args.shapes:
         B, S, Hq, Hkv, D = SHAPES[name]
         torch.manual_seed(0)

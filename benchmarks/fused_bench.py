@@ -111,7 +111,7 @@ def bench_rs(world, rank, dev, page, n, iters, flush, blocks):
             "blocks": blocks}
 
 
-def bench_ag(world, rank, dev, page, iters, flush, copiers):
+def bench_ag(world, rank, dev, page, iters, flush):
     _, tf, src = peaks()
     M, N, K = 16384, 28672, 8192
     symm = SymmetricBuffer(N * K * 2)
@@ -128,8 +128,7 @@ def bench_ag(world, rank, dev, page, iters, flush, copiers):
         w[rank * rows:(rank + 1) * rows].copy_(shard)
 
     def run_fused():
-        fused.ag_gemm(world, rank, symm.ptr_array(), page.ptr_array(), page.next_seq("ag"), x, N, out=y,
-                      num_copiers=copiers)
+        fused.ag_gemm(world, rank, symm.ptr_array(), page.ptr_array(), page.next_seq("ag"), x, N, out=y)
 
     gathered = torch.empty(N, K, device=dev, dtype=torch.bfloat16)
 
@@ -155,16 +154,51 @@ def bench_ag(world, rank, dev, page, iters, flush, copiers):
     return {"bench": "ag_gemm", "M": M, "N": N, "K": K, "world": world, "fused_ms": t_f,
             "nccl_cublas_ms": t_n, "roofline_ms": roof_ms, "fused_frac_of_roofline": roof_ms / t_f,
             "nccl_frac_of_roofline": roof_ms / t_n, "speedup_vs_nccl": t_n / t_f, "rel_err": err,
-            "peaks": src, "copiers": copiers}
+            "peaks": src, "form": "CTA pairs, one copy warp per CTA"}
+
+
+def bench_gather(world, rank, dev, page, nbytes, iters, flush, blocks):
+    """Whole-unit gather as the engine issues it: every rank owns 1/world of a flat buffer of
+    ``nbytes`` (the bf16 parameters of one layer) and pulls the rest from its peers.
+    ``ft_peer_gather`` in both forms against NCCL ``all_gather_into_tensor``; the roofline is
+    the inbound bytes at the measured peer-copy rate."""
+    from flextrain_b200.ops.native import cuda_lib
+    shard = nbytes // world // 4096 * 4096
+    symm = SymmetricBuffer(shard * world)
+    flat = symm.tensor(torch.uint8)
+    flat.random_(0, 255)
+    mine = flat[rank * shard:(rank + 1) * shard].clone()
+    gathered = torch.empty(shard * world, dtype=torch.uint8, device=dev)
+    lib = cuda_lib()
+    res = {"bench": "unit_gather", "bytes": shard * world, "world": world, "blocks": blocks}
+
+    def run_peer():
+        fused.peer_gather(world, rank, symm.ptr_array(), page.ptr_array(), page.next_seq("pg"), shard, blocks)
+
+    for mode, name in ((1, "peer_ldst_ms"), (0, "peer_bulk_ms")):
+        lib.ft_gather_set_mode(mode)
+        res[name] = timed(run_peer, iters, flush, world)
+    lib.ft_gather_set_mode(1)
+    res["nccl_ms"] = timed(lambda: tdist.all_gather_into_tensor(gathered, mine), iters, flush, world)
+    roof_ms = (world - 1) * shard / (NVLINK_GBS * 1e9) * 1e3
+    res["roofline_ms"] = roof_ms
+    res["peer_ldst_frac_of_roofline"] = roof_ms / res["peer_ldst_ms"]
+    res["peer_bulk_frac_of_roofline"] = roof_ms / res["peer_bulk_ms"]
+    res["nccl_frac_of_roofline"] = roof_ms / res["nccl_ms"]
+    res["inbound_gbs_ldst"] = (world - 1) * shard / res["peer_ldst_ms"] / 1e6
+    assert lib.ft_gemm_error() == 0
+    symm.close()
+    return res
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", nargs="+", default=["rs", "ag"])
+    ap.add_argument("--what", nargs="+", default=["rs", "ag"], help="rs, ag, gather")
+    ap.add_argument("--gather-mib", nargs="+", type=int, default=[605, 1632],
+                    help="unit sizes of the gather benchmark (13B and 70B layers in bf16)")
     ap.add_argument("--sizes", nargs="+", default=["1M", "16M", "256M", "1B"])
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--blocks", type=int, default=64)
-    ap.add_argument("--copiers", type=int, default=16)
+    ap.add_argument("--blocks", type=int, default=148)
     args = ap.parse_args()
     ft.init_distributed("nccl")
     world, rank = ft.distributed.get_world_size(), ft.distributed.get_rank()
@@ -175,8 +209,11 @@ def main():
     if "rs" in args.what:
         for name in args.sizes:
             out.append(bench_rs(world, rank, dev, page, SIZES[name], args.iters, flush, args.blocks))
+    if "gather" in args.what:
+        for mib in args.gather_mib:
+            out.append(bench_gather(world, rank, dev, page, mib << 20, args.iters, flush, args.blocks))
     if "ag" in args.what:
-        out.append(bench_ag(world, rank, dev, page, args.iters, flush, args.copiers))
+        out.append(bench_ag(world, rank, dev, page, args.iters, flush))
     if rank == 0:
         for r in out:
             print(json.dumps(r), flush=True)

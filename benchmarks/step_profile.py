@@ -124,7 +124,12 @@ def main():
     ft.init_distributed(dist_backend="nccl", force_init=False)
     dev = ft.distributed.current_device()
     hbm_free, _ = torch.cuda.mem_get_info()
-    name, mcfg, mbs, mbpr, split, _ = bench.pick_model(args, 1, hbm_free, psutil.virtual_memory().available)
+    args.nvme_gib_per_rank = 0.0
+    dram, node_gpus = psutil.virtual_memory().available, torch.cuda.device_count()
+    name, _ = bench.pick_model(args, hbm_free, dram, node_gpus)
+    mcfg = bench._model_cfg(name, args)
+    mbs, mbpr = bench.MICRO_BATCH.get(name, 2), args.micro_batches_per_rank or 1
+    split = bench.plan_split(args, name, 1, hbm_free, dram, node_gpus)
     if split is None:
         raise SystemExit(f"{name} does not fit on one GPU")
     cfg = {"batch_size": mbs * mbpr, "micro_batch_size": mbs, "checkpoint_interval": 1, "split_ratio": split,

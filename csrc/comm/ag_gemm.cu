@@ -2,18 +2,15 @@
 // consumes the gathered weight, and the stand-alone peer gather the engine uses
 // for whole units.
 //
-// ft_ag_gemm: y[M,N] = x[M,K] * W[N,K]^T where W is row-sharded over `world`
-// ranks (rank r owns rows [r*N/world, (r+1)*N/world) of every rank's peer-mapped
-// [N,K] buffer).  One persistent launch.  Default form (M > 128): the CTA-pair
-// tcgen05 pipeline of kernels/gemm2_kernel.cuh on every SM, with one more warp
-// per CTA that pulls its share of the remote shards into the local buffer with
-// non-multicast bulk copies (peer HBM -> shared memory -> local HBM) and
-// publishes one counter per 256-row block.  Fallback form: the first
-// `num_copiers` CTAs only copy and the others run the single-CTA pipeline of
-// kernels/gemm_kernel.cuh.  Either way the output tiles are walked from the
-// local shard outwards in arrival order, the TMA producers waiting (bounded) for
-// a block's counter before loading it, so the transfer overlaps the math tile by
-// tile and the weight crosses NVLink exactly once.
+// ft_ag_gemm: y[M,N] = x[M,K] * W[N,K]^T where W is a window of a flat, peer-mapped buffer
+// that the ranks shard in contiguous pieces (a layer's parameters as the engine keeps them, or
+// a matrix row-sharded by itself).  One persistent launch of the CTA-pair tcgen05 pipeline of
+// kernels/gemm2_kernel.cuh on every SM, with one more warp per CTA that pulls its share of the
+// window's remote chunks into the local buffer with non-multicast bulk copies (peer HBM ->
+// shared memory -> local HBM) and publishes one counter per 256-row block.  The output tiles
+// are walked from the rows this rank owns outwards, in the order the copies are issued, the
+// TMA producers waiting (bounded) for a block's counter before loading it, so the transfer
+// overlaps the math tile by tile and the weight crosses NVLink exactly once.
 //
 // ft_peer_gather: the copier role alone, for any flat sharded buffer.
 //
@@ -69,10 +66,14 @@ peer_gather_kernel(const __grid_constant__ GatherArgs gather, int* __restrict__ 
   }
 }
 
-// The same gather with plain 16-byte peer loads and local stores issued by every thread
+// The stand-alone gather with plain 16-byte peer loads and local stores issued by every thread
 // (four loads in flight per thread), no shared memory: one CTA per SM keeps ~4.8 MB of
 // requests in flight, more than the link's bandwidth-delay product, and the CTAs fit beside
-// any resident kernel.  Start / end barriers as in gather_role; CTAs never wait for each other.
+// any resident kernel.  It covers a window [w_off_bytes, w_off_bytes + w_bytes) of the flat
+// sharded buffer (the whole buffer, or what is left of a unit beside the matrix that the
+// all-gather GEMM brings in itself); bytes this rank owns are skipped.  Every rank starts at
+// a different place of the window so that the owners' links are loaded evenly.  Start / end
+// barriers as in gather_role; CTAs never wait for each other.
 constexpr int LS_THREADS = 512;
 constexpr int LS_UNROLL = 4;
 
@@ -94,30 +95,30 @@ peer_gather_ldst_kernel(const __grid_constant__ GatherArgs G, int* __restrict__ 
   }
   __syncthreads();
   if (s_ok) {
-    // 16-byte vectors; vector q of the call: peer (R + 1 + q_chunk % (W-1)) so that consecutive
-    // chunks of LS_THREADS vectors go to different links
-    const int64_t vec_per_shard = G.shard_bytes / 16;
-    const int64_t chunks_per_shard = (vec_per_shard + LS_THREADS - 1) / LS_THREADS;
-    const int64_t total_chunks = chunks_per_shard * (W - 1);
-    for (int64_t c0 = (int64_t)blockIdx.x * LS_UNROLL; c0 < total_chunks; c0 += (int64_t)gridDim.x * LS_UNROLL) {
+    const int64_t nvec = G.w_bytes / 16;
+    const int64_t chunks = (nvec + LS_THREADS - 1) / LS_THREADS;
+    const int64_t rot = ((int64_t)R * chunks) / W;
+    const int64_t own_lo = (int64_t)R * G.shard_bytes, own_hi = own_lo + G.shard_bytes;
+    for (int64_t c0 = (int64_t)blockIdx.x * LS_UNROLL; c0 < chunks; c0 += (int64_t)gridDim.x * LS_UNROLL) {
       uint4 v[LS_UNROLL];
-      int64_t off[LS_UNROLL];
+      int64_t iv[LS_UNROLL];
 #pragma unroll
       for (int u = 0; u < LS_UNROLL; ++u) {
-        const int64_t c = c0 + u;
-        off[u] = -1;
-        if (c < total_chunks) {
-          const int p = (R + 1 + (int)(c % (W - 1))) % W;
-          const int64_t iv = (c / (W - 1)) * LS_THREADS + threadIdx.x;
-          if (iv < vec_per_shard) {
-            off[u] = (int64_t)p * vec_per_shard + iv;
-            v[u] = __ldcg(reinterpret_cast<const uint4*>(G.w_peer[p]) + off[u]);
+        iv[u] = -1;
+        if (c0 + u < chunks) {
+          const int64_t i = ((c0 + u + rot) % chunks) * LS_THREADS + threadIdx.x;
+          const int64_t flat = G.w_off_bytes + i * 16;
+          if (i < nvec && (flat < own_lo || flat >= own_hi)) {
+            int p = (int)(flat / G.shard_bytes);
+            if (p >= W) p = W - 1;
+            iv[u] = i;
+            v[u] = __ldcg(reinterpret_cast<const uint4*>(G.w_peer[p]) + i);
           }
         }
       }
 #pragma unroll
       for (int u = 0; u < LS_UNROLL; ++u)
-        if (off[u] >= 0) reinterpret_cast<uint4*>(G.w_local)[off[u]] = v[u];
+        if (iv[u] >= 0) reinterpret_cast<uint4*>(G.w_local)[iv[u]] = v[u];
     }
   }
   __syncthreads();
@@ -185,15 +186,9 @@ int launch_pair_gather(const CUtensorMap& ta, const CUtensorMap& tb, void* y, in
   return e == cudaSuccess ? 0 : (int)e;
 }
 
-int g_ag_pair = -1;   // -1: read FLEXTRAIN_AG_GEMM_PAIR on first use (default on)
-
 }  // namespace
 
 extern "C" {
-
-// Selects the CTA-pair form (1, default) or the single-CTA form with dedicated copy
-// CTAs (0) for later ft_ag_gemm calls.
-void ft_ag_gemm_set_pair(int on) { g_ag_pair = on ? 1 : 0; }
 
 void ft_ag_set_spin_budget(long long cycles) { g_spin_budget = cycles; }
 
@@ -205,94 +200,115 @@ void ft_gather_set_mode(int mode) { g_gather_mode = mode ? 1 : 0; }
 // 1 = lagged by NSTAGE-1 store groups (default), 0 = one store at a time.
 void ft_gather_set_lag(int on) { g_gather_lag = on ? 1 : 0; }
 
-// y[M,N] = x[M,K] * W^T with W gathered from its row shards inside the same launch.
-// w_ptrs[r]: this process's mapping of rank r's [N,K] buffer (16-bit dtype `ab_dtype`).
-// Requires N % (world * 256) == 0 and K % 64 == 0.  Returns 0, <0 for bad arguments,
-// >0 for a CUDA error.
-int ft_ag_gemm(int world, int rank, const void* const* w_ptrs, uint32_t* const* flags, uint32_t seq,
-               int start_slot, int done_slot, const void* x, int64_t lda, void* y, int64_t ldc,
-               int c_dtype, int M, int N, int K, int ab_dtype, int num_copiers, cudaStream_t stream) {
+// y[M,N] = x[M,K] * W^T with W[N,K] gathered from its owners inside the same launch.
+// W is a window of a flat buffer that the ranks shard in contiguous pieces: buf_ptrs[r] is this
+// process's mapping of rank r's whole flat buffer, rank r owns its bytes
+// [r * shard_bytes, (r+1) * shard_bytes), and W starts w_off_bytes into it (16-bit dtype
+// `ab_dtype`, row stride K).  The own part of the window must be in place in buf_ptrs[rank];
+// afterwards the whole window is.  A matrix that is row-sharded by itself is the case
+// w_off_bytes = 0, shard_bytes = (N / world) * K * 2.
+// Requires M > 128 (the CTA-pair pipeline), K % 64 == 0 and shard_bytes, w_off_bytes multiples
+// of 8192.  Returns 0, <0 for bad arguments (-7: shape outside the fused kernel, gather and
+// multiply separately), >0 for a CUDA error.
+int ft_ag_gemm(int world, int rank, const void* const* buf_ptrs, uint32_t* const* flags, uint32_t seq,
+               int start_slot, int done_slot, int64_t w_off_bytes, int64_t shard_bytes, const void* x,
+               int64_t lda, void* y, int64_t ldc, int c_dtype, int M, int N, int K, int ab_dtype,
+               cudaStream_t stream) {
   if (world < 1 || world > peer::kMaxRanks || rank < 0 || rank >= world) return -1;
-  if (N % (world * BN) || K % 64 || M <= 0) return -2;
+  if (K % 64 || M <= 0 || N <= 0) return -2;
+  if (M <= 128) return -7;
   if (ab_dtype != kBF16 && ab_dtype != kF16) return -3;
   if (c_dtype != ab_dtype && c_dtype != kF32) return -3;
+  if (shard_bytes <= 0 || shard_bytes % G2_CHUNK || w_off_bytes < 0 || w_off_bytes % G2_CHUNK) return -2;
   int dev = 0;
   cudaGetDevice(&dev);
   if (ensure_state(dev)) return -4;
-  const int nt = N / BN;
+  const int nt = (N + P_BN - 1) / P_BN;
   if (nt > kReadyWords) return -5;
   const int sms = sm_count(dev);
-  if (world == 1) num_copiers = 0;
-  if (num_copiers < 0 || num_copiers >= sms) return -6;
-  if (world > 1 && num_copiers == 0) return -6;
   GatherArgs G;
-  fill_gather(G, world, rank, w_ptrs, flags, seq, start_slot, done_slot, num_copiers, dev);
+  fill_gather(G, world, rank, buf_ptrs, flags, seq, start_slot, done_slot, 0, dev);
+  for (int r = 0; r < world; ++r)
+    G.w_peer[r] = reinterpret_cast<const uint8_t*>(buf_ptrs[r]) + w_off_bytes;
+  G.w_local = const_cast<uint8_t*>(reinterpret_cast<const uint8_t*>(buf_ptrs[rank]) + w_off_bytes);
   G.row_bytes = (int64_t)K * 2;
-  G.rows_per_rank = N / world;
-  G.shard_bytes = (int64_t)G.rows_per_rank * G.row_bytes;
-  G.block_bytes = (int64_t)BN * G.row_bytes;
-  if (g_ag_pair < 0) {
-    const char* e = getenv("FLEXTRAIN_AG_GEMM_PAIR");
-    g_ag_pair = e ? atoi(e) : 1;
-  }
-  const bool pair = g_ag_pair != 0 && M > 128;
+  G.shard_bytes = shard_bytes;
+  G.block_bytes = (int64_t)P_BN * G.row_bytes;
+  G.w_off_bytes = w_off_bytes;
+  G.w_bytes = (int64_t)N * G.row_bytes;
   CUtensorMap ta, tb;
   int rc = make_tmap(&ta, x, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM, ab_dtype);
   if (rc) return rc;
-  rc = make_tmap(&tb, w_ptrs[rank], (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, pair ? 128 : BN, ab_dtype);
+  rc = make_tmap(&tb, G.w_local, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, 128, ab_dtype);
   if (rc) return rc;
   cudaMemsetAsync(g_ready[dev], 0, nt * sizeof(uint32_t), stream);
-  if (pair) {
-    const int ptiles = ((M + P_BM - 1) / P_BM) * (N / P_BN);
-    int pgrid = 2 * ptiles < sms ? 2 * ptiles : (sms & ~1);
-    G.num_copiers = pgrid;
-    int* perr = error_word(dev);
-    if (ab_dtype == kBF16)
-      rc = c_dtype == kF32
-               ? launch_pair_gather<__nv_bfloat16, kStore32>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream)
-               : launch_pair_gather<__nv_bfloat16, kStore16>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream);
-    else
-      rc = c_dtype == kF32
-               ? launch_pair_gather<__half, kStore32>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream)
-               : launch_pair_gather<__half, kStore16>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream);
-    if (rc) return rc;
-    FT_LAUNCHED(1);
-    FT_CUDA_RETURN_IF_ERROR();
-    return 0;
-  }
-  const int tiles = ((M + BM - 1) / BM) * nt;
-  int grid = tiles + num_copiers < sms ? tiles + num_copiers : sms;
-  int* err = error_word(dev);
-#define FT_AG_LAUNCH(T, MODE)                                                                   \
-  {                                                                                             \
-    auto kern = gemm_kernel<T, false, false, MODE, true>;                                       \
-    static bool configured = false;                                                             \
-    if (!configured) {                                                                          \
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);      \
-      configured = true;                                                                        \
-    }                                                                                           \
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, y, ldc, M, N, K, err, G);           \
-  }
-  if (ab_dtype == kBF16) {
-    if (c_dtype == kF32) FT_AG_LAUNCH(__nv_bfloat16, kStore32) else FT_AG_LAUNCH(__nv_bfloat16, kStore16)
-  } else {
-    if (c_dtype == kF32) FT_AG_LAUNCH(__half, kStore32) else FT_AG_LAUNCH(__half, kStore16)
-  }
-#undef FT_AG_LAUNCH
+  const int ptiles = ((M + P_BM - 1) / P_BM) * nt;
+  const int pgrid = 2 * ptiles < sms ? 2 * ptiles : (sms & ~1);
+  G.num_copiers = world > 1 ? pgrid : 0;
+  int* perr = error_word(dev);
+  if (ab_dtype == kBF16)
+    rc = c_dtype == kF32
+             ? launch_pair_gather<__nv_bfloat16, kStore32>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream)
+             : launch_pair_gather<__nv_bfloat16, kStore16>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream);
+  else
+    rc = c_dtype == kF32
+             ? launch_pair_gather<__half, kStore32>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream)
+             : launch_pair_gather<__half, kStore16>(ta, tb, y, ldc, M, N, K, perr, pgrid, G, stream);
+  if (rc) return rc;
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;
 }
 
-// Pull every remote shard of a flat buffer sharded in `shard_bytes` pieces
-// (rank r owns bytes [r*shard_bytes, (r+1)*shard_bytes) of every rank's buffer)
-// into the local buffer.  shard_bytes must be a multiple of 16.
+// Pull the bytes [range_lo, range_hi) of a flat buffer sharded in `shard_bytes` pieces (rank r
+// owns bytes [r*shard_bytes, (r+1)*shard_bytes) of every rank's buffer) from their owners into
+// the local buffer; what this rank owns is left alone.  All three are multiples of 16.
+int ft_peer_gather_range(int world, int rank, const void* const* buf_ptrs, uint32_t* const* flags,
+                         uint32_t seq, int start_slot, int done_slot, int64_t shard_bytes, int64_t range_lo,
+                         int64_t range_hi, int num_copiers, cudaStream_t stream) {
+  if (world < 1 || world > peer::kMaxRanks || rank < 0 || rank >= world) return -1;
+  if (shard_bytes % 16 || shard_bytes <= 0 || range_lo % 16 || range_hi % 16) return -2;
+  if (range_lo < 0 || range_hi > shard_bytes * world || range_hi < range_lo) return -2;
+  if (world == 1) return 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (ensure_state(dev)) return -4;
+  if (num_copiers < 1) num_copiers = 1;
+  GatherArgs G;
+  fill_gather(G, world, rank, buf_ptrs, flags, seq, start_slot, done_slot, num_copiers, dev);
+  for (int r = 0; r < world; ++r)
+    G.w_peer[r] = reinterpret_cast<const uint8_t*>(buf_ptrs[r]) + range_lo;
+  G.w_local = const_cast<uint8_t*>(reinterpret_cast<const uint8_t*>(buf_ptrs[rank]) + range_lo);
+  G.shard_bytes = shard_bytes;
+  G.w_off_bytes = range_lo;
+  G.w_bytes = range_hi - range_lo;
+  // at least one CTA even for an empty window: the barriers are part of the protocol
+  const int64_t chunks = (G.w_bytes / 16 + LS_THREADS - 1) / LS_THREADS;
+  int64_t want = (chunks + LS_UNROLL - 1) / LS_UNROLL;
+  if (want < 1) want = 1;
+  const int grid = (int)(want < (int64_t)num_copiers ? want : num_copiers);
+  peer_gather_ldst_kernel<<<grid, LS_THREADS, 0, stream>>>(G, error_word(dev));
+  FT_LAUNCHED(1);
+  FT_CUDA_RETURN_IF_ERROR();
+  return 0;
+}
+
+// Pull every remote shard of a flat buffer sharded in `shard_bytes` pieces into the local
+// buffer.  shard_bytes must be a multiple of 16.  Two forms (ft_gather_set_mode): loads / stores
+// by every thread (default) or bulk copies through shared memory by one thread per CTA.
 int ft_peer_gather(int world, int rank, const void* const* buf_ptrs, uint32_t* const* flags,
                    uint32_t seq, int start_slot, int done_slot, int64_t shard_bytes, int num_copiers,
                    cudaStream_t stream) {
   if (world < 1 || world > peer::kMaxRanks || rank < 0 || rank >= world) return -1;
   if (shard_bytes % 16 || shard_bytes <= 0) return -2;
   if (world == 1) return 0;
+  if (g_gather_mode < 0) {
+    const char* e = getenv("FLEXTRAIN_PEER_GATHER");
+    g_gather_mode = (e && !strcmp(e, "bulk")) ? 0 : 1;
+  }
+  if (g_gather_mode == 1)
+    return ft_peer_gather_range(world, rank, buf_ptrs, flags, seq, start_slot, done_slot, shard_bytes, 0,
+                                shard_bytes * world, num_copiers, stream);
   int dev = 0;
   cudaGetDevice(&dev);
   if (ensure_state(dev)) return -4;
@@ -303,18 +319,7 @@ int ft_peer_gather(int world, int rank, const void* const* buf_ptrs, uint32_t* c
   G.shard_bytes = shard_bytes;
   G.block_bytes = (shard_bytes * world + kReadyWords - 1) / kReadyWords;
   if (G.block_bytes < PG_CHUNK) G.block_bytes = PG_CHUNK;
-  if (g_gather_mode < 0) {
-    const char* e = getenv("FLEXTRAIN_PEER_GATHER");
-    g_gather_mode = (e && !strcmp(e, "bulk")) ? 0 : 1;
-  }
-  if (g_gather_mode == 1) {
-    const int64_t chunks = ((shard_bytes / 16 + LS_THREADS - 1) / LS_THREADS) * (world - 1);
-    const int64_t want = (chunks + LS_UNROLL - 1) / LS_UNROLL;
-    const int grid = (int)(want < (int64_t)num_copiers ? want : num_copiers);
-    peer_gather_ldst_kernel<<<grid, LS_THREADS, 0, stream>>>(G, error_word(dev));
-  } else {
-    peer_gather_kernel<<<num_copiers, 32, 0, stream>>>(G, error_word(dev));
-  }
+  peer_gather_kernel<<<num_copiers, 32, 0, stream>>>(G, error_word(dev));
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;

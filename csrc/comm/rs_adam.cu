@@ -119,8 +119,59 @@ __device__ __forceinline__ void store8(void* base, int dtype, int64_t idx, const
   }
 }
 
+// Everything that happens to one reduced 8-element chunk: unscale, finite check, the optional
+// in-place copy of the reduced gradient, Adam on the HBM share or the hand-off to the host.
+__device__ __forceinline__ void finish_chunk(const RsAdamParams& P, int R, int64_t base, int64_t i, float (&g)[8],
+                                             bool& bad) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    g[j] *= P.scale;
+    bad |= !(fabsf(g[j]) < INFINITY);
+  }
+  if (P.reduced_out) store8(P.reduced_out, P.grad_dtype, i, g);
+  if (i < P.og) {
+    if (P.do_adam) {
+      int s = 0;
+      while (s + 1 < P.nseg && i >= P.seg[s].hi) ++s;
+      const Segment& a = P.seg[s];
+      float4* pm = reinterpret_cast<float4*>(P.master + i);
+      float4* mm = reinterpret_cast<float4*>(P.m + i);
+      float4* vm = reinterpret_cast<float4*>(P.v + i);
+      float pv[8], mv[8], vv[8];
+      *reinterpret_cast<float4*>(pv) = pm[0]; *reinterpret_cast<float4*>(pv + 4) = pm[1];
+      *reinterpret_cast<float4*>(mv) = mm[0]; *reinterpret_cast<float4*>(mv + 4) = mm[1];
+      *reinterpret_cast<float4*>(vv) = vm[0]; *reinterpret_cast<float4*>(vv + 4) = vm[1];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float gr = g[j] + a.l2_decay * pv[j];
+        mv[j] = mv[j] + (gr - mv[j]) * a.one_m_beta1;
+        vv[j] = a.beta2 * vv[j] + (a.one_m_beta2 * gr) * gr;
+        float denom = sqrtf(vv[j]) / a.sqrt_bc2 + a.eps;
+        pv[j] = pv[j] * a.decay_factor - a.step_size * (mv[j] / denom);
+      }
+      pm[0] = *reinterpret_cast<float4*>(pv); pm[1] = *reinterpret_cast<float4*>(pv + 4);
+      mm[0] = *reinterpret_cast<float4*>(mv); mm[1] = *reinterpret_cast<float4*>(mv + 4);
+      vm[0] = *reinterpret_cast<float4*>(vv); vm[1] = *reinterpret_cast<float4*>(vv + 4);
+      if (i < P.a_hi) {
+        if (P.param_a) store8(P.param_a, P.param_dtype, i, pv);
+      } else if (P.param_b) {
+        store8(P.param_b, P.param_dtype, i - P.a_hi, pv);
+      }
+      for (int k = 0; k < P.npush; ++k) store8(P.push[(R + k) % P.npush], P.param_dtype, base + i, pv);
+    }
+  } else if (P.host_grad) {
+    store8(P.host_grad, P.host_grad_dtype, i - P.og, g);
+  }
+}
+
+// CTAs of kThreads threads, at most 80 registers: two of them fit on an SM beside a resident
+// GEMM CTA.  A thread works on two chunks at a time and issues the loads of two ranks for both
+// before it adds anything, so four requests per thread are in flight whatever the number of
+// ranks: ~4.8 MB per GPU at one 512-thread group per SM, above the link's bandwidth-delay
+// product (the reduction is bound by the NVLink round trip, not by issue rate).
+constexpr int kThreads = 256;
+
 template <typename G>
-// 80 registers x 512 threads: a CTA fits on an SM beside a resident GEMM CTA
 __global__ void __maxnreg__(80) rs_adam_kernel(const __grid_constant__ RsAdamParams P) {
   __shared__ int s_ok;
   const int W = P.peers.world, R = P.peers.rank;
@@ -151,63 +202,36 @@ __global__ void __maxnreg__(80) rs_adam_kernel(const __grid_constant__ RsAdamPar
 
   // ---- reduce + update
   const int64_t base = (int64_t)R * P.shard;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x * 8;
   bool bad = false;
-  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; run && i < P.shard;
-       i += (int64_t)gridDim.x * blockDim.x * 8) {
-    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    // four ranks per batch (16 or 32 raw registers): four requests per thread in flight
-    constexpr int PB = 4;
+  for (int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; run && i0 < P.shard; i0 += 2 * stride) {
+    const int64_t i1 = i0 + stride;
+    const bool two = i1 < P.shard;
+    float g0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float g1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    // two ranks per batch: four raw vectors (two chunks x two ranks) are loaded before any is added
+    constexpr int PB = 2;
 #pragma unroll
     for (int k0 = 0; k0 < kMaxRanks; k0 += PB) {
-      Raw8<G> raw[PB];
+      Raw8<G> r0[PB], r1[PB];
 #pragma unroll
       for (int k = 0; k < PB; ++k) {         // local copy first, peers spread over the links
-        if (k0 + k < W) raw[k] = load_raw8<G>(P.grads[(R + k0 + k) % W], base + i);
+        if (k0 + k < W) {
+          const void* src = P.grads[(R + k0 + k) % W];
+          r0[k] = load_raw8<G>(src, base + i0);
+          if (two) r1[k] = load_raw8<G>(src, base + i1);
+        }
       }
 #pragma unroll
       for (int k = 0; k < PB; ++k) {         // fixed summation order: the result does not depend on timing
-        if (k0 + k < W) add_raw8<G>(raw[k], g);
+        if (k0 + k < W) {
+          add_raw8<G>(r0[k], g0);
+          if (two) add_raw8<G>(r1[k], g1);
+        }
       }
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      g[j] *= P.scale;
-      bad |= !(fabsf(g[j]) < INFINITY);
-    }
-    if (P.reduced_out) store8(P.reduced_out, P.grad_dtype, i, g);
-    if (i < P.og) {
-      if (P.do_adam) {
-        int s = 0;
-        while (s + 1 < P.nseg && i >= P.seg[s].hi) ++s;
-        const Segment& a = P.seg[s];
-        float4* pm = reinterpret_cast<float4*>(P.master + i);
-        float4* mm = reinterpret_cast<float4*>(P.m + i);
-        float4* vm = reinterpret_cast<float4*>(P.v + i);
-        float pv[8], mv[8], vv[8];
-        *reinterpret_cast<float4*>(pv) = pm[0]; *reinterpret_cast<float4*>(pv + 4) = pm[1];
-        *reinterpret_cast<float4*>(mv) = mm[0]; *reinterpret_cast<float4*>(mv + 4) = mm[1];
-        *reinterpret_cast<float4*>(vv) = vm[0]; *reinterpret_cast<float4*>(vv + 4) = vm[1];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float gr = g[j] + a.l2_decay * pv[j];
-          mv[j] = mv[j] + (gr - mv[j]) * a.one_m_beta1;
-          vv[j] = a.beta2 * vv[j] + (a.one_m_beta2 * gr) * gr;
-          float denom = sqrtf(vv[j]) / a.sqrt_bc2 + a.eps;
-          pv[j] = pv[j] * a.decay_factor - a.step_size * (mv[j] / denom);
-        }
-        pm[0] = *reinterpret_cast<float4*>(pv); pm[1] = *reinterpret_cast<float4*>(pv + 4);
-        mm[0] = *reinterpret_cast<float4*>(mv); mm[1] = *reinterpret_cast<float4*>(mv + 4);
-        vm[0] = *reinterpret_cast<float4*>(vv); vm[1] = *reinterpret_cast<float4*>(vv + 4);
-        if (i < P.a_hi) {
-          if (P.param_a) store8(P.param_a, P.param_dtype, i, pv);
-        } else if (P.param_b) {
-          store8(P.param_b, P.param_dtype, i - P.a_hi, pv);
-        }
-        for (int k = 0; k < P.npush; ++k) store8(P.push[(R + k) % P.npush], P.param_dtype, base + i, pv);
-      }
-    } else if (P.host_grad) {
-      store8(P.host_grad, P.host_grad_dtype, i - P.og, g);
-    }
+    finish_chunk(P, R, base, i0, g0, bad);
+    if (two) finish_chunk(P, R, base, i1, g1, bad);
   }
   if (bad && P.finite_flag) atomicOr(P.finite_flag, 1);
 
@@ -321,12 +345,14 @@ static int rs_adam_impl(int world, int rank, const void* const* grads, uint32_t*
     o.l2_decay = in.adamw ? 0.f : in.weight_decay;
     o.decay_factor = in.adamw ? (float)(1.0 - (double)in.lr * (double)in.weight_decay) : 1.f;
   }
-  int64_t work = (shard / 8 + 511) / 512;
-  int grid = (int)(work < (int64_t)max_blocks ? work : max_blocks);
+  // `max_blocks` counts 512-thread groups (one per SM by default): two CTAs of kThreads each
+  const int64_t work = (shard / 8 + 2 * kThreads - 1) / (2 * kThreads);
+  const int64_t cap = (int64_t)max_blocks * (512 / kThreads);
+  int grid = (int)(work < cap ? work : cap);
   if (grid < 1) grid = 1;
-  if (grad_dtype == kF32) rs_adam_kernel<float><<<grid, 512, 0, stream>>>(P);
-  else if (grad_dtype == kBF16) rs_adam_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(P);
-  else rs_adam_kernel<__half><<<grid, 512, 0, stream>>>(P);
+  if (grad_dtype == kF32) rs_adam_kernel<float><<<grid, kThreads, 0, stream>>>(P);
+  else if (grad_dtype == kBF16) rs_adam_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(P);
+  else rs_adam_kernel<__half><<<grid, kThreads, 0, stream>>>(P);
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;

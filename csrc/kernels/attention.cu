@@ -6,7 +6,6 @@
 
 #include "attention_bwd.cuh"
 #include "attention_fwd2.cuh"
-#include "attention_fwd4.cuh"
 #include "gemm_host.h"
 
 namespace {
@@ -16,11 +15,10 @@ using namespace ft::attn;
 
 // dynamic shared memory a CTA may ask for on sm_100 (227 KB)
 constexpr int kMaxDynamicSmem = 232448;
-static_assert(Fwd2Smem<128>::BYTES <= kMaxDynamicSmem && Fwd4Smem<128>::BYTES <= kMaxDynamicSmem &&
-                  BwdSmem<128>::BYTES <= kMaxDynamicSmem,
+static_assert(Fwd2Smem<128>::BYTES <= kMaxDynamicSmem && BwdSmem<128>::BYTES <= kMaxDynamicSmem,
               "an attention kernel outgrew the shared memory of an SM");
 
-// Forward, one CTA per pair of query blocks, one thread per score row.
+// Forward: one CTA per pair of query blocks.
 template <typename T, int D>
 int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
                 cudaStream_t s) {
@@ -33,38 +31,6 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   const int num_pairs = ((P.S + BQ - 1) / BQ + 1) / 2;
   kern<<<P.B * P.Hq * num_pairs, F2_THREADS, Fwd2Smem<D>::BYTES, s>>>(tq, tk, tv, P);
   return 0;
-}
-
-// Forward with two threads per score row.
-template <typename T, int D>
-int launch_fwd4(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
-                cudaStream_t s) {
-  auto kern = attn_fwd4_kernel<T, D>;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd4Smem<D>::BYTES);
-    configured = true;
-  }
-  const int num_pairs = ((P.S + BQ - 1) / BQ + 1) / 2;
-  kern<<<P.B * P.Hq * num_pairs, F4_THREADS, Fwd4Smem<D>::BYTES, s>>>(tq, tk, tv, P);
-  return 0;
-}
-
-int g_fwd_version = -1;   // -1: read FLEXTRAIN_ATTN_FWD on first use (2 or 4)
-
-int fwd_version() {
-  if (g_fwd_version < 0) {
-    const char* e = getenv("FLEXTRAIN_ATTN_FWD");
-    g_fwd_version = e ? atoi(e) : 2;
-    if (g_fwd_version != 2 && g_fwd_version != 4) g_fwd_version = 2;
-  }
-  return g_fwd_version;
-}
-
-template <typename T, int D>
-int launch_fwd_any(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
-                   cudaStream_t s) {
-  return fwd_version() == 4 ? launch_fwd4<T, D>(tq, tk, tv, P, s) : launch_fwd2<T, D>(tq, tk, tv, P, s);
 }
 
 template <typename T, int D>
@@ -100,9 +66,6 @@ void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_strid
 
 extern "C" {
 
-// Selects the forward kernel for later ft_attn_fwd calls: 2 (one thread per score row) or 4 (two).
-void ft_attn_set_fwd_version(int v) { g_fwd_version = (v == 4) ? 4 : 2; }
-
 // o[B,S,Hq,D], lse[B,Hq,S] <- causal attention of q[B,S,Hq,D], k/v[B,S,Hkv,D].
 // *_stride: elements between consecutive tokens of that tensor.  D in {64, 128}.
 int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
@@ -116,10 +79,9 @@ int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   CUtensorMap tq, tk, tv;
   int rc = gemm::make_tmap(&tq, q, (uint64_t)Hq * D, (uint64_t)B * S, (uint64_t)q_stride, 64, BQ, dtype);
   if (rc) return rc;
-  const uint32_t kv_box = BKV;
-  rc = gemm::make_tmap(&tk, k, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)k_stride, 64, kv_box, dtype);
+  rc = gemm::make_tmap(&tk, k, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)k_stride, 64, BKV, dtype);
   if (rc) return rc;
-  rc = gemm::make_tmap(&tv, v, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)v_stride, 64, kv_box, dtype);
+  rc = gemm::make_tmap(&tv, v, (uint64_t)Hkv * D, (uint64_t)B * S, (uint64_t)v_stride, 64, BKV, dtype);
   if (rc) return rc;
   FwdParams P;
   P.o = o; P.lse = lse; P.B = B; P.S = S; P.Hq = Hq; P.Hkv = Hkv;
@@ -128,11 +90,11 @@ int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.q_col0 = P.k_col0 = P.v_col0 = 0;
   P.err = gemm::error_word(dev);
   if (dtype == kBF16) {
-    if (D == 128) launch_fwd_any<__nv_bfloat16, 128>(tq, tk, tv, P, stream);
-    else launch_fwd_any<__nv_bfloat16, 64>(tq, tk, tv, P, stream);
+    if (D == 128) launch_fwd2<__nv_bfloat16, 128>(tq, tk, tv, P, stream);
+    else launch_fwd2<__nv_bfloat16, 64>(tq, tk, tv, P, stream);
   } else {
-    if (D == 128) launch_fwd_any<__half, 128>(tq, tk, tv, P, stream);
-    else launch_fwd_any<__half, 64>(tq, tk, tv, P, stream);
+    if (D == 128) launch_fwd2<__half, 128>(tq, tk, tv, P, stream);
+    else launch_fwd2<__half, 64>(tq, tk, tv, P, stream);
   }
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();

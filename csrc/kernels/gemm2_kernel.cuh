@@ -105,7 +105,136 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPeerBitMask) : "memory");
 }
 
-// With GATHER, B is row-sharded over the ranks of `gather.peers` (see GatherArgs): warp 6
+// Ownership arithmetic of the gathered window (see GatherArgs), in chunks of G2_CHUNK bytes.
+// Host code guarantees that shard_bytes and w_off_bytes are multiples of the chunk, so a
+// chunk has exactly one owner and this rank's part of the window is one run of whole chunks.
+struct WindowOwnership {
+  int64_t n_total;         // chunks of the window (the last one may be short)
+  int64_t oc_lo, oc_hi;    // this rank's chunks [oc_lo, oc_hi); empty when equal
+  int64_t start;           // first remote chunk in copy order: right behind the own run
+  __device__ __forceinline__ int64_t n_remote() const { return n_total - (oc_hi - oc_lo); }
+};
+
+__device__ __forceinline__ WindowOwnership window_ownership(const GatherArgs& G) {
+  WindowOwnership w;
+  const int64_t R = G.peers.rank, W = G.peers.world;
+  w.n_total = (G.w_bytes + G2_CHUNK - 1) / G2_CHUNK;
+  int64_t lo = R * G.shard_bytes - G.w_off_bytes, hi = (R + 1) * G.shard_bytes - G.w_off_bytes;
+  lo = lo < 0 ? 0 : (lo > G.w_bytes ? G.w_bytes : lo);
+  hi = hi < 0 ? 0 : (hi > G.w_bytes ? G.w_bytes : hi);
+  w.oc_lo = lo / G2_CHUNK;
+  w.oc_hi = (hi + G2_CHUNK - 1) / G2_CHUNK;
+  if (hi <= lo) { w.oc_lo = w.oc_hi = 0; }
+  // nothing of the window here: every rank starts at a different place, so that the owners'
+  // links are loaded evenly
+  w.start = w.oc_hi > w.oc_lo ? w.oc_hi % w.n_total : (R * w.n_total) / W;
+  return w;
+}
+
+// chunks of 256-row block `nb` that come from a peer
+__device__ __forceinline__ uint32_t remote_chunks_in_block(const GatherArgs& G, const WindowOwnership& w,
+                                                           int nb) {
+  const int64_t per_block = G.block_bytes / G2_CHUNK;
+  int64_t c0 = (int64_t)nb * per_block, c1 = c0 + per_block;
+  if (c1 > w.n_total) c1 = w.n_total;
+  if (c1 <= c0) return 0;
+  const int64_t a = c0 > w.oc_lo ? c0 : w.oc_lo, b = c1 < w.oc_hi ? c1 : w.oc_hi;
+  return (uint32_t)((c1 - c0) - (b > a ? b - a : 0));
+}
+
+// Copy role of the CTA-pair all-gather GEMM: one thread per CTA pulls its share of the
+// window's remote chunks (peer HBM -> shared memory -> local HBM, bulk copies, never multicast),
+// completion announced per 256-row block NSTAGE-1 store groups late so that the copy stream
+// never waits for a store to land.  Start / end barriers as in gather_role.
+__device__ __forceinline__ void gather_role_w(const GatherArgs& G, uint8_t* smem, uint64_t* full_bars, int* err) {
+  constexpr int NSTAGE = G2_STAGES, CHUNK = G2_CHUNK, LAG = NSTAGE - 1;
+  const int W = G.peers.world, R = G.peers.rank;
+  if (W <= 1) return;
+  uint32_t* mine = G.peers.flags[R];
+  if (blockIdx.x == 0) {                      // tell every peer that the local shard is in place
+    __threadfence_system();
+    for (int p = 0; p < W; ++p)
+      if (p != R) peer::st_release_sys(G.peers.flags[p] + G.start_slot * peer::kMaxRanks + R, G.seq);
+  }
+  bool ok = true;
+  for (int p = 0; p < W && ok; ++p)
+    if (p != R && !peer::wait_seq(mine + G.start_slot * peer::kMaxRanks + p, G.seq, G.spin_budget)) ok = false;
+  if (!ok) {
+    atomicCAS(err, 0, 201);
+  } else {
+    const WindowOwnership own = window_ownership(G);
+    const int64_t total = own.n_remote();
+    auto locate = [&](int64_t q, const uint8_t*& src, uint8_t*& dst, int& nblk, uint32_t& bytes) {
+      const int64_t c = (own.start + blockIdx.x + q * G.num_copiers) % own.n_total;
+      const int64_t off = c * CHUNK;
+      const int64_t left = G.w_bytes - off;
+      bytes = (uint32_t)(left < CHUNK ? left : CHUNK);
+      const int p = (int)((G.w_off_bytes + off) / G.shard_bytes);
+      src = reinterpret_cast<const uint8_t*>(G.w_peer[p]) + off;
+      dst = reinterpret_cast<uint8_t*>(G.w_local) + off;
+      nblk = (int)(off / G.block_bytes);
+    };
+    const int64_t n = total > blockIdx.x ? (total - blockIdx.x + G.num_copiers - 1) / G.num_copiers : 0;
+    uint32_t phase[NSTAGE];
+    for (int s = 0; s < NSTAGE; ++s) phase[s] = 0;
+    for (int64_t q = 0; q < n && q < NSTAGE - 1; ++q) {
+      const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
+      locate(q, src, dst, nb, bytes);
+      const int s = (int)(q % NSTAGE);
+      mbar_expect_tx(&full_bars[s], bytes);
+      bulk_load(smem + s * CHUNK, src, bytes, &full_bars[s]);
+    }
+    int pending[NSTAGE];
+    int64_t q = 0;
+    for (; q < n; ++q) {
+      const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
+      locate(q, src, dst, nb, bytes);
+      const int s = (int)(q % NSTAGE);
+      if (!mbar_wait(&full_bars[s], phase[s])) { atomicCAS(err, 0, 202); break; }
+      phase[s] ^= 1;
+      bulk_store(dst, smem + s * CHUNK, bytes);
+      bulk_commit();
+      pending[s] = nb;
+      asm volatile("cp.async.bulk.wait_group %0;" ::"n"(LAG) : "memory");
+      if (q >= LAG) {                         // chunk q - LAG is in local memory
+        fence_proxy_async_all();
+        __threadfence();
+        red_release_add(G.ready + pending[(int)((q - LAG) % NSTAGE)], 1u);
+      }
+      const int64_t nq = q + NSTAGE - 1;
+      if (nq < n) {
+        const uint8_t* src2; uint8_t* dst2; int nb2; uint32_t bytes2;
+        locate(nq, src2, dst2, nb2, bytes2);
+        const int s2 = (int)(nq % NSTAGE);    // stage of chunk q - 1
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        mbar_expect_tx(&full_bars[s2], bytes2);
+        bulk_load(smem + s2 * CHUNK, src2, bytes2, &full_bars[s2]);
+      }
+    }
+    bulk_wait_all();
+    fence_proxy_async_all();
+    __threadfence();
+    // the chunks stored but not yet announced: the last LAG of those that were stored
+    for (int64_t r = (q > LAG ? q - LAG : 0); r < q; ++r) {
+      const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
+      locate(r, src, dst, nb, bytes);
+      red_release_add(G.ready + nb, 1u);
+    }
+  }
+  // end barrier: the last copier tells the peers that this rank reads their shards no more
+  __threadfence_system();
+  const unsigned int done = atomicAdd(G.block_counter, 1u);
+  if (done == (unsigned int)G.num_copiers - 1) {
+    *G.block_counter = 0;
+    for (int p = 0; p < W; ++p)
+      if (p != R) peer::st_release_sys(G.peers.flags[p] + G.done_slot * peer::kMaxRanks + R, G.seq);
+    for (int p = 0; p < W && ok; ++p)
+      if (p != R && !peer::wait_seq(mine + G.done_slot * peer::kMaxRanks + p, G.seq, G.spin_budget))
+        atomicCAS(err, 0, 203);
+  }
+}
+
+// With GATHER, B is a window of a flat buffer sharded over the ranks of `gather.peers` (see GatherArgs): warp 6
 // of every CTA copies its share of the remote rows into the local buffer (peer HBM ->
 // shared memory -> local HBM, bulk copies without multicast) and counts finished
 // chunks per 256-row block; tiles are walked from the local shard outwards and each
@@ -124,8 +253,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int pair = (int)(blockIdx.x >> 1), num_pairs = (int)(gridDim.x >> 1);
   const int mt = (M + P_BM - 1) / P_BM, nt = (N + P_BN - 1) / P_BN, kt = (K + BK - 1) / BK;
   const int num_tiles = mt * nt;
-  const int nt_local = GATHER ? gather.rows_per_rank / P_BN : 0;
-  const int n_rot = GATHER ? gather.peers.rank * nt_local : 0;
+  // with GATHER the columns are walked from this rank's own rows outwards, in copy order
+  WindowOwnership own = {};
+  int n_rot = 0;
+  if constexpr (GATHER) {
+    own = window_ownership(gather);
+    n_rot = (int)((own.start * G2_CHUNK) / gather.block_bytes) % nt;
+    if (own.oc_hi > own.oc_lo) n_rot = (int)((own.oc_lo * G2_CHUNK) / gather.block_bytes);
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
@@ -163,8 +298,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tile_coords(t, mt, nt, mb, nb);
         if constexpr (GATHER) {
           nb = (nb + n_rot) % nt;
-          if (nb < n_rot || nb >= n_rot + nt_local) {      // rows that come from a peer
-            const uint32_t need = (uint32_t)(gather.block_bytes / G2_CHUNK);
+          const uint32_t need = remote_chunks_in_block(gather, own, nb);
+          if (need > 0) {                                  // rows that come from a peer
             const long long t0 = clock64();
             bool ok = true;
             while (ld_acquire_gpu(gather.ready + nb) < need) {
@@ -252,7 +387,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ------------------------------------------------------------ copy warp (both CTAs)
     if (lane == 0) {
       uint8_t* ring = smem + P_STAGES * P_STAGE_BYTES + 256;
-      gather_role<G2_CHUNK, G2_STAGES, G2_CHUNK>(gather, ring, bars->gather_full, err);
+      gather_role_w(gather, ring, bars->gather_full, err);
     }
   } else {
     // ---------------------------------------------------------- epilogue (both CTAs)

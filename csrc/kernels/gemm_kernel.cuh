@@ -45,6 +45,12 @@ struct GatherArgs {
   unsigned int* block_counter;
   int lagged;              // 1: announce a chunk NSTAGE-1 store groups late (keeps the copy stream
                            //    full); 0: wait for each store before the next (the first form)
+  // CTA-pair GEMM (gather_role_w): B is a window [w_off_bytes, w_off_bytes + w_bytes) of a flat
+  // buffer that is sharded in contiguous pieces of `shard_bytes` (rank r owns flat bytes
+  // [r * shard_bytes, (r+1) * shard_bytes)); w_peer / w_local point at the window's first byte.
+  // A row-sharded matrix is the case w_off_bytes = 0, shard_bytes = rows_per_rank * row_bytes.
+  int64_t w_off_bytes;
+  int64_t w_bytes;
 };
 
 constexpr int COPY_CHUNK = 32768;

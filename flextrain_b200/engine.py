@@ -500,9 +500,10 @@ class FlexTrainEngine:
                 "last_step_seconds": self.timer.last, "phase_ms": self.phase_times_ms()}
 
     # bounded waits of the peer-memory kernels that ran out: start / end barriers of the
-    # reduce kernels (101, 102) and of the gather (201 .. 204, reported in the GEMM error word)
+    # reduce kernels (101, 102) and of the gather (201 .. 204, and 15: a GEMM producer waiting for
+    # rows that never arrived; reported in the GEMM error word)
     _COMM_TIMEOUTS = (101, 102)
-    _GATHER_TIMEOUTS = (201, 202, 203, 204)
+    _GATHER_TIMEOUTS = (15, 201, 202, 203, 204)
 
     def _set_fused_wait(self, first_step: bool):
         """Wait limit of the fused kernels: longer during the first step, whose one-off

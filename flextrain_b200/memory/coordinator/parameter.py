@@ -39,6 +39,37 @@ from .. import (tier_copy, ContiguousParaGroup, FlexTrainDataID, FlexTrainDataTy
 from ..nvme_swapper import get_nvme_swapper
 
 
+class _PendingFirstGemm:
+    """Marker on a parameter whose rows are not all in the gathered buffer yet: the first
+    ``linear`` that uses the parameter runs the all-gather GEMM, which completes the buffer."""
+
+    def __init__(self, coordinator, unit: int, idx: int):
+        self.coordinator, self.unit, self.idx = coordinator, unit, idx
+
+    def covers(self, rows: int, cols: int) -> bool:
+        from ...parallel import fused
+        return fused.ag_gemm_covers(rows, cols, 0, fused.AG_GEMM_CHUNK)
+
+    def run(self, x2: torch.Tensor, out: torch.Tensor):
+        c = self.coordinator
+        c._run_first_gemm(self.unit, self.idx, x2, out)
+        c._first_gemm_pending.pop(self.idx, None)
+        c._first_gemm[self.unit][0]._ft_gather = None
+
+    def complete_without_product(self):
+        """Bring the matrix in with a plain range gather (a product the fused kernel does not
+        cover, e.g. fewer than 129 rows)."""
+        c = self.coordinator
+        from ...parallel import fused
+        _p, w_lo, rows, cols = c._first_gemm[self.unit]
+        page = c._flag_page
+        fused.peer_gather_range(c.world, c.rank, c._symm[self.idx].ptr_array(), page.ptr_array(),
+                                page.next_seq("gather"), c.shard_numel * c.itemsize, w_lo,
+                                w_lo + rows * cols * c.itemsize, num_copiers=c._cfg.engine.fused_blocks)
+        c._first_gemm_pending.pop(self.idx, None)
+        c._first_gemm[self.unit][0]._ft_gather = None
+
+
 class FlexTrainParaCoordinator:
     def __init__(self):
         self._initialized = False
@@ -102,6 +133,13 @@ class FlexTrainParaCoordinator:
         self._nvme_loads: Dict[int, tuple] = {}    # unit -> (landing index, read handle)
         self._landing_busy = [DONE for _ in self._nvme_landing]
         self._nvme_next = 0
+        # The matrix a unit's forward multiplies first can be left out of the unit gather and
+        # brought in by the all-gather GEMM itself (``ops.cuda_ops.linear`` sees the marker that
+        # ``acquire`` puts on the parameter): unit -> (parameter, byte offset, rows, columns)
+        self._first_gemm: Dict[int, tuple] = {}
+        self._first_gemm_pending: Dict[int, int] = {}      # buffer index -> unit still without it
+        self._first_gemm_on = self._peer_gather and cfg.engine.fused_first_gemm is not False
+        self.first_gemm_calls = 0
         self._initialized = True
         rank0_logger.info(
             f"parameter geometry: units={self.num_units} unit_numel={self.unit_numel} "
@@ -121,6 +159,30 @@ class FlexTrainParaCoordinator:
             from ...parallel import fused
             fused.set_gather_lag(lag is not False)
         return bool(ok)
+
+    def _note_first_gemm(self, unit: int, layers, group: ContiguousParaGroup):
+        """A layer class may name, in ``ft_first_gemm_weight``, the 2-D parameter its forward
+        multiplies first.  When the placement suits the fused kernel the unit gather leaves that
+        matrix out and the first product of the unit brings it in."""
+        if not self._first_gemm_on or not layers:
+            return
+        name = getattr(layers[0], "ft_first_gemm_weight", None)
+        w = getattr(layers[0], name, None) if name else None
+        if w is None:
+            return
+        from ...parallel import fused
+        for p, off, shape in zip(group.paras, group.offsets, group.shapes):
+            if p is w and len(shape) == 2 and self.itemsize == 2:
+                shard_bytes = self.shard_numel * self.itemsize
+                if fused.ag_gemm_covers(1 << 20, shape[1], off * self.itemsize, shard_bytes):
+                    self._first_gemm[unit] = (p, off * self.itemsize, shape[0], shape[1])
+                return
+
+    def fused_first_gemm_state(self) -> str:
+        if not getattr(self, "_first_gemm", None) or not self._peer_gather:
+            return "separate"
+        return (f"ft_ag_gemm (all-gather fused into the first GEMM of {len(self._first_gemm)} of "
+                f"{self.num_units} units, {self.first_gemm_calls} calls so far)")
 
     def shard_range(self):
         return self.rank * self.shard_numel, (self.rank + 1) * self.shard_numel
@@ -148,6 +210,7 @@ class FlexTrainParaCoordinator:
             raise ValueError("every unit must hold at most as many parameters as the first one")
         self._unit_groups[unit_index] = group
         self._unit_layers[unit_index] = list(layers)
+        self._note_first_gemm(unit_index, layers, group)
         buf = self._buffers[0]
         for p, off, n in zip(group.paras, group.offsets, group.numels):
             buf[off:off + n].copy_(p.data.reshape(-1))
@@ -279,22 +342,50 @@ class FlexTrainParaCoordinator:
                 tier_copy(shard[g + c:], self._nvme_landing[land_idx])
                 self._landing_busy[land_idx] = st.h2d.record()
             if self.world > 1:
-                self._all_gather(buf, shard, idx)
+                self._all_gather(buf, shard, idx, unit)
             ready = st.h2d.record()
         self._inflight[unit] = (idx, ready)
 
-    def _all_gather(self, buf: torch.Tensor, shard: torch.Tensor, idx: int = -1):
+    def _all_gather(self, buf: torch.Tensor, shard: torch.Tensor, idx: int = -1, unit: int = -1):
         if self.world > 1:
             from .. import TRAFFIC
             TRAFFIC.add("gather", (self.world - 1) * self.shard_numel * self.itemsize)
+        self._first_gemm_pending.pop(idx, None)
         if self._peer_gather and idx >= 0:
             from ...parallel import fused
             page = self._flag_page
-            fused.peer_gather(self.world, self.rank, self._symm[idx].ptr_array(), page.ptr_array(),
-                              page.next_seq("gather"), self.shard_numel * self.itemsize,
-                              num_copiers=self._cfg.engine.fused_blocks)
+            ptrs, flags = self._symm[idx].ptr_array(), page.ptr_array()
+            shard_bytes = self.shard_numel * self.itemsize
+            blocks = self._cfg.engine.fused_blocks
+            first = self._first_gemm.get(unit) if self._first_gemm_on else None
+            if first is None:
+                fused.peer_gather(self.world, self.rank, ptrs, flags, page.next_seq("gather"), shard_bytes,
+                                  num_copiers=blocks)
+                return
+            # everything but the first matrix now; that one arrives inside the product that uses it
+            _p, w_lo, rows, cols = first
+            w_hi = w_lo + rows * cols * self.itemsize
+            total = shard_bytes * self.world
+            for lo, hi in ((0, w_lo), (w_hi, total)):
+                if hi > lo:
+                    fused.peer_gather_range(self.world, self.rank, ptrs, flags, page.next_seq("gather"),
+                                            shard_bytes, lo, hi, num_copiers=blocks)
+            self._first_gemm_pending[idx] = unit
         else:
             dist.all_gather(buf, shard)
+
+    def _run_first_gemm(self, unit: int, idx: int, x2: torch.Tensor, out: torch.Tensor):
+        """``out = x2 @ W.T`` for the unit's first matrix, gathering it into ring buffer ``idx``
+        on the way (compute stream; every rank calls it at the same point of its step)."""
+        from ...parallel import fused
+        _p, w_lo, rows, cols = self._first_gemm[unit]
+        page = self._flag_page
+        fused.ag_gemm(self.world, self.rank, self._symm[idx].ptr_array(), page.ptr_array(),
+                      page.next_seq("ag"), x2, rows, out=out, w_off_bytes=w_lo,
+                      shard_bytes=self.shard_numel * self.itemsize)
+        self.first_gemm_calls += 1
+        from .. import TRAFFIC
+        TRAFFIC.add("gather_in_gemm", rows * cols * self.itemsize * (self.world - 1) // self.world)
 
     def acquire(self, unit: int):
         """Block the compute stream until ``unit`` is gathered; link its parameters."""
@@ -312,6 +403,8 @@ class FlexTrainParaCoordinator:
         self._unit_groups[unit].link_para_to(self._gpu_base[unit] if idx < 0 else self._buffers[idx])
         self._held[unit] = idx
         self._held_version[unit] = self._version.get(unit, 0)
+        if idx >= 0 and self._first_gemm_pending.get(idx) == unit:
+            self._first_gemm[unit][0]._ft_gather = _PendingFirstGemm(self, unit, idx)
 
     def release(self, unit: int, keep: bool = False):
         """Unlink ``unit`` and give its buffer back behind a compute-stream
@@ -325,6 +418,12 @@ class FlexTrainParaCoordinator:
             p.data = torch.empty(0, dtype=self.device_dtype, device=self.device)
         if idx < 0:
             return
+        if self._first_gemm_pending.get(idx) == unit:
+            # the unit was let go before any product used its first matrix (a drained prefetch):
+            # the buffer is incomplete and must not be kept as a gathered copy
+            self._first_gemm_pending.pop(idx, None)
+            self._first_gemm[unit][0]._ft_gather = None
+            keep = False
         ev = self.streams.compute.record()
         fresh = self._held_version.pop(unit, 0) == self._version.get(unit, 0)
         if keep and fresh and self.num_buffers > 2:

@@ -72,6 +72,10 @@ def preset(name: str, **overrides) -> LlamaConfig:
 
 
 class LlamaBlock(nn.Module):
+    # the parameter the block multiplies first: on several GPUs the engine may leave it out of
+    # the layer's parameter gather and let that product fetch it (all-gather fused into the GEMM)
+    ft_first_gemm_weight = "wqkv"
+
     def __init__(self, cfg: LlamaConfig, dtype=torch.float32):
         super().__init__()
         self.cfg = cfg

@@ -50,7 +50,17 @@ class _Linear(torch.autograd.Function):
             x2 = x2.contiguous()
         n = w.shape[0]
         y = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
-        gemm(x2, False, w, False, x2.shape[0], n, k, out=y.view(-1, n))
+        pending = getattr(w, "_ft_gather", None)
+        if pending is not None:
+            # the rows of this weight that other ranks own are not in the gathered buffer yet:
+            # one kernel brings them in over NVLink and multiplies (csrc/comm/ag_gemm.cu)
+            if pending.covers(x2.shape[0], k):
+                pending.run(x2, y.view(-1, n))
+            else:
+                pending.complete_without_product()
+                gemm(x2, False, w, False, x2.shape[0], n, k, out=y.view(-1, n))
+        else:
+            gemm(x2, False, w, False, x2.shape[0], n, k, out=y.view(-1, n))
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
         return y

@@ -115,33 +115,48 @@ def _ag_lib():
     global _AG_DECLARED
     lib = cuda_lib()
     if not _AG_DECLARED:
-        lib.ft_ag_gemm.argtypes = [c_int, c_int, c_void_p, c_void_p, c_uint32, c_int, c_int, c_void_p,
-                                   c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+        lib.ft_ag_gemm.argtypes = [c_int, c_int, c_void_p, c_void_p, c_uint32, c_int, c_int, c_int64, c_int64,
+                                   c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                                    c_void_p]
         lib.ft_peer_gather.argtypes = [c_int, c_int, c_void_p, c_void_p, c_uint32, c_int, c_int, c_int64,
                                        c_int, c_void_p]
+        lib.ft_peer_gather_range.argtypes = [c_int, c_int, c_void_p, c_void_p, c_uint32, c_int, c_int,
+                                             c_int64, c_int64, c_int64, c_int, c_void_p]
         lib.ft_ag_set_spin_budget.argtypes = [ctypes.c_longlong]
         _AG_DECLARED = True
     return lib
 
 
-def ag_gemm(world: int, rank: int, w_ptrs, flag_ptrs, seq: int, x: torch.Tensor, n: int,
-            out: Optional[torch.Tensor] = None, num_copiers: int = 16, start_slot: int = 2,
-            done_slot: int = 3) -> torch.Tensor:
-    """``out[M, n] = x[M, K] @ W.T`` where ``W [n, K]`` is row-sharded over the
-    ranks and gathered inside the same kernel.  ``w_ptrs`` are the peer mappings
-    of every rank's full-size weight buffer (own shard already in place)."""
+AG_GEMM_CHUNK = 8192          # granularity of ownership inside the all-gather GEMM (bytes)
+
+
+def ag_gemm(world: int, rank: int, buf_ptrs, flag_ptrs, seq: int, x: torch.Tensor, n: int,
+            out: Optional[torch.Tensor] = None, w_off_bytes: int = 0, shard_bytes: Optional[int] = None,
+            start_slot: int = 2, done_slot: int = 3) -> torch.Tensor:
+    """``out[M, n] = x[M, K] @ W.T`` with ``W [n, K]`` gathered inside the same kernel.
+    ``buf_ptrs`` are the peer mappings of every rank's flat buffer, sharded in contiguous
+    pieces of ``shard_bytes``; ``W`` starts ``w_off_bytes`` into it and the part of it this
+    rank owns is in place.  Default: the buffer is ``W`` itself, row-sharded evenly."""
     m, k = x.shape
     if out is None:
         out = torch.empty(m, n, dtype=x.dtype, device=x.device)
-    rc = _ag_lib().ft_ag_gemm(world, rank, ctypes.cast(w_ptrs, c_void_p),
+    if shard_bytes is None:
+        if n % world:
+            raise ValueError("a row-sharded weight needs its rows to divide by the world size")
+        shard_bytes = n // world * k * x.element_size()
+    rc = _ag_lib().ft_ag_gemm(world, rank, ctypes.cast(buf_ptrs, c_void_p),
                               ctypes.cast(flag_ptrs, c_void_p) if flag_ptrs is not None else None, seq,
-                              start_slot, done_slot, ptr(x), x.stride(0), ptr(out), out.stride(0),
-                              dtype_code(out.dtype), m, n, k, dtype_code(x.dtype), num_copiers,
+                              start_slot, done_slot, int(w_off_bytes), int(shard_bytes), ptr(x), x.stride(0),
+                              ptr(out), out.stride(0), dtype_code(out.dtype), m, n, k, dtype_code(x.dtype),
                               stream_handle())
     if rc != 0:
         raise RuntimeError(f"ft_ag_gemm failed (code {rc})")
     return out
+
+
+def ag_gemm_covers(m: int, k: int, w_off_bytes: int, shard_bytes: int) -> bool:
+    """Whether ``ft_ag_gemm`` takes this shape and placement."""
+    return m > 128 and k % 64 == 0 and w_off_bytes % AG_GEMM_CHUNK == 0 and shard_bytes % AG_GEMM_CHUNK == 0
 
 
 def set_wait_seconds(seconds: float, device=None):
@@ -177,3 +192,15 @@ def peer_gather(world: int, rank: int, buf_ptrs, flag_ptrs, seq: int, shard_byte
                                   shard_bytes, num_copiers, stream_handle())
     if rc != 0:
         raise RuntimeError(f"ft_peer_gather failed (code {rc})")
+
+
+def peer_gather_range(world: int, rank: int, buf_ptrs, flag_ptrs, seq: int, shard_bytes: int,
+                      range_lo: int, range_hi: int, num_copiers: int = 148, start_slot: int = 4,
+                      done_slot: int = 5):
+    """Pull bytes ``[range_lo, range_hi)`` of a flat peer-mapped buffer from their owners
+    (what this rank owns is left alone)."""
+    rc = _ag_lib().ft_peer_gather_range(world, rank, ctypes.cast(buf_ptrs, c_void_p),
+                                        ctypes.cast(flag_ptrs, c_void_p), seq, start_slot, done_slot,
+                                        shard_bytes, range_lo, range_hi, num_copiers, stream_handle())
+    if rc != 0:
+        raise RuntimeError(f"ft_peer_gather_range failed (code {rc})")

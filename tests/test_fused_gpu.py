@@ -135,8 +135,8 @@ def test_bounded_wait_reports_instead_of_hanging():
 
 @pytest.mark.parametrize("world", [1, 2, 4])
 def test_ag_gemm_emulated_ranks(world):
-    """All ranks' weight buffers on one GPU, barriers pre-satisfied: the copier
-    CTAs pull the 'remote' row shards while the other CTAs multiply."""
+    """All ranks' weight buffers on one GPU, barriers pre-satisfied: the copy warps
+    pull the 'remote' row shards while the tensor cores multiply."""
     from flextrain_b200.ops.native import cuda_lib
     from flextrain_b200.parallel import fused
     dev = torch.device("cuda", 0)
@@ -155,14 +155,84 @@ def test_ag_gemm_emulated_ranks(world):
     fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
     want = x.float() @ W.float().t()
     for rank in range(world):
-        y = fused.ag_gemm(world, rank, wp, fp, 5, x, N, num_copiers=4)
+        y = fused.ag_gemm(world, rank, wp, fp, 5, x, N)
         torch.cuda.synchronize()
         assert cuda_lib().ft_gemm_error() == 0
         err = ((y.float() - want).norm() / want.norm()).item()
         assert err < 1e-2, f"rank {rank}: {err}"
         assert torch.equal(bufs[rank], W), "the local buffer must hold the whole weight afterwards"
-        # put the buffer back to 'own shard only' for the next emulated rank's peers
-    
+
+
+@pytest.mark.parametrize("world,w_off_chunks,n", [(2, 0, 520), (4, 3, 1000), (8, 5, 300), (8, 0, 1536), (3, 40, 264)])
+def test_ag_gemm_window_of_a_flat_sharded_buffer(world, w_off_chunks, n):
+    """The weight is a window of a larger flat buffer that the ranks shard in contiguous
+    pieces, as the engine keeps a layer: ownership boundaries fall anywhere in the matrix
+    (inside a 256-row block, some ranks own nothing of it), rows are not a multiple of 256."""
+    from flextrain_b200.ops.native import cuda_lib
+    from flextrain_b200.parallel import fused
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(world * 100 + n)
+    M, K = 384, 256
+    chunk = fused.AG_GEMM_CHUNK
+    w_off = w_off_chunks * chunk
+    w_bytes = n * K * 2
+    total = w_off + w_bytes + 7 * chunk                      # other parameters follow the matrix
+    shard = -(-total // (world * chunk)) * chunk              # contiguous pieces, chunk-aligned
+    full = torch.randint(0, 255, (shard * world,), dtype=torch.uint8, device=dev)
+    Wm = (torch.randn(n, K, device=dev) * 0.1).to(torch.bfloat16)
+    full[w_off:w_off + w_bytes] = Wm.view(torch.uint8).reshape(-1)
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    want = x.float() @ Wm.float().t()
+    bufs = []
+    for r in range(world):
+        b = torch.full((shard * world,), 0, dtype=torch.uint8, device=dev)
+        b[r * shard:(r + 1) * shard] = full[r * shard:(r + 1) * shard]
+        bufs.append(b)
+    flags = [torch.full((128 * 8,), 2, dtype=torch.int32, device=dev) for _ in range(world)]
+    bp = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    for rank in range(world):
+        before = bufs[rank].clone()
+        y = fused.ag_gemm(world, rank, bp, fp, 2, x, n, w_off_bytes=w_off, shard_bytes=shard)
+        torch.cuda.synchronize()
+        assert cuda_lib().ft_gemm_error() == 0
+        err = ((y.float() - want).norm() / want.norm()).item()
+        assert err < 1e-2, f"rank {rank}: {err}"
+        got = bufs[rank]
+        assert torch.equal(got[w_off:w_off + w_bytes], full[w_off:w_off + w_bytes])
+        # nothing outside the window was touched
+        assert torch.equal(got[:w_off], before[:w_off]) and torch.equal(got[w_off + w_bytes:], before[w_off + w_bytes:])
+        bufs[rank].copy_(before)                              # the next emulated rank's peers own only their shards
+
+
+@pytest.mark.parametrize("world,lo_chunks,hi_chunks", [(4, 0, 0), (4, 3, 9), (8, 1, 2), (2, 0, 5)])
+def test_peer_gather_range_emulated_ranks(world, lo_chunks, hi_chunks):
+    """Gather of a byte range of the flat buffer: everything outside the range and everything
+    this rank owns stay as they were."""
+    from flextrain_b200.ops.native import cuda_lib
+    from flextrain_b200.parallel import fused
+    dev = torch.device("cuda", 0)
+    shard = 4096 * 5
+    total = shard * world
+    lo, hi = lo_chunks * 4096 + 16 * 3, total - hi_chunks * 4096 - 16 * 5
+    full = torch.randint(1, 255, (total,), dtype=torch.uint8, device=dev)
+    bufs = []
+    for r in range(world):
+        b = torch.zeros(total, dtype=torch.uint8, device=dev)
+        b[r * shard:(r + 1) * shard] = full[r * shard:(r + 1) * shard]
+        bufs.append(b)
+    flags = [torch.full((128 * 8,), 4, dtype=torch.int32, device=dev) for _ in range(world)]
+    bp = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    rank = world - 1
+    fused.peer_gather_range(world, rank, bp, fp, 4, shard, lo, hi, num_copiers=5)
+    torch.cuda.synchronize()
+    assert cuda_lib().ft_gemm_error() == 0
+    want = torch.zeros(total, dtype=torch.uint8, device=dev)
+    want[rank * shard:(rank + 1) * shard] = full[rank * shard:(rank + 1) * shard]
+    want[lo:hi] = full[lo:hi]
+    assert torch.equal(bufs[rank], want)
+
 
 @pytest.mark.parametrize("mode", [1, 0])
 def test_peer_gather_emulated_ranks(mode):

@@ -33,5 +33,12 @@ def test_two_ranks(case):
 
 
 @pytest.mark.skipif(_gpus() < 4, reason="needs at least 4 GPUs")
-def test_rs_adam_four_ranks():
-    _launch("rs_adam", 4)
+@pytest.mark.parametrize("case", ["rs_adam", "engine", "ag_gemm"])
+def test_four_ranks(case):
+    _launch(case, 4)
+
+
+@pytest.mark.skipif(_gpus() < 8, reason="needs 8 GPUs")
+@pytest.mark.parametrize("case", ["rs_adam", "engine", "ag_gemm"])
+def test_eight_ranks(case):
+    _launch(case, 8)

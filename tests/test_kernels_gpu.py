@@ -280,7 +280,6 @@ def _attention_oracle(q, k, v, scale):
     return (torch.softmax(s, -1) @ vf).permute(0, 2, 1, 3), torch.logsumexp(s, -1)
 
 
-@pytest.mark.parametrize("version", [2, 4])
 @pytest.mark.parametrize("shape", [
     (1, 128, 1, 1, 128, torch.bfloat16, 1.0),      # one block, second tile of the pair absent
     (1, 256, 1, 1, 128, torch.bfloat16, 1.0),      # exactly one pair
@@ -290,28 +289,24 @@ def _attention_oracle(q, k, v, scale):
     (1, 1000, 2, 2, 128, torch.bfloat16, 1.0),     # sequence not a multiple of the block
     (1, 2048, 2, 1, 128, torch.bfloat16, 6.0),     # large scores: the running maximum keeps growing
 ])
-def test_attention_forward_generations(version, shape):
-    """Both forward kernels (one and two threads per score row) against the fp32
-    oracle: output and log-sum-exp, including shapes that exercise the absent
-    second tile, the ragged last block and the lazy rescale of the accumulator."""
+def test_attention_forward(shape):
+    """The forward kernel against the fp32 oracle: output and log-sum-exp, including
+    shapes that exercise the absent second tile, the ragged last block and the lazy
+    rescale of the accumulator."""
     import math
     from flextrain_b200.ops.attention_native import attention_forward
     from flextrain_b200.ops.native import cuda_lib
     B, S, Hq, Hkv, D, dt, amp = shape
     lib = cuda_lib()
-    lib.ft_attn_set_fwd_version(version)
-    try:
-        torch.manual_seed(S + D)
-        q = (torch.randn(B, S, Hq, D, device=_dev()) * amp).to(dt)
-        k = torch.randn(B, S, Hkv, D, device=_dev()).to(dt)
-        v = torch.randn(B, S, Hkv, D, device=_dev()).to(dt)
-        scale = 1.0 / math.sqrt(D)
-        for _ in range(3):                          # repeated: ordering bugs are timing dependent
-            o, lse, _ = attention_forward(q, k, v, scale)
-            torch.cuda.synchronize()
-            assert lib.ft_gemm_error() == 0
-            want_o, want_lse = _attention_oracle(q, k, v, scale)
-            assert _rel_err(o, want_o) < 2e-2
-            assert float((lse - want_lse).abs().max()) < 2e-2
-    finally:
-        lib.ft_attn_set_fwd_version(2)
+    torch.manual_seed(S + D)
+    q = (torch.randn(B, S, Hq, D, device=_dev()) * amp).to(dt)
+    k = torch.randn(B, S, Hkv, D, device=_dev()).to(dt)
+    v = torch.randn(B, S, Hkv, D, device=_dev()).to(dt)
+    scale = 1.0 / math.sqrt(D)
+    for _ in range(3):                          # repeated: ordering bugs are timing dependent
+        o, lse, _ = attention_forward(q, k, v, scale)
+        torch.cuda.synchronize()
+        assert lib.ft_gemm_error() == 0
+        want_o, want_lse = _attention_oracle(q, k, v, scale)
+        assert _rel_err(o, want_o) < 2e-2
+        assert float((lse - want_lse).abs().max()) < 2e-2
