@@ -334,15 +334,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (ok) {
       tc_fence_after();
       const int kv_pos = nb * BKV + r;
-      if (kv_pos < P.S) {
-        T* dk_row = reinterpret_cast<T*>(P.dk) + (int64_t)(batch * P.S + kv_pos) * P.dk_stride + kv_head * D;
-        T* dv_row = reinterpret_cast<T*>(P.dv) + (int64_t)(batch * P.S + kv_pos) * P.dv_stride + kv_head * D;
+      // every lane of a warp issues the same tensor-memory loads (they are warp-wide
+      // instructions); only the stores depend on whether the lane's row exists
+      const bool row_ok = kv_pos < P.S;
+      const int64_t row = (int64_t)(batch * P.S + (row_ok ? kv_pos : 0));
+      T* dk_row = reinterpret_cast<T*>(P.dk) + row * P.dk_stride + kv_head * D;
+      T* dv_row = reinterpret_cast<T*>(P.dv) + row * P.dv_stride + kv_head * D;
 #pragma unroll 1
-        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-          uint32_t a[32], b[32];
-          tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
-          tmem_ld_32x32(tm_dv + lane_addr + c * 32, b);
-          tmem_ld_wait();
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        uint32_t a[32], b[32];
+        tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
+        tmem_ld_32x32(tm_dv + lane_addr + c * 32, b);
+        tmem_ld_wait();
+        if (row_ok) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             float t[8], w[8];
@@ -354,14 +358,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             *reinterpret_cast<uint4*>(dk_row + c * 32 + u * 8) = pack8<T>(t);
             *reinterpret_cast<uint4*>(dv_row + c * 32 + u * 8) = pack8<T>(w);
           }
-        }
-      } else {
-        // rows past the end of the sequence still have to drain their TMEM loads uniformly
-#pragma unroll 1
-        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-          uint32_t a[32];
-          tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
-          tmem_ld_wait();
         }
       }
     } else {

@@ -49,10 +49,14 @@ def case_rs_adam():
             assert fused.comm_error() == 0
             tol = 2e-2 if gdt == torch.bfloat16 else 1e-5
             assert torch.allclose(host.float().to(dev), want[og:], rtol=tol, atol=tol), "host grads"
-            # first Adam step from zero state: p = -lr * g / (|g| + eps)
+            # first Adam step from zero state: m = (1 - beta1) * g is linear in the reduced
+            # gradient; p = -lr * g / (|g| + eps) is checked away from g = 0, where the order of
+            # the fp32 sum over more than two ranks decides its sign
             g = want[:og]
+            assert torch.allclose(m / 0.1, g, rtol=tol, atol=tol), "adam first moment"
             expect = -1e-3 * g / (g.abs() + 1e-8)
-            assert torch.allclose(master, expect, rtol=1e-3, atol=1e-6), "adam"
+            big = g.abs() > 1e-2
+            assert torch.allclose(master[big], expect[big], rtol=1e-3, atol=1e-6), "adam"
             tdist.barrier()
         symm.close()
     page.close()

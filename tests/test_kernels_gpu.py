@@ -249,10 +249,11 @@ def test_finite_flag_and_accumulate():
     assert torch.equal(dst, srcf.to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("S", [320, 1000])     # 1000: the last block's valid rows end inside a warp
 @pytest.mark.parametrize("hq,hkv,d", [(4, 4, 64), (8, 2, 128)])
-def test_causal_attention(hq, hkv, d):
+def test_causal_attention(hq, hkv, d, S):
     from flextrain_b200.ops.functional import causal_attention
-    B, S = 2, 320
+    B = 2
     q = torch.randn(B, S, hq, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
     k = torch.randn(B, S, hkv, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
     v = torch.randn(B, S, hkv, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
