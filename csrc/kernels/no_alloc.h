@@ -33,11 +33,19 @@ extern "C" {
 //
 // Returns 0 on success, -2 if H is not a multiple of 8, -3 if H exceeds
 // FT_RMSNORM_NOALLOC_MAX_H (use `ft_rmsnorm_bwd` with your own scratch then),
-// -1 for an unsupported dtype, or a positive CUDA error code.
+// -1 for an unsupported dtype, -4 if the current device's index is 64 or more
+// (the per-device address table has 64 entries), or a positive CUDA error code.
 //
 // Set-up: the first call on each device looks up the device address of the
 // scratch array (one `cudaGetSymbolAddress` with that device current) and caches
-// it.  Make that first call before any CUDA stream capture on the device.
+// it.  Make that first call before any CUDA stream capture on the device.  With
+// lazy module loading that look-up is also what brings the 9.25 MiB array into
+// being on the device, so a caller whose memory is about to be frozen should make
+// one warm-up call (any small shape) before it freezes its pools.
+//
+// Threads: two host threads that make the first call on a device at the same time
+// both look the address up and both store the same value, which is harmless; the
+// function takes no lock.
 //
 // Sharing: all calls on one device use the same array, and it keeps whatever the
 // previous call left in it.  Each call overwrites every scratch element it later

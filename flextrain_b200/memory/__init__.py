@@ -35,13 +35,31 @@ class FlexTrainDataType(Enum):
 
 @dataclass(frozen=True)
 class FlexTrainDataID:
-    """Names one swappable object; ``str()`` is its swap-file name
-    ``rank{r}_{TYPE}_layer{i}.swp`` (the on-disk format of the reference)."""
+    """Names one swappable object of a unit; ``str()`` is its swap-file name.  As in the
+    reference (flextrain/memory/__init__.py:40-49) a unit is named by the layers it holds:
+    ``rank{r}_{TYPE}_layer{i}.swp`` with one layer per unit, ``..._layer{first}-{last}.swp`` with
+    ``checkpoint_interval`` > 1.  Objects that exist once per micro-batch (activation
+    checkpoints) carry ``.mb{j}`` in addition, which the reference has no need for because
+    it packs a unit's micro-batches into one file.  A string is used as the layer part as is."""
     data_type: FlexTrainDataType
-    layer_index: object          # int or "i-j" for multi-index objects
+    unit_index: object           # unit number, or a ready-made layer label
+    micro_batch: Optional[int] = None
+
+    def layer_label(self) -> str:
+        if not isinstance(self.unit_index, int):
+            return str(self.unit_index)
+        interval = 1
+        try:
+            from ..config import get_flextrain_config
+            interval = int(get_flextrain_config().checkpoint_interval)
+        except RuntimeError:
+            pass
+        first = self.unit_index * interval
+        return f"{first}-{first + interval - 1}" if interval > 1 else str(first)
 
     def __str__(self):
-        return f"rank{dist.get_rank()}_{self.data_type.name}_layer{self.layer_index}.swp"
+        mb = "" if self.micro_batch is None else f".mb{self.micro_batch}"
+        return f"rank{dist.get_rank()}_{self.data_type.name}_layer{self.layer_label()}{mb}.swp"
 
 
 # ------------------------------------------------------------------ handles

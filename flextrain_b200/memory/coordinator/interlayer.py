@@ -72,7 +72,8 @@ class TieredTensorStore:
         self._landing = []
         self._landing_free = []
         self._nvme_stage = []
-        self._pool_cpu = []        # recycled pinned pieces
+        self._pool_cpu = []
+        self._pool_cpu_wide = []        # pinned buffers of DRAM + NVMe share (margin micro-batches)        # recycled pinned pieces
         self._pool_gpu = []
         self.bytes_d2h = 0
         self.bytes_h2d = 0
@@ -99,9 +100,9 @@ class TieredTensorStore:
                 self._stage_next = 0
 
     def _data_id(self, key):
-        if isinstance(key, tuple):
-            return FlexTrainDataID(self.data_type, "-".join(str(k) for k in key))
-        return FlexTrainDataID(self.data_type, key)
+        if isinstance(key, tuple):                  # (unit, micro-batch)
+            return FlexTrainDataID(self.data_type, key[0], micro_batch=key[1])
+        return FlexTrainDataID(self.data_type, "all", micro_batch=key)
 
     # ------------------------------------------------------------------ put
     @torch.no_grad()
@@ -143,7 +144,9 @@ class TieredTensorStore:
             if pin_to_dram and n:
                 # whole non-HBM part stays in DRAM
                 if slot.cpu is None or slot.cpu.numel() != c + n:
-                    slot.cpu = allocate_memory(c + n, tensor.dtype, "cpu", True)
+                    # margin micro-batches come back every step: their wide buffers are pooled too
+                    slot.cpu = self._pool_cpu_wide.pop() if self._pool_cpu_wide else \
+                        allocate_memory(c + n, tensor.dtype, "cpu", True)
                 tier_copy(slot.cpu, flat[g:])
                 slot.nvme_id = None
             else:
@@ -245,6 +248,9 @@ class TieredTensorStore:
             self._landing_free[slot.landing] = self.streams.compute.record()
         if slot.cpu is not None and self._tiers and slot.cpu.numel() == self._tiers[1]:
             self._pool_cpu.append(slot.cpu)
+        elif slot.cpu is not None and self._tiers and self._tiers[2] and \
+                slot.cpu.numel() == self._tiers[1] + self._tiers[2]:
+            self._pool_cpu_wide.append(slot.cpu)
         if slot.gpu is not None:
             self._pool_gpu.append(slot.gpu)
         if slot.nvme_id is not None and slot.io is not None:

@@ -31,6 +31,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ...config import get_flextrain_config
+from ...defaults import PAGE_SIZE
 from ...utils import distributed as dist
 from ...utils.device import DONE, Event, get_streams
 from ...utils.logging import rank0_logger
@@ -96,7 +97,10 @@ class FlexTrainParaCoordinator:
         self.checkpoint_interval = cfg.checkpoint_interval
         self.num_units = (num_layers - 1) // cfg.checkpoint_interval + 1
         self.unit_numel = first_unit_numel
-        self.aligned_unit_numel = partition_aligned_numel(first_unit_numel, self.world, self.itemsize)
+        # one rank's shard is a multiple of the page (O_DIRECT pieces) and, on several ranks, of the
+        # 8 KiB ownership granule of the all-gather GEMM
+        page = 8192 if self.world > 1 else PAGE_SIZE
+        self.aligned_unit_numel = partition_aligned_numel(first_unit_numel, self.world, self.itemsize, page)
         self.shard_numel = self.aligned_unit_numel // self.world
         self.tier_numels = get_split_numels(self.shard_numel, cfg.split_ratio.parameter, self.itemsize)
         g, c, n = self.tier_numels

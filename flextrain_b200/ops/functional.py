@@ -104,7 +104,7 @@ def attention_packed(qkv, hq, hkv, d, scale=None):
     import math
     import os
     from .attention import native_available
-    if os.environ.get("FLEXTRAIN_ATTN", "native") != "native" or not native_available(d):
+    if os.environ.get("FLEXTRAIN_ATTN", "native") == "sdpa" or not native_available(d):
         return None
     from .attention_native import attention_packed as impl
     return impl(qkv, hq, hkv, d, scale if scale is not None else 1.0 / math.sqrt(d))

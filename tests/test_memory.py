@@ -103,8 +103,18 @@ def test_pin_memory_blocks_shape():
 
 def test_data_ids():
     from flextrain_b200.memory import FlexTrainDataID, FlexTrainDataType
-    assert str(FlexTrainDataID(FlexTrainDataType.CKPT, "3-1")) == "rank0_CKPT_layer3-1.swp"
+    from flextrain_b200.config import init_flextrain_config, reset_flextrain_config
+    reset_flextrain_config()
+    assert str(FlexTrainDataID(FlexTrainDataType.CKPT, 3, micro_batch=1)) == "rank0_CKPT_layer3.mb1.swp"
     assert str(FlexTrainDataID(FlexTrainDataType.OPTS, 7)) == "rank0_OPTS_layer7.swp"
+    assert str(FlexTrainDataID(FlexTrainDataType.PARA, "3-1")) == "rank0_PARA_layer3-1.swp"
+    # with several layers per unit the name carries the layer range, as the reference's does
+    init_flextrain_config({"batch_size": 1, "micro_batch_size": 1, "checkpoint_interval": 4}, log=False)
+    try:
+        assert str(FlexTrainDataID(FlexTrainDataType.PARA, 2)) == "rank0_PARA_layer8-11.swp"
+        assert str(FlexTrainDataID(FlexTrainDataType.CKPT, 2, micro_batch=0)) == "rank0_CKPT_layer8-11.mb0.swp"
+    finally:
+        reset_flextrain_config()
 
 
 def test_host_memcpy_and_locked_tensors():
