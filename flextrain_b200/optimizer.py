@@ -222,10 +222,10 @@ class FlexTrainOptimizer:
         nl = self._cfg.engine.fused_nonlayer
         if nl is False:
             return False
-        from .ops.adam import FlexTrainAdam
+        from .ops.adam import FlexTrainCPUAdam
         from .parallel.fused import segments_aligned
         from .parallel.symm_mem import peer_access_available
-        if not isinstance(self.cpu_optimizer, FlexTrainAdam):
+        if not isinstance(self.cpu_optimizer, FlexTrainCPUAdam):
             return False
         if self.master_dtype != torch.float32 or self.optimizer_state_per_element != 2:
             return False

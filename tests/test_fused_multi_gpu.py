@@ -19,7 +19,11 @@ def _launch(case, nproc):
            "--master-addr", "127.0.0.1", "--master-port", str(29400 + os.getpid() % 500),
            os.path.join(HERE, "_multi_gpu_worker.py"), case]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
-    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    if proc.returncode != 0:
+        # the ranks' own tracebacks come before the launcher's summary: show the lines that name an error
+        lines = (proc.stdout + proc.stderr).splitlines()
+        named = [ln for ln in lines if "Error" in ln or "assert" in ln.lower() or "rank" in ln.lower()][:60]
+        raise AssertionError("\n".join(named) + "\n--- tail ---\n" + proc.stderr[-2500:])
 
 
 def _gpus():
