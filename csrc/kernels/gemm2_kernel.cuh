@@ -253,6 +253,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int pair = (int)(blockIdx.x >> 1), num_pairs = (int)(gridDim.x >> 1);
   const int mt = (M + P_BM - 1) / P_BM, nt = (N + P_BN - 1) / P_BN, kt = (K + BK - 1) / BK;
   const int num_tiles = mt * nt;
+  const int group_m = gather.group_m > 0 ? gather.group_m : GROUP_M;
   // with GATHER the columns are walked from this rank's own rows outwards, in copy order
   WindowOwnership own = {};
   int n_rot = 0;
@@ -295,7 +296,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
         int mb, nb;
-        tile_coords(t, mt, nt, mb, nb);
+        tile_coords(t, mt, nt, mb, nb, group_m);
         if constexpr (GATHER) {
           nb = (nb + n_rot) % nt;
           const uint32_t need = remote_chunks_in_block(gather, own, nb);
@@ -395,7 +396,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int it = 0;
     for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++it) {
       int mb, nb;
-      tile_coords(t, mt, nt, mb, nb);
+      tile_coords(t, mt, nt, mb, nb, group_m);
       if constexpr (GATHER) nb = (nb + n_rot) % nt;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;

@@ -51,6 +51,7 @@ struct GatherArgs {
   // A row-sharded matrix is the case w_off_bytes = 0, shard_bytes = rows_per_rank * row_bytes.
   int64_t w_off_bytes;
   int64_t w_bytes;
+  int group_m;             // CTA-pair GEMM, with or without gather: row blocks per group of the tile walk (0: GROUP_M)
 };
 
 constexpr int COPY_CHUNK = 32768;
@@ -64,11 +65,13 @@ struct Barriers {
   uint32_t abort;
 };
 
-__device__ __forceinline__ void tile_coords(int t, int mt, int nt, int& mb, int& nb) {
-  const int group_size = GROUP_M * nt;
+// Tile t of the walk: groups of `group_m` row blocks, inside a group column by column, so that
+// the tiles in flight at one time share few A and few B blocks (L2 reuse).
+__device__ __forceinline__ void tile_coords(int t, int mt, int nt, int& mb, int& nb, int group_m = GROUP_M) {
+  const int group_size = group_m * nt;
   const int group = t / group_size;
-  const int first_m = group * GROUP_M;
-  const int gm = min(mt - first_m, GROUP_M);
+  const int first_m = group * group_m;
+  const int gm = min(mt - first_m, group_m);
   const int in_group = t - group * group_size;
   mb = first_m + in_group % gm;
   nb = in_group / gm;

@@ -173,6 +173,17 @@ int launch_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
 }
 
 // ---- CTA-pair kernel (cluster of 2)
+// Row blocks per group of the CTA-pair kernel's tile walk (FLEXTRAIN_GEMM_GROUP_M, default 16).
+int pair_group_m() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("FLEXTRAIN_GEMM_GROUP_M");
+    v = e ? atoi(e) : GROUP_M;
+    if (v < 1) v = GROUP_M;
+  }
+  return v;
+}
+
 template <typename T, bool A_MN, bool B_MN, int MODE>
 int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64_t ldc, int M, int N, int K,
                     int* err, int grid, cudaStream_t s) {
@@ -194,7 +205,9 @@ int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, ldc, M, N, K, err, GatherArgs{});
+  GatherArgs none{};
+  none.group_m = pair_group_m();
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, ldc, M, N, K, err, none);
   return e == cudaSuccess ? 0 : (int)e;
 }
 
