@@ -109,11 +109,13 @@ class FlexTrainConfigSolver:
         lp.add_eq({"gpu_grad": 1, "cpu_grad": 1}, 1.0)
         lp.var("T_f", 0.0, None)
         lp.var("T_b", 0.0, None)
+        # Among placements of equal step time (a compute-bound step leaves the LP indifferent)
+        # prefer the nearer tier for every kind of data: a whole share in NVMe is charged a tenth of
+        # a layer's forward time, a whole share in host memory a fiftieth.
+        far, near = 10 * D.REGULARIZATION_PENALTY * p.layer_fwd_time, 2 * D.REGULARIZATION_PENALTY * p.layer_fwd_time
         lp.minimise({"T_f": 1.0, "T_b": 1.0,
-                     "nvme_para": D.REGULARIZATION_PENALTY * p.layer_fwd_time,
-                     "nvme_opts": D.REGULARIZATION_PENALTY * p.layer_fwd_time,
-                     "cpu_opts": 1e-3 * D.REGULARIZATION_PENALTY * p.layer_fwd_time,
-                     "cpu_para": 1e-3 * D.REGULARIZATION_PENALTY * p.layer_fwd_time})
+                     "nvme_para": far, "nvme_opts": far, "nvme_ckpt": far,
+                     "cpu_opts": near, "cpu_para": near, "cpu_ckpt": near, "cpu_grad": near})
         opt_bytes = P * m * (S + 1)
         # ---- capacity
         lp.add_le({"gpu_para": P * L * d, "gpu_opts": opt_bytes * L, "gpu_ckpt": mbpr * A * L * d,
@@ -356,9 +358,10 @@ def measure_machine(engine, iters: int = 10, swap_dir: Optional[str] = None) -> 
     t_f, t_b, t_pp = benchmark_layers(engine, iters)
     itemsize = lambda dt: torch.empty((), dtype=dt).element_size()  # noqa: E731
     if dev.type == "cuda":
+        # what the driver reports free plus what the current placement spends on movable state;
+        # blocks cached by the allocator are the step's working set and stay out of the budget
         free, _total = torch.cuda.mem_get_info()
-        vram = (free + torch.cuda.memory_reserved() - torch.cuda.memory_allocated()
-                + _tier_bytes(engine, "hbm")) * D.ACCESSIBLE_GPU_MEMORY_RATIO
+        vram = (free + _tier_bytes(engine, "hbm")) * D.ACCESSIBLE_GPU_MEMORY_RATIO
     else:
         vram = 8e9
     dram = min(cfg.max_dram_usage * 1e9 if cfg.max_dram_usage > 0 else float("inf"),
@@ -424,7 +427,11 @@ def system_auto_config(engine, iters: int = 10) -> List[ConfigResult]:
     if dist.get_rank() == 0:
         rank0_logger.info(format_results(results))
     engine.last_auto_config = results
-    results = sorted(results, key=lambda r: -r.throughput)
+    # best first; within 1 % of each other the smaller batch (less memory, same rate) comes first
+    top = max((r.throughput for r in results), default=0.0)
+    results = sorted(results, key=lambda r: (0 if r.throughput >= top / D.THROUGHPUT_STABLE_THRESHOLD else 1,
+                                             r.micro_batches_per_rank if r.throughput >= top / D.THROUGHPUT_STABLE_THRESHOLD
+                                             else -r.throughput))
     engine.auto_config_report = {
         "measurements": asdict(perf),
         "candidates": [{"micro_batches_per_rank": r.micro_batches_per_rank, "alpha": r.alpha,

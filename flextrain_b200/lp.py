@@ -67,6 +67,15 @@ class LinearProgram:
     def solve(self, prefer_scipy: bool = True) -> Optional[Dict[str, float]]:
         """Optimal assignment, or None when infeasible / unbounded."""
         c, A_ub, b_ub, A_eq, b_eq = self._dense()
+        # Rows arrive in their natural units (bytes ~1e11 next to seconds ~1e-2): scale every row to
+        # a largest coefficient of 1, or the solver's absolute tolerances swallow the small objective
+        # terms that break ties between placements of equal step time.
+        for A, b in ((A_ub, b_ub), (A_eq, b_eq)):
+            for r in range(len(b)):
+                scale = np.abs(A[r]).max()
+                if scale > 0:
+                    A[r] /= scale
+                    b[r] /= scale
         x = None
         if prefer_scipy:
             try:
