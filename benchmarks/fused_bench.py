@@ -160,7 +160,7 @@ def bench_ag(world, rank, dev, page, iters, flush):
 def bench_gather(world, rank, dev, page, nbytes, iters, flush, blocks):
     """Whole-unit gather as the engine issues it: every rank owns 1/world of a flat buffer of
     ``nbytes`` (the bf16 parameters of one layer) and pulls the rest from its peers.
-    ``ft_peer_gather`` in both forms against NCCL ``all_gather_into_tensor``; the roofline is
+    ``ft_peer_gather`` against NCCL ``all_gather_into_tensor``; the roofline is
     the inbound bytes at the measured peer-copy rate."""
     from flextrain_b200.ops.native import cuda_lib
     shard = nbytes // world // 4096 * 4096
@@ -175,15 +175,11 @@ def bench_gather(world, rank, dev, page, nbytes, iters, flush, blocks):
     def run_peer():
         fused.peer_gather(world, rank, symm.ptr_array(), page.ptr_array(), page.next_seq("pg"), shard, blocks)
 
-    for mode, name in ((1, "peer_ldst_ms"), (0, "peer_bulk_ms")):
-        lib.ft_gather_set_mode(mode)
-        res[name] = timed(run_peer, iters, flush, world)
-    lib.ft_gather_set_mode(1)
+    res["peer_ldst_ms"] = timed(run_peer, iters, flush, world)
     res["nccl_ms"] = timed(lambda: tdist.all_gather_into_tensor(gathered, mine), iters, flush, world)
     roof_ms = (world - 1) * shard / (NVLINK_GBS * 1e9) * 1e3
     res["roofline_ms"] = roof_ms
     res["peer_ldst_frac_of_roofline"] = roof_ms / res["peer_ldst_ms"]
-    res["peer_bulk_frac_of_roofline"] = roof_ms / res["peer_bulk_ms"]
     res["nccl_frac_of_roofline"] = roof_ms / res["nccl_ms"]
     res["inbound_gbs_ldst"] = (world - 1) * shard / res["peer_ldst_ms"] / 1e6
     assert lib.ft_gemm_error() == 0

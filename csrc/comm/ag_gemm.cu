@@ -12,7 +12,8 @@
 // TMA producers waiting (bounded) for a block's counter before loading it, so the transfer
 // overlaps the math tile by tile and the weight crosses NVLink exactly once.
 //
-// ft_peer_gather: the copier role alone, for any flat sharded buffer.
+// ft_peer_gather / ft_peer_gather_range: the gather alone, for a flat sharded buffer or a byte range of it
+// (loads and stores by every thread of one CTA per SM).
 //
 // Both replace the NCCL all_gather_into_tensor of
 // flextrain/memory/coordinator/parameter.py:516 (and, for ft_ag_gemm, the cuBLAS
@@ -37,7 +38,6 @@ constexpr int kCounters = 64;
 uint32_t* g_ready[16] = {nullptr};
 unsigned int* g_counter[16] = {nullptr};
 long long g_spin_budget = 0;
-int g_gather_lag = 1;   // see ft_gather_set_lag
 
 int ensure_state(int dev) {
   if (!g_ready[dev]) {
@@ -48,22 +48,6 @@ int ensure_state(int dev) {
     cudaMemset(g_counter[dev], 0, kCounters * sizeof(unsigned int));
   }
   return 0;
-}
-
-// Small footprint on purpose (3 x 8 KiB of shared memory, one warp): these CTAs
-// must fit on an SM beside a resident GEMM CTA, otherwise a gather that runs on
-// a side stream would take whole SMs away from the compute stream.
-constexpr int PG_CHUNK = 8192, PG_STAGES = 3;
-
-__global__ void __launch_bounds__(32)
-peer_gather_kernel(const __grid_constant__ GatherArgs gather, int* __restrict__ err) {
-  __shared__ __align__(128) uint8_t ring[PG_STAGES * PG_CHUNK];
-  __shared__ uint64_t full_bars[PG_STAGES];
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < PG_STAGES; ++s) mbar_init(&full_bars[s], 1);
-    fence_barrier_init();
-    gather_role<PG_CHUNK, PG_STAGES, PG_CHUNK>(gather, ring, full_bars, err);
-  }
 }
 
 // The stand-alone gather with plain 16-byte peer loads and local stores issued by every thread
@@ -136,8 +120,6 @@ peer_gather_ldst_kernel(const __grid_constant__ GatherArgs G, int* __restrict__ 
   }
 }
 
-int g_gather_mode = -1;   // -1: read FLEXTRAIN_PEER_GATHER on first use; 0 bulk copies, 1 loads / stores
-
 int fill_gather(GatherArgs& G, int world, int rank, const void* const* w_ptrs, uint32_t* const* flags,
                 uint32_t seq, int start_slot, int done_slot, int num_copiers, int dev) {
   memset(&G, 0, sizeof(G));
@@ -154,7 +136,6 @@ int fill_gather(GatherArgs& G, int world, int rank, const void* const* w_ptrs, u
   G.spin_budget = g_spin_budget > 0 ? g_spin_budget : peer::kSpinCycles;
   G.num_copiers = num_copiers;
   G.ready = g_ready[dev];
-  G.lagged = g_gather_lag;
   G.block_counter = g_counter[dev] + (start_slot & (kCounters - 1));
   return 0;
 }
@@ -192,14 +173,6 @@ extern "C" {
 
 void ft_ag_set_spin_budget(long long cycles) { g_spin_budget = cycles; }
 
-// Form of ft_peer_gather: 1 = loads / stores by every thread (default), 0 = bulk copies through
-// shared memory by one thread per CTA.
-void ft_gather_set_mode(int mode) { g_gather_mode = mode ? 1 : 0; }
-
-// Completion signalling of the copy role for later ft_ag_gemm / ft_peer_gather calls:
-// 1 = lagged by NSTAGE-1 store groups (default), 0 = one store at a time.
-void ft_gather_set_lag(int on) { g_gather_lag = on ? 1 : 0; }
-
 // y[M,N] = x[M,K] * W^T with W[N,K] gathered from its owners inside the same launch.
 // W is a window of a flat buffer that the ranks shard in contiguous pieces: buf_ptrs[r] is this
 // process's mapping of rank r's whole flat buffer, rank r owns its bytes
@@ -231,11 +204,10 @@ int ft_ag_gemm(int world, int rank, const void* const* buf_ptrs, uint32_t* const
   for (int r = 0; r < world; ++r)
     G.w_peer[r] = reinterpret_cast<const uint8_t*>(buf_ptrs[r]) + w_off_bytes;
   G.w_local = const_cast<uint8_t*>(reinterpret_cast<const uint8_t*>(buf_ptrs[rank]) + w_off_bytes);
-  G.row_bytes = (int64_t)K * 2;
   G.shard_bytes = shard_bytes;
-  G.block_bytes = (int64_t)P_BN * G.row_bytes;
+  G.block_bytes = (int64_t)P_BN * K * 2;
   G.w_off_bytes = w_off_bytes;
-  G.w_bytes = (int64_t)N * G.row_bytes;
+  G.w_bytes = (int64_t)N * K * 2;
   CUtensorMap ta, tb;
   int rc = make_tmap(&ta, x, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM, ab_dtype);
   if (rc) return rc;
@@ -294,35 +266,12 @@ int ft_peer_gather_range(int world, int rank, const void* const* buf_ptrs, uint3
 }
 
 // Pull every remote shard of a flat buffer sharded in `shard_bytes` pieces into the local
-// buffer.  shard_bytes must be a multiple of 16.  Two forms (ft_gather_set_mode): loads / stores
-// by every thread (default) or bulk copies through shared memory by one thread per CTA.
+// buffer.  shard_bytes must be a multiple of 16.
 int ft_peer_gather(int world, int rank, const void* const* buf_ptrs, uint32_t* const* flags,
                    uint32_t seq, int start_slot, int done_slot, int64_t shard_bytes, int num_copiers,
                    cudaStream_t stream) {
-  if (world < 1 || world > peer::kMaxRanks || rank < 0 || rank >= world) return -1;
-  if (shard_bytes % 16 || shard_bytes <= 0) return -2;
-  if (world == 1) return 0;
-  if (g_gather_mode < 0) {
-    const char* e = getenv("FLEXTRAIN_PEER_GATHER");
-    g_gather_mode = (e && !strcmp(e, "bulk")) ? 0 : 1;
-  }
-  if (g_gather_mode == 1)
-    return ft_peer_gather_range(world, rank, buf_ptrs, flags, seq, start_slot, done_slot, shard_bytes, 0,
-                                shard_bytes * world, num_copiers, stream);
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (ensure_state(dev)) return -4;
-  if (num_copiers < 1) num_copiers = 1;
-  GatherArgs G;
-  fill_gather(G, world, rank, buf_ptrs, flags, seq, start_slot, done_slot, num_copiers, dev);
-  G.ready = g_ready[dev] + kReadyWords;
-  G.shard_bytes = shard_bytes;
-  G.block_bytes = (shard_bytes * world + kReadyWords - 1) / kReadyWords;
-  if (G.block_bytes < PG_CHUNK) G.block_bytes = PG_CHUNK;
-  peer_gather_kernel<<<num_copiers, 32, 0, stream>>>(G, error_word(dev));
-  FT_LAUNCHED(1);
-  FT_CUDA_RETURN_IF_ERROR();
-  return 0;
+  return ft_peer_gather_range(world, rank, buf_ptrs, flags, seq, start_slot, done_slot, shard_bytes, 0,
+                              shard_bytes * world, num_copiers, stream);
 }
 
 }  // extern "C"

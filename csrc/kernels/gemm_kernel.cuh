@@ -21,14 +21,14 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
 enum OutMode : int { kStore16 = 0, kStore32 = 1, kAcc16 = 2, kAcc32 = 3 };
 
-// Arguments of the all-gather role (used only when the kernel is instantiated with
-// GATHER = true).  B is row-sharded over `peers.world` ranks: rank r owns rows
-// [r * rows_per_rank, (r+1) * rows_per_rank) of every rank's [N, K] buffer.
-// CTAs [0, num_copiers) pull the remote shards into the local buffer with bulk
-// copies (peer global -> shared -> local global) and count finished chunks per
-// 256-row block in `ready`; the TMA producers of the other CTAs wait for a block's
-// count before they load it.  Tiles are walked starting with the local shard and
-// then in the order the shards arrive.
+// Arguments of the all-gather role of the CTA-pair kernel (gemm2_kernel.cuh, GATHER = true) and
+// of the stand-alone gather (comm/ag_gemm.cu).  The gathered bytes are a window
+// [w_off_bytes, w_off_bytes + w_bytes) of a flat buffer that the ranks shard in contiguous
+// pieces of `shard_bytes` (rank r owns flat bytes [r * shard_bytes, (r+1) * shard_bytes));
+// w_peer / w_local point at the window's first byte in every rank's / this rank's buffer.
+// A row-sharded matrix is the case w_off_bytes = 0, shard_bytes = rows_per_rank * row_bytes.
+// The copy warps count finished chunks per 256-row block in `ready`; the TMA producers wait for
+// a block's count before they load it.
 struct GatherArgs {
   peer::Peers peers;
   uint32_t seq;
@@ -36,25 +36,15 @@ struct GatherArgs {
   long long spin_budget;
   const void* w_peer[peer::kMaxRanks];
   void* w_local;
-  int64_t row_bytes;       // GEMM use: bytes of one row of B
-  int rows_per_rank;       // GEMM use: rows of B owned by each rank
-  int64_t shard_bytes;     // bytes each rank owns (multiple of 16)
+  int64_t shard_bytes;     // bytes of the flat buffer each rank owns
   int64_t block_bytes;     // bytes covered by one `ready` counter
   int num_copiers;
   uint32_t* ready;
   unsigned int* block_counter;
-  int lagged;              // 1: announce a chunk NSTAGE-1 store groups late (keeps the copy stream
-                           //    full); 0: wait for each store before the next (the first form)
-  // CTA-pair GEMM (gather_role_w): B is a window [w_off_bytes, w_off_bytes + w_bytes) of a flat
-  // buffer that is sharded in contiguous pieces of `shard_bytes` (rank r owns flat bytes
-  // [r * shard_bytes, (r+1) * shard_bytes)); w_peer / w_local point at the window's first byte.
-  // A row-sharded matrix is the case w_off_bytes = 0, shard_bytes = rows_per_rank * row_bytes.
   int64_t w_off_bytes;
   int64_t w_bytes;
   int group_m;             // CTA-pair GEMM, with or without gather: row blocks per group of the tile walk (0: GROUP_M)
 };
-
-constexpr int COPY_CHUNK = 32768;
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -156,140 +146,8 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   return v;
 }
 
-// The copier role of one CTA: thread 0 streams this CTA's share of the remote
-// chunks through the shared-memory ring, STAGES - 1 loads in flight.
-// CHUNK bytes per bulk copy, NSTAGE ring slots of STRIDE bytes, one mbarrier per slot.
-template <int CHUNK, int NSTAGE, int STRIDE>
-__device__ __forceinline__ void gather_role(const GatherArgs& G, uint8_t* smem, uint64_t* full_bars, int* err) {
-  const int W = G.peers.world, R = G.peers.rank;
-  if (W <= 1) return;
-  uint32_t* mine = G.peers.flags[R];
-  if (blockIdx.x == 0) {                      // tell every peer that the local shard is in place
-    __threadfence_system();
-    for (int p = 0; p < W; ++p)
-      if (p != R) peer::st_release_sys(G.peers.flags[p] + G.start_slot * peer::kMaxRanks + R, G.seq);
-  }
-  bool ok = true;
-  for (int p = 0; p < W && ok; ++p)
-    if (p != R && !peer::wait_seq(mine + G.start_slot * peer::kMaxRanks + p, G.seq, G.spin_budget)) ok = false;
-  if (!ok) {
-    atomicCAS(err, 0, 201);
-  } else {
-    const int64_t shard_bytes = G.shard_bytes;
-    const int64_t chunks_per_shard = (shard_bytes + CHUNK - 1) / CHUNK;
-    const int64_t total = chunks_per_shard * (W - 1);
-    const int64_t block_bytes = G.block_bytes;
-    // chunk q of this CTA: global index blockIdx.x + q * num_copiers (the last chunk of a
-    // shard may be short)
-    auto locate = [&](int64_t q, const uint8_t*& src, uint8_t*& dst, int& nblk, uint32_t& bytes) {
-      const int64_t gq = blockIdx.x + q * G.num_copiers;
-      const int k = (int)(gq / chunks_per_shard);
-      const int p = (R + 1 + k) % W;
-      const int64_t in_shard = (gq % chunks_per_shard) * CHUNK;
-      const int64_t off = (int64_t)p * shard_bytes + in_shard;
-      const int64_t left = shard_bytes - in_shard;
-      bytes = (uint32_t)(left < CHUNK ? left : CHUNK);
-      src = reinterpret_cast<const uint8_t*>(G.w_peer[p]) + off;
-      dst = reinterpret_cast<uint8_t*>(G.w_local) + off;
-      nblk = (int)(off / block_bytes);
-    };
-    const int64_t n = total > blockIdx.x ? (total - blockIdx.x + G.num_copiers - 1) / G.num_copiers : 0;
-    uint32_t phase[NSTAGE];
-    for (int s = 0; s < NSTAGE; ++s) phase[s] = 0;
-    for (int64_t q = 0; q < n && q < NSTAGE - 1; ++q) {
-      const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
-      locate(q, src, dst, nb, bytes);
-      const int s = (int)(q % NSTAGE);
-      mbar_expect_tx(&full_bars[s], bytes);
-      bulk_load(smem + s * STRIDE, src, bytes, &full_bars[s]);
-    }
-    if (G.lagged) {
-      // Stage reuse only needs the previous store to have *read* shared memory; a chunk is
-      // announced once its store group has fully completed, which is checked LAG groups late
-      // so that the completion latency never stalls the copy stream.
-      constexpr int LAG = NSTAGE - 1;
-      int pending[NSTAGE];
-      for (int64_t q = 0; q < n; ++q) {
-        const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
-        locate(q, src, dst, nb, bytes);
-        const int s = (int)(q % NSTAGE);
-        if (!mbar_wait(&full_bars[s], phase[s])) { atomicCAS(err, 0, 202); break; }
-        phase[s] ^= 1;
-        bulk_store(dst, smem + s * STRIDE, bytes);
-        bulk_commit();
-        pending[s] = nb;
-        asm volatile("cp.async.bulk.wait_group %0;" ::"n"(LAG) : "memory");
-        if (q >= LAG) {                         // chunk q - LAG is in local memory
-          fence_proxy_async_all();
-          __threadfence();
-          red_release_add(G.ready + pending[(int)((q - LAG) % NSTAGE)], 1u);
-        }
-        const int64_t nq = q + NSTAGE - 1;
-        if (nq < n) {
-          const uint8_t* src2; uint8_t* dst2; int nb2; uint32_t bytes2;
-          locate(nq, src2, dst2, nb2, bytes2);
-          const int s2 = (int)(nq % NSTAGE);    // stage of chunk q - 1
-          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          mbar_expect_tx(&full_bars[s2], bytes2);
-          bulk_load(smem + s2 * STRIDE, src2, bytes2, &full_bars[s2]);
-        }
-      }
-      bulk_wait_all();
-      fence_proxy_async_all();
-      __threadfence();
-      for (int64_t q = (n > LAG ? n - LAG : 0); q < n; ++q) {
-        const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
-        locate(q, src, dst, nb, bytes);
-        red_release_add(G.ready + nb, 1u);
-      }
-    } else {
-      int prev_nb = -1;
-      for (int64_t q = 0; q < n; ++q) {
-        const uint8_t* src; uint8_t* dst; int nb; uint32_t bytes;
-        locate(q, src, dst, nb, bytes);
-        const int s = (int)(q % NSTAGE);
-        if (!mbar_wait(&full_bars[s], phase[s])) { atomicCAS(err, 0, 202); break; }
-        phase[s] ^= 1;
-        bulk_store(dst, smem + s * STRIDE, bytes);
-        bulk_commit();
-        bulk_wait_all_but_1();                  // every chunk before this one is in local memory
-        if (q >= 1) {
-          fence_proxy_async_all();
-          __threadfence();
-          red_release_add(G.ready + prev_nb, 1u);
-        }
-        prev_nb = nb;
-        const int64_t nq = q + NSTAGE - 1;
-        if (nq < n) {
-          const uint8_t* src2; uint8_t* dst2; int nb2; uint32_t bytes2;
-          locate(nq, src2, dst2, nb2, bytes2);
-          const int s2 = (int)(nq % NSTAGE);    // stage of chunk q - 1, whose store has completed
-          mbar_expect_tx(&full_bars[s2], bytes2);
-          bulk_load(smem + s2 * STRIDE, src2, bytes2, &full_bars[s2]);
-        }
-      }
-      bulk_wait_all();
-      if (prev_nb >= 0) {
-        fence_proxy_async_all();
-        __threadfence();
-        red_release_add(G.ready + prev_nb, 1u);
-      }
-    }
-  }
-  // end barrier: the last copier tells the peers that this rank reads their shards no more
-  __threadfence_system();
-  const unsigned int done = atomicAdd(G.block_counter, 1u);
-  if (done == (unsigned int)G.num_copiers - 1) {
-    *G.block_counter = 0;
-    for (int p = 0; p < W; ++p)
-      if (p != R) peer::st_release_sys(G.peers.flags[p] + G.done_slot * peer::kMaxRanks + R, G.seq);
-    for (int p = 0; p < W; ++p)
-      if (p != R && !peer::wait_seq(mine + G.done_slot * peer::kMaxRanks + p, G.seq, G.spin_budget))
-        atomicCAS(err, 0, 203);
-  }
-}
-
-template <typename T, bool A_MN, bool B_MN, int MODE, bool GATHER = false>
+// `gather` is unused by this kernel (it shares the launch signature of the CTA-pair kernel).
+template <typename T, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             void* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err,
@@ -301,12 +159,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mt = (M + BM - 1) / BM, nt = (N + BN - 1) / BN, kt = (K + BK - 1) / BK;
   const int num_tiles = mt * nt;
-  // with GATHER the first CTAs copy and the rest share the tiles among themselves
-  const int copiers = GATHER ? gather.num_copiers : 0;
-  const int first_tile = (int)blockIdx.x - copiers;
-  const int tile_step = (int)gridDim.x - copiers;
-  const int nt_local = GATHER ? gather.rows_per_rank / BN : 0;
-  const int n_rot = GATHER ? gather.peers.rank * nt_local : 0;
+  const int first_tile = (int)blockIdx.x;
+  const int tile_step = (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -332,10 +186,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t tmem_base = bars->tmem_base;
   volatile uint32_t* abort_flag = &bars->abort;
 
-  if (GATHER && first_tile < 0) {
-    // ------------------------------------------------------- gather role
-    if (threadIdx.x == 0) gather_role<COPY_CHUNK, STAGES, STAGE_BYTES>(gather, smem, bars->full, err);
-  } else if (warp == 0) {
+  if (warp == 0) {
     // ------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
@@ -343,20 +194,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step) {
         int mb, nb;
         tile_coords(t, mt, nt, mb, nb);
-        if constexpr (GATHER) {
-          nb = (nb + n_rot) % nt;
-          if (nb < n_rot || nb >= n_rot + nt_local) {      // rows that come from a peer
-            const uint32_t need = (uint32_t)(gather.block_bytes / COPY_CHUNK);
-            const long long t0 = clock64();
-            bool ok = true;
-            while (ld_acquire_gpu(gather.ready + nb) < need) {
-              if (clock64() - t0 > gather.spin_budget) { ok = false; break; }
-              __nanosleep(128);
-            }
-            if (!ok) { *abort_flag = 1; atomicCAS(err, 0, 204); break; }
-            fence_proxy_async_all();
-          }
-        }
         for (int kb = 0; kb < kt; ++kb) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1)) {
             *abort_flag = 1;
@@ -436,7 +273,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step, ++it) {
       int mb, nb;
       tile_coords(t, mt, nt, mb, nb);
-      if constexpr (GATHER) nb = (nb + n_rot) % nt;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&bars->tmem_full[acc], acc_phase)) {

@@ -192,16 +192,14 @@ class EngineConfig(_Section):
             raise ValueError("engine.fused_wait_seconds must be a positive number or [steady, first step]")
         self.fused_wait_seconds = (float(waits[0]), float(waits[1]))
         self.fused_nonlayer = section.get(D.FUSED_NONLAYER, D.FUSED_NONLAYER_DEFAULT)
-        self.gather_lag = section.get(D.GATHER_LAG, D.GATHER_LAG_DEFAULT)
         self.fused_timeout_action = str(section.get(D.FUSED_TIMEOUT_ACTION, D.FUSED_TIMEOUT_ACTION_DEFAULT))
         if self.fused_timeout_action not in ("raise", "fallback"):
             raise ValueError("engine.fused_timeout_action must be 'raise' or 'fallback'")
         self.fused_first_gemm = section.get(D.FUSED_FIRST_GEMM, D.FUSED_FIRST_GEMM_DEFAULT)
         if self.fused_first_gemm not in ("auto", True, False):
             raise ValueError("engine.fused_first_gemm must be 'auto', true or false")
-        for key, val in ((D.FUSED_NONLAYER, self.fused_nonlayer), (D.GATHER_LAG, self.gather_lag)):
-            if val not in ("auto", True, False):
-                raise ValueError(f"engine.{key} must be 'auto', true or false")
+        if self.fused_nonlayer not in ("auto", True, False):
+            raise ValueError("engine.fused_nonlayer must be 'auto', true or false")
 
     @property
     def fused_blocks(self) -> int:

@@ -99,8 +99,6 @@ FUSED_COLLECTIVES = "fused_collectives"    # peer-memory kernels instead of NCCL
 FUSED_COLLECTIVES_DEFAULT = "auto"         # "auto" | True | False
 FUSED_NONLAYER = "fused_nonlayer"          # fused all-reduce + sharded Adam for non-layerwise params
 FUSED_NONLAYER_DEFAULT = "auto"            # "auto": on wherever the fused collectives are
-GATHER_LAG = "gather_lag"                  # lagged completion signalling in the peer gather
-GATHER_LAG_DEFAULT = "auto"                # "auto": on
 FUSED_FIRST_GEMM = "fused_first_gemm"      # all-gather of a unit's first matrix inside the GEMM that uses it
 FUSED_FIRST_GEMM_DEFAULT = "auto"          # "auto" | True | False
 FUSED_BLOCKS = "fused_blocks"              # CTAs of the fused collective kernels

@@ -158,10 +158,6 @@ class FlexTrainParaCoordinator:
         ok = peer_access_available()
         if want is True and not ok:
             raise RuntimeError("engine.fused_collectives=true needs peer access between all ranks")
-        if ok:
-            lag = cfg.engine.gather_lag
-            from ...parallel import fused
-            fused.set_gather_lag(lag is not False)
         return bool(ok)
 
     def _note_first_gemm(self, unit: int, layers, group: ContiguousParaGroup):

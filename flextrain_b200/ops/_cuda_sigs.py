@@ -22,7 +22,6 @@ def declare(lib):
     lib.ft_norm_bwd.argtypes = [P, P, P, P, P, P, P, P, P, P, L, I, I, I, P]
     lib.ft_add_norm_fwd.argtypes = [P, P, P, P, P, P, P, P, L, I, F, I, I, P]
     lib.ft_add_norm_bwd.argtypes = [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, P]
-    lib.ft_gather_set_mode.argtypes = [I]
     lib.ft_bias_act_fwd.argtypes = [P, P, P, L, I, I, I, P]
     lib.ft_bias_act_bwd_parts.argtypes = [L, I]
     lib.ft_bias_act_bwd_parts.restype = I

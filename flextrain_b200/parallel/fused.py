@@ -176,14 +176,6 @@ def set_wait_seconds(seconds: float, device=None):
     return cycles
 
 
-def set_gather_lag(on: bool):
-    """Completion signalling of the copy role in ``ag_gemm`` / ``peer_gather``:
-    lagged by the ring depth (keeps the copy stream full) or one store at a time."""
-    lib = _ag_lib()
-    lib.ft_gather_set_lag.argtypes = [c_int]
-    lib.ft_gather_set_lag(int(bool(on)))
-
-
 def peer_gather(world: int, rank: int, buf_ptrs, flag_ptrs, seq: int, shard_bytes: int,
                 num_copiers: int = 16, start_slot: int = 4, done_slot: int = 5):
     """Pull every remote shard of a flat peer-mapped buffer into the local copy."""

@@ -148,18 +148,15 @@ def case_ag_gemm():
     flat = symm.tensor(torch.uint8)
     shard = symm.nbytes // world
     ref = torch.arange(symm.nbytes, device=dev, dtype=torch.int64).remainder_(251).to(torch.uint8)
-    for mode in (1, 0):                       # loads / stores by every thread, then bulk copies
-        cuda_lib().ft_gather_set_mode(mode)
-        flat.zero_()
-        flat[rank * shard:(rank + 1) * shard].copy_(ref[rank * shard:(rank + 1) * shard])
-        torch.cuda.synchronize()
-        tdist.barrier()
-        fused.peer_gather(world, rank, symm.ptr_array(), page.ptr_array(), page.next_seq("pg"), shard, 8)
-        torch.cuda.synchronize()
-        assert cuda_lib().ft_gemm_error() == 0
-        assert torch.equal(flat, ref)
-        tdist.barrier()
-    cuda_lib().ft_gather_set_mode(1)
+    flat.zero_()
+    flat[rank * shard:(rank + 1) * shard].copy_(ref[rank * shard:(rank + 1) * shard])
+    torch.cuda.synchronize()
+    tdist.barrier()
+    fused.peer_gather(world, rank, symm.ptr_array(), page.ptr_array(), page.next_seq("pg"), shard, 8)
+    torch.cuda.synchronize()
+    assert cuda_lib().ft_gemm_error() == 0
+    assert torch.equal(flat, ref)
+    tdist.barrier()
     symm.close()
     page.close()
     print(f"rank {rank}: ag_gemm ok", flush=True)

@@ -67,7 +67,6 @@ def _declared():
     from flextrain_b200.parallel import fused
     fused._lib()
     fused._ag_lib()
-    fused.set_gather_lag(False)
     try:
         from flextrain_b200.parallel import symm_mem
         for name in ("_lib", "_declare"):

@@ -234,15 +234,11 @@ def test_peer_gather_range_emulated_ranks(world, lo_chunks, hi_chunks):
     assert torch.equal(bufs[rank], want)
 
 
-@pytest.mark.parametrize("mode", [1, 0])
-def test_peer_gather_emulated_ranks(mode):
-    """Both forms of the stand-alone gather: loads / stores by every thread (1) and bulk
-    copies through shared memory (0)."""
+def test_peer_gather_emulated_ranks():
     from flextrain_b200.ops.native import cuda_lib
     from flextrain_b200.parallel import fused
     dev = torch.device("cuda", 0)
     world = 4
-    cuda_lib().ft_gather_set_mode(mode)
     shard = 4096 * 37 + 4096                      # bytes, page aligned, not a multiple of 32 KiB
     full = torch.randint(0, 255, (world * shard,), dtype=torch.uint8, device=dev)
     bufs = []
@@ -253,11 +249,8 @@ def test_peer_gather_emulated_ranks(mode):
     flags = [torch.full((128 * 8,), 9, dtype=torch.int32, device=dev) for _ in range(world)]
     bp = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
     fp = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
-    try:
-        fused.peer_gather(world, 2, bp, fp, 9, shard, num_copiers=3)
-        torch.cuda.synchronize()
-    finally:
-        cuda_lib().ft_gather_set_mode(1)
+    fused.peer_gather(world, 2, bp, fp, 9, shard, num_copiers=3)
+    torch.cuda.synchronize()
     assert cuda_lib().ft_gemm_error() == 0
     assert torch.equal(bufs[2], full)
 

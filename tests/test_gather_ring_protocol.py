@@ -1,8 +1,9 @@
-"""Host restatement of the copy ring of ``gather_role`` (csrc/kernels/gemm_kernel.cuh): one
-thread streams chunks peer HBM -> shared memory (bulk load, mbarrier per stage) -> local HBM
-(bulk store, one commit group per chunk) through NSTAGE stages, in the lagged form (a chunk is
-announced LAG groups after its store was issued; a stage is reloaded as soon as the previous
-store has READ it) and in the one-store-at-a-time form.
+"""Host restatement of the copy ring of ``gather_role_w`` (csrc/kernels/gemm2_kernel.cuh), the
+copy warp of the all-gather GEMM: one thread streams chunks peer HBM -> shared memory (bulk
+load, mbarrier per stage) -> local HBM (bulk store, one commit group per chunk) through NSTAGE
+stages.  The kernel uses the lagged form (a chunk is announced LAG groups after its store was
+issued; a stage is reloaded as soon as the previous store has READ it); the one-store-at-a-time
+form is replayed as well, as the simpler protocol the lagged one must be equivalent to.
 
 Replayed with asynchronous loads and stores that finish after random delays, stores finishing
 their read of shared memory before their write to global memory, and the semantics of
