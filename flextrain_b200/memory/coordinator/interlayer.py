@@ -14,11 +14,21 @@ re-assembles a tensor into one of two HBM landing buffers on the h2d stream one
 task ahead of its consumer; ``get`` makes the compute stream wait for it.  With
 an HBM share of 1.0 the store keeps the tensor itself and nothing is copied -
 the normal case on a 180 GB part.  The NVMe piece of a checkpoint is the file
-``rank{r}_CKPT_layer{u}-{mb}.swp``; the first and last micro-batch of every
+``rank{r}_CKPT_layer{u}.mb{j}.swp``; the first and last micro-batch of every
 unit (the snake turn) never go to NVMe.
+
+NVMe pieces never make the Python thread wait for a disk or a copy: a worker thread
+per store writes a piece once its device-to-host copy has landed in a staging buffer,
+and on the way back reads it into another staging buffer and itself queues the
+host-to-device copies that assemble the landing buffer.  The consumer only waits (on
+the host) for that queueing to have happened and (on the compute stream) for the event
+recorded behind it.
 """
 from __future__ import annotations
 
+import queue
+import threading
+from concurrent.futures import Future
 from dataclasses import dataclass
 from typing import Dict, Hashable, Optional, Tuple
 
@@ -41,9 +51,42 @@ class InterLayerTask(LLMTask):
 
 
 
+class _DiskWorker:
+    """One thread that runs the NVMe transfers of a store in the order they were queued."""
+
+    def __init__(self, device):
+        self._q: "queue.Queue" = queue.Queue()
+        self._device = device
+        self._thread = threading.Thread(target=self._run, name="ft-ckpt-nvme", daemon=True)
+        self._thread.start()
+
+    def submit(self, fn) -> Future:
+        fut: Future = Future()
+        self._q.put((fn, fut))
+        return fut
+
+    def _run(self):
+        if self._device.type == "cuda":
+            torch.cuda.set_device(self._device)
+        while True:
+            fn, fut = self._q.get()
+            if fn is None:
+                fut.set_result(None)
+                return
+            try:
+                fut.set_result(fn())
+            except BaseException as exc:          # surfaced by whoever waits on the future
+                fut.set_exception(exc)
+
+    def shutdown(self):
+        fut: Future = Future()
+        self._q.put((None, fut))
+        fut.result()
+
+
 class _Slot:
     __slots__ = ("shape", "dtype", "whole", "hot", "gpu", "cpu", "nvme_id", "stored", "landing",
-                 "ready", "io")
+                 "ready", "io", "ready_future")
 
     def __init__(self):
         self.whole = None      # the tensor itself when everything stays in HBM
@@ -54,7 +97,8 @@ class _Slot:
         self.stored: Event = DONE
         self.landing = None
         self.ready: Optional[Event] = None
-        self.io = None
+        self.io = None              # Future of the NVMe write of this slot's piece
+        self.ready_future = None    # Future -> Event: the worker queued the copies into the landing buffer
 
 
 class TieredTensorStore:
@@ -72,9 +116,10 @@ class TieredTensorStore:
         self._landing = []
         self._landing_free = []
         self._nvme_stage = []
-        self._pool_cpu = []
-        self._pool_cpu_wide = []        # pinned buffers of DRAM + NVMe share (margin micro-batches)        # recycled pinned pieces
+        self._pool_cpu = []             # recycled pinned pieces
+        self._pool_cpu_wide = []        # pinned buffers of DRAM + NVMe share (margin micro-batches)
         self._pool_gpu = []
+        self._worker: Optional[_DiskWorker] = None
         self.bytes_d2h = 0
         self.bytes_h2d = 0
 
@@ -92,12 +137,15 @@ class TieredTensorStore:
             self._landing = [allocate_memory(self._numel, t.dtype, self.device) for _ in range(2)]
             self._landing_free = [DONE, DONE]
             if self._tiers[2]:
-                self._nvme_stage = [allocate_memory(self._tiers[2], t.dtype, "cpu", True)
-                                    for _ in range(2)]
-                for stage in self._nvme_stage:
+                # two staging buffers per direction: a piece on its way out never waits for one coming in
+                self._out_stage = [allocate_memory(self._tiers[2], t.dtype, "cpu", True) for _ in range(2)]
+                self._in_stage = [allocate_memory(self._tiers[2], t.dtype, "cpu", True) for _ in range(2)]
+                for stage in self._out_stage + self._in_stage:
                     get_nvme_swapper().register_staging(stage)
-                self._stage_busy = [None, None]
-                self._stage_next = 0
+                self._out_busy = [None, None]          # Future of the write that last used the buffer
+                self._in_copied = [DONE, DONE]         # event: the last copy out of the buffer has run
+                self._out_next = self._in_next = 0
+                self._worker = _DiskWorker(self.device)
 
     def _data_id(self, key):
         if isinstance(key, tuple):                  # (unit, micro-batch)
@@ -120,6 +168,7 @@ class TieredTensorStore:
         slot = self._slots.get(key) or _Slot()
         self._slots[key] = slot
         slot.shape, slot.dtype = tensor.shape, tensor.dtype
+        self._settle(slot)
         if slot.landing is not None:
             self._landing_free[slot.landing] = self.streams.compute.record()
         slot.ready, slot.landing = None, None
@@ -156,17 +205,22 @@ class TieredTensorStore:
                             allocate_memory(c, tensor.dtype, "cpu", True)
                     tier_copy(slot.cpu, flat[g:g + c])
                 if n:
-                    i = self._stage_next
-                    self._stage_next = (i + 1) % 2
-                    if self._stage_busy[i] is not None:
-                        self._stage_busy[i].wait()
-                    stage = self._nvme_stage[i]
+                    i = self._out_next
+                    self._out_next = (i + 1) % 2
+                    if self._out_busy[i] is not None:
+                        self._out_busy[i].result()        # the write two pieces back still owns the buffer
+                    stage = self._out_stage[i]
                     tier_copy(stage, flat[g + c:])
                     copied = st.d2h.record()
-                    copied.synchronize()
-                    slot.nvme_id = self._data_id(key)
-                    slot.io = get_nvme_swapper().swap_out(slot.nvme_id, stage, async_op=True)
-                    self._stage_busy[i] = slot.io
+                    nvme_id = self._data_id(key)
+                    slot.nvme_id = nvme_id
+
+                    def write(copied=copied, stage=stage, nvme_id=nvme_id):
+                        copied.synchronize()
+                        get_nvme_swapper().swap_out(nvme_id, stage)
+
+                    slot.io = self._worker.submit(write)
+                    self._out_busy[i] = slot.io
             self.bytes_d2h += (self._numel - g) * tensor.element_size()
             slot.stored = st.d2h.record()
         # the producer's storage may be recycled only after the copies have read it
@@ -178,7 +232,8 @@ class TieredTensorStore:
     def prefetch(self, key):
         """Start re-assembling ``key`` into a landing buffer (h2d stream)."""
         slot = self._slots.get(key)
-        if slot is None or self.all_hbm or slot.ready is not None or slot.hot is not None:
+        if slot is None or self.all_hbm or slot.ready is not None or slot.ready_future is not None \
+                or slot.hot is not None:
             return
         g, c, n = self._tiers
         idx = 0 if self._landing_free[0] is not None else 1
@@ -188,18 +243,31 @@ class TieredTensorStore:
         self._landing_free[idx] = None
         land = self._landing[idx]
         st = self.streams
-        stage = None
-        if slot.nvme_id is not None:
-            if slot.io is not None:
-                slot.io.wait()
-                slot.io = None
-            i = self._stage_next
-            self._stage_next = (i + 1) % 2
-            if self._stage_busy[i] is not None:
-                self._stage_busy[i].wait()
-                self._stage_busy[i] = None
-            stage = self._nvme_stage[i]
-            get_nvme_swapper().swap_in(slot.nvme_id, stage)
+        slot.landing = idx
+        if slot.nvme_id is None:
+            slot.ready = self._assemble(slot, land, free_ev, None, None)
+            return
+        # the NVMe piece comes back on the worker thread, which then queues every copy into the
+        # landing buffer itself; the Python thread goes on
+        i = self._in_next
+        self._in_next = (i + 1) % 2
+        stage, written = self._in_stage[i], slot.io
+
+        def read(i=i, stage=stage, written=written, nvme_id=slot.nvme_id):
+            if written is not None:
+                written.result()                       # the piece is on disk
+            self._in_copied[i].synchronize()            # the previous piece has left the buffer
+            get_nvme_swapper().swap_in(nvme_id, stage)
+            ready = self._assemble(slot, land, free_ev, stage, i)
+            return ready
+
+        slot.ready_future = self._worker.submit(read)
+        slot.io = None
+
+    def _assemble(self, slot, land, free_ev, stage, stage_index) -> Event:
+        """Queue the copies that put a tensor together in its landing buffer (h2d stream)."""
+        g, c, n = self._tiers
+        st = self.streams
         with st.h2d.use():
             st.h2d.wait(free_ev)
             st.h2d.wait(slot.stored)
@@ -210,10 +278,10 @@ class TieredTensorStore:
             if stage is not None:
                 tier_copy(land[g + c:], stage)
             self.bytes_h2d += (self._numel - g) * land.element_size()
-            slot.ready = st.h2d.record()
+            ready = st.h2d.record()
         if stage is not None:
-            slot.ready.synchronize()      # the stage buffer is reused by the next transfer
-        slot.landing = idx
+            self._in_copied[stage_index] = ready
+        return ready
 
     # ------------------------------------------------------------------ get
     def get(self, key) -> torch.Tensor:
@@ -224,16 +292,27 @@ class TieredTensorStore:
         if slot.hot is not None:
             hot, slot.hot = slot.hot, None
             return hot
-        if slot.ready is None:
+        if slot.ready is None and slot.ready_future is None:
             self.prefetch(key)
+        if slot.ready_future is not None:
+            slot.ready, slot.ready_future = slot.ready_future.result(), None
         self.streams.compute.wait(slot.ready)
         return self._landing[slot.landing].view(slot.shape)
+
+    @staticmethod
+    def _settle(slot):
+        """A read-back that was started and never consumed must have queued its copies before
+        the landing buffer changes hands."""
+        if slot.ready_future is not None:
+            fut, slot.ready_future = slot.ready_future, None
+            slot.ready = fut.result()
 
     def done_with(self, key, drop: bool = False):
         """The consumer has queued its last read of ``key`` on the compute stream."""
         slot = self._slots.get(key)
         if slot is None:
             return
+        self._settle(slot)
         if slot.landing is not None:
             self._landing_free[slot.landing] = self.streams.compute.record()
             slot.landing, slot.ready = None, None
@@ -244,6 +323,7 @@ class TieredTensorStore:
         slot = self._slots.pop(key, None)
         if slot is None:
             return
+        self._settle(slot)
         if slot.landing is not None:
             self._landing_free[slot.landing] = self.streams.compute.record()
         if slot.cpu is not None and self._tiers and slot.cpu.numel() == self._tiers[1]:
@@ -254,7 +334,7 @@ class TieredTensorStore:
         if slot.gpu is not None:
             self._pool_gpu.append(slot.gpu)
         if slot.nvme_id is not None and slot.io is not None:
-            slot.io.wait()
+            slot.io.result()
 
     def __contains__(self, key):
         return key in self._slots
@@ -262,6 +342,12 @@ class TieredTensorStore:
     def clear(self):
         for key in list(self._slots):
             self.drop(key)
+
+    def close(self):
+        """Stop the worker thread (after what it still holds has run)."""
+        if self._worker is not None:
+            self._worker.shutdown()
+            self._worker = None
 
 
 class FlexTrainInterLayerCoordinator:
@@ -290,4 +376,7 @@ def get_interlayer_coordinator() -> FlexTrainInterLayerCoordinator:
 
 def reset_interlayer_coordinator():
     global _INTER
+    if _INTER is not None:
+        _INTER.ckpt.close()
+        _INTER.grad.close()
     _INTER = None
