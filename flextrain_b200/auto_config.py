@@ -252,8 +252,10 @@ def benchmark_pcie(device, nbytes: int = 1 << 28, iters: int = 20, h2d: bool = F
     return nbytes / t
 
 
-def benchmark_nvme(swap_dir: str, nbytes: int = 1 << 28, iters: int = 4):
-    """(read B/s, write B/s) of the NVMe engine on ``swap_dir``; (0, 0) if unusable."""
+def benchmark_nvme(swap_dir: str, nbytes: int = 1 << 30, iters: int = 3):
+    """(read B/s, write B/s) of the NVMe engine on ``swap_dir``; (0, 0) if unusable.  The
+    transfers are large (1 GiB each, like a unit's optimizer state) because what the planner
+    needs is the rate the device sustains, not what a cache in front of it absorbs."""
     from .memory.nvme_swapper import NVMeEngine
     try:
         os.makedirs(swap_dir, exist_ok=True)

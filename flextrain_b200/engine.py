@@ -601,30 +601,45 @@ class FlexTrainEngine:
 
     # ------------------------------------------------------ save / resume
     def save(self, directory: str):
-        """Write this rank's training state to ``directory/rank{r}_state.pt``:
-        the fp32 master weights and optimizer states of every unit shard
-        (whatever tier they live in), the non-layerwise parameters' state, the
-        param groups' hyper-parameters and step counters, the loss scaler and
-        the RNG state.  The reference has no persistent checkpoint at all
-        (its only on-disk artefacts are transient swap files)."""
+        """Write this rank's training state to ``directory``: ``rank{r}_unit{u}.pt`` with the
+        fp32 master weights and optimizer states of every unit shard (whatever tier they
+        live in) and ``rank{r}_state.pt`` with the non-layerwise parameters' state, the
+        param groups' hyper-parameters and step counters, the loss scaler and the RNG
+        state.  The reference has no persistent checkpoint at all (its only on-disk
+        artefacts are transient swap files)."""
         import os
         self.synchronize()
         os.makedirs(directory, exist_ok=True)
+        rank = dist.get_rank()
+        # one file per unit, written as its states are read out of their tiers: the host never
+        # holds more than one unit's fp32 master weights and moments at a time
+        for u in range(self.num_units):
+            torch.save(self.opts.read_states(u), os.path.join(directory, f"rank{rank}_unit{u}.pt"))
         state = {
-            "world_size": self.world, "rank": dist.get_rank(), "global_steps": self.global_steps,
+            "world_size": self.world, "rank": rank, "global_steps": self.global_steps,
             "skipped_steps": self.skipped_steps, "num_units": self.num_units,
             "shard_numel": self.para.shard_numel, "unit_numel": self.para.unit_numel,
-            "units": [self.opts.read_states(u) for u in range(self.num_units)],
+            "unit_files": True, "state_kinds": self.opts.K,
             "non_layerwise": self.optimizer.non_layerwise_state(),
             "param_groups": self.optimizer.hyper_state(),
             "loss_scaler": self.loss_scaler.state_dict(),
             "rng_cpu": torch.get_rng_state(),
             "rng_cuda": torch.cuda.get_rng_state() if self.device.type == "cuda" else None,
         }
-        path = os.path.join(directory, f"rank{dist.get_rank()}_state.pt")
+        path = os.path.join(directory, f"rank{rank}_state.pt")
         torch.save(state, path)
         dist.barrier()
         return path
+
+    @staticmethod
+    def _unit_states(directory: str, head: Dict[str, Any], rank: int, unit: int, mmap: bool):
+        """(master, moments...) of one unit of one rank's checkpoint: its own file, or - in
+        checkpoints written before units had files of their own - an entry of the rank's state."""
+        import os
+        if head.get("unit_files"):
+            return torch.load(os.path.join(directory, f"rank{rank}_unit{unit}.pt"), map_location="cpu",
+                              weights_only=False, mmap=mmap)
+        return head["units"][unit]
 
     def load(self, directory: str):
         """Restore what ``save`` wrote.  With the world size and partition geometry
@@ -644,8 +659,8 @@ class FlexTrainEngine:
         same = head["world_size"] == self.world and head["shard_numel"] == self.para.shard_numel
         if same:
             state = torch.load(own, map_location="cpu", weights_only=False)
-            for u, states in enumerate(state["units"]):
-                self.opts.write_states(u, states)
+            for u in range(self.num_units):
+                self.opts.write_states(u, self._unit_states(directory, state, dist.get_rank(), u, mmap=False))
             self.optimizer.load_non_layerwise_state(state["non_layerwise"])
         else:
             state = head
@@ -680,12 +695,12 @@ class FlexTrainEngine:
             return files[rank]
 
         lo, hi = dist.get_rank() * new_shard, (dist.get_rank() + 1) * new_shard
-        kinds = len(head["units"][0])
+        kinds = head.get("state_kinds") or len(head["units"][0])
         for u in range(self.num_units):
             states = [torch.zeros(new_shard, dtype=torch.float32) for _ in range(kinds)]
             for r in range(lo // old_shard, min(old_world, (hi - 1) // old_shard + 1)):
                 a, b = max(lo, r * old_shard), min(hi, (r + 1) * old_shard)
-                src = old(r)["units"][u]
+                src = self._unit_states(directory, old(r), r, u, mmap=True)
                 for k in range(kinds):
                     states[k][a - lo:b - lo].copy_(src[k][a - r * old_shard:b - r * old_shard])
             # what lies past the unit's true size is padding in either layout

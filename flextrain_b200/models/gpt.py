@@ -79,6 +79,10 @@ def preset(name: str, **overrides) -> GPTConfig:
 
 
 class GPTBlock(nn.Module):
+    # the parameter the block multiplies first: on several GPUs the engine may leave it out of
+    # the layer's parameter gather and let that product fetch it (all-gather fused into the GEMM)
+    ft_first_gemm_weight = "wqkv"
+
     def __init__(self, cfg: GPTConfig, dtype=torch.float32, layer_index: int = 0):
         super().__init__()
         self.cfg = cfg

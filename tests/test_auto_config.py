@@ -69,3 +69,23 @@ def test_enumeration_stops_and_formats():
     assert "mbpr=" in text and "alpha=" in text
     cfg = results[0].to_config()
     assert set(cfg["split_ratio"]) >= {"parameter", "optimizer", "checkpoint", "gradient", "alpha"}
+
+
+def test_lp_rows_in_natural_units_do_not_swallow_the_tie_break():
+    """Capacity rows carry coefficients around 1e11 (bytes), the objective's tie-breaking terms are
+    around 1e-4: the solver must still return the vertex with the smaller objective (it did not
+    before the rows were scaled: a compute-bound step left two thirds of the optimizer state on
+    the host although HBM had room)."""
+    from flextrain_b200.lp import LinearProgram
+    for prefer_scipy in (True, False):
+        lp = LinearProgram()
+        lp.var("gpu", 0.0, 1.0)
+        lp.var("cpu", 0.0, 1.0)
+        lp.var("T", 0.0, None)
+        lp.add_eq({"gpu": 1, "cpu": 1}, 1.0)
+        lp.add_le({"gpu": 1.52e11}, 1.4e11)            # HBM holds 92 % of the state
+        lp.add_le({"cpu": 1.52e11}, 1.0e11)            # host memory 66 %
+        lp.add_ge({"T": 1.0}, 0.065)                   # compute-bound: placement does not change T
+        lp.minimise({"T": 1.0, "cpu": 3.9e-4})
+        sol = lp.solve(prefer_scipy=prefer_scipy)
+        assert sol is not None and abs(sol["gpu"] - 1.4e11 / 1.52e11) < 1e-6, sol

@@ -37,7 +37,8 @@ def test_save_resume_matches_uninterrupted_run(tmp_path):
     assert all(r["tokens_per_s"] > 0 for r in rows)
     ck = str(tmp_path / "ck")
     first = _run(common + ["--steps", "3", "--save-dir", ck], str(tmp_path))
-    assert sorted(os.listdir(ck)) == ["rank0_data.json", "rank0_state.pt"]
+    # one state file per rank, one file per unit (the checkpoint is written unit by unit)
+    assert sorted(os.listdir(ck)) == ["rank0_data.json", "rank0_state.pt"] + [f"rank0_unit{u}.pt" for u in range(4)]
     second = _run(common + ["--steps", "2", "--resume", ck], str(tmp_path))
     assert second["steps_done"] == 5
     assert first["losses"] + second["losses"] == whole["losses"]
