@@ -25,10 +25,11 @@
 namespace ft {
 namespace attn {
 
-// 2 control warps + 8 compute warps + the dQ store warp: warps 2-5 own S / dP / dQ / dK /
-// dV columns of the first half, warps 6-9 those of the second half (each warp still reads
-// only its own TMEM lane quarter, warp % 4); warp 10 issues the dQ reduce-adds.
-constexpr int BWD_THREADS = 352;
+// 2 control warps + 4 * SPLIT compute warps + the dQ store warp.  The 128 columns of S / dP (and
+// the D columns of dQ / dK / dV) are cut into SPLIT parts; warps 2 + 4 * part .. 5 + 4 * part own
+// part `part` (each warp still reads only its own TMEM lane quarter, warp % 4), so every score
+// row is shared by SPLIT threads.  The warp after them issues the dQ reduce-adds.
+constexpr int bwd_threads(int split) { return 32 * (2 + 4 * split + 1); }
 
 template <int D>
 struct BwdSmem {
@@ -65,8 +66,8 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const vo
       : "memory");
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+template <typename T, int D, int SPLIT>
+__global__ void __launch_bounds__(bwd_threads(SPLIT), 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                 const __grid_constant__ CUtensorMap tmap_dq, const __grid_constant__ BwdParams P) {
@@ -100,12 +101,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars->qdo_empty, 1);
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->dp_full, 1);
-    mbar_init(&bars->p_full, 256);
-    mbar_init(&bars->ds_full, 256);
+    mbar_init(&bars->p_full, 128 * SPLIT);
+    mbar_init(&bars->ds_full, 128 * SPLIT);
     mbar_init(&bars->dq_full, 1);
-    mbar_init(&bars->s_free, 256);
+    mbar_init(&bars->s_free, 128 * SPLIT);
     mbar_init(&bars->acc_full, 1);
-    mbar_init(&bars->dqs_full, 256);
+    mbar_init(&bars->dqs_full, 128 * SPLIT);
     mbar_init(&bars->stage_free, 1);
     bars->abort = 0;
     fence_barrier_init();
@@ -197,7 +198,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (ok) umma_commit(&bars->acc_full);
       else *abort_flag = 1;
     }
-  } else if (warp == 10) {
+  } else if (warp == 2 + 4 * SPLIT) {
     // ------------------------------------------------------------ dQ store warp
     if (lane == 0) {
       for (int it = 0; it < iters && !*abort_flag; ++it) {
@@ -215,12 +216,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   } else {
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;                // which half of the columns this warp owns
+    const int part = (warp - 2) >> 2;                // which part of the columns this warp owns
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float log2e = 1.4426950408889634f;
     const uint64_t scale2 = pm::pack2(P.scale_log2, P.scale_log2);
-    constexpr int NC = BKV / 64;                     // 32-column chunks per warp
+    constexpr int NC = BKV / (32 * SPLIT);           // 32-column chunks of S / dP per warp
+    static_assert(NC >= 1, "at most four parts of 32 columns");
+    // 32-column chunks of dQ / dK / dV per warp; with fewer chunks than parts the last parts have none
+    constexpr int DC = (D / 32 >= SPLIT) ? (D / 32) / SPLIT : 1;
+    const bool owns_d = part * DC < D / 32;
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
       const uint32_t ph = it & 1;
@@ -244,11 +249,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       {
         uint32_t sv[NC][32];
 #pragma unroll
-        for (int cc = 0; cc < NC; ++cc) tmem_ld_32x32(tm_s + lane_addr + (half * NC + cc) * 32, sv[cc]);
+        for (int cc = 0; cc < NC; ++cc) tmem_ld_32x32(tm_s + lane_addr + (part * NC + cc) * 32, sv[cc]);
         tmem_ld_wait();
 #pragma unroll
         for (int cc = 0; cc < NC; ++cc) {
-          const int c = half * NC + cc;
+          const int c = part * NC + cc;
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             float a, b;
@@ -283,11 +288,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       {
         uint32_t dv[NC][32];
 #pragma unroll
-        for (int cc = 0; cc < NC; ++cc) tmem_ld_32x32(tm_dp + lane_addr + (half * NC + cc) * 32, dv[cc]);
+        for (int cc = 0; cc < NC; ++cc) tmem_ld_32x32(tm_dp + lane_addr + (part * NC + cc) * 32, dv[cc]);
         tmem_ld_wait();
 #pragma unroll
         for (int cc = 0; cc < NC; ++cc) {
-          const int c = half * NC + cc;
+          const int c = part * NC + cc;
           uint8_t* dc = sdS + (c / 2) * CHUNK_BYTES;
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -311,21 +316,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_after();
       // dQ tile -> fp32 staging (32-column slabs of [128 rows][128 B], 128B-swizzled); rows
       // past the end of the sequence hold exact zeros (their P and dS are zero)
-      {
-        uint32_t v[D / 64][32];
+      if (owns_d) {                                  // uniform per warp
+        uint32_t v[DC][32];
 #pragma unroll
-        for (int cc = 0; cc < D / 64; ++cc) tmem_ld_32x32(tm_dq + lane_addr + (half * (D / 64) + cc) * 32, v[cc]);
+        for (int cc = 0; cc < DC; ++cc) tmem_ld_32x32(tm_dq + lane_addr + (part * DC + cc) * 32, v[cc]);
         tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&bars->s_free);                  // the S columns may be overwritten
 #pragma unroll
-        for (int cc = 0; cc < D / 64; ++cc) {
-          uint8_t* slab = sP + (half * (D / 64) + cc) * (BQ * 128);
+        for (int cc = 0; cc < DC; ++cc) {
+          uint8_t* slab = sP + (part * DC + cc) * (BQ * 128);
 #pragma unroll
           for (int u = 0; u < 8; ++u)
             *reinterpret_cast<uint4*>(slab + swz(r, u)) =
                 make_uint4(v[cc][u * 4], v[cc][u * 4 + 1], v[cc][u * 4 + 2], v[cc][u * 4 + 3]);
         }
+      } else {
+        tc_fence_before();
+        mbar_arrive(&bars->s_free);
       }
       fence_proxy_async();
       mbar_arrive(&bars->dqs_full);
@@ -341,7 +349,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       T* dk_row = reinterpret_cast<T*>(P.dk) + row * P.dk_stride + kv_head * D;
       T* dv_row = reinterpret_cast<T*>(P.dv) + row * P.dv_stride + kv_head * D;
 #pragma unroll 1
-      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+      for (int c = part * DC; owns_d && c < (part + 1) * DC; ++c) {
         uint32_t a[32], b[32];
         tmem_ld_32x32(tm_dk + lane_addr + c * 32, a);
         tmem_ld_32x32(tm_dv + lane_addr + c * 32, b);
