@@ -1,0 +1,67 @@
+#!/usr/bin/env python
+"""Timeline of one CTA of the attention backward kernel.
+
+    python benchmarks/attn_timeline.py [--shape 13b] [--cta 0] [--it0 8]
+
+Runs the backward once with its timeline instantiation: the CTA ``--cta`` records
+clock64() at every hand-over point of eight consecutive (head, query block)
+iterations starting at ``--it0``.  Prints, per iteration, the clock of each point
+relative to the moment the product warp begins that iteration, and the mean
+iteration period.  The roles:
+
+    load   0 Q/dO buffer free
+    mma    0 begin | 1 Q/dO landed | 2 S columns free | 3 S, dP issued | 4 P written |
+           5 dV issued | 6 dS written | 7 dK, dQ issued
+    smx    0 begin | 1 S complete | 2 staging free | 3 S loaded | 4 P stored | 5 P signalled |
+           6 dP complete | 7 dP loaded | 8 dS stored | 9 dS signalled | 10 dQ complete |
+           11 dQ loaded, S released | 12 dQ staged, signalled     (first / last softmax warp)
+    red    0 staging full | 1 reduce-add has read the staging
+"""
+import argparse
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from flextrain_b200.ops.attention_backward import attention_backward  # noqa: E402
+from flextrain_b200.ops.attention_native import attention_forward  # noqa: E402
+
+SHAPES = {"small": (1, 4096, 16, 16, 128), "7b": (4, 4096, 32, 32, 128), "13b": (8, 4096, 40, 40, 128),
+          "70b": (2, 4096, 64, 8, 128)}
+ROLES = ("load", "mma", "smx-first", "smx-last", "red")
+SITES = (1, 8, 13, 13, 2)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="13b")
+    ap.add_argument("--cta", type=int, default=0)
+    ap.add_argument("--it0", type=int, default=8)
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    B, S, Hq, Hkv, D = SHAPES[args.shape]
+    torch.manual_seed(0)
+    mk = lambda h: torch.randn(B, S, h, D, device=dev, dtype=torch.bfloat16)  # noqa: E731
+    q, k, v, do = mk(Hq), mk(Hkv), mk(Hkv), mk(Hq)
+    scale = 1.0 / math.sqrt(D)
+    o, lse, _ = attention_forward(q, k, v, scale)
+    for _ in range(2):
+        attention_backward(q, k, v, o, lse, do, scale)
+    buf = torch.zeros(5 * 16 * 8, dtype=torch.int64, device=dev)
+    attention_backward(q, k, v, o, lse, do, scale, trace=(buf, args.cta, args.it0))
+    torch.cuda.synchronize()
+    t = buf.cpu().view(5, 16, 8)
+    base = t[1, 0]                                   # product warp begins the iteration
+    print(f"shape {args.shape} cta {args.cta} iterations {args.it0}..{args.it0 + 7}")
+    period = (base[1:] - base[:-1]).float()
+    print("iteration period (clocks):", [int(x) for x in period], "mean", int(period.mean()))
+    for r, name in enumerate(ROLES):
+        for j in range(8):
+            rel = [int(t[r, s_, j] - base[j]) for s_ in range(SITES[r])]
+            print(f"{name:9s} it+{j}: {rel}")
+
+
+if __name__ == "__main__":
+    main()

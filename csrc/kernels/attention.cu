@@ -37,10 +37,10 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
 // instead of 158).
 constexpr int kBwdSplit = 4;
 
-template <typename T, int D>
-int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-               const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
-  auto kern = attn_bwd_kernel<T, D, kBwdSplit>;
+template <typename T, int D, bool TRACE>
+int launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                 const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
+  auto kern = attn_bwd_kernel<T, D, kBwdSplit, TRACE>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::BYTES);
@@ -49,6 +49,16 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   const int num_blk = (P.S + BQ - 1) / BQ;
   kern<<<P.B * P.Hkv * num_blk, bwd_threads(kBwdSplit), BwdSmem<D>::BYTES, s>>>(tq, tk, tv, tdo, tdq, P);
   return 0;
+}
+
+// The timeline instantiation exists for bf16 at head size 128 only (the benchmark shapes).
+template <typename T, int D>
+int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+               const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value && D == 128) {
+    if (P.trace != nullptr) return launch_bwd_t<T, D, true>(tq, tk, tv, tdo, tdq, P, s);
+  }
+  return launch_bwd_t<T, D, false>(tq, tk, tv, tdo, tdq, P, s);
 }
 
 template <typename T>
@@ -105,15 +115,16 @@ int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   return 0;
 }
 
-// Gradients of ft_attn_fwd.  d_o is [B,S,Hq,D] with token stride do_stride; o and
+// Gradients of ft_attn_fwd (ft_attn_bwd), optionally with a timeline of one CTA: `trace` is
+// nullptr or a device buffer of 5 * 16 * 8 clock values (see BwdParams).  d_o is [B,S,Hq,D] with token stride do_stride; o and
 // lse are the forward's outputs.  Scratch provided by the caller: delta
 // [B*Hq*S] floats and dq_acc [B*S*Hq*D] floats (zeroed here).  dq / dk / dv are
 // written with their own token strides, so they may be views of one packed tensor.
-int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
-                int64_t v_stride, const void* o, const void* d_o, int64_t do_stride, const float* lse,
-                float* delta, float* dq_acc, void* dq, int64_t dq_stride, void* dk, int64_t dk_stride,
-                void* dv, int64_t dv_stride, int B, int S, int Hq, int Hkv, int D, float scale, int dtype,
-                cudaStream_t stream) {
+int ft_attn_bwd_traced(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                       int64_t v_stride, const void* o, const void* d_o, int64_t do_stride, const float* lse,
+                       float* delta, float* dq_acc, void* dq, int64_t dq_stride, void* dk, int64_t dk_stride,
+                       void* dv, int64_t dv_stride, int B, int S, int Hq, int Hkv, int D, float scale,
+                       int dtype, cudaStream_t stream, long long* trace, int trace_cta, int trace_it0) {
   if (D != 64 && D != 128) return -1;
   if (dtype != kBF16 && dtype != kF16) return -2;
   if (Hq % Hkv) return -3;
@@ -139,6 +150,7 @@ int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.B = B; P.S = S; P.Hq = Hq; P.Hkv = Hkv;
   P.scale = scale; P.scale_log2 = scale * 1.4426950408889634f;
   P.err = gemm::error_word(dev);
+  P.trace = trace; P.trace_cta = trace_cta; P.trace_it0 = trace_it0;
   if (dtype == kBF16) {
     launch_pre_post<__nv_bfloat16>(false, o, d_o, do_stride, delta, nullptr, nullptr, 0, B, S, Hq, D, scale, stream);
     if (D == 128) launch_bwd<__nv_bfloat16, 128>(tq, tk, tv, tdo, tdq, P, stream);
@@ -153,6 +165,16 @@ int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   FT_LAUNCHED(3);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;
+}
+
+int ft_attn_bwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                int64_t v_stride, const void* o, const void* d_o, int64_t do_stride, const float* lse,
+                float* delta, float* dq_acc, void* dq, int64_t dq_stride, void* dk, int64_t dk_stride,
+                void* dv, int64_t dv_stride, int B, int S, int Hq, int Hkv, int D, float scale, int dtype,
+                cudaStream_t stream) {
+  return ft_attn_bwd_traced(q, q_stride, k, k_stride, v, v_stride, o, d_o, do_stride, lse, delta, dq_acc, dq,
+                            dq_stride, dk, dk_stride, dv, dv_stride, B, S, Hq, Hkv, D, scale, dtype, stream,
+                            nullptr, 0, 0);
 }
 
 }  // extern "C"

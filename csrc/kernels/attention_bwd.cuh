@@ -54,6 +54,10 @@ struct BwdParams {
   int B, S, Hq, Hkv;
   float scale, scale_log2;
   int* err;
+  // timeline capture (TRACE instantiation only): clock64() of CTA trace_cta at the hand-over points
+  // of iterations trace_it0 .. trace_it0 + 7, as trace[(role * 16 + site) * 8 + iteration]
+  long long* trace;
+  int trace_cta, trace_it0;
 };
 
 // fp32 tile in shared memory (128B-swizzled [rows][32] slab) added into global memory
@@ -66,7 +70,7 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const vo
       : "memory");
 }
 
-template <typename T, int D, int SPLIT>
+template <typename T, int D, int SPLIT, bool TRACE = false>
 __global__ void __launch_bounds__(bwd_threads(SPLIT), 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -94,6 +98,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int q_blocks = num_blk - nb;                 // m = nb .. num_blk-1
   const int iters = group * q_blocks;
   const int kv_row0 = batch * P.S + nb * BKV;
+  // role: 0 loads, 1 products, 2 first softmax warp, 3 last softmax warp, 4 dQ reduce warp
+  auto stamp = [&](int role, int site, int it) {
+    if constexpr (TRACE) {
+      if ((int)blockIdx.x == P.trace_cta && it >= P.trace_it0 && it < P.trace_it0 + 8)
+        P.trace[(role * 16 + site) * 8 + (it - P.trace_it0)] = clock64();
+    }
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->kv_full, 1);
@@ -134,6 +145,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int m = nb + it % q_blocks;
         const int q_row0 = batch * P.S + m * BQ;
         if (!mbar_wait(&bars->qdo_empty, (it & 1) ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 401); break; }
+        stamp(0, 0, it);
         mbar_expect_tx(&bars->qdo_full, 2 * TILE);
         for (int c = 0; c < CHUNKS; ++c) {
           tma_load_2d(sQ + c * CHUNK_BYTES, &tmap_q, &bars->qdo_full, head * D + c * 64, q_row0);
@@ -153,8 +165,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (!ok) atomicCAS(P.err, 0, 402);
       for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
         const uint32_t ph = it & 1;
+        stamp(1, 0, it);
         if (!mbar_wait(&bars->qdo_full, ph)) { atomicCAS(P.err, 0, 403); ok = false; break; }
+        stamp(1, 1, it);
         if (!mbar_wait(&bars->s_free, ph ^ 1)) { atomicCAS(P.err, 0, 404); ok = false; break; }
+        stamp(1, 2, it);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -170,7 +185,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                    kk != 0);
         }
         umma_commit(&bars->dp_full);
+        stamp(1, 3, it);
         if (!mbar_wait(&bars->p_full, ph)) { atomicCAS(P.err, 0, 405); ok = false; break; }
+        stamp(1, 4, it);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {       // reduction over the 128 query rows
@@ -178,7 +195,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dv, make_smem_desc(aP + row_off, CHUNK_BYTES, 1024),
                    make_smem_desc(aDO + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
         }
+        stamp(1, 5, it);
         if (!mbar_wait(&bars->ds_full, ph)) { atomicCAS(P.err, 0, 409); ok = false; break; }
+        stamp(1, 6, it);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {
@@ -194,6 +213,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         umma_commit(&bars->qdo_empty);
         umma_commit(&bars->dq_full);
+        stamp(1, 7, it);
       }
       if (ok) umma_commit(&bars->acc_full);
       else *abort_flag = 1;
@@ -205,11 +225,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int head = kv_head * group + it / q_blocks;
         const int m = nb + it % q_blocks;
         if (!mbar_wait(&bars->dqs_full, it & 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 411); break; }
+        stamp(4, 0, it);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c)
           tma_reduce_add_2d(&tmap_dq, sP + c * (BQ * 128), head * D + c * 32, batch * P.S + m * BQ);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        stamp(4, 1, it);
         mbar_arrive(&bars->stage_free);
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -227,6 +249,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     constexpr int DC = (D / 32 >= SPLIT) ? (D / 32) / SPLIT : 1;
     const bool owns_d = part * DC < D / 32;
     bool ok = true;
+    // the first and the last softmax warp record the timeline
+    const int trole = (lane == 0 && warp == 2) ? 2 : ((lane == 0 && warp == 1 + 4 * SPLIT) ? 3 : -1);
+    auto sstamp = [&](int site, int it) { if (TRACE && trole >= 0) stamp(trole, site, it); };
     for (int it = 0; it < iters; ++it) {
       const uint32_t ph = it & 1;
       const int head = kv_head * group + it / q_blocks;
@@ -241,16 +266,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint64_t neg_delta2 = pm::pack2(neg_delta, neg_delta);
       const bool diag = (m == nb);
       float p[NC][32];
+      sstamp(0, it);
       // ---- P as soon as S is complete
       if (!mbar_wait(&bars->s_full, ph)) { atomicCAS(P.err, 0, 406); ok = false; break; }
+      sstamp(1, it);
       // the P / dS tiles double as the dQ staging area: the previous reduce must have read it
       if (it > 0 && !mbar_wait(&bars->stage_free, (it - 1) & 1)) { atomicCAS(P.err, 0, 412); ok = false; break; }
+      sstamp(2, it);
       tc_fence_after();
       {
         uint32_t sv[NC][32];
 #pragma unroll
         for (int cc = 0; cc < NC; ++cc) tmem_ld_32x32(tm_s + lane_addr + (part * NC + cc) * 32, sv[cc]);
         tmem_ld_wait();
+        sstamp(3, it);
 #pragma unroll
         for (int cc = 0; cc < NC; ++cc) {
           const int c = part * NC + cc;
@@ -279,17 +308,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
         }
       }
+      sstamp(4, it);
       tc_fence_before();
       fence_proxy_async();
       mbar_arrive(&bars->p_full);
+      sstamp(5, it);
       // ---- dS once dP is complete
       if (!mbar_wait(&bars->dp_full, ph)) { atomicCAS(P.err, 0, 410); ok = false; break; }
+      sstamp(6, it);
       tc_fence_after();
       {
         uint32_t dv[NC][32];
 #pragma unroll
         for (int cc = 0; cc < NC; ++cc) tmem_ld_32x32(tm_dp + lane_addr + (part * NC + cc) * 32, dv[cc]);
         tmem_ld_wait();
+        sstamp(7, it);
 #pragma unroll
         for (int cc = 0; cc < NC; ++cc) {
           const int c = part * NC + cc;
@@ -309,10 +342,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
         }
       }
+      sstamp(8, it);
       tc_fence_before();
       fence_proxy_async();
       mbar_arrive(&bars->ds_full);
+      sstamp(9, it);
       if (!mbar_wait(&bars->dq_full, ph)) { atomicCAS(P.err, 0, 407); ok = false; break; }
+      sstamp(10, it);
       tc_fence_after();
       // dQ tile -> fp32 staging (32-column slabs of [128 rows][128 B], 128B-swizzled); rows
       // past the end of the sequence hold exact zeros (their P and dS are zero)
@@ -323,6 +359,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&bars->s_free);                  // the S columns may be overwritten
+        sstamp(11, it);
 #pragma unroll
         for (int cc = 0; cc < DC; ++cc) {
           uint8_t* slab = sP + (part * DC + cc) * (BQ * 128);
@@ -337,6 +374,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       fence_proxy_async();
       mbar_arrive(&bars->dqs_full);
+      sstamp(12, it);
     }
     if (ok && !mbar_wait(&bars->acc_full, 0)) { atomicCAS(P.err, 0, 408); ok = false; }
     if (ok) {

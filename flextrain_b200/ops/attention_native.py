@@ -25,6 +25,9 @@ def _lib():
                                         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                         c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                                         c_int, c_float, c_int, c_void_p]
+        if hasattr(lib, "ft_attn_bwd_traced"):
+            lib.ft_attn_bwd_traced.argtypes = list(lib.ft_attn_bwd.argtypes) + [c_void_p, c_int, c_int]
+            lib.ft_attn_bwd_traced.restype = c_int
         _DECLARED = True
     return lib
 
