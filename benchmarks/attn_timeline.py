@@ -9,13 +9,14 @@ iterations starting at ``--it0``.  Prints, per iteration, the clock of each poin
 relative to the moment the product warp begins that iteration, and the mean
 iteration period.  The roles:
 
-    load   0 Q/dO buffer free
-    mma    0 begin | 1 Q/dO landed | 2 S columns free | 3 S, dP issued | 4 P written |
+    load   0 dO buffer free | 1 Q buffer free
+    mma    0 begin | 1 Q landed | 2 S columns free | 3 S, dP issued | 4 P written |
            5 dV issued | 6 dS written | 7 dK, dQ issued
-    smx    0 begin | 1 S complete | 2 staging free | 3 S loaded | 4 P stored | 5 P signalled |
-           6 dP complete | 7 dP loaded | 8 dS stored | 9 dS signalled | 10 dQ complete |
-           11 dQ loaded, S released | 12 dQ staged, signalled     (first / last softmax warp)
-    red    0 staging full | 1 reduce-add has read the staging
+    smx    0 begin | 1 S complete | 2 dS tile free again (after 6) | 3 S loaded | 4 P stored |
+           5 P signalled | 6 dP complete | 7 dP loaded | 8 dS stored | 9 dS signalled |
+           10 dQ complete | 11 dQ loaded, S released | 12 dQ staged, signalled
+           (first / last softmax warp)
+    red    0 dQ slabs full | 1 slabs inside the dS tile read | 2 all slabs read
 """
 import argparse
 import math
@@ -28,10 +29,10 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from flextrain_b200.ops.attention_backward import attention_backward  # noqa: E402
 from flextrain_b200.ops.attention_native import attention_forward  # noqa: E402
 
-SHAPES = {"small": (1, 4096, 16, 16, 128), "7b": (4, 4096, 32, 32, 128), "13b": (8, 4096, 40, 40, 128),
+SHAPES = {"one": (1, 4096, 1, 1, 128), "four": (1, 4096, 4, 4, 128), "small": (1, 4096, 16, 16, 128), "7b": (4, 4096, 32, 32, 128), "13b": (8, 4096, 40, 40, 128),
           "70b": (2, 4096, 64, 8, 128)}
 ROLES = ("load", "mma", "smx-first", "smx-last", "red")
-SITES = (1, 8, 13, 13, 2)
+SITES = (2, 8, 13, 13, 3)
 
 
 def main():

@@ -11,9 +11,11 @@
 //            once when it is written and dQ by the conversion pass.
 //   MMA      dV += P^T dO as soon as P is written (dS is still being computed),
 //            dK += dS^T Q (both accumulated in TMEM over the whole walk),
-//            dQ_m = dS K                    -> TMEM -> fp32 staging in shared memory (the P / dS
-//            tiles, idle by then) -> one TMA reduce-add per 32-column slab into dq_acc,
-//            issued by a dedicated warp so it overlaps the next block's S / dP
+//            dQ_m = dS K                    -> TMEM -> fp32 slabs in shared memory (half of them in
+//            memory of their own, half in the dS tile, idle by then) -> one TMA reduce-add per
+//            32-column slab into dq_acc, issued by a dedicated warp; nothing of the next block
+//            waits for it except the next dS, which needs its tile back
+// dO is released for the next load as soon as dV is complete and Q as soon as dK is.
 // The same shared-memory bytes serve as K-major operand (reduction over the 64
 // contiguous columns) and as MN-major operand (reduction over the rows), so no
 // tile is ever transposed.  dK / dV are written once at the end; dq_acc is
@@ -35,12 +37,18 @@ template <int D>
 struct BwdSmem {
   static constexpr int TILE = BQ * D * 2;
   static constexpr int P_BYTES = BQ * BKV * 2;
-  static constexpr int BYTES = 4 * TILE + 2 * P_BYTES + 1024 + 256;
+  // dQ leaves through fp32 slabs of [128 rows][32 columns] (16 KB each).  At head size 128 the
+  // first two have shared memory of their own and the last two reuse the dS tile, which is idle
+  // between the dQ product and the next dS; at head size 64 both slabs have their own.
+  static constexpr int SLAB = BQ * 128;
+  static constexpr int OWN_SLABS = 2;
+  static constexpr int BYTES = 4 * TILE + 2 * P_BYTES + OWN_SLABS * SLAB + 1024 + 256;
 };
 
 struct BwdBars {
-  uint64_t kv_full, qdo_full, qdo_empty, s_full, dp_full, p_full, ds_full, dq_full, s_free, acc_full;
-  uint64_t dqs_full, stage_free;
+  uint64_t kv_full, q_full, do_full, q_empty, do_empty, s_full, dp_full, p_full, ds_full, dq_full, s_free,
+      acc_full;
+  uint64_t dqs_full, own_free, shared_free;
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -70,7 +78,9 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const vo
       : "memory");
 }
 
-template <typename T, int D, int SPLIT, bool TRACE = false>
+// POLY: which of every eight pairs of P values take the polynomial 2^x (bit j = pair j); the
+// rest use the special-function unit, so both pipes work on one score row.
+template <typename T, int D, int SPLIT, bool TRACE = false, unsigned POLY = 0xAAu>
 __global__ void __launch_bounds__(bwd_threads(SPLIT), 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -87,7 +97,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* sdO = sQ + TILE;
   uint8_t* sP = sdO + TILE;
   uint8_t* sdS = sP + BwdSmem<D>::P_BYTES;
-  BwdBars* bars = reinterpret_cast<BwdBars*>(sdS + BwdSmem<D>::P_BYTES);
+  uint8_t* sStage = sdS + BwdSmem<D>::P_BYTES;
+  BwdBars* bars = reinterpret_cast<BwdBars*>(sStage + BwdSmem<D>::OWN_SLABS * BwdSmem<D>::SLAB);
+  constexpr int OWN_SLABS = BwdSmem<D>::OWN_SLABS;
+  // fp32 slab c of the dQ tile
+  auto slab_ptr = [&](int c) -> uint8_t* {
+    return c < OWN_SLABS ? sStage + c * BwdSmem<D>::SLAB : sdS + (c - OWN_SLABS) * BwdSmem<D>::SLAB;
+  };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_blk = (P.S + BQ - 1) / BQ;
@@ -108,8 +124,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->kv_full, 1);
-    mbar_init(&bars->qdo_full, 1);
-    mbar_init(&bars->qdo_empty, 1);
+    mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->do_full, 1);
+    mbar_init(&bars->q_empty, 1);
+    mbar_init(&bars->do_empty, 1);
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->dp_full, 1);
     mbar_init(&bars->p_full, 128 * SPLIT);
@@ -118,7 +136,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars->s_free, 128 * SPLIT);
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->dqs_full, 128 * SPLIT);
-    mbar_init(&bars->stage_free, 1);
+    mbar_init(&bars->own_free, 1);
+    mbar_init(&bars->shared_free, 1);
     bars->abort = 0;
     fence_barrier_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
@@ -144,13 +163,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int head = kv_head * group + it / q_blocks;
         const int m = nb + it % q_blocks;
         const int q_row0 = batch * P.S + m * BQ;
-        if (!mbar_wait(&bars->qdo_empty, (it & 1) ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 401); break; }
+        // dO is released first (after the dV product), Q after the dK product
+        if (!mbar_wait(&bars->do_empty, (it & 1) ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 401); break; }
         stamp(0, 0, it);
-        mbar_expect_tx(&bars->qdo_full, 2 * TILE);
-        for (int c = 0; c < CHUNKS; ++c) {
-          tma_load_2d(sQ + c * CHUNK_BYTES, &tmap_q, &bars->qdo_full, head * D + c * 64, q_row0);
-          tma_load_2d(sdO + c * CHUNK_BYTES, &tmap_do, &bars->qdo_full, head * D + c * 64, q_row0);
-        }
+        mbar_expect_tx(&bars->do_full, TILE);
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_2d(sdO + c * CHUNK_BYTES, &tmap_do, &bars->do_full, head * D + c * 64, q_row0);
+        if (!mbar_wait(&bars->q_empty, (it & 1) ^ 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 413); break; }
+        stamp(0, 1, it);
+        mbar_expect_tx(&bars->q_full, TILE);
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_2d(sQ + c * CHUNK_BYTES, &tmap_q, &bars->q_full, head * D + c * 64, q_row0);
       }
     }
   } else if (warp == 1) {
@@ -166,7 +189,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
         const uint32_t ph = it & 1;
         stamp(1, 0, it);
-        if (!mbar_wait(&bars->qdo_full, ph)) { atomicCAS(P.err, 0, 403); ok = false; break; }
+        if (!mbar_wait(&bars->q_full, ph)) { atomicCAS(P.err, 0, 403); ok = false; break; }
         stamp(1, 1, it);
         if (!mbar_wait(&bars->s_free, ph ^ 1)) { atomicCAS(P.err, 0, 404); ok = false; break; }
         stamp(1, 2, it);
@@ -178,6 +201,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                    kk != 0);
         }
         umma_commit(&bars->s_full);
+        if (!mbar_wait(&bars->do_full, ph)) { atomicCAS(P.err, 0, 414); ok = false; break; }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
@@ -195,6 +219,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dv, make_smem_desc(aP + row_off, CHUNK_BYTES, 1024),
                    make_smem_desc(aDO + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
         }
+        umma_commit(&bars->do_empty);
         stamp(1, 5, it);
         if (!mbar_wait(&bars->ds_full, ph)) { atomicCAS(P.err, 0, 409); ok = false; break; }
         stamp(1, 6, it);
@@ -205,13 +230,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dk, make_smem_desc(aDS + row_off, CHUNK_BYTES, 1024),
                    make_smem_desc(aQ + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
         }
+        umma_commit(&bars->q_empty);
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {      // reduction over the 128 kv rows
           const uint32_t a_off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
           umma_f16(tm_dq, make_smem_desc(aDS + a_off, 16, 1024),
                    make_smem_desc(aK + kk * 2048, CHUNK_BYTES, 1024), id_q, kk != 0);
         }
-        umma_commit(&bars->qdo_empty);
         umma_commit(&bars->dq_full);
         stamp(1, 7, it);
       }
@@ -226,13 +251,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int m = nb + it % q_blocks;
         if (!mbar_wait(&bars->dqs_full, it & 1)) { *abort_flag = 1; atomicCAS(P.err, 0, 411); break; }
         stamp(4, 0, it);
+        // the slabs inside the dS tile first: the next dS waits for them to be read
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c)
-          tma_reduce_add_2d(&tmap_dq, sP + c * (BQ * 128), head * D + c * 32, batch * P.S + m * BQ);
+        for (int c = OWN_SLABS; c < D / 32; ++c)
+          tma_reduce_add_2d(&tmap_dq, slab_ptr(c), head * D + c * 32, batch * P.S + m * BQ);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < OWN_SLABS && c < D / 32; ++c)
+          tma_reduce_add_2d(&tmap_dq, slab_ptr(c), head * D + c * 32, batch * P.S + m * BQ);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         stamp(4, 1, it);
-        mbar_arrive(&bars->stage_free);
+        mbar_arrive(&bars->shared_free);
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        stamp(4, 2, it);
+        mbar_arrive(&bars->own_free);
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
@@ -270,9 +303,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ---- P as soon as S is complete
       if (!mbar_wait(&bars->s_full, ph)) { atomicCAS(P.err, 0, 406); ok = false; break; }
       sstamp(1, it);
-      // the P / dS tiles double as the dQ staging area: the previous reduce must have read it
-      if (it > 0 && !mbar_wait(&bars->stage_free, (it - 1) & 1)) { atomicCAS(P.err, 0, 412); ok = false; break; }
-      sstamp(2, it);
       tc_fence_after();
       {
         uint32_t sv[NC][32];
@@ -288,8 +318,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             float a, b;
             pm::unpack2(pm::fma2(pm::pack2(__uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1])), scale2,
                                  neg_lse22), a, b);
-            p[cc][i] = pm::ex2(a);
-            p[cc][i + 1] = pm::ex2(b);
+            if ((POLY >> ((i >> 1) & 7)) & 1u) {
+              pm::ex2_poly2(a, b, p[cc][i], p[cc][i + 1]);
+            } else {
+              p[cc][i] = pm::ex2(a);
+              p[cc][i + 1] = pm::ex2(b);
+            }
           }
           if (diag) {
 #pragma unroll
@@ -316,6 +350,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ---- dS once dP is complete
       if (!mbar_wait(&bars->dp_full, ph)) { atomicCAS(P.err, 0, 410); ok = false; break; }
       sstamp(6, it);
+      // part of the previous dQ tile left through the dS tile: its reduce-add must have read it
+      if (it > 0 && !mbar_wait(&bars->shared_free, (it - 1) & 1)) { atomicCAS(P.err, 0, 412); ok = false; break; }
+      sstamp(2, it);
       tc_fence_after();
       {
         uint32_t dv[NC][32];
@@ -360,9 +397,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tc_fence_before();
         mbar_arrive(&bars->s_free);                  // the S columns may be overwritten
         sstamp(11, it);
+        if (it > 0 && !mbar_wait(&bars->own_free, (it - 1) & 1)) { atomicCAS(P.err, 0, 415); ok = false; break; }
 #pragma unroll
         for (int cc = 0; cc < DC; ++cc) {
-          uint8_t* slab = sP + (part * DC + cc) * (BQ * 128);
+          uint8_t* slab = slab_ptr(part * DC + cc);
 #pragma unroll
           for (int u = 0; u < 8; ++u)
             *reinterpret_cast<uint4*>(slab + swz(r, u)) =

@@ -41,7 +41,10 @@ struct Fwd2Bars {
   uint32_t abort;
 };
 
-template <typename T, int D>
+// POLY: which of every eight pairs of probabilities take the polynomial 2^x of packed_math.cuh
+// (bit j = pair j) instead of the special-function unit, whose 16 results per clock would
+// otherwise take as long per K/V block as the four products on the tensor pipe.
+template <typename T, int D, unsigned POLY = 0xAAu>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams P) {
@@ -240,8 +243,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           float a, b;
           pm::unpack2(pm::fma2(pm::pack2(__uint_as_float(v[c][2 * i]), __uint_as_float(v[c][2 * i + 1])), scale2,
                                neg_m2), a, b);
-          a = pm::ex2(a);
-          b = pm::ex2(b);
+          if ((POLY >> (i & 7)) & 1u) {
+            pm::ex2_poly2(a, b, a, b);
+          } else {
+            a = pm::ex2(a);
+            b = pm::ex2(b);
+          }
           ls[c] = pm::add2(ls[c], pm::pack2(a, b));
           pk[i] = pm::cvt2<T>(a, b);
         }
