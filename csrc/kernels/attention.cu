@@ -19,10 +19,10 @@ static_assert(Fwd2Smem<128>::BYTES <= kMaxDynamicSmem && BwdSmem<128>::BYTES <= 
               "an attention kernel outgrew the shared memory of an SM");
 
 // Forward: one CTA per pair of query blocks.
-template <typename T, int D, unsigned POLY = 0xAAu>
-int launch_fwd2_p(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
-                  cudaStream_t s) {
-  auto kern = attn_fwd2_kernel<T, D, POLY>;
+template <typename T, int D>
+int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
+                cudaStream_t s) {
+  auto kern = attn_fwd2_kernel<T, D>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<D>::BYTES);
@@ -33,26 +33,15 @@ int launch_fwd2_p(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMa
   return 0;
 }
 
-template <typename T, int D>
-int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
-                cudaStream_t s) {
-  if constexpr (std::is_same<T, __nv_bfloat16>::value && D == 128) {
-    static const int poly = std::getenv("FT_EXP_POLY") ? std::atoi(std::getenv("FT_EXP_POLY")) : 4;
-    if (poly == 0) return launch_fwd2_p<T, D, 0x00u>(tq, tk, tv, P, s);
-    if (poly == 3) return launch_fwd2_p<T, D, 0x4Au>(tq, tk, tv, P, s);
-    if (poly == 5) return launch_fwd2_p<T, D, 0xB5u>(tq, tk, tv, P, s);
-  }
-  return launch_fwd2_p<T, D>(tq, tk, tv, P, s);
-}
-
 // Backward: four threads per score row (2.6 % faster than two at the 13B shape, 96 registers
-// instead of 158).
+// instead of 158); every other pair of probabilities takes the polynomial 2^x (4.524 ms against
+// 4.752 ms with none and 4.635 ms with five of eight at the 13B shape).
 constexpr int kBwdSplit = 4;
 
-template <typename T, int D, bool TRACE, unsigned POLY = 0xAAu>
+template <typename T, int D, bool TRACE>
 int launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                  const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
-  auto kern = attn_bwd_kernel<T, D, kBwdSplit, TRACE, POLY>;
+  auto kern = attn_bwd_kernel<T, D, kBwdSplit, TRACE>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::BYTES);
@@ -69,10 +58,6 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
                const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
   if constexpr (std::is_same<T, __nv_bfloat16>::value && D == 128) {
     if (P.trace != nullptr) return launch_bwd_t<T, D, true>(tq, tk, tv, tdo, tdq, P, s);
-    static const int poly = std::getenv("FT_EXP_POLY") ? std::atoi(std::getenv("FT_EXP_POLY")) : 4;
-    if (poly == 0) return launch_bwd_t<T, D, false, 0x00u>(tq, tk, tv, tdo, tdq, P, s);
-    if (poly == 3) return launch_bwd_t<T, D, false, 0x4Au>(tq, tk, tv, tdo, tdq, P, s);
-    if (poly == 5) return launch_bwd_t<T, D, false, 0xB5u>(tq, tk, tv, tdo, tdq, P, s);
   }
   return launch_bwd_t<T, D, false>(tq, tk, tv, tdo, tdq, P, s);
 }

@@ -42,9 +42,10 @@ struct Fwd2Bars {
 };
 
 // POLY: which of every eight pairs of probabilities take the polynomial 2^x of packed_math.cuh
-// (bit j = pair j) instead of the special-function unit, whose 16 results per clock would
-// otherwise take as long per K/V block as the four products on the tensor pipe.
-template <typename T, int D, unsigned POLY = 0xAAu>
+// (bit j = pair j) instead of the special-function unit.  None by default: with one thread per
+// score row the extra instructions cost more than the unit's 16 results per clock (13B shape:
+// 1.466 ms with none, 1.553 ms with four of eight, 1.699 ms with five).
+template <typename T, int D, unsigned POLY = 0x00u>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams P) {
