@@ -13,7 +13,9 @@ stays small and the step is barely disturbed) and prints
     was running (union over streams), and the time during which the compute stream's
     kernels were running: ``span - busy`` is what the GPU spent waiting;
   * busy time per stream;
-  * the kernels with the largest total duration (count, total, mean);
+  * the kernels with the largest total duration (count, total, mean), and for each the
+    median duration of the calls that ran alone and of those that overlapped work of
+    another stream (copies, the optimizer's kernels);
   * the longest idle gaps of the union timeline with the work on either side.
 
 Times from a profiled step explain a number, they are not one: quote ``bench.py``.
@@ -61,6 +63,24 @@ def summarize_trace(events, top=20, gaps=12):
     busy += cur_e - cur_s
     idle.sort(reverse=True)
     main_stream = max(per_stream, key=per_stream.get)
+    # per kernel name: durations of the calls that ran alone and of those that shared the GPU with
+    # work of another stream for at least a tenth of their time
+    stream_of = lambda e: str(e.get("args", {}).get("stream", "?"))   # noqa: E731
+    alone, shared = defaultdict(list), defaultdict(list)
+    others = [(e["ts"], e["ts"] + e["dur"], stream_of(e)) for e in dev]
+    lo = 0
+    for e in dev:
+        s0, s1, st = e["ts"], e["ts"] + e["dur"], stream_of(e)
+        while lo < len(others) and others[lo][1] < s0 - 5e5:        # nothing runs for half a second
+            lo += 1
+        ov = 0.0
+        for a, b, ost in others[lo:]:
+            if a >= s1:
+                break
+            if ost != st:
+                ov += max(0.0, min(b, s1) - max(a, s0))
+        (shared if ov > 0.1 * e["dur"] else alone)[e["name"]].append(e["dur"])
+    med = lambda v: sorted(v)[len(v) // 2] if v else None             # noqa: E731
     ms = 1e-3
     short = lambda n: n if len(n) <= 90 else n[:87] + "..."          # noqa: E731
     return {
@@ -70,7 +90,10 @@ def summarize_trace(events, top=20, gaps=12):
         "idle_ms": (t1 - t0 - busy) * ms,
         "busiest_stream": main_stream,
         "per_stream_busy_ms": {k: v * ms for k, v in sorted(per_stream.items(), key=lambda kv: -kv[1])},
-        "top_kernels": [{"name": short(n), "count": c, "total_ms": t * ms, "mean_us": t / c}
+        "top_kernels": [{"name": short(n), "count": c, "total_ms": t * ms, "mean_us": t / c,
+                         "alone": len(alone[n]), "alone_median_us": med(alone[n]),
+                         "alone_min_us": min(alone[n]) if alone[n] else None,
+                         "shared": len(shared[n]), "shared_median_us": med(shared[n])}
                         for n, (c, t) in sorted(by_name.items(), key=lambda kv: -kv[1][1])[:top]],
         "idle_gaps": [{"gap_us": g, "at_ms": at * ms, "after": short(a), "before": short(b)}
                       for g, at, a, b in idle[:gaps]],
@@ -87,9 +110,13 @@ def format_summary(s) -> str:
            f"({100 * s['idle_ms'] / s['span_ms']:.1f} %), of which {s['idle_in_gaps_over_50us_ms']:.1f} ms "
            f"in gaps over 50 us ({s['idle_gap_count']} gaps)"]
     out.append("busy per stream (ms): " + ", ".join(f"{k}: {v:.1f}" for k, v in s["per_stream_busy_ms"].items()))
-    out.append("top kernels by total time:")
+    out.append("top kernels by total time (calls that ran alone: count, min, median; calls that shared the GPU "
+               "with another stream: count, median):")
+    us = lambda v: "-" if v is None else f"{v:.0f}"                   # noqa: E731
     for k in s["top_kernels"]:
-        out.append(f"  {k['total_ms']:9.2f} ms  x{k['count']:<6d} {k['mean_us']:9.1f} us  {k['name']}")
+        out.append(f"  {k['total_ms']:9.2f} ms  x{k['count']:<6d} {k['mean_us']:9.1f} us  "
+                   f"[alone x{k.get('alone', 0)} min {us(k.get('alone_min_us'))} med {us(k.get('alone_median_us'))} | "
+                   f"shared x{k.get('shared', 0)} med {us(k.get('shared_median_us'))}]  {k['name']}")
     out.append("longest idle gaps:")
     for g in s["idle_gaps"]:
         out.append(f"  {g['gap_us']:9.1f} us at +{g['at_ms']:8.1f} ms  after [{g['after']}]  before [{g['before']}]")
