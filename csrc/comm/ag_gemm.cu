@@ -199,7 +199,7 @@ int ft_ag_gemm(int world, int rank, const void* const* buf_ptrs, uint32_t* const
   const int nt = (N + P_BN - 1) / P_BN;
   if (nt > kReadyWords) return -5;
   const int sms = sm_count(dev);
-  GatherArgs G;
+  GatherArgs G{};
   fill_gather(G, world, rank, buf_ptrs, flags, seq, start_slot, done_slot, 0, dev);
   for (int r = 0; r < world; ++r)
     G.w_peer[r] = reinterpret_cast<const uint8_t*>(buf_ptrs[r]) + w_off_bytes;
@@ -246,7 +246,7 @@ int ft_peer_gather_range(int world, int rank, const void* const* buf_ptrs, uint3
   cudaGetDevice(&dev);
   if (ensure_state(dev)) return -4;
   if (num_copiers < 1) num_copiers = 1;
-  GatherArgs G;
+  GatherArgs G{};
   fill_gather(G, world, rank, buf_ptrs, flags, seq, start_slot, done_slot, num_copiers, dev);
   for (int r = 0; r < world; ++r)
     G.w_peer[r] = reinterpret_cast<const uint8_t*>(buf_ptrs[r]) + range_lo;

@@ -68,8 +68,9 @@ void launch_pre_post(bool post, const void* o, const void* d_o, int64_t do_strid
                      float scale, cudaStream_t s) {
   if (!post) {
     const int64_t rows = (int64_t)B * S * Hq;
-    attn_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const T*)o, (const T*)d_o, do_stride,
-                                                                   delta, B, S, Hq, D);
+    const int per_block = kDeltaRowsPerBlock(D);
+    attn_delta_kernel<T><<<(unsigned)((rows + per_block - 1) / per_block), 256, 0, s>>>(
+        (const T*)o, (const T*)d_o, do_stride, delta, B, S, Hq, D);
   } else {
     const int64_t tokens = (int64_t)B * S;
     attn_dq_cast_kernel<T><<<grid_for(tokens * (Hq * D / 8), 256), 256, 0, s>>>(dq_acc, (T*)dq, dq_stride,

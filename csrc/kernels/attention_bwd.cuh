@@ -453,30 +453,46 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
-// delta[b,h,s] = sum_d dO * O   (one warp per (token, head) row)
+// delta[b,h,s] = sum_d dO * O.  D / 8 lanes per (head, token) row (16 bytes of each tensor per
+// lane), so a warp covers 32 * 8 / D rows at once, and every thread does that for two rows with
+// all four loads in flight.  Rows are numbered in the order of delta ([b, h, s]), so neighbouring
+// lanes write neighbouring floats; the reads are whole 2 * D-byte pieces either way.  D in {64, 128}.
+constexpr int kDeltaRowsPerBlock(int D) { return 2 * 8 * (256 / D); }   // 2 passes x 8 warps x rows per warp
+
 template <typename T>
 __global__ void __launch_bounds__(256) attn_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
                                                          int64_t do_stride, float* __restrict__ delta,
                                                          int B, int S, int Hq, int D) {
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= (int64_t)B * S * Hq) return;
-  const int64_t tok = row / Hq;
-  const int h = (int)(row % Hq);
-  const T* op = o + row * D;
-  const T* dp = d_o + tok * do_stride + (int64_t)h * D;
-  float acc = 0.f;
-  for (int i = lane * 8; i < D; i += 256) {
-    float a[8], b[8];
-    unpack8<T>(*reinterpret_cast<const uint4*>(op + i), a);
-    unpack8<T>(*reinterpret_cast<const uint4*>(dp + i), b);
+  const int lpr = D / 8, rpw = 32 / lpr;             // lanes per row, rows per warp
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % lpr;
+  const int64_t rows = (int64_t)B * S * Hq;
+  const int64_t row0 = (int64_t)blockIdx.x * (2 * 8 * rpw) + warp * rpw + lane / lpr;
+  float acc[2];
+  uint4 a[2], b[2];
+  bool ok[2];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc += a[k] * b[k];
+  for (int p = 0; p < 2; ++p) {
+    const int64_t row = row0 + (int64_t)p * 8 * rpw;
+    ok[p] = row < rows;
+    const int64_t r = ok[p] ? row : 0;
+    const int64_t bh = r / S;
+    const int64_t tok = (bh / Hq) * S + r % S;
+    const int h = (int)(bh % Hq);
+    a[p] = *reinterpret_cast<const uint4*>(o + (tok * Hq + h) * D + sub * 8);
+    b[p] = *reinterpret_cast<const uint4*>(d_o + tok * do_stride + (int64_t)h * D + sub * 8);
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
-    const int64_t b_idx = tok / S, s_idx = tok % S;
-    delta[(b_idx * Hq + h) * S + s_idx] = acc;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    float x[8], y[8];
+    unpack8<T>(a[p], x);
+    unpack8<T>(b[p], y);
+    acc[p] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[p] += x[k] * y[k];
+    for (int off = lpr / 2; off > 0; off >>= 1) acc[p] += __shfl_xor_sync(0xffffffffu, acc[p], off);
+    const int64_t row = row0 + (int64_t)p * 8 * rpw;
+    if (ok[p] && sub == 0) delta[row] = acc[p];
   }
 }
 

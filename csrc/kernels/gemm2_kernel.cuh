@@ -393,6 +393,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else {
     // ---------------------------------------------------------- epilogue (both CTAs)
     const int quarter = warp & 3;
+    const void* add_src = gather.add_src ? gather.add_src : C;
+    const int64_t add_ld = gather.add_src ? gather.add_ld : ldc;
     int it = 0;
     for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++it) {
       int mb, nb;
@@ -415,7 +417,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        store_chunk<T, MODE>(r, C, ldc, row, col0, M, N);
+        store_chunk<T, MODE>(r, C, ldc, row, col0, M, N, add_src, add_ld);
       }
       tc_fence_before();
       __syncwarp();

@@ -44,6 +44,10 @@ struct GatherArgs {
   int64_t w_off_bytes;
   int64_t w_bytes;
   int group_m;             // CTA-pair GEMM, with or without gather: row blocks per group of the tile walk (0: GROUP_M)
+  // accumulating epilogues (kAcc16 / kAcc32), with or without gather: the matrix that is added to
+  // the product, of C's type and shape with row stride add_ld; nullptr = C itself (in-place +=)
+  const void* add_src;
+  int64_t add_ld;
 };
 
 struct Barriers {
@@ -69,29 +73,34 @@ __device__ __forceinline__ void tile_coords(int t, int mt, int nt, int& mb, int&
 
 template <typename T, int MODE>
 __device__ __forceinline__ void store_chunk(const uint32_t (&acc)[32], void* C, int64_t ldc, int row,
-                                            int col0, int M, int N) {
+                                            int col0, int M, int N, const void* R = nullptr,
+                                            int64_t ldr = 0) {
   if (row >= M) return;
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
   if constexpr (MODE == kStore32 || MODE == kAcc32) {
     float* p = reinterpret_cast<float*>(C) + (int64_t)row * ldc + col0;
-    if (col0 + 32 <= N && (ldc % 4 == 0)) {
+    const float* rp = p;                             // what an accumulating mode adds to the product
+    if constexpr (MODE == kAcc32) rp = reinterpret_cast<const float*>(R) + (int64_t)row * ldr + col0;
+    if (col0 + 32 <= N && (ldc % 4 == 0) && (MODE != kAcc32 || ldr % 4 == 0)) {
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         if constexpr (MODE == kAcc32) {
-          float4 old = reinterpret_cast<float4*>(p)[q];
+          float4 old = reinterpret_cast<const float4*>(rp)[q];
           o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
         }
         reinterpret_cast<float4*>(p)[q] = o;
       }
     } else {
-      for (int j = 0; j < 32 && col0 + j < N; ++j) p[j] = (MODE == kAcc32 ? p[j] : 0.f) + v[j];
+      for (int j = 0; j < 32 && col0 + j < N; ++j) p[j] = (MODE == kAcc32 ? rp[j] : 0.f) + v[j];
     }
   } else {
     T* p = reinterpret_cast<T*>(C) + (int64_t)row * ldc + col0;
-    if (col0 + 32 <= N && (ldc % 8 == 0)) {
+    const T* rp = p;
+    if constexpr (MODE == kAcc16) rp = reinterpret_cast<const T*>(R) + (int64_t)row * ldr + col0;
+    if (col0 + 32 <= N && (ldc % 8 == 0) && (MODE != kAcc16 || ldr % 8 == 0)) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         float o[8];
@@ -99,7 +108,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&acc)[32], void* C, 
         for (int j = 0; j < 8; ++j) o[j] = v[8 * q + j];
         if constexpr (MODE == kAcc16) {
           float old[8];
-          unpack8<T>(reinterpret_cast<uint4*>(p)[q], old);
+          unpack8<T>(reinterpret_cast<const uint4*>(rp)[q], old);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += old[j];
         }
@@ -107,7 +116,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&acc)[32], void* C, 
       }
     } else {
       for (int j = 0; j < 32 && col0 + j < N; ++j)
-        p[j] = from_float<T>((MODE == kAcc16 ? to_float(p[j]) : 0.f) + v[j]);
+        p[j] = from_float<T>((MODE == kAcc16 ? to_float(rp[j]) : 0.f) + v[j]);
     }
   }
 }
@@ -146,7 +155,8 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   return v;
 }
 
-// `gather` is unused by this kernel (it shares the launch signature of the CTA-pair kernel).
+// Of `gather` this kernel uses only the add source of its accumulating epilogue (it shares the
+// launch signature of the CTA-pair kernel).
 template <typename T, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -269,6 +279,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else {
     // ---------------------------------------------------------- epilogue
     const int quarter = warp & 3;                    // TMEM lane quarter this warp may read
+    const void* add_src = gather.add_src ? gather.add_src : C;
+    const int64_t add_ld = gather.add_src ? gather.add_ld : ldc;
     int it = 0;
     for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step, ++it) {
       int mb, nb;
@@ -290,7 +302,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        store_chunk<T, MODE>(r, C, ldc, row, col0, M, N);
+        store_chunk<T, MODE>(r, C, ldc, row, col0, M, N, add_src, add_ld);
       }
       tc_fence_before();
       __syncwarp();

@@ -150,7 +150,10 @@ static_assert(SMEM_BYTES <= 232448 && P_SMEM_BYTES <= 232448 && P_SMEM_BYTES_GAT
 
 template <typename T, bool A_MN, bool B_MN>
 int launch_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64_t ldc, int M, int N,
-                int K, int* err, int grid, cudaStream_t s) {
+                int K, int* err, int grid, cudaStream_t s, const void* R, int64_t ldr) {
+  GatherArgs side{};
+  side.add_src = R;
+  side.add_ld = ldr;
 #define FT_LAUNCH(MODE)                                                                              \
   {                                                                                                  \
     auto kern = gemm_kernel<T, A_MN, B_MN, MODE>;                                                    \
@@ -159,7 +162,7 @@ int launch_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);           \
       configured = true;                                                                             \
     }                                                                                                \
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, C, ldc, M, N, K, err, GatherArgs{});                        \
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, C, ldc, M, N, K, err, side);                  \
   }
   switch (mode) {
     case kStore16: FT_LAUNCH(kStore16); break;
@@ -186,7 +189,7 @@ int pair_group_m() {
 
 template <typename T, bool A_MN, bool B_MN, int MODE>
 int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64_t ldc, int M, int N, int K,
-                    int* err, int grid, cudaStream_t s) {
+                    int* err, int grid, cudaStream_t s, const void* R, int64_t ldr) {
   auto kern = gemm_pair_kernel<T, A_MN, B_MN, MODE>;
   static bool configured = false;
   if (!configured) {
@@ -207,29 +210,32 @@ int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64
   cfg.numAttrs = 1;
   GatherArgs none{};
   none.group_m = pair_group_m();
+  none.add_src = R;
+  none.add_ld = ldr;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, C, ldc, M, N, K, err, none);
   return e == cudaSuccess ? 0 : (int)e;
 }
 
 template <typename T, bool A_MN, bool B_MN>
 int launch_pair_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int64_t ldc, int M,
-                     int N, int K, int* err, int grid, cudaStream_t s) {
+                     int N, int K, int* err, int grid, cudaStream_t s, const void* R, int64_t ldr) {
   switch (mode) {
-    case kStore16: return launch_pair_one<T, A_MN, B_MN, kStore16>(ta, tb, C, ldc, M, N, K, err, grid, s);
-    case kStore32: return launch_pair_one<T, A_MN, B_MN, kStore32>(ta, tb, C, ldc, M, N, K, err, grid, s);
-    case kAcc16: return launch_pair_one<T, A_MN, B_MN, kAcc16>(ta, tb, C, ldc, M, N, K, err, grid, s);
-    case kAcc32: return launch_pair_one<T, A_MN, B_MN, kAcc32>(ta, tb, C, ldc, M, N, K, err, grid, s);
+    case kStore16: return launch_pair_one<T, A_MN, B_MN, kStore16>(ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+    case kStore32: return launch_pair_one<T, A_MN, B_MN, kStore32>(ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+    case kAcc16: return launch_pair_one<T, A_MN, B_MN, kAcc16>(ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+    case kAcc32: return launch_pair_one<T, A_MN, B_MN, kAcc32>(ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
     default: return -3;
   }
 }
 
 template <typename T>
 int launch_pair(int a_mn, int b_mn, int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
-                int64_t ldc, int M, int N, int K, int* err, int grid, cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch_pair_mode<T, false, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
-  if (!a_mn && b_mn) return launch_pair_mode<T, false, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
-  if (a_mn && b_mn) return launch_pair_mode<T, true, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
-  return launch_pair_mode<T, true, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
+                int64_t ldc, int M, int N, int K, int* err, int grid, cudaStream_t s, const void* R,
+                int64_t ldr) {
+  if (!a_mn && !b_mn) return launch_pair_mode<T, false, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+  if (!a_mn && b_mn) return launch_pair_mode<T, false, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+  if (a_mn && b_mn) return launch_pair_mode<T, true, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+  return launch_pair_mode<T, true, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
 }
 
 int g_use_pair = -1;   // -1: read FLEXTRAIN_GEMM_PAIR on first use
@@ -261,11 +267,12 @@ int launch_pair_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, void* act, 
 
 template <typename T>
 int launch_layout(int a_mn, int b_mn, int mode, const CUtensorMap& ta, const CUtensorMap& tb, void* C,
-                  int64_t ldc, int M, int N, int K, int* err, int grid, cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch_mode<T, false, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
-  if (!a_mn && b_mn) return launch_mode<T, false, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
-  if (a_mn && b_mn) return launch_mode<T, true, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
-  return launch_mode<T, true, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s);
+                  int64_t ldc, int M, int N, int K, int* err, int grid, cudaStream_t s, const void* R,
+                  int64_t ldr) {
+  if (!a_mn && !b_mn) return launch_mode<T, false, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+  if (!a_mn && b_mn) return launch_mode<T, false, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+  if (a_mn && b_mn) return launch_mode<T, true, true>(mode, ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
+  return launch_mode<T, true, false>(mode, ta, tb, C, ldc, M, N, K, err, grid, s, R, ldr);
 }
 
 }  // namespace
@@ -278,10 +285,14 @@ extern "C" {
 //   C: [M,N], row stride ldc, dtype c_dtype (same 16-bit type as A/B, or fp32);
 //      accumulate != 0 adds into C.
 // Returns 0, a negative argument error, or a positive CUDA error code.
-int ft_gemm(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* C,
-            int64_t ldc, int c_dtype, int accumulate, int M, int N, int K, int ab_dtype,
-            cudaStream_t stream) {
+// C = A B + R: the accumulating epilogue of ft_gemm with the addend read from a matrix R of C's
+// type and shape (row stride ldr) instead of from C.  R = nullptr gives C = A B (accumulate 0) or
+// C += A B (accumulate 1).  R may not overlap C unless it is C.
+int ft_gemm_add(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* C,
+                int64_t ldc, int c_dtype, int accumulate, const void* R, int64_t ldr, int M, int N, int K,
+                int ab_dtype, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (R != nullptr) accumulate = 1;
   if (ab_dtype != kBF16 && ab_dtype != kF16) return -1;
   if (c_dtype != kF32 && c_dtype != ab_dtype) return -2;
   int dev = 0;
@@ -308,21 +319,28 @@ int ft_gemm(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64
     const int pairs = sm_count(dev) / 2;
     const int grid = 2 * (tiles < pairs ? tiles : pairs);
     if (ab_dtype == kBF16)
-      rc = launch_pair<__nv_bfloat16>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+      rc = launch_pair<__nv_bfloat16>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream, R, ldr);
     else
-      rc = launch_pair<__half>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+      rc = launch_pair<__half>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream, R, ldr);
   } else {
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
     if (ab_dtype == kBF16)
-      rc = launch_layout<__nv_bfloat16>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+      rc = launch_layout<__nv_bfloat16>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream, R, ldr);
     else
-      rc = launch_layout<__half>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream);
+      rc = launch_layout<__half>(a_mn, b_mn, mode, ta, tb, C, ldc, M, N, K, err, grid, stream, R, ldr);
   }
   if (rc) return rc;
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;
+}
+
+int ft_gemm(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* C,
+            int64_t ldc, int c_dtype, int accumulate, int M, int N, int K, int ab_dtype,
+            cudaStream_t stream) {
+  return ft_gemm_add(A, a_mn, lda, B, b_mn, ldb, C, ldc, c_dtype, accumulate, nullptr, 0, M, N, K, ab_dtype,
+                     stream);
 }
 
 // act[M,F] = silu(X Wg^T) * (X Wu^T) with W = [Wg ; Wu] stored [2F, K] (row stride ldw), X stored

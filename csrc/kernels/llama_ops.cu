@@ -124,39 +124,71 @@ __global__ void __launch_bounds__(256) rmsnorm_dw_reduce_kernel(const float* __r
 // -------------------------------------------------------------------- RoPE
 // x viewed as [tokens, heads, D] with token strides in elements; rotate-half
 // pairs (i, i + D/2); position = token % seq_len.  sin_sign = -1 gives the
-// transpose rotation (backward).  8 elements of the first half per thread.
+// transpose rotation (backward).  One thread per (token, 8 columns of the first half): it
+// loads its 8 cosines and sines once and walks the heads, four at a time, so the tables are
+// read once per token instead of once per head and eight 16-byte loads are in flight per thread.
+template <typename T>
+__device__ __forceinline__ void rope_rotate8(const uint4& xa, const uint4& xb, const float (&c)[8],
+                                             const float (&s)[8], uint4& ya, uint4& yb) {
+  float a[8], b[8], oa[8], ob[8];
+  unpack8<T>(xa, a);
+  unpack8<T>(xb, b);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    oa[k] = a[k] * c[k] - b[k] * s[k];
+    ob[k] = b[k] * c[k] + a[k] * s[k];
+  }
+  ya = pack8<T>(oa);
+  yb = pack8<T>(ob);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) rope_kernel(const T* __restrict__ x, int64_t x_tok_stride,
                                                    T* __restrict__ y, int64_t y_tok_stride,
                                                    const float* __restrict__ cos_t,
                                                    const float* __restrict__ sin_t, int64_t tokens,
                                                    int heads, int D, int seq_len, float sin_sign) {
-  const int half = D / 2, vec_per_head = half / 8;
-  const int64_t total = tokens * heads * vec_per_head;
+  const int half = D / 2, vec = half / 8;
+  const int64_t total = tokens * vec;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
-    const int v = (int)(idx % vec_per_head);
-    const int h = (int)((idx / vec_per_head) % heads);
-    const int64_t tok = idx / ((int64_t)vec_per_head * heads);
+    const int v = (int)(idx % vec);
+    const int64_t tok = idx / vec;
     const int pos = (int)(tok % seq_len);
-    const T* xp = x + tok * x_tok_stride + (int64_t)h * D + v * 8;
-    T* yp = y + tok * y_tok_stride + (int64_t)h * D + v * 8;
-    float a[8], b[8], c[8], s[8], oa[8], ob[8];
-    unpack8<T>(*reinterpret_cast<const uint4*>(xp), a);
-    unpack8<T>(*reinterpret_cast<const uint4*>(xp + half), b);
+    float c[8], s[8];
     const float4* cp = reinterpret_cast<const float4*>(cos_t + (int64_t)pos * half + v * 8);
     const float4* sp = reinterpret_cast<const float4*>(sin_t + (int64_t)pos * half + v * 8);
-    float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
     c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
     s[0] = s0.x; s[1] = s0.y; s[2] = s0.z; s[3] = s0.w; s[4] = s1.x; s[5] = s1.y; s[6] = s1.z; s[7] = s1.w;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float sn = s[k] * sin_sign;
-      oa[k] = a[k] * c[k] - b[k] * sn;
-      ob[k] = b[k] * c[k] + a[k] * sn;
+    for (int k = 0; k < 8; ++k) s[k] *= sin_sign;
+    const T* xp = x + tok * x_tok_stride + v * 8;
+    T* yp = y + tok * y_tok_stride + v * 8;
+    int h = 0;
+    for (; h + 4 <= heads; h += 4) {
+      uint4 xa[4], xb[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {                  // all loads before any store: x may be y
+        xa[u] = *reinterpret_cast<const uint4*>(xp + (int64_t)(h + u) * D);
+        xb[u] = *reinterpret_cast<const uint4*>(xp + (int64_t)(h + u) * D + half);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint4 ya, yb;
+        rope_rotate8<T>(xa[u], xb[u], c, s, ya, yb);
+        *reinterpret_cast<uint4*>(yp + (int64_t)(h + u) * D) = ya;
+        *reinterpret_cast<uint4*>(yp + (int64_t)(h + u) * D + half) = yb;
+      }
     }
-    *reinterpret_cast<uint4*>(yp) = pack8<T>(oa);
-    *reinterpret_cast<uint4*>(yp + half) = pack8<T>(ob);
+    for (; h < heads; ++h) {
+      const uint4 xa = *reinterpret_cast<const uint4*>(xp + (int64_t)h * D);
+      const uint4 xb = *reinterpret_cast<const uint4*>(xp + (int64_t)h * D + half);
+      uint4 ya, yb;
+      rope_rotate8<T>(xa, xb, c, s, ya, yb);
+      *reinterpret_cast<uint4*>(yp + (int64_t)h * D) = ya;
+      *reinterpret_cast<uint4*>(yp + (int64_t)h * D + half) = yb;
+    }
   }
 }
 
@@ -341,7 +373,7 @@ int ft_rope(const void* x, int64_t x_tok_stride, void* y, int64_t y_tok_stride, 
             cudaStream_t s) {
   if (tokens <= 0) return 0;
   if (D % 16 || x_tok_stride % 8 || y_tok_stride % 8) return -2;
-  int64_t total = tokens * heads * (D / 16);
+  int64_t total = tokens * (D / 16);
   FT_DISPATCH_16(dt, T, (rope_kernel<T><<<grid_for(total, 256), 256, 0, s>>>(
                             (const T*)x, x_tok_stride, (T*)y, y_tok_stride, cos_t, sin_t, tokens, heads,
                             D, seq_len, sin_sign)));

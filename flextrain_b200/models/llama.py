@@ -102,7 +102,7 @@ class LlamaBlock(nn.Module):
             packed = F.attention_packed(qkv, nh, nkv, d)
             if packed is not None:
                 x, h = F.add_rmsnorm(x, F.linear(packed, self.wo), self.ffn_norm, cfg.eps)
-                return x + F.linear(F.linear_swiglu(h, self.w_gate_up), self.w_down)
+                return F.linear_add(F.linear_swiglu(h, self.w_gate_up), self.w_down, x)
         q = qkv[..., : nh * d].unflatten(-1, (nh, d))
         k = qkv[..., nh * d: (nh + nkv) * d].unflatten(-1, (nkv, d))
         v = qkv[..., (nh + nkv) * d:].unflatten(-1, (nkv, d))
@@ -110,8 +110,7 @@ class LlamaBlock(nn.Module):
             q, k = F.rope(q, cos, sin), F.rope(k, cos, sin)
         a = F.causal_attention(q, k, v).reshape(B, S, H)
         x, h = F.add_rmsnorm(x, F.linear(a, self.wo), self.ffn_norm, cfg.eps)
-        x = x + F.linear(F.linear_swiglu(h, self.w_gate_up), self.w_down)
-        return x
+        return F.linear_add(F.linear_swiglu(h, self.w_gate_up), self.w_down, x)
 
 
 class LlamaModel(nn.Module):

@@ -33,6 +33,8 @@ def declare(lib):
     lib.ft_xent_bwd.argtypes = [P, L, P, L, I, L, P, P, F, I, P]
     lib.ft_count_valid.argtypes = [P, L, L, I, P, P]
     lib.ft_gemm.argtypes = [P, I, L, P, I, L, P, L, I, I, I, I, I, I, P]
+    lib.ft_gemm_add.argtypes = [P, I, L, P, I, L, P, L, I, I, P, L, I, I, I, I, P]
+    lib.ft_gemm_add.restype = I
     lib.ft_gemm_swiglu.argtypes = [P, L, P, L, P, L, P, L, I, I, I, I, P]
     lib.ft_gemm_error.restype = I
     lib.ft_launch_count.restype = c_int64

@@ -22,11 +22,12 @@ def _check(rc: int, what: str):
 # --------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, a_mn: bool, b: torch.Tensor, b_mn: bool, m: int, n: int, k: int,
          out: Optional[torch.Tensor] = None, accumulate: bool = False,
-         out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+         out_dtype: Optional[torch.dtype] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[m, n] (+)= sum_k A(m, k) B(n, k)`` on the tcgen05 tensor cores.
     ``a`` is stored ``[m, k]`` (``a_mn=False``) or ``[k, m]`` (``a_mn=True``);
     ``b`` is stored ``[n, k]`` or ``[k, n]`` likewise.  Inputs are 2-D with unit
-    inner stride."""
+    inner stride.  ``add`` (``[m, n]``, the type of ``out``, unit inner stride) is added
+    to the product in the epilogue: ``out = A B^T + add``."""
     if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError("gemm operands must both be bf16 or both fp16")
     if a.stride(-1) != 1 or b.stride(-1) != 1:
@@ -34,6 +35,14 @@ def gemm(a: torch.Tensor, a_mn: bool, b: torch.Tensor, b_mn: bool, m: int, n: in
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype or a.dtype, device=a.device)
         accumulate = False
+    if add is not None:
+        if add.shape != (m, n) or add.dtype != out.dtype or add.stride(-1) != 1:
+            raise ValueError("gemm: `add` must be [m, n] of the output's type with unit inner stride")
+        rc = cuda_lib().ft_gemm_add(ptr(a), int(a_mn), a.stride(0), ptr(b), int(b_mn), b.stride(0), ptr(out),
+                                    out.stride(0), dtype_code(out.dtype), 1, ptr(add), add.stride(0), m, n, k,
+                                    dtype_code(a.dtype), stream_handle())
+        _check(rc, "ft_gemm_add")
+        return out
     rc = cuda_lib().ft_gemm(ptr(a), int(a_mn), a.stride(0), ptr(b), int(b_mn), b.stride(0), ptr(out),
                             out.stride(0), dtype_code(out.dtype), int(accumulate), m, n, k,
                             dtype_code(a.dtype), stream_handle())
@@ -88,6 +97,39 @@ class _Linear(torch.autograd.Function):
 
 def linear(x, w):
     return _Linear.apply(x, w)
+
+
+class _LinearAdd(torch.autograd.Function):
+    """``res + x w^T`` with the addition in the GEMM epilogue (one read of ``res`` instead of an
+    element-wise pass over two tensors).  The gradient of ``res`` is the output gradient itself."""
+
+    @staticmethod
+    def forward(ctx, x, w, res):
+        k = x.shape[-1]
+        x2 = x.reshape(-1, k)
+        if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16:
+            x2 = x2.contiguous()
+        n = w.shape[0]
+        r2 = res.reshape(-1, n)
+        if r2.stride(-1) != 1:
+            r2 = r2.contiguous()
+        y = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+        pending = getattr(w, "_ft_gather", None)
+        if pending is not None:
+            pending.complete_without_product()
+        gemm(x2, False, w, False, x2.shape[0], n, k, out=y.view(-1, n), add=r2)
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        dx, dw = _Linear.backward(ctx, dy)
+        return dx, dw, (dy if ctx.needs_input_grad[2] else None)
+
+
+def linear_add(x, w, res):
+    return _LinearAdd.apply(x, w, res)
 
 
 # ------------------------------------------------------------------ RMSNorm

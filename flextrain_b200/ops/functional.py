@@ -24,6 +24,14 @@ def linear(x, w):
     return ref.linear(x, w)
 
 
+def linear_add(x, w, res):
+    """``res + linear(x, w)``; on CUDA the addition runs in the epilogue of the GEMM."""
+    if _cuda(x):
+        from . import cuda_ops
+        return cuda_ops.linear_add(x, w, res)
+    return res + ref.linear(x, w)
+
+
 def rmsnorm(x, weight, eps):
     if _cuda(x):
         from . import cuda_ops

@@ -83,6 +83,27 @@ def test_linear_autograd_matches_reference():
     assert _rel_err(w.grad, wr.grad) < 1e-2
 
 
+@pytest.mark.parametrize("rows,k,n", [(192, 320, 520), (40, 128, 256), (300, 512, 1024)])
+def test_linear_add_puts_the_residual_in_the_epilogue(rows, k, n):
+    """``res + x w^T`` from one GEMM launch (CTA-pair kernel above 128 rows, single-CTA below),
+    against fp32 PyTorch, with all three gradients; the residual itself must stay untouched."""
+    from flextrain_b200.ops.cuda_ops import linear_add
+    x = torch.randn(rows, k, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(n, k, device=_dev()) / k ** 0.5).to(torch.bfloat16).requires_grad_()
+    res = torch.randn(rows, n, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    keep = res.detach().clone()
+    dy = torch.randn(rows, n, device=_dev(), dtype=torch.bfloat16)
+    y = linear_add(x, w, res)
+    y.backward(dy)
+    assert torch.equal(res.detach(), keep)
+    xr, wr, rr = (t.detach().float().requires_grad_() for t in (x, w, res))
+    yr = rr + torch.nn.functional.linear(xr, wr)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(w.grad, wr.grad) < 1e-2
+    assert torch.equal(res.grad, dy)
+
+
 def test_linear_accumulates_into_existing_grad():
     from flextrain_b200.ops.cuda_ops import linear
     x = torch.randn(256, 128, device=_dev(), dtype=torch.bfloat16)
