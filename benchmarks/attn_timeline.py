@@ -1,9 +1,9 @@
 #!/usr/bin/env python
-"""Timeline of one CTA of the attention backward kernel.
+"""Timeline of one CTA of the attention backward (default) or forward kernel.
 
-    python benchmarks/attn_timeline.py [--shape 13b] [--cta 0] [--it0 8]
+    python benchmarks/attn_timeline.py [--pass bwd|fwd] [--shape 13b] [--cta 0] [--it0 8]
 
-Runs the backward once with its timeline instantiation: the CTA ``--cta`` records
+Backward.  Runs the backward once with its timeline instantiation: the CTA ``--cta`` records
 clock64() at every hand-over point of eight consecutive (head, query block)
 iterations starting at ``--it0``.  Prints, per iteration, the clock of each point
 relative to the moment the product warp begins that iteration, and the mean
@@ -17,6 +17,15 @@ iteration period.  The roles:
            10 dQ complete | 11 dQ loaded, S released | 12 dQ staged, signalled
            (first / last softmax warp)
     red    0 dQ slabs full | 1 slabs inside the dS tile read | 2 all slabs read
+
+Forward.  The CTA ``--cta`` (CTA 0 is the pair of query blocks with the most K/V blocks) records
+eight consecutive K/V blocks j starting at ``--it0``:
+
+    mma    0 begin of block j | 1 PV of tile 0 issued (after V_j landed and P0_j was written) |
+           2 QK of tile 0 for block j+1 issued | 3 PV of tile 1 issued | 4 QK of tile 1 issued
+    smx0 / smx1 (first softmax warp of tile 0 / 1)
+           0 begin | 1 S complete | 2 S in registers | 3 row maximum known, O rescaled if needed |
+           4 exponentials done, P stored | 5 P signalled
 """
 import argparse
 import math
@@ -40,6 +49,7 @@ def main():
     ap.add_argument("--shape", default="13b")
     ap.add_argument("--cta", type=int, default=0)
     ap.add_argument("--it0", type=int, default=8)
+    ap.add_argument("--pass", dest="which", default="bwd", choices=("bwd", "fwd"))
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     B, S, Hq, Hkv, D = SHAPES[args.shape]
@@ -47,6 +57,21 @@ def main():
     mk = lambda h: torch.randn(B, S, h, D, device=dev, dtype=torch.bfloat16)  # noqa: E731
     q, k, v, do = mk(Hq), mk(Hkv), mk(Hkv), mk(Hq)
     scale = 1.0 / math.sqrt(D)
+    if args.which == "fwd":
+        for _ in range(2):
+            attention_forward(q, k, v, scale)
+        buf = torch.zeros(3 * 8 * 8, dtype=torch.int64, device=dev)
+        attention_forward(q, k, v, scale, trace=(buf, args.cta, args.it0))
+        torch.cuda.synchronize()
+        t = buf.cpu().view(3, 8, 8)
+        base = t[0, 0]
+        print(f"forward, shape {args.shape} cta {args.cta} K/V blocks {args.it0}..{args.it0 + 7}")
+        period = (base[1:] - base[:-1]).float()
+        print("block period (clocks):", [int(x) for x in period], "mean", int(period.mean()))
+        for r, (name, sites) in enumerate((("mma", 5), ("smx0", 6), ("smx1", 6))):
+            for j in range(8):
+                print(f"{name:9s} j+{j}: {[int(t[r, s_, j] - base[j]) for s_ in range(sites)]}")
+        return
     o, lse, _ = attention_forward(q, k, v, scale)
     for _ in range(2):
         attention_backward(q, k, v, o, lse, do, scale)

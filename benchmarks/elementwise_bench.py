@@ -15,6 +15,7 @@ warm-up calls), algorithmic bytes moved, achieved GB/s and its fraction of ``--p
   swiglu fwd / bwd      separate kernels; the GEMM-epilogue form is timed as a GEMM
                         (``benchmarks/gemm_bench.py`` shapes) and not here
   bias + gelu fwd / bwd native vs ATen
+  rope                  in place on the q and k heads of a packed QKV tensor
 """
 import argparse
 import os
@@ -91,6 +92,15 @@ def main():
             3 * unit_f)
     fwd_bwd("bias+gelu ATen", lambda: TF.gelu(pre + bias_f, approximate="tanh"), (pre, bias_f), dact,
             2 * unit_f, 3 * unit_f)
+    # rotary embedding in place on the q and k heads of a packed QKV row (MHA layout: 3 * hidden wide)
+    from flextrain_b200.ops import reference as ref
+    d, seq = 128, 4096
+    heads = 2 * (H // d)
+    qkv = torch.randn(T // seq, seq, 3 * H, device=dev, dtype=bf)
+    cos, sin = ref.rope_tables(seq, d, 10000.0, device=dev)
+    with torch.no_grad():
+        report("rope in place (q and k heads)", timed(lambda: cuda_ops.rope_heads_inplace(qkv, cos, sin, heads, d),
+                                                      args.iters), 2 * 2 * unit)
     from flextrain_b200.ops.native import cuda_lib
     print("error word", cuda_lib().ft_gemm_error())
 

@@ -19,10 +19,10 @@ static_assert(Fwd2Smem<128>::BYTES <= kMaxDynamicSmem && BwdSmem<128>::BYTES <= 
               "an attention kernel outgrew the shared memory of an SM");
 
 // Forward: one CTA per pair of query blocks.
-template <typename T, int D>
-int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
-                cudaStream_t s) {
-  auto kern = attn_fwd2_kernel<T, D>;
+template <typename T, int D, bool TRACE>
+int launch_fwd2_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
+                  cudaStream_t s) {
+  auto kern = attn_fwd2_kernel<T, D, 0x00u, TRACE>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<D>::BYTES);
@@ -31,6 +31,16 @@ int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   const int num_pairs = ((P.S + BQ - 1) / BQ + 1) / 2;
   kern<<<P.B * P.Hq * num_pairs, F2_THREADS, Fwd2Smem<D>::BYTES, s>>>(tq, tk, tv, P);
   return 0;
+}
+
+// The timeline instantiations exist for bf16 at head size 128 only (the benchmark shapes).
+template <typename T, int D>
+int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
+                cudaStream_t s) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value && D == 128) {
+    if (P.trace != nullptr) return launch_fwd2_t<T, D, true>(tq, tk, tv, P, s);
+  }
+  return launch_fwd2_t<T, D, false>(tq, tk, tv, P, s);
 }
 
 // Backward: four threads per score row (2.6 % faster than two at the 13B shape, 96 registers
@@ -52,7 +62,6 @@ int launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap
   return 0;
 }
 
-// The timeline instantiation exists for bf16 at head size 128 only (the benchmark shapes).
 template <typename T, int D>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                const CUtensorMap& tdq, const BwdParams& P, cudaStream_t s) {
@@ -84,9 +93,12 @@ extern "C" {
 
 // o[B,S,Hq,D], lse[B,Hq,S] <- causal attention of q[B,S,Hq,D], k/v[B,S,Hkv,D].
 // *_stride: elements between consecutive tokens of that tensor.  D in {64, 128}.
-int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
-                int64_t v_stride, void* o, float* lse, int B, int S, int Hq, int Hkv, int D, float scale,
-                int dtype, cudaStream_t stream) {
+// ft_attn_fwd_traced additionally records the timeline of one CTA: `trace` is nullptr or a device
+// buffer of 3 * 8 * 8 clock values (see FwdParams).
+int ft_attn_fwd_traced(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                       int64_t v_stride, void* o, float* lse, int B, int S, int Hq, int Hkv, int D,
+                       float scale, int dtype, cudaStream_t stream, long long* trace, int trace_cta,
+                       int trace_it0) {
   if (D != 64 && D != 128) return -1;
   if (dtype != kBF16 && dtype != kF16) return -2;
   if (Hq % Hkv) return -3;
@@ -105,6 +117,7 @@ int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   P.scale_ln = scale;
   P.q_col0 = P.k_col0 = P.v_col0 = 0;
   P.err = gemm::error_word(dev);
+  P.trace = trace; P.trace_cta = trace_cta; P.trace_it0 = trace_it0;
   if (dtype == kBF16) {
     if (D == 128) launch_fwd2<__nv_bfloat16, 128>(tq, tk, tv, P, stream);
     else launch_fwd2<__nv_bfloat16, 64>(tq, tk, tv, P, stream);
@@ -115,6 +128,13 @@ int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
   return 0;
+}
+
+int ft_attn_fwd(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                int64_t v_stride, void* o, float* lse, int B, int S, int Hq, int Hkv, int D, float scale,
+                int dtype, cudaStream_t stream) {
+  return ft_attn_fwd_traced(q, q_stride, k, k_stride, v, v_stride, o, lse, B, S, Hq, Hkv, D, scale, dtype,
+                            stream, nullptr, 0, 0);
 }
 
 // Gradients of ft_attn_fwd (ft_attn_bwd), optionally with a timeline of one CTA: `trace` is

@@ -1,5 +1,5 @@
 // Definitions shared by the causal flash-attention kernels (attention_fwd2.cuh,
-// attention_fwd4.cuh, attention_bwd.cuh): tile sizes, the forward parameter block and the
+// attention_bwd.cuh): tile sizes, the forward parameter block and the
 // 128-byte swizzle of a [rows][64] shared-memory chunk.
 #pragma once
 #include "common.cuh"
@@ -20,6 +20,10 @@ struct FwdParams {
   float scale_ln;          // softmax scale
   int q_col0, k_col0, v_col0;   // column of head 0 inside the respective tensor map rows
   int* err;
+  // timeline capture (TRACE instantiation only): clock64() of CTA trace_cta at the hand-over points
+  // of K/V blocks trace_it0 .. trace_it0 + 7, as trace[(role * 8 + site) * 8 + block]
+  long long* trace;
+  int trace_cta, trace_it0;
 };
 
 // byte offset of 16-byte unit `u` (0..7) of row `r` inside a 128B-swizzled [rows][64] chunk

@@ -45,7 +45,7 @@ struct Fwd2Bars {
 // (bit j = pair j) instead of the special-function unit.  None by default: with one thread per
 // score row the extra instructions cost more than the unit's 16 results per clock (13B shape:
 // 1.466 ms with none, 1.553 ms with four of eight, 1.699 ms with five).
-template <typename T, int D, unsigned POLY = 0x00u>
+template <typename T, int D, unsigned POLY = 0x00u, bool TRACE = false>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams P) {
@@ -71,6 +71,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int n0 = qb0 + 1;                            // K/V blocks tile 0 needs (causal)
   const int n1 = qb1 < num_qb ? qb1 + 1 : 0;         // tile 1 may not exist
   const int nmax = n0 > n1 ? n0 : n1;
+  // role: 0 product warp, 1 first softmax warp of tile 0, 2 first softmax warp of tile 1
+  auto stamp = [&](int role, int site, int j) {
+    if constexpr (TRACE) {
+      if ((int)blockIdx.x == P.trace_cta && j >= P.trace_it0 && j < P.trace_it0 + 8)
+        P.trace[(role * 8 + site) * 8 + (j - P.trace_it0)] = clock64();
+    }
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -157,10 +164,15 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (ok) qk(0, 0);
       if (ok && n1 > 0) qk(1, 0);
       for (int j = 0; j < nmax && ok && !*abort_flag; ++j) {
+        stamp(0, 0, j);
         if (j < n0) pv(0, j);
+        stamp(0, 1, j);
         if (ok && j + 1 < n0) qk(0, j + 1);
+        stamp(0, 2, j);
         if (ok && j < n1) pv(1, j);
+        stamp(0, 3, j);
         if (ok && j + 1 < n1) qk(1, j + 1);
+        stamp(0, 4, j);
       }
       if (!ok) *abort_flag = 1;
     }
@@ -178,8 +190,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint64_t scale2 = pm::pack2(P.scale_log2, P.scale_log2);
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
+    const int trole = (lane == 0 && quarter == 2) ? 1 + t : -1;     // warps 2 and 6
+    auto sstamp = [&](int site, int j) { if (TRACE && trole >= 0) stamp(trole, site, j); };
     for (int j = 0; j < n_t; ++j) {
+      sstamp(0, j);
       if (!mbar_wait(&bars->s_full[t], j & 1)) { atomicCAS(P.err, 0, 326); ok = false; break; }
+      sstamp(1, j);
       tc_fence_after();
       const bool diag = (j == qb);
       const int kv0 = j * BKV;
@@ -188,6 +204,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
       for (int c = 0; c < BKV / 32; ++c) tmem_ld_32x32(tm_s + c * 32, v[c]);
       tmem_ld_wait();
+      sstamp(2, j);
       if (diag) {
 #pragma unroll
         for (int c = 0; c < BKV / 32; ++c)
@@ -231,6 +248,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         m_used = m_new;
       }
+      sstamp(3, j);
       // p = 2^((s - m) * scale), row sum, P written over the first half of S
       const float neg_m = -m_used * P.scale_log2;
       const uint64_t neg_m2 = pm::pack2(neg_m, neg_m);
@@ -259,9 +277,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       float la, lb;
       pm::unpack2(l2, la, lb);
       l_run += la + lb;
+      sstamp(4, j);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[t]);
+      sstamp(5, j);
     }
     if (ok && n_t > 0) {
       if (!mbar_wait(&bars->o_full[t], (n_t - 1) & 1)) { atomicCAS(P.err, 0, 328); ok = false; }

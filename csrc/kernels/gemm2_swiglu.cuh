@@ -152,7 +152,7 @@ gemm_pair_swiglu_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const float gv = __uint_as_float(g[j]);
-          g[j] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[j]));
+          g[j] = __float_as_uint(__fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[j]));
         }
         store_chunk<T, kStore16>(g, act, ld_act, row, col0, M, F);
       }

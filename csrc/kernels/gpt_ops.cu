@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(256) parts_reduce_kernel(const float* __restri
 // ------------------------------------------------------------ bias + activation
 __device__ __forceinline__ float tanh_fast(float z) {
   // 1 - 2 / (1 + e^{2z}); exact limits at +-inf
-  return 1.f - 2.f / (1.f + __expf(2.f * z));
+  return 1.f - __fdividef(2.f, 1.f + __expf(2.f * z));
 }
 
 constexpr float kGeluK = 0.7978845608028654f;    // sqrt(2 / pi)

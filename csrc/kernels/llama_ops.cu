@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ g
     unpack8<T>(*reinterpret_cast<const uint4*>(gu + r * 2 * F + c), g);
     unpack8<T>(*reinterpret_cast<const uint4*>(gu + r * 2 * F + F + c), u);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+    for (int k = 0; k < 8; ++k) o[k] = __fdividef(g[k], 1.f + __expf(-g[k])) * u[k];
     *reinterpret_cast<uint4*>(out + r * F + c) = pack8<T>(o);
   }
 }
@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const T* __restrict__ g
     unpack8<T>(*reinterpret_cast<const uint4*>(dout + r * F + c), d);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      float sig = 1.f / (1.f + __expf(-g[k]));
+      float sig = __fdividef(1.f, 1.f + __expf(-g[k]));   // approximate reciprocal: the result is rounded to 16 bits
       float silu = g[k] * sig;
       dg[k] = d[k] * u[k] * sig * (1.f + g[k] * (1.f - sig));
       du[k] = d[k] * silu;

@@ -20,6 +20,9 @@ def _lib():
         from ctypes import c_float, c_int, c_int64, c_void_p
         lib.ft_attn_fwd.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]
+        if hasattr(lib, "ft_attn_fwd_traced"):
+            lib.ft_attn_fwd_traced.argtypes = list(lib.ft_attn_fwd.argtypes) + [c_void_p, c_int, c_int]
+            lib.ft_attn_fwd_traced.restype = c_int
         if hasattr(lib, "ft_attn_bwd"):
             lib.ft_attn_bwd.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
@@ -42,7 +45,9 @@ def _rows(t: torch.Tensor):
     return t, t.stride(1)
 
 
-def attention_forward(q, k, v, scale):
+def attention_forward(q, k, v, scale, trace=None):
+    """``trace = (int64 tensor of 3*8*8, cta, first K/V block)`` records the timeline of one CTA
+    (bf16, head size 128; see ``benchmarks/attn_timeline.py``)."""
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     q, qs = _rows(q)
@@ -50,8 +55,14 @@ def attention_forward(q, k, v, scale):
     v, vs = _rows(v)
     o = torch.empty(B, S, Hq, D, dtype=q.dtype, device=q.device)
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
-    rc = _lib().ft_attn_fwd(ptr(q), qs, ptr(k), ks, ptr(v), vs, ptr(o), ptr(lse), B, S, Hq, Hkv, D,
-                            float(scale), dtype_code(q.dtype), stream_handle())
+    args = (ptr(q), qs, ptr(k), ks, ptr(v), vs, ptr(o), ptr(lse), B, S, Hq, Hkv, D,
+            float(scale), dtype_code(q.dtype), stream_handle())
+    if trace is None:
+        rc = _lib().ft_attn_fwd(*args)
+    else:
+        buf, cta, it0 = trace
+        assert buf.dtype == torch.int64 and buf.numel() >= 3 * 8 * 8 and buf.is_cuda
+        rc = _lib().ft_attn_fwd_traced(*args, ptr(buf), int(cta), int(it0))
     if rc != 0:
         raise RuntimeError(f"ft_attn_fwd failed (code {rc})")
     return o, lse, (q, k, v)
