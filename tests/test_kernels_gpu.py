@@ -332,3 +332,33 @@ def test_attention_forward(shape):
         want_o, want_lse = _attention_oracle(q, k, v, scale)
         assert _rel_err(o, want_o) < 2e-2
         assert float((lse - want_lse).abs().max()) < 2e-2
+
+
+def test_attention_timeline_instantiations_compute_the_same_and_fill_the_trace():
+    """The timeline builds of the two attention kernels (``benchmarks/attn_timeline.py``) must give
+    the results of the regular builds, and the clocks they record must be in program order."""
+    import math
+    from flextrain_b200.ops.attention_backward import attention_backward
+    from flextrain_b200.ops.attention_native import attention_forward
+    B, S, H, D = 1, 1024, 2, 128
+    torch.manual_seed(3)
+    q, k, v, do = (torch.randn(B, S, H, D, device=_dev()).to(torch.bfloat16) for _ in range(4))
+    scale = 1.0 / math.sqrt(D)
+    o, lse, _ = attention_forward(q, k, v, scale)
+    fbuf = torch.zeros(3 * 8 * 8, dtype=torch.int64, device=_dev())
+    o2, lse2, _ = attention_forward(q, k, v, scale, trace=(fbuf, 0, 0))     # CTA 0: 8 K/V blocks
+    torch.cuda.synchronize()
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    f = fbuf.cpu().view(3, 8, 8)
+    assert (f[0, :5, :8] > 0).all() and (f[1, :6, :7] > 0).all()
+    assert (f[0, 1:5] >= f[0, 0:4]).all()                 # the product warp's sites follow one another
+    assert (f[1, 1:6, :7] >= f[1, 0:5, :7]).all()         # so do the softmax warp's
+    want = attention_backward(q, k, v, o, lse, do, scale)
+    bbuf = torch.zeros(5 * 16 * 8, dtype=torch.int64, device=_dev())
+    got = attention_backward(q, k, v, o, lse, do, scale, trace=(bbuf, 0, 0))  # CTA 0: kv block 0, 8 q blocks
+    torch.cuda.synchronize()
+    for a, b_ in zip(got, want):
+        assert _rel_err(a, b_) < 1e-3                     # dq is summed by reduce-adds: order may differ
+    t = bbuf.cpu().view(5, 16, 8)
+    assert (t[1, :8] > 0).all() and (t[1, 1:8] >= t[1, 0:7]).all()
+    assert (t[4, :3] > 0).all() and (t[4, 1:3] >= t[4, 0:2]).all()
