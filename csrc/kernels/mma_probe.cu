@@ -1,0 +1,137 @@
+// Rate of 128-deep tcgen05 products (eight 128xNx16 instructions) for the operand placements the
+// attention kernels use, measured in SM clocks by the issuing thread itself.  One CTA per SM
+// holds fixed zero-filled tiles in shared memory; one thread issues `rounds` products back to
+// back (the tensor pipe's queue holds it back, so the time per round is the pipe's time per
+// product) and records clock64() around them.  Used by benchmarks/mma_rate.py to tell what a
+// kernel can expect from the tensor pipe before any of its own overheads.
+//
+//   mode 0  A, B K-major in shared memory, N = 128          (S = Q K^T, dP = dO V^T)
+//   mode 1  A, B MN-major in shared memory, N = 128         (dV = P^T dO, dK = dS^T Q)
+//   mode 2  A K-major, B MN-major in shared memory, N = 128 (dQ = dS K)
+//   mode 3  A in tensor memory, B MN-major, N = 128         (O += P V)
+//   mode 4  A, B K-major in shared memory, N = 256
+//   mode 5  mode 0 while four warps keep loading 128 columns of tensor memory
+//   mode 6  mode 0 while four warps keep storing to shared memory (16 bytes per thread and turn)
+//   mode 7  mode 3 while four warps keep loading 128 columns of tensor memory
+#include "common.cuh"
+#include "gemm_host.h"
+#include "tcgen05.cuh"
+
+namespace {
+
+using namespace ft;
+using namespace ft::sm100;
+
+constexpr int kProbeThreads = 192;                   // warp 0 issues, warp 1 owns tensor memory, 2-5 disturb
+constexpr int kChunk = 128 * 128;                    // [128 rows][64 columns] of 16-bit values
+constexpr int kSmem = 2 * kChunk /* A */ + 4 * kChunk /* B, up to 256 rows */ + 32 * 1024 /* scratch */ + 2048;
+
+struct ProbeBars {
+  uint64_t done;
+  uint32_t tmem_base;
+  volatile uint32_t stop;
+};
+
+__global__ void __launch_bounds__(kProbeThreads, 1)
+mma_probe_kernel(int mode, int rounds, long long* __restrict__ out, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + 2 * kChunk;
+  uint8_t* sX = sB + 4 * kChunk;
+  ProbeBars* bars = reinterpret_cast<ProbeBars*>(sX + 32 * 1024);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  for (int i = threadIdx.x; i < (6 * kChunk + 32 * 1024) / 16; i += kProbeThreads)
+    reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->done, 1);
+    bars->stop = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
+      const int base = (mode == 5 || mode == 6) ? 0 : (mode == 7 ? 3 : mode);
+      const int n = base == 4 ? 256 : 128;
+      const uint32_t idesc = make_idesc_f16(1, base == 1, base == 1 || base == 2 || base == 3, 128, n);
+      const long long t0 = clock64();
+      for (int r = 0; r < rounds; ++r) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t k_off = (kk / 4) * kChunk + (kk % 4) * 32;          // K-major, 128 rows
+          const uint32_t k_off256 = (kk / 4) * 2 * kChunk + (kk % 4) * 32;   // K-major, 256 rows
+          const uint32_t mn_off = kk * 2048;                                  // MN-major
+          uint64_t ad, bd;
+          if (base == 1) ad = make_smem_desc(aA + mn_off, kChunk, 1024);
+          else ad = make_smem_desc(aA + k_off, 16, 1024);
+          if (base == 0) bd = make_smem_desc(aB + k_off, 16, 1024);
+          else if (base == 4) bd = make_smem_desc(aB + k_off256, 16, 1024);
+          else bd = make_smem_desc(aB + mn_off, kChunk, 1024);
+          if (base == 3) umma_f16_ts(tmem + 256, tmem + kk * 8, bd, idesc, (r | kk) != 0);
+          else umma_f16(tmem + 256, ad, bd, idesc, (r | kk) != 0);
+        }
+      }
+      umma_commit(&bars->done);
+      const bool ok = mbar_wait(&bars->done, 0);
+      const long long t1 = clock64();
+      if (!ok) atomicCAS(err, 0, 501);
+      out[blockIdx.x] = t1 - t0;
+      bars->stop = 1;
+    }
+  } else if (warp >= 2 && (mode == 5 || mode == 6 || mode == 7)) {
+    // the disturbing warps: bounded by the issuing thread's stop flag and by a turn count
+    const int quarter = warp & 3;
+    const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16);
+    uint32_t sink = 0;
+    for (int turn = 0; turn < (1 << 22) && !bars->stop; ++turn) {
+      if (mode == 6) {
+        uint4* p = reinterpret_cast<uint4*>(sX) + ((turn * 128 + (warp - 2) * 32 + lane) & 2047);
+        *p = make_uint4(turn, sink, 0, 0);
+      } else {
+        uint32_t v[32];
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_32x32(taddr + c * 32, v);          // columns 0-127: not the accumulator
+          tmem_ld_wait();
+          sink ^= v[0] ^ v[31];
+        }
+      }
+    }
+    if (sink == 0x12345678u) out[gridDim.x] = sink;  // keeps the loads alive
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+}  // namespace
+
+extern "C" {
+
+// out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
+int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
+  if (mode < 0 || mode > 7 || rounds < 1 || rounds > 4096) return -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(mma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    configured = true;
+  }
+  mma_probe_kernel<<<ft::gemm::sm_count(dev), kProbeThreads, kSmem, stream>>>(mode, rounds, out,
+                                                                              ft::gemm::error_word(dev));
+  FT_LAUNCHED(1);
+  FT_CUDA_RETURN_IF_ERROR();
+  return 0;
+}
+
+}  // extern "C"
