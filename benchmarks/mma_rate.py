@@ -28,6 +28,9 @@ MODES = (
     (5, 128, "mode 0 while four warps keep loading tensor memory"),
     (6, 128, "mode 0 while four warps keep storing to shared memory"),
     (7, 128, "mode 3 while four warps keep loading tensor memory"),
+    (8, 256, "two independent mode-0 products, instructions interleaved (clocks per pair)"),
+    (9, 256, "two independent mode-1 products, instructions interleaved (clocks per pair)"),
+    (10, 256, "two independent mode-3 products, instructions interleaved (clocks per pair)"),
 )
 
 

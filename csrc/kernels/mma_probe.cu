@@ -13,6 +13,9 @@
 //   mode 5  mode 0 while four warps keep loading 128 columns of tensor memory
 //   mode 6  mode 0 while four warps keep storing to shared memory (16 bytes per thread and turn)
 //   mode 7  mode 3 while four warps keep loading 128 columns of tensor memory
+//   mode 8  mode 0 with the instructions of two independent products interleaved (two accumulators):
+//           clocks per PAIR of products
+//   mode 9  mode 1 likewise          mode 10  mode 3 likewise
 #include "common.cuh"
 #include "gemm_host.h"
 #include "tcgen05.cuh"
@@ -60,7 +63,9 @@ mma_probe_kernel(int mode, int rounds, long long* __restrict__ out, int* __restr
   if (warp == 0) {
     if (lane == 0) {
       const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
-      const int base = (mode == 5 || mode == 6) ? 0 : (mode == 7 ? 3 : mode);
+      const bool two = mode >= 8;                    // two accumulators, instructions alternating
+      const int base = (mode == 5 || mode == 6 || mode == 8) ? 0
+                       : (mode == 7 || mode == 10) ? 3 : (mode == 9 ? 1 : mode);
       const int n = base == 4 ? 256 : 128;
       const uint32_t idesc = make_idesc_f16(1, base == 1, base == 1 || base == 2 || base == 3, 128, n);
       const long long t0 = clock64();
@@ -78,6 +83,10 @@ mma_probe_kernel(int mode, int rounds, long long* __restrict__ out, int* __restr
           else bd = make_smem_desc(aB + mn_off, kChunk, 1024);
           if (base == 3) umma_f16_ts(tmem + 256, tmem + kk * 8, bd, idesc, (r | kk) != 0);
           else umma_f16(tmem + 256, ad, bd, idesc, (r | kk) != 0);
+          if (two) {
+            if (base == 3) umma_f16_ts(tmem + 384, tmem + 64 + kk * 8, bd, idesc, (r | kk) != 0);
+            else umma_f16(tmem + 384, ad, bd, idesc, (r | kk) != 0);
+          }
         }
       }
       umma_commit(&bars->done);
@@ -119,7 +128,7 @@ extern "C" {
 
 // out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
 int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
-  if (mode < 0 || mode > 7 || rounds < 1 || rounds > 4096) return -1;
+  if (mode < 0 || mode > 10 || rounds < 1 || rounds > 4096) return -1;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured = false;
