@@ -31,6 +31,7 @@ MODES = (
     (8, 256, "two independent mode-0 products, instructions interleaved (clocks per pair)"),
     (9, 256, "two independent mode-1 products, instructions interleaved (clocks per pair)"),
     (10, 256, "two independent mode-3 products, instructions interleaved (clocks per pair)"),
+    (11, 128, "mode 0 with every descriptor built from the tile address inside the issue loop"),
 )
 
 

@@ -16,6 +16,8 @@
 //   mode 8  mode 0 with the instructions of two independent products interleaved (two accumulators):
 //           clocks per PAIR of products
 //   mode 9  mode 1 likewise          mode 10  mode 3 likewise
+//   mode 11 mode 0 with each instruction's descriptors built from the tile address inside the loop
+//           (every other mode adds a constant to a descriptor half prepared before the loop)
 #include "common.cuh"
 #include "gemm_host.h"
 #include "tcgen05.cuh"
@@ -63,29 +65,49 @@ mma_probe_kernel(int mode, int rounds, long long* __restrict__ out, int* __restr
   if (warp == 0) {
     if (lane == 0) {
       const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
-      const bool two = mode >= 8;                    // two accumulators, instructions alternating
-      const int base = (mode == 5 || mode == 6 || mode == 8) ? 0
+      const bool two = mode >= 8 && mode <= 10;      // two accumulators, instructions alternating
+      const bool rebuilt = mode == 11;               // mode 0 with every descriptor built from scratch
+      const int base = (mode == 5 || mode == 6 || mode == 8 || mode == 11) ? 0
                        : (mode == 7 || mode == 10) ? 3 : (mode == 9 ? 1 : mode);
       const int n = base == 4 ? 256 : 128;
       const uint32_t idesc = make_idesc_f16(1, base == 1, base == 1 || base == 2 || base == 3, 128, n);
-      const long long t0 = clock64();
-      for (int r = 0; r < rounds; ++r) {
+      // descriptors of the eight instructions of a product, low halves; the tiles never move
+      uint32_t a_lo[8], b_lo[8];
+      const uint32_t hi = smem_desc_hi(1024);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t k_off = (kk / 4) * kChunk + (kk % 4) * 32;          // K-major, 128 rows
-          const uint32_t k_off256 = (kk / 4) * 2 * kChunk + (kk % 4) * 32;   // K-major, 256 rows
-          const uint32_t mn_off = kk * 2048;                                  // MN-major
-          uint64_t ad, bd;
-          if (base == 1) ad = make_smem_desc(aA + mn_off, kChunk, 1024);
-          else ad = make_smem_desc(aA + k_off, 16, 1024);
-          if (base == 0) bd = make_smem_desc(aB + k_off, 16, 1024);
-          else if (base == 4) bd = make_smem_desc(aB + k_off256, 16, 1024);
-          else bd = make_smem_desc(aB + mn_off, kChunk, 1024);
-          if (base == 3) umma_f16_ts(tmem + 256, tmem + kk * 8, bd, idesc, (r | kk) != 0);
-          else umma_f16(tmem + 256, ad, bd, idesc, (r | kk) != 0);
-          if (two) {
-            if (base == 3) umma_f16_ts(tmem + 384, tmem + 64 + kk * 8, bd, idesc, (r | kk) != 0);
-            else umma_f16(tmem + 384, ad, bd, idesc, (r | kk) != 0);
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t k_off = (kk / 4) * kChunk + (kk % 4) * 32;            // K-major, 128 rows
+        const uint32_t k_off256 = (kk / 4) * 2 * kChunk + (kk % 4) * 32;     // K-major, 256 rows
+        const uint32_t mn_off = kk * 2048;                                    // MN-major
+        a_lo[kk] = base == 1 ? smem_desc_lo(aA, kChunk) + (mn_off >> 4) : smem_desc_lo(aA, 16) + (k_off >> 4);
+        b_lo[kk] = base == 0 ? smem_desc_lo(aB, 16) + (k_off >> 4)
+                   : base == 4 ? smem_desc_lo(aB, 16) + (k_off256 >> 4)
+                               : smem_desc_lo(aB, kChunk) + (mn_off >> 4);
+      }
+      const long long t0 = clock64();
+      if (rebuilt) {
+        for (int r = 0; r < rounds; ++r) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t k_off = (kk / 4) * kChunk + (kk % 4) * 32;
+            umma_f16(tmem + 256, make_smem_desc(aA + k_off, 16, 1024), make_smem_desc(aB + k_off, 16, 1024),
+                     idesc, (r | kk) != 0);
+          }
+        }
+      } else if (base == 3) {
+        for (int r = 0; r < rounds; ++r) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            umma_f16_ts(tmem + 256, tmem + kk * 8, smem_desc_join(b_lo[kk], hi), idesc, (r | kk) != 0);
+            if (two) umma_f16_ts(tmem + 384, tmem + 64 + kk * 8, smem_desc_join(b_lo[kk], hi), idesc, (r | kk) != 0);
+          }
+        }
+      } else {
+        for (int r = 0; r < rounds; ++r) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            umma_f16(tmem + 256, smem_desc_join(a_lo[kk], hi), smem_desc_join(b_lo[kk], hi), idesc, (r | kk) != 0);
+            if (two) umma_f16(tmem + 384, smem_desc_join(a_lo[kk], hi), smem_desc_join(b_lo[kk], hi), idesc, (r | kk) != 0);
           }
         }
       }
@@ -128,7 +150,7 @@ extern "C" {
 
 // out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
 int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
-  if (mode < 0 || mode > 10 || rounds < 1 || rounds > 4096) return -1;
+  if (mode < 0 || mode > 11 || rounds < 1 || rounds > 4096) return -1;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured = false;

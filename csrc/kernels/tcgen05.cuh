@@ -206,6 +206,23 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
+// The same descriptor in two 32-bit halves, for issue loops that walk a tile: the high half is
+// fixed by the layout and the low half of a tile at `smem_addr + off` (off a multiple of 16) is
+// `smem_desc_lo(smem_addr, lbo) + (off >> 4)`, one integer add per instruction instead of the
+// whole construction.  A lone issuing thread runs its dependent integer instructions several
+// clocks apart, so this matters when the tensor instructions themselves are short (N = 128).
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFF) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+__host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint64_t smem_desc_join(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptor for kind::f16: fp32 accumulate, A/B both bf16 (1) or
 // fp16 (0), per-operand major (0 = K-major, 1 = MN-major), tile M x N.
 __host__ __device__ constexpr uint32_t make_idesc_f16(int ab_format, int a_mn_major, int b_mn_major,
