@@ -182,8 +182,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       constexpr uint32_t id_s = make_idesc_f16(AB, 0, 0, BQ, BKV);     // K-major x K-major
       constexpr uint32_t id_t = make_idesc_f16(AB, 1, 1, BKV, D);      // MN-major x MN-major
       constexpr uint32_t id_q = make_idesc_f16(AB, 0, 1, BQ, D);       // K-major x MN-major
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sdO),
-                     aP = smem_u32(sP), aDS = smem_u32(sdS);
+      // Descriptor halves of the six tiles, prepared once: inside the loop an instruction costs
+      // this thread two integer adds, not two descriptor constructions.  A lone thread runs its
+      // dependent integer instructions several clocks apart, and with the constructions in the
+      // loop it fed the pipe one 128-wide instruction per ~105 clocks where the pipe takes 64
+      // (csrc/kernels/mma_probe.cu measures both).
+      constexpr uint32_t dhi = smem_desc_hi(1024);
+      const uint32_t q_k = smem_desc_lo(smem_u32(sQ), 16), k_k = smem_desc_lo(smem_u32(sK), 16),
+                     do_k = smem_desc_lo(smem_u32(sdO), 16), v_k = smem_desc_lo(smem_u32(sV), 16),
+                     ds_k = smem_desc_lo(smem_u32(sdS), 16);
+      const uint32_t p_m = smem_desc_lo(smem_u32(sP), CHUNK_BYTES), do_m = smem_desc_lo(smem_u32(sdO), CHUNK_BYTES),
+                     ds_m = smem_desc_lo(smem_u32(sdS), CHUNK_BYTES), q_m = smem_desc_lo(smem_u32(sQ), CHUNK_BYTES),
+                     k_m = smem_desc_lo(smem_u32(sK), CHUNK_BYTES);
+      auto desc = [&](uint32_t lo, uint32_t off_bytes) { return smem_desc_join(lo + (off_bytes >> 4), dhi); };
       bool ok = mbar_wait(&bars->kv_full, 0);
       if (!ok) atomicCAS(P.err, 0, 402);
       for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
@@ -197,16 +208,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
-          umma_f16(tm_s, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), id_s,
-                   kk != 0);
+          umma_f16(tm_s, desc(q_k, off), desc(k_k, off), id_s, kk != 0);
         }
         umma_commit(&bars->s_full);
         if (!mbar_wait(&bars->do_full, ph)) { atomicCAS(P.err, 0, 414); ok = false; break; }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
-          umma_f16(tm_dp, make_smem_desc(aDO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024), id_s,
-                   kk != 0);
+          umma_f16(tm_dp, desc(do_k, off), desc(v_k, off), id_s, kk != 0);
         }
         umma_commit(&bars->dp_full);
         stamp(1, 3, it);
@@ -216,8 +225,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {       // reduction over the 128 query rows
           const uint32_t row_off = kk * 2048;
-          umma_f16(tm_dv, make_smem_desc(aP + row_off, CHUNK_BYTES, 1024),
-                   make_smem_desc(aDO + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
+          umma_f16(tm_dv, desc(p_m, row_off), desc(do_m, row_off), id_t, (it | kk) != 0);
         }
         umma_commit(&bars->do_empty);
         stamp(1, 5, it);
@@ -227,15 +235,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {
           const uint32_t row_off = kk * 2048;
-          umma_f16(tm_dk, make_smem_desc(aDS + row_off, CHUNK_BYTES, 1024),
-                   make_smem_desc(aQ + row_off, CHUNK_BYTES, 1024), id_t, (it | kk) != 0);
+          umma_f16(tm_dk, desc(ds_m, row_off), desc(q_m, row_off), id_t, (it | kk) != 0);
         }
         umma_commit(&bars->q_empty);
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {      // reduction over the 128 kv rows
           const uint32_t a_off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
-          umma_f16(tm_dq, make_smem_desc(aDS + a_off, 16, 1024),
-                   make_smem_desc(aK + kk * 2048, CHUNK_BYTES, 1024), id_q, kk != 0);
+          umma_f16(tm_dq, desc(ds_k, a_off), desc(k_m, kk * 2048), id_q, kk != 0);
         }
         umma_commit(&bars->dq_full);
         stamp(1, 7, it);

@@ -131,18 +131,28 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = make_idesc_f16(AB, 0, 0, BQ, BKV);      // Q, K both K-major
       constexpr uint32_t idesc_o = make_idesc_f16(AB, 0, 1, BQ, D);        // P (tmem) K-major, V MN-major
-      const uint32_t q_addr = smem_u32(sQ);
+      // descriptor halves prepared once: per instruction this thread then spends an integer add
+      // or two, which is what lets it feed the pipe a 128-wide instruction every 64 clocks
+      // (csrc/kernels/mma_probe.cu)
+      constexpr uint32_t dhi = smem_desc_hi(1024);
+      const uint32_t q_lo[2] = {smem_desc_lo(smem_u32(sQ), 16), smem_desc_lo(smem_u32(sQ + TILE), 16)};
+      uint32_t k_lo[KV_STAGES], v_lo[KV_STAGES];
+#pragma unroll
+      for (int s = 0; s < KV_STAGES; ++s) {
+        k_lo[s] = smem_desc_lo(smem_u32(sK + s * TILE), 16);
+        v_lo[s] = smem_desc_lo(smem_u32(sV + s * TILE), CHUNK_BYTES);
+      }
       bool ok = true;
       auto qk = [&](int t, int j) {
         const int s = j % KV_STAGES;
         if (!mbar_wait(&bars->k_full[s], (j / KV_STAGES) & 1)) { atomicCAS(P.err, 0, 323); ok = false; return; }
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + s * TILE);
+        const uint32_t ql = q_lo[t], kl = k_lo[s];
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
-          umma_f16(tmem + t * 128, make_smem_desc(q_addr + t * TILE + off, 16, 1024),
-                   make_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0);
+          const uint32_t off = ((kk / 4) * CHUNK_BYTES + (kk % 4) * 32) >> 4;
+          umma_f16(tmem + t * 128, smem_desc_join(ql + off, dhi), smem_desc_join(kl + off, dhi), idesc_s,
+                   kk != 0);
         }
         if (t == 1 || j >= n1) umma_commit(&bars->k_empty[s]);       // last reader of K_j
         umma_commit(&bars->s_full[t]);
@@ -152,11 +162,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (!mbar_wait(&bars->v_full[s], (j / KV_STAGES) & 1)) { atomicCAS(P.err, 0, 324); ok = false; return; }
         if (!mbar_wait(&bars->p_full[t], j & 1)) { atomicCAS(P.err, 0, 325); ok = false; return; }
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(sV + s * TILE);
+        const uint32_t vl = v_lo[s];
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)
-          umma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
-                      make_smem_desc(v_addr + kk * 2048, CHUNK_BYTES, 1024), idesc_o, (j | kk) != 0);
+          umma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, smem_desc_join(vl + kk * 128, dhi), idesc_o,
+                      (j | kk) != 0);
         if (t == 1 || j >= n1) umma_commit(&bars->v_empty[s]);       // last reader of V_j
         umma_commit(&bars->o_full[t]);
       };
