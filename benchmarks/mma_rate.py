@@ -32,6 +32,8 @@ MODES = (
     (9, 256, "two independent mode-1 products, instructions interleaved (clocks per pair)"),
     (10, 256, "two independent mode-3 products, instructions interleaved (clocks per pair)"),
     (11, 128, "mode 0 with every descriptor built from the tile address inside the issue loop"),
+    (12, 128, "mode 0, tile address changing per round, issued inside `if (lane == 0)`"),
+    (13, 128, "mode 0, tile address changing per round, issued by an elected lane of a whole warp"),
 )
 
 

@@ -18,6 +18,10 @@
 //   mode 9  mode 1 likewise          mode 10  mode 3 likewise
 //   mode 11 mode 0 with each instruction's descriptors built from the tile address inside the loop
 //           (every other mode adds a constant to a descriptor half prepared before the loop)
+//   mode 12 mode 0 with tile addresses that change from round to round (as a kernel's stages do),
+//           issued from inside `if (lane == 0)`
+//   mode 13 the same issued by an elected lane of a warp that runs the loop as a whole, so that the
+//           descriptor arithmetic is warp-uniform
 #include "common.cuh"
 #include "gemm_host.h"
 #include "tcgen05.cuh"
@@ -38,7 +42,7 @@ struct ProbeBars {
 };
 
 __global__ void __launch_bounds__(kProbeThreads, 1)
-mma_probe_kernel(int mode, int rounds, long long* __restrict__ out, int* __restrict__ err) {
+mma_probe_kernel(int mode, int rounds, int wobble, long long* __restrict__ out, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -62,8 +66,53 @@ mma_probe_kernel(int mode, int rounds, long long* __restrict__ out, int* __restr
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0) {
-    if (lane == 0) {
+  if (warp == 0 && mode == 13) {
+    // the whole warp runs the loop; one elected lane issues
+    const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
+    constexpr uint32_t idesc = make_idesc_f16(1, 0, 0, 128, 128);
+    constexpr uint32_t hi = smem_desc_hi(1024);
+    const long long t0 = clock64();
+    for (int r = 0; r < rounds; ++r) {
+      const uint32_t a_lo = smem_desc_lo(aA + (r & 1) * wobble, 16), b_lo = smem_desc_lo(aB + (r & 1) * wobble, 16);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t off = ((kk / 4) * kChunk + (kk % 4) * 32) >> 4;
+        if (elect_one())
+          umma_f16(tmem + 256, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi), idesc, (r | kk) != 0);
+        __syncwarp();
+      }
+    }
+    bool ok = true;
+    if (elect_one()) {
+      umma_commit(&bars->done);
+      ok = mbar_wait(&bars->done, 0);
+      const long long t1 = clock64();
+      if (!ok) atomicCAS(err, 0, 501);
+      out[blockIdx.x] = t1 - t0;
+      bars->stop = 1;
+    }
+    __syncwarp();
+  } else if (warp == 0) {
+    if (lane == 0 && mode == 12) {
+      const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
+      constexpr uint32_t idesc = make_idesc_f16(1, 0, 0, 128, 128);
+      constexpr uint32_t hi = smem_desc_hi(1024);
+      const long long t0 = clock64();
+      for (int r = 0; r < rounds; ++r) {
+        const uint32_t a_lo = smem_desc_lo(aA + (r & 1) * wobble, 16), b_lo = smem_desc_lo(aB + (r & 1) * wobble, 16);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = ((kk / 4) * kChunk + (kk % 4) * 32) >> 4;
+          umma_f16(tmem + 256, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi), idesc, (r | kk) != 0);
+        }
+      }
+      umma_commit(&bars->done);
+      const bool ok = mbar_wait(&bars->done, 0);
+      const long long t1 = clock64();
+      if (!ok) atomicCAS(err, 0, 501);
+      out[blockIdx.x] = t1 - t0;
+      bars->stop = 1;
+    } else if (lane == 0) {
       const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
       const bool two = mode >= 8 && mode <= 10;      // two accumulators, instructions alternating
       const bool rebuilt = mode == 11;               // mode 0 with every descriptor built from scratch
@@ -150,7 +199,7 @@ extern "C" {
 
 // out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
 int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
-  if (mode < 0 || mode > 11 || rounds < 1 || rounds > 4096) return -1;
+  if (mode < 0 || mode > 13 || rounds < 1 || rounds > 4096) return -1;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured = false;
@@ -158,7 +207,8 @@ int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
     cudaFuncSetAttribute(mma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     configured = true;
   }
-  mma_probe_kernel<<<ft::gemm::sm_count(dev), kProbeThreads, kSmem, stream>>>(mode, rounds, out,
+  // the third argument is a tile offset the compiler cannot see is zero (modes 12 and 13)
+  mma_probe_kernel<<<ft::gemm::sm_count(dev), kProbeThreads, kSmem, stream>>>(mode, rounds, 0, out,
                                                                               ft::gemm::error_word(dev));
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
