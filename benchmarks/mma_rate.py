@@ -34,6 +34,11 @@ MODES = (
     (11, 128, "mode 0 with every descriptor built from the tile address inside the issue loop"),
     (12, 128, "mode 0, tile address changing per round, issued inside `if (lane == 0)`"),
     (13, 128, "mode 0, tile address changing per round, issued by an elected lane of a whole warp"),
+    (14, 128, "mode 12 + a commit after every product"),
+    (15, 128, "mode 12 + a tcgen05 fence before every product"),
+    (16, 128, "mode 12 + an mbarrier wait that succeeds at once before every product"),
+    (17, 128, "mode 12 + wait, fence and commit"),
+    (18, 128, "mode 17 with the accumulator rotating over four regions"),
 )
 
 

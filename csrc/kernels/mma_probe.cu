@@ -20,6 +20,10 @@
 //           (every other mode adds a constant to a descriptor half prepared before the loop)
 //   mode 12 mode 0 with tile addresses that change from round to round (as a kernel's stages do),
 //           issued from inside `if (lane == 0)`
+//   modes 14-18: mode 12 plus, per product, what a pipelined kernel does around it:
+//           14 a tcgen05.commit to a barrier nobody waits on   15 a tcgen05.fence::after_thread_sync
+//           16 an mbarrier try_wait that succeeds at once      17 all three
+//           18 all three, and the accumulator rotating over four regions of tensor memory
 //   mode 13 the same issued by an elected lane of a warp that runs the loop as a whole, so that the
 //           descriptor arithmetic is warp-uniform
 #include "common.cuh"
@@ -36,7 +40,7 @@ constexpr int kChunk = 128 * 128;                    // [128 rows][64 columns] o
 constexpr int kSmem = 2 * kChunk /* A */ + 4 * kChunk /* B, up to 256 rows */ + 32 * 1024 /* scratch */ + 2048;
 
 struct ProbeBars {
-  uint64_t done;
+  uint64_t done, idle, fresh;
   uint32_t tmem_base;
   volatile uint32_t stop;
 };
@@ -56,6 +60,8 @@ mma_probe_kernel(int mode, int rounds, int wobble, long long* __restrict__ out, 
     reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
   if (threadIdx.x == 0) {
     mbar_init(&bars->done, 1);
+    mbar_init(&bars->idle, 1);                       // receives commits, nobody waits
+    mbar_init(&bars->fresh, 1);                      // never completes: waiting for parity 1 succeeds at once
     bars->stop = 0;
     fence_barrier_init();
   }
@@ -93,18 +99,24 @@ mma_probe_kernel(int mode, int rounds, int wobble, long long* __restrict__ out, 
     }
     __syncwarp();
   } else if (warp == 0) {
-    if (lane == 0 && mode == 12) {
+    if (lane == 0 && mode >= 12 && mode != 13) {
+      const bool with_commit = mode == 14 || mode >= 17, with_fence = mode == 15 || mode >= 17,
+                 with_wait = mode == 16 || mode >= 17, rotate = mode == 18;
       const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
       constexpr uint32_t idesc = make_idesc_f16(1, 0, 0, 128, 128);
       constexpr uint32_t hi = smem_desc_hi(1024);
       const long long t0 = clock64();
       for (int r = 0; r < rounds; ++r) {
         const uint32_t a_lo = smem_desc_lo(aA + (r & 1) * wobble, 16), b_lo = smem_desc_lo(aB + (r & 1) * wobble, 16);
+        const uint32_t acc = tmem + (rotate ? (r & 3) * 128 : 256);
+        if (with_wait && !mbar_wait(&bars->fresh, 1)) break;
+        if (with_fence) tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = ((kk / 4) * kChunk + (kk % 4) * 32) >> 4;
-          umma_f16(tmem + 256, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi), idesc, (r | kk) != 0);
+          umma_f16(acc, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi), idesc, (r | kk) != 0);
         }
+        if (with_commit) umma_commit(&bars->idle);
       }
       umma_commit(&bars->done);
       const bool ok = mbar_wait(&bars->done, 0);
@@ -199,7 +211,7 @@ extern "C" {
 
 // out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
 int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
-  if (mode < 0 || mode > 13 || rounds < 1 || rounds > 4096) return -1;
+  if (mode < 0 || mode > 18 || rounds < 1 || rounds > 4096) return -1;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured = false;
