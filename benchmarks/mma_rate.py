@@ -39,6 +39,8 @@ MODES = (
     (16, 128, "mode 12 + an mbarrier wait that succeeds at once before every product"),
     (17, 128, "mode 12 + wait, fence and commit"),
     (18, 128, "mode 17 with the accumulator rotating over four regions"),
+    (19, 128, "wait + fence + product + commit, no run-time switches, inside `if (lane == 0)`"),
+    (20, 128, "wait + fence + product + commit, whole warp with an elected issuer"),
 )
 
 

@@ -24,6 +24,8 @@
 //           14 a tcgen05.commit to a barrier nobody waits on   15 a tcgen05.fence::after_thread_sync
 //           16 an mbarrier try_wait that succeeds at once      17 all three
 //           18 all three, and the accumulator rotating over four regions of tensor memory
+//   mode 19 wait + fence + product + commit, accumulator rotating, written without run-time switches,
+//           inside `if (lane == 0)`        mode 20 the same, whole warp with an elected issuer
 //   mode 13 the same issued by an elected lane of a warp that runs the loop as a whole, so that the
 //           descriptor arithmetic is warp-uniform
 #include "common.cuh"
@@ -72,7 +74,63 @@ mma_probe_kernel(int mode, int rounds, int wobble, long long* __restrict__ out, 
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0 && mode == 13) {
+  if (warp == 0 && mode == 20) {
+    const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
+    constexpr uint32_t idesc = make_idesc_f16(1, 0, 0, 128, 128);
+    constexpr uint32_t hi = smem_desc_hi(1024);
+    const long long t0 = clock64();
+    bool ok = true;
+    for (int r = 0; r < rounds && ok; ++r) {
+      const uint32_t a_lo = smem_desc_lo(aA + (r & 1) * wobble, 16), b_lo = smem_desc_lo(aB + (r & 1) * wobble, 16);
+      const uint32_t acc = tmem + (r & 3) * 128;
+      ok = mbar_wait(&bars->fresh, 1);               // every lane waits: uniform
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = ((kk / 4) * kChunk + (kk % 4) * 32) >> 4;
+          umma_f16(acc, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi), idesc, (r | kk) != 0);
+        }
+        umma_commit(&bars->idle);
+      }
+      __syncwarp();
+    }
+    if (elect_one()) {
+      umma_commit(&bars->done);
+      ok = ok && mbar_wait(&bars->done, 0);
+      const long long t1 = clock64();
+      if (!ok) atomicCAS(err, 0, 501);
+      out[blockIdx.x] = t1 - t0;
+      bars->stop = 1;
+    }
+    __syncwarp();
+  } else if (warp == 0 && mode == 19) {
+    if (lane == 0) {
+      const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
+      constexpr uint32_t idesc = make_idesc_f16(1, 0, 0, 128, 128);
+      constexpr uint32_t hi = smem_desc_hi(1024);
+      const long long t0 = clock64();
+      bool ok = true;
+      for (int r = 0; r < rounds; ++r) {
+        const uint32_t a_lo = smem_desc_lo(aA + (r & 1) * wobble, 16), b_lo = smem_desc_lo(aB + (r & 1) * wobble, 16);
+        const uint32_t acc = tmem + (r & 3) * 128;
+        if (!mbar_wait(&bars->fresh, 1)) { atomicCAS(err, 0, 502); ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = ((kk / 4) * kChunk + (kk % 4) * 32) >> 4;
+          umma_f16(acc, smem_desc_join(a_lo + off, hi), smem_desc_join(b_lo + off, hi), idesc, (r | kk) != 0);
+        }
+        umma_commit(&bars->idle);
+      }
+      umma_commit(&bars->done);
+      ok = ok && mbar_wait(&bars->done, 0);
+      const long long t1 = clock64();
+      if (!ok) atomicCAS(err, 0, 501);
+      out[blockIdx.x] = t1 - t0;
+      bars->stop = 1;
+    }
+  } else if (warp == 0 && mode == 13) {
     // the whole warp runs the loop; one elected lane issues
     const uint32_t aA = smem_u32(sA), aB = smem_u32(sB);
     constexpr uint32_t idesc = make_idesc_f16(1, 0, 0, 128, 128);
@@ -211,7 +269,7 @@ extern "C" {
 
 // out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
 int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
-  if (mode < 0 || mode > 18 || rounds < 1 || rounds > 4096) return -1;
+  if (mode < 0 || mode > 20 || rounds < 1 || rounds > 4096) return -1;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured = false;
