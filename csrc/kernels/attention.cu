@@ -94,7 +94,7 @@ extern "C" {
 // o[B,S,Hq,D], lse[B,Hq,S] <- causal attention of q[B,S,Hq,D], k/v[B,S,Hkv,D].
 // *_stride: elements between consecutive tokens of that tensor.  D in {64, 128}.
 // ft_attn_fwd_traced additionally records the timeline of one CTA: `trace` is nullptr or a device
-// buffer of 4 * 8 * 8 clock values (see FwdParams).
+// buffer of 3 * 8 * 8 clock values (see FwdParams).
 int ft_attn_fwd_traced(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
                        int64_t v_stride, void* o, float* lse, int B, int S, int Hq, int Hkv, int D,
                        float scale, int dtype, cudaStream_t stream, long long* trace, int trace_cta,

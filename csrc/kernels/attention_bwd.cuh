@@ -203,6 +203,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (!mbar_wait(&bars->q_full, ph)) { atomicCAS(P.err, 0, 403); ok = false; break; }
         stamp(1, 1, it);
         if (!mbar_wait(&bars->s_free, ph ^ 1)) { atomicCAS(P.err, 0, 404); ok = false; break; }
+        // dO landed before Q did (it is released first); waiting for it here keeps the sixteen
+        // instructions of S and dP back to back
+        if (!mbar_wait(&bars->do_full, ph)) { atomicCAS(P.err, 0, 414); ok = false; break; }
         stamp(1, 2, it);
         tc_fence_after();
 #pragma unroll
@@ -211,7 +214,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_s, desc(q_k, off), desc(k_k, off), id_s, kk != 0);
         }
         umma_commit(&bars->s_full);
-        if (!mbar_wait(&bars->do_full, ph)) { atomicCAS(P.err, 0, 414); ok = false; break; }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;

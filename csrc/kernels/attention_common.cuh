@@ -21,7 +21,7 @@ struct FwdParams {
   int q_col0, k_col0, v_col0;   // column of head 0 inside the respective tensor map rows
   int* err;
   // timeline capture (TRACE instantiation only): clock64() of CTA trace_cta at the hand-over points
-  // of K/V blocks trace_it0 .. trace_it0 + 7, as trace[(role * 8 + site) * 8 + block], roles 0..3
+  // of K/V blocks trace_it0 .. trace_it0 + 7, as trace[(role * 8 + site) * 8 + block]
   long long* trace;
   int trace_cta, trace_it0;
 };

@@ -4,7 +4,7 @@
 // share every K/V block that streams through a 2-stage TMA ring, and while the
 // softmax of one tile runs the tensor core works on the other tile:
 //   warp 0      TMA producer (Q tiles once, then K_j / V_j)
-//   warp 1      MMA issuer of tile 0, warp 10 of tile 1, each in the order PV(j) QK(j+1)
+//   warp 1      MMA issuer, in the order  PV0(j) QK0(j+1) PV1(j) QK1(j+1)
 //   warps 2-5   softmax of tile 0;  warps 6-9  softmax of tile 1 (one row per thread)
 // Tensor memory (512 columns): S0 | S1 | O0 | O1.  The probabilities P_j are
 // written back into the first 64 columns of their S buffer as packed 16-bit pairs
@@ -23,7 +23,7 @@
 namespace ft {
 namespace attn {
 
-constexpr int F2_THREADS = 352;
+constexpr int F2_THREADS = 320;
 constexpr float kRescaleLog2 = 8.f;
 
 template <int D>
@@ -71,7 +71,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int n0 = qb0 + 1;                            // K/V blocks tile 0 needs (causal)
   const int n1 = qb1 < num_qb ? qb1 + 1 : 0;         // tile 1 may not exist
   const int nmax = n0 > n1 ? n0 : n1;
-  // role: 0 / 3 issuing thread of tile 0 / 1, 1 / 2 first softmax warp of tile 0 / 1
+  // role: 0 product warp, 1 first softmax warp of tile 0, 2 first softmax warp of tile 1
   auto stamp = [&](int role, int site, int j) {
     if constexpr (TRACE) {
       if ((int)blockIdx.x == P.trace_cta && j >= P.trace_it0 && j < P.trace_it0 + 8)
@@ -82,8 +82,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 2);     // both issuing threads
-      mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 2);
+      mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&bars->s_full[t], 1);
@@ -125,71 +125,79 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                       P.v_col0 + kv_head * D + c * 64, kv_row0);
       }
     }
-  } else if (warp == 1 || warp == F2_THREADS / 32 - 1) {
+  } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA
-    // One issuing thread per tile (warp 1: tile 0, the last warp: tile 1).  The tensor pipe takes
-    // instructions from both, so while one thread is between products - waiting on a barrier,
-    // committing - the other's instructions keep the pipe busy; with a single issuer those gaps
-    // cost 150-250 clocks per 512-clock product (csrc/kernels/mma_probe.cu, modes 13 / 19 / 20).
-    // Each thread walks all nmax blocks and arrives once per block on the K and on the V stage it
-    // belongs to (a commit behind its own product, a plain arrive for a block its tile has not).
-    if (lane == 0) {
-      const int t = warp == 1 ? 0 : 1;
-      const int n_t = t ? n1 : n0;
-      constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idesc_s = make_idesc_f16(AB, 0, 0, BQ, BKV);      // Q, K both K-major
-      constexpr uint32_t idesc_o = make_idesc_f16(AB, 0, 1, BQ, D);        // P (tmem) K-major, V MN-major
-      constexpr uint32_t dhi = smem_desc_hi(1024);
-      const uint32_t ql = smem_desc_lo(smem_u32(sQ + t * TILE), 16);
-      uint32_t k_lo[KV_STAGES], v_lo[KV_STAGES];
+    // The whole warp runs this loop and one elected lane issues: with warp-uniform control flow
+    // around them the waits, fences and commits between two products cost the issuing thread
+    // less, and what they cost is time the tensor pipe stands still (its queue covers about two
+    // 128-wide instructions; csrc/kernels/mma_probe.cu, modes 13 / 19 / 20).  K_j and V_j are
+    // waited for once per block, not once per tile.
+    constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+    constexpr uint32_t idesc_s = make_idesc_f16(AB, 0, 0, BQ, BKV);      // Q, K both K-major
+    constexpr uint32_t idesc_o = make_idesc_f16(AB, 0, 1, BQ, D);        // P (tmem) K-major, V MN-major
+    constexpr uint32_t dhi = smem_desc_hi(1024);
+    const uint32_t q_lo[2] = {smem_desc_lo(smem_u32(sQ), 16), smem_desc_lo(smem_u32(sQ + TILE), 16)};
+    uint32_t k_lo[KV_STAGES], v_lo[KV_STAGES];
 #pragma unroll
-      for (int s = 0; s < KV_STAGES; ++s) {
-        k_lo[s] = smem_desc_lo(smem_u32(sK + s * TILE), 16);
-        v_lo[s] = smem_desc_lo(smem_u32(sV + s * TILE), CHUNK_BYTES);
-      }
-      const uint32_t tm_s = tmem + t * 128, tm_o = tmem + 256 + t * 128;
-      bool ok = true;
-      auto k_step = [&](int j) {                       // S_t = Q_t K_j^T, or just the arrival
-        const int s = j % KV_STAGES;
-        // also a tile without this block waits until the block has landed: its arrivals must not
-        // run ahead of the other tile's by more than the ring, or a stage would be released twice
-        // by one thread
-        if (!mbar_wait(&bars->k_full[s], (j / KV_STAGES) & 1)) { atomicCAS(P.err, 0, 323); ok = false; return; }
-        if (j >= n_t) { mbar_arrive(&bars->k_empty[s]); return; }
-        tc_fence_after();
-        const uint32_t kl = k_lo[s];
+    for (int s = 0; s < KV_STAGES; ++s) {
+      k_lo[s] = smem_desc_lo(smem_u32(sK + s * TILE), 16);
+      v_lo[s] = smem_desc_lo(smem_u32(sV + s * TILE), CHUNK_BYTES);
+    }
+    bool ok = true;
+    auto fail = [&](int code) { if (lane == 0) atomicCAS(P.err, 0, code); ok = false; };
+    // the lanes poll on their own, so a wait that runs out is made the whole warp's verdict
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
+    };
+    // first = this is the first product that reads K_j (V_j): wait for the block to land
+    auto qk = [&](int t, int j, bool first) {
+      const int s = j % KV_STAGES;
+      if (first && !wait_all(&bars->k_full[s], (j / KV_STAGES) & 1)) { fail(323); return; }
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t ql = q_lo[t], kl = k_lo[s];
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk / 4) * CHUNK_BYTES + (kk % 4) * 32) >> 4;
-          umma_f16(tm_s, smem_desc_join(ql + off, dhi), smem_desc_join(kl + off, dhi), idesc_s, kk != 0);
+          umma_f16(tmem + t * 128, smem_desc_join(ql + off, dhi), smem_desc_join(kl + off, dhi), idesc_s,
+                   kk != 0);
         }
-        umma_commit(&bars->k_empty[s]);
+        if (t == 1 || j >= n1) umma_commit(&bars->k_empty[s]);       // last reader of K_j
         umma_commit(&bars->s_full[t]);
-      };
-      auto v_step = [&](int j) {                       // O_t += P_t V_j, or just the arrival
-        const int s = j % KV_STAGES;
-        if (!mbar_wait(&bars->v_full[s], (j / KV_STAGES) & 1)) { atomicCAS(P.err, 0, 324); ok = false; return; }
-        if (j >= n_t) { mbar_arrive(&bars->v_empty[s]); return; }
-        if (!mbar_wait(&bars->p_full[t], j & 1)) { atomicCAS(P.err, 0, 325); ok = false; return; }
-        tc_fence_after();
+      }
+      __syncwarp();
+    };
+    auto pv = [&](int t, int j, bool first) {
+      const int s = j % KV_STAGES;
+      if (first && !wait_all(&bars->v_full[s], (j / KV_STAGES) & 1)) { fail(324); return; }
+      if (!wait_all(&bars->p_full[t], j & 1)) { fail(325); return; }
+      tc_fence_after();
+      if (elect_one()) {
         const uint32_t vl = v_lo[s];
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)
-          umma_f16_ts(tm_o, tm_s + kk * 8, smem_desc_join(vl + kk * 128, dhi), idesc_o, (j | kk) != 0);
-        umma_commit(&bars->v_empty[s]);
+          umma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, smem_desc_join(vl + kk * 128, dhi), idesc_o,
+                      (j | kk) != 0);
+        if (t == 1 || j >= n1) umma_commit(&bars->v_empty[s]);       // last reader of V_j
         umma_commit(&bars->o_full[t]);
-      };
-      if (!mbar_wait(&bars->q_full, 0)) { atomicCAS(P.err, 0, 320); ok = false; }
-      if (ok) k_step(0);
-      for (int j = 0; j < nmax && ok && !*abort_flag; ++j) {
-        stamp(3 * t, 0, j);
-        v_step(j);
-        stamp(3 * t, 1, j);
-        if (ok && j + 1 < nmax) k_step(j + 1);
-        stamp(3 * t, 2, j);
       }
-      if (!ok) *abort_flag = 1;
+      __syncwarp();
+    };
+    if (!wait_all(&bars->q_full, 0)) fail(320);
+    if (ok) qk(0, 0, true);
+    if (ok && n1 > 0) qk(1, 0, false);
+    for (int j = 0; j < nmax && ok && !*abort_flag; ++j) {
+      if (lane == 0) stamp(0, 0, j);
+      if (j < n0) pv(0, j, true);
+      if (lane == 0) stamp(0, 1, j);
+      if (ok && j + 1 < n0) qk(0, j + 1, true);
+      if (lane == 0) stamp(0, 2, j);
+      if (ok && j < n1) pv(1, j, j >= n0);
+      if (lane == 0) stamp(0, 3, j);
+      if (ok && j + 1 < n1) qk(1, j + 1, j + 1 >= n0);
+      if (lane == 0) stamp(0, 4, j);
     }
+    if (!ok) *abort_flag = 1;
   } else {
     // ------------------------------------------------------------ softmax
     const int t = (warp - 2) >> 2;
