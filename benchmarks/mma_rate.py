@@ -5,7 +5,8 @@
 
 Runs ``ft_mma_probe`` (csrc/kernels/mma_probe.cu) in each mode: one CTA per SM issues
 ``--rounds`` products of eight 128xNx16 instructions back to back on fixed tiles and times
-them with clock64().  Prints the median over the CTAs of clocks per product, and the fraction
+them with clock64(); modes 5 and 6 put between the products what a pipelined kernel has
+there (a barrier wait, a fence, a commit).  Prints the median over the CTAs of clocks per product, and the fraction
 of the tensor pipe's rate that is (a 128x128x128 product is 512 clocks at 8192 dense bf16
 FLOP per clock and SM, a 128x256x128 product 1024).
 """
@@ -20,29 +21,17 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from flextrain_b200.ops.native import cuda_lib, ptr, stream_handle  # noqa: E402
 
 MODES = (
-    (0, 128, "A, B K-major in shared memory (S = Q K^T, dP = dO V^T)"),
+    (0, 128, "A, B K-major in shared memory (S = Q K^T, dP = dO V^T); nothing between the products"),
     (1, 128, "A, B MN-major in shared memory (dV = P^T dO, dK = dS^T Q)"),
     (2, 128, "A K-major, B MN-major in shared memory (dQ = dS K)"),
     (3, 128, "A in tensor memory, B MN-major (O += P V)"),
     (4, 256, "A, B K-major in shared memory, N = 256"),
-    (5, 128, "mode 0 while four warps keep loading tensor memory"),
-    (6, 128, "mode 0 while four warps keep storing to shared memory"),
-    (7, 128, "mode 3 while four warps keep loading tensor memory"),
-    (8, 256, "two independent mode-0 products, instructions interleaved (clocks per pair)"),
-    (9, 256, "two independent mode-1 products, instructions interleaved (clocks per pair)"),
-    (10, 256, "two independent mode-3 products, instructions interleaved (clocks per pair)"),
-    (11, 128, "mode 0 with every descriptor built from the tile address inside the issue loop"),
-    (12, 128, "mode 0, tile address changing per round, issued inside `if (lane == 0)`"),
-    (13, 128, "mode 0, tile address changing per round, issued by an elected lane of a whole warp"),
-    (14, 128, "mode 12 + a commit after every product"),
-    (15, 128, "mode 12 + a tcgen05 fence before every product"),
-    (16, 128, "mode 12 + an mbarrier wait that succeeds at once before every product"),
-    (17, 128, "mode 12 + wait, fence and commit"),
-    (18, 128, "mode 17 with the accumulator rotating over four regions"),
-    (19, 128, "wait + fence + product + commit, no run-time switches, inside `if (lane == 0)`"),
-    (20, 128, "wait + fence + product + commit, whole warp with an elected issuer"),
+    (5, 128, "mode 0 + per product: barrier wait, fence, commit; issued inside `if (lane == 0)`"),
+    (6, 128, "mode 0 + per product: barrier wait, fence, commit; whole warp, elected issuer"),
+    (7, 128, "mode 0 while four warps keep loading tensor memory"),
+    (8, 128, "mode 0 while four warps keep storing to shared memory"),
+    (9, 128, "mode 3 while four warps keep loading tensor memory"),
 )
-
 
 def main():
     ap = argparse.ArgumentParser()
