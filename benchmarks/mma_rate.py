@@ -31,6 +31,7 @@ MODES = (
     (7, 128, "mode 0 while four warps keep loading tensor memory"),
     (8, 128, "mode 0 while four warps keep storing to shared memory"),
     (9, 128, "mode 3 while four warps keep loading tensor memory"),
+    (10, 128, "mode 6 with the next product's barrier looked at between this product's 6th and 7th instruction"),
 )
 
 def main():

@@ -20,10 +20,13 @@
 //                  1  per product: barrier wait (succeeds at once), tcgen05 fence, product, commit;
 //                     issued inside `if (lane == 0)`
 //                  2  the same, whole warp with an elected issuer
+//                  3  as 2, but the barrier of the NEXT product is looked at (mbarrier.test_wait)
+//                     between the sixth and the seventh instruction of this one, while the pipe
+//                     still has queued work; the blocking wait remains only for a miss
 // Others (DISTURB): 0 idle   1 four warps keep loading tensor memory   2 four warps keep storing
 //                     to shared memory
 //   mode = OPS (0-4, STYLE 0, idle) | 5, 6 = OPS 0 with STYLE 1, 2 | 7, 8 = OPS 0, STYLE 0 with
-//   DISTURB 1, 2 | 9 = OPS 3, STYLE 0, DISTURB 1
+//   DISTURB 1, 2 | 9 = OPS 3, STYLE 0, DISTURB 1 | 10 = OPS 0 with STYLE 3
 #include "common.cuh"
 #include "gemm_host.h"
 #include "tcgen05.cuh"
@@ -44,14 +47,14 @@ struct ProbeBars {
 };
 
 // One product: eight instructions on the tiles at offsets a_off / b_off (bytes, uniform).
-template <int OPS>
+template <int OPS, int KK0 = 0, int KK1 = 8>
 __device__ __forceinline__ void issue_product(uint32_t acc, uint32_t tmem_a, uint32_t aA, uint32_t aB, bool first) {
   constexpr uint32_t hi = smem_desc_hi(1024);
   constexpr uint32_t idesc = make_idesc_f16(1, OPS == 1, OPS == 1 || OPS == 2 || OPS == 3, 128, OPS == 4 ? 256 : 128);
   const uint32_t a_lo = smem_desc_lo(aA, OPS == 1 ? kChunk : 16);
   const uint32_t b_lo = smem_desc_lo(aB, (OPS == 0 || OPS == 4) ? 16 : kChunk);
 #pragma unroll
-  for (int kk = 0; kk < 8; ++kk) {
+  for (int kk = KK0; kk < KK1; ++kk) {
     const uint32_t k_off = ((kk / 4) * kChunk + (kk % 4) * 32) >> 4;            // K-major, 128 rows
     const uint32_t k_off256 = ((kk / 4) * 2 * kChunk + (kk % 4) * 32) >> 4;     // K-major, 256 rows
     const uint32_t mn_off = (kk * 2048) >> 4;                                    // MN-major
@@ -111,6 +114,31 @@ mma_probe_kernel(int rounds, int wobble, long long* __restrict__ out, int* __res
         out[blockIdx.x] = t1 - t0;
         bars->stop = 1;
       }
+    } else if constexpr (STYLE == 3) {
+      const long long t0 = clock64();
+      bool ok = true, ready = false;
+      for (int r = 0; r < rounds && ok; ++r) {
+        if (!ready) ok = __all_sync(0xffffffffu, mbar_wait(&bars->fresh, 1)) != 0;
+        tc_fence_after();
+        if (elect_one())
+          issue_product<OPS, 0, 6>(tmem + 256, tmem, aA + (r & 1) * wobble, aB + (r & 1) * wobble, r == 0);
+        __syncwarp();
+        ready = __all_sync(0xffffffffu, mbar_test(&bars->fresh, 1)) != 0;     // next product's barrier
+        if (elect_one()) {
+          issue_product<OPS, 6, 8>(tmem + 256, tmem, aA + (r & 1) * wobble, aB + (r & 1) * wobble, false);
+          umma_commit(&bars->idle);
+        }
+        __syncwarp();
+      }
+      if (elect_one()) {
+        umma_commit(&bars->done);
+        ok = mbar_wait(&bars->done, 0) && ok;
+        const long long t1 = clock64();
+        if (!ok) atomicCAS(err, 0, 501);
+        out[blockIdx.x] = t1 - t0;
+        bars->stop = 1;
+      }
+      __syncwarp();
     } else {
       const long long t0 = clock64();
       bool ok = true;
@@ -175,7 +203,7 @@ extern "C" {
 
 // out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
 int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
-  if (mode < 0 || mode > 9 || rounds < 1 || rounds > 4096) return -1;
+  if (mode < 0 || mode > 10 || rounds < 1 || rounds > 4096) return -1;
   int dev = 0;
   cudaGetDevice(&dev);
   switch (mode) {
@@ -188,7 +216,8 @@ int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
     case 6: launch_probe<0, 2, 0>(rounds, out, dev, stream); break;
     case 7: launch_probe<0, 0, 1>(rounds, out, dev, stream); break;
     case 8: launch_probe<0, 0, 2>(rounds, out, dev, stream); break;
-    default: launch_probe<3, 0, 1>(rounds, out, dev, stream); break;
+    case 9: launch_probe<3, 0, 1>(rounds, out, dev, stream); break;
+    default: launch_probe<0, 3, 0>(rounds, out, dev, stream); break;
   }
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
