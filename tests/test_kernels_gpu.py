@@ -362,3 +362,27 @@ def test_attention_timeline_instantiations_compute_the_same_and_fill_the_trace()
     t = bbuf.cpu().view(5, 16, 8)
     assert (t[1, :8] > 0).all() and (t[1, 1:8] >= t[1, 0:7]).all()
     assert (t[4, :3] > 0).all() and (t[4, 1:3] >= t[4, 0:2]).all()
+
+
+def test_tensor_pipe_probe_reads_the_full_rate_for_bare_products():
+    """``ft_mma_probe`` (benchmarks/mma_rate.py): back-to-back 128x128x128 products with nothing
+    between them take the pipe's 512 clocks, whether A comes from shared or from tensor memory,
+    and a 128x256x128 product takes 1024."""
+    import ctypes
+    from flextrain_b200.ops.native import cuda_lib, ptr, stream_handle
+    lib = cuda_lib()
+    lib.ft_mma_probe.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    lib.ft_mma_probe.restype = ctypes.c_int
+    sms = torch.cuda.get_device_properties(_dev()).multi_processor_count
+    out = torch.zeros(sms + 1, dtype=torch.int64, device=_dev())
+    for mode, ideal in ((0, 512.0), (3, 512.0), (4, 1024.0), (6, 512.0)):
+        for _ in range(2):
+            out.zero_()
+            assert lib.ft_mma_probe(mode, 500, ptr(out), stream_handle()) == 0
+            torch.cuda.synchronize()
+        per = (out[:sms].float() / 500).median().item()
+        if mode == 6:                                   # with a wait, a fence and a commit per product
+            assert ideal <= per < 2.0 * ideal, (mode, per)
+        else:
+            assert 0.98 * ideal <= per < 1.15 * ideal, (mode, per)
+    assert lib.ft_gemm_error() == 0
