@@ -271,14 +271,15 @@ def test_finite_flag_and_accumulate():
 
 
 @pytest.mark.parametrize("S", [320, 1000])     # 1000: the last block's valid rows end inside a warp
-@pytest.mark.parametrize("hq,hkv,d", [(4, 4, 64), (8, 2, 128)])
-def test_causal_attention(hq, hkv, d, S):
+@pytest.mark.parametrize("hq,hkv,d,dt", [(4, 4, 64, torch.bfloat16), (8, 2, 128, torch.bfloat16),
+                                         (4, 2, 128, torch.float16)])
+def test_causal_attention(hq, hkv, d, dt, S):
     from flextrain_b200.ops.functional import causal_attention
     B = 2
-    q = torch.randn(B, S, hq, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
-    k = torch.randn(B, S, hkv, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
-    v = torch.randn(B, S, hkv, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
-    do = torch.randn(B, S, hq, d, device=_dev(), dtype=torch.bfloat16)
+    q = torch.randn(B, S, hq, d, device=_dev(), dtype=dt, requires_grad=True)
+    k = torch.randn(B, S, hkv, d, device=_dev(), dtype=dt, requires_grad=True)
+    v = torch.randn(B, S, hkv, d, device=_dev(), dtype=dt, requires_grad=True)
+    do = torch.randn(B, S, hq, d, device=_dev(), dtype=dt)
     o = causal_attention(q, k, v)
     o.backward(do)
     qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
