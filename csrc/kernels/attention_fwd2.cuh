@@ -130,7 +130,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // The whole warp runs this loop and one elected lane issues: with warp-uniform control flow
     // around them the waits, fences and commits between two products cost the issuing thread
     // less, and what they cost is time the tensor pipe stands still (its queue covers about two
-    // 128-wide instructions; csrc/kernels/mma_probe.cu, modes 13 / 19 / 20).  K_j and V_j are
+    // 128-wide instructions; csrc/kernels/mma_probe.cu, issue styles 1 and 2).  K_j and V_j are
     // waited for once per block, not once per tile.
     constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
     constexpr uint32_t idesc_s = make_idesc_f16(AB, 0, 0, BQ, BKV);      // Q, K both K-major
@@ -149,53 +149,65 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     auto wait_all = [&](uint64_t* bar, uint32_t parity) {
       return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
     };
-    // first = this is the first product that reads K_j (V_j): wait for the block to land
-    auto qk = [&](int t, int j, bool first) {
+    // S_t = Q_t K_j^T
+    auto qk_issue = [&](int t, int j) {
       const int s = j % KV_STAGES;
-      if (first && !wait_all(&bars->k_full[s], (j / KV_STAGES) & 1)) { fail(323); return; }
-      tc_fence_after();
-      if (elect_one()) {
-        const uint32_t ql = q_lo[t], kl = k_lo[s];
+      const uint32_t ql = q_lo[t], kl = k_lo[s];
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = ((kk / 4) * CHUNK_BYTES + (kk % 4) * 32) >> 4;
-          umma_f16(tmem + t * 128, smem_desc_join(ql + off, dhi), smem_desc_join(kl + off, dhi), idesc_s,
-                   kk != 0);
-        }
-        if (t == 1 || j >= n1) umma_commit(&bars->k_empty[s]);       // last reader of K_j
-        umma_commit(&bars->s_full[t]);
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = ((kk / 4) * CHUNK_BYTES + (kk % 4) * 32) >> 4;
+        umma_f16(tmem + t * 128, smem_desc_join(ql + off, dhi), smem_desc_join(kl + off, dhi), idesc_s, kk != 0);
       }
-      __syncwarp();
+      if (t == 1 || j >= n1) umma_commit(&bars->k_empty[s]);       // last reader of K_j
+      umma_commit(&bars->s_full[t]);
     };
-    auto pv = [&](int t, int j, bool first) {
+    // O_t += P_t V_j
+    auto pv_issue = [&](int t, int j) {
       const int s = j % KV_STAGES;
-      if (first && !wait_all(&bars->v_full[s], (j / KV_STAGES) & 1)) { fail(324); return; }
-      if (!wait_all(&bars->p_full[t], j & 1)) { fail(325); return; }
+      const uint32_t vl = v_lo[s];
+#pragma unroll
+      for (int kk = 0; kk < BKV / 16; ++kk)
+        umma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, smem_desc_join(vl + kk * 128, dhi), idesc_o,
+                    (j | kk) != 0);
+      if (t == 1 || j >= n1) umma_commit(&bars->v_empty[s]);       // last reader of V_j
+      umma_commit(&bars->o_full[t]);
+    };
+    // One hand-over per tile and block: everything PV_t(j) and QK_t(j+1) wait for is waited for
+    // first (K_{j+1} landed long ago, its stage was released a block earlier), then the sixteen
+    // instructions go out back to back with their commits behind them.
+    // first_v / first_k: this tile is the first to read V_j / K_{j+1} and waits for it to land
+    auto tile_step = [&](int t, int j, int n_t, bool first_v, bool first_k) {
+      const bool has_pv = j < n_t, has_qk = j + 1 < n_t;
+      if (has_pv) {
+        if (first_v && !wait_all(&bars->v_full[j % KV_STAGES], (j / KV_STAGES) & 1)) { fail(324); return; }
+        if (!wait_all(&bars->p_full[t], j & 1)) { fail(325); return; }
+      }
+      if (has_qk && first_k &&
+          !wait_all(&bars->k_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1)) { fail(323); return; }
+      if (!has_pv && !has_qk) return;
       tc_fence_after();
       if (elect_one()) {
-        const uint32_t vl = v_lo[s];
-#pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk)
-          umma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, smem_desc_join(vl + kk * 128, dhi), idesc_o,
-                      (j | kk) != 0);
-        if (t == 1 || j >= n1) umma_commit(&bars->v_empty[s]);       // last reader of V_j
-        umma_commit(&bars->o_full[t]);
+        if (has_pv) pv_issue(t, j);
+        if (has_qk) qk_issue(t, j + 1);
       }
       __syncwarp();
     };
     if (!wait_all(&bars->q_full, 0)) fail(320);
-    if (ok) qk(0, 0, true);
-    if (ok && n1 > 0) qk(1, 0, false);
+    if (ok && !wait_all(&bars->k_full[0], 0)) fail(323);
+    if (ok) {
+      tc_fence_after();
+      if (elect_one()) {
+        qk_issue(0, 0);
+        if (n1 > 0) qk_issue(1, 0);
+      }
+      __syncwarp();
+    }
     for (int j = 0; j < nmax && ok && !*abort_flag; ++j) {
       if (lane == 0) stamp(0, 0, j);
-      if (j < n0) pv(0, j, true);
+      tile_step(0, j, n0, true, true);
       if (lane == 0) stamp(0, 1, j);
-      if (ok && j + 1 < n0) qk(0, j + 1, true);
+      if (ok) tile_step(1, j, n1, j >= n0, j + 1 >= n0);     // tile 1 is first only where tile 0 has no product
       if (lane == 0) stamp(0, 2, j);
-      if (ok && j < n1) pv(1, j, j >= n0);
-      if (lane == 0) stamp(0, 3, j);
-      if (ok && j + 1 < n1) qk(1, j + 1, j + 1 >= n0);
-      if (lane == 0) stamp(0, 4, j);
     }
     if (!ok) *abort_flag = 1;
   } else {
