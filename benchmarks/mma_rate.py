@@ -32,6 +32,9 @@ MODES = (
     (8, 128, "mode 0 while four warps keep storing to shared memory"),
     (9, 128, "mode 3 while four warps keep loading tensor memory"),
     (10, 128, "mode 6 with the next product's barrier looked at between this product's 6th and 7th instruction"),
+    (11, 128, "mode 0 while eight warps keep computing exponentials"),
+    (12, 128, "mode 3 while eight warps keep computing exponentials"),
+    (13, 128, "mode 3 while four warps keep storing to the tensor-memory columns A is read from"),
 )
 
 def main():

@@ -24,9 +24,12 @@
 //                     between the sixth and the seventh instruction of this one, while the pipe
 //                     still has queued work; the blocking wait remains only for a miss
 // Others (DISTURB): 0 idle   1 four warps keep loading tensor memory   2 four warps keep storing
-//                     to shared memory
+//                     to shared memory   3 eight warps keep computing exponentials (special-function
+//                     unit and fma pipe, no memory)   4 four warps keep storing to tensor memory
+//                     (the columns the A operand of OPS 3 is read from)
 //   mode = OPS (0-4, STYLE 0, idle) | 5, 6 = OPS 0 with STYLE 1, 2 | 7, 8 = OPS 0, STYLE 0 with
-//   DISTURB 1, 2 | 9 = OPS 3, STYLE 0, DISTURB 1 | 10 = OPS 0 with STYLE 3
+//   DISTURB 1, 2 | 9 = OPS 3, STYLE 0, DISTURB 1 | 10 = OPS 0 with STYLE 3 |
+//   11, 12 = OPS 0, 3 with DISTURB 3 | 13 = OPS 3 with DISTURB 4
 #include "common.cuh"
 #include "gemm_host.h"
 #include "tcgen05.cuh"
@@ -36,7 +39,7 @@ namespace {
 using namespace ft;
 using namespace ft::sm100;
 
-constexpr int kProbeThreads = 192;                   // warp 0 issues, warp 1 owns tensor memory, 2-5 disturb
+constexpr int kProbeThreads = 320;                   // warp 0 issues, warp 1 owns tensor memory, 2-9 disturb
 constexpr int kChunk = 128 * 128;                    // [128 rows][64 columns] of 16-bit values
 constexpr int kSmem = 2 * kChunk /* A */ + 4 * kChunk /* B, up to 256 rows */ + 32 * 1024 /* scratch */ + 2048;
 
@@ -163,13 +166,31 @@ mma_probe_kernel(int rounds, int wobble, long long* __restrict__ out, int* __res
       }
       __syncwarp();
     }
-  } else if (warp >= 2 && DISTURB != 0) {
+  } else if (warp >= 2 && DISTURB != 0 && (DISTURB == 3 || warp < 6)) {
     // the disturbing warps: bounded by the issuing warp's stop flag and by a turn count
     const int quarter = warp & 3;
     const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16);
     uint32_t sink = 0;
     for (int turn = 0; turn < (1 << 22) && !bars->stop; ++turn) {
-      if constexpr (DISTURB == 2) {
+      if constexpr (DISTURB == 3) {
+        float x = __uint_as_float(0x3f000000u + (turn & 0xffff) + lane);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          float y;
+          asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+          x = fmaf(y, 0.25f, -0.125f);
+        }
+        sink ^= __float_as_uint(x);
+      } else if constexpr (DISTURB == 4) {
+        if (warp < 6) {
+          uint32_t v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = turn + i;
+          tmem_st_32x32(taddr, v);
+          tmem_st_32x32(taddr + 32, v);
+          tmem_st_wait();
+        }
+      } else if constexpr (DISTURB == 2) {
         uint4* p = reinterpret_cast<uint4*>(sX) + ((turn * 128 + (warp - 2) * 32 + lane) & 2047);
         *p = make_uint4(turn, sink, 0, 0);
       } else {
@@ -203,7 +224,7 @@ extern "C" {
 
 // out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
 int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
-  if (mode < 0 || mode > 10 || rounds < 1 || rounds > 4096) return -1;
+  if (mode < 0 || mode > 13 || rounds < 1 || rounds > 4096) return -1;
   int dev = 0;
   cudaGetDevice(&dev);
   switch (mode) {
@@ -217,7 +238,10 @@ int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
     case 7: launch_probe<0, 0, 1>(rounds, out, dev, stream); break;
     case 8: launch_probe<0, 0, 2>(rounds, out, dev, stream); break;
     case 9: launch_probe<3, 0, 1>(rounds, out, dev, stream); break;
-    default: launch_probe<0, 3, 0>(rounds, out, dev, stream); break;
+    case 10: launch_probe<0, 3, 0>(rounds, out, dev, stream); break;
+    case 11: launch_probe<0, 0, 3>(rounds, out, dev, stream); break;
+    case 12: launch_probe<3, 0, 3>(rounds, out, dev, stream); break;
+    default: launch_probe<3, 0, 4>(rounds, out, dev, stream); break;
   }
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
