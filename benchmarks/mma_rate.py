@@ -35,6 +35,8 @@ MODES = (
     (11, 128, "mode 0 while eight warps keep computing exponentials"),
     (12, 128, "mode 3 while eight warps keep computing exponentials"),
     (13, 128, "mode 3 while four warps keep storing to the tensor-memory columns A is read from"),
+    (14, 256, "pair per round: O += P V (P in columns 0-63), then S = Q K^T over columns 0-127 (clocks per pair)"),
+    (15, 256, "the same pair with S written to other columns (clocks per pair)"),
 )
 
 def main():

@@ -16,6 +16,9 @@
 //                  2  A K-major, B MN-major in shared memory      (dQ = dS K)
 //                  3  A in tensor memory, B MN-major, N = 128     (O += P V)
 //                  4  A, B K-major in shared memory, N = 256
+//                  5  a pair per round, as the attention forward issues them: O += P V with P read from
+//                     tensor-memory columns 0-63, then S = Q K^T written over columns 0-127 (the
+//                     columns P was just read from)      6  the same pair with S written elsewhere
 // Issue (STYLE):   0  elected lane of a whole warp, nothing between the products
 //                  1  per product: barrier wait (succeeds at once), tcgen05 fence, product, commit;
 //                     issued inside `if (lane == 0)`
@@ -29,7 +32,7 @@
 //                     (the columns the A operand of OPS 3 is read from)
 //   mode = OPS (0-4, STYLE 0, idle) | 5, 6 = OPS 0 with STYLE 1, 2 | 7, 8 = OPS 0, STYLE 0 with
 //   DISTURB 1, 2 | 9 = OPS 3, STYLE 0, DISTURB 1 | 10 = OPS 0 with STYLE 3 |
-//   11, 12 = OPS 0, 3 with DISTURB 3 | 13 = OPS 3 with DISTURB 4
+//   11, 12 = OPS 0, 3 with DISTURB 3 | 13 = OPS 3 with DISTURB 4 | 14, 15 = OPS 5, 6 (clocks per pair)
 #include "common.cuh"
 #include "gemm_host.h"
 #include "tcgen05.cuh"
@@ -51,6 +54,16 @@ struct ProbeBars {
 
 // One product: eight instructions on the tiles at offsets a_off / b_off (bytes, uniform).
 template <int OPS, int KK0 = 0, int KK1 = 8>
+__device__ __forceinline__ void issue_product(uint32_t acc, uint32_t tmem_a, uint32_t aA, uint32_t aB, bool first);
+
+// OPS 5 / 6: the pair PV, QK
+template <int OPS>
+__device__ __forceinline__ void issue_pair(uint32_t tmem, uint32_t aA, uint32_t aB, bool first) {
+  issue_product<3>(tmem + 256, tmem, aA, aB, first);
+  issue_product<0>(tmem + (OPS == 5 ? 0 : 128), tmem, aA, aB, true);
+}
+
+template <int OPS, int KK0, int KK1>
 __device__ __forceinline__ void issue_product(uint32_t acc, uint32_t tmem_a, uint32_t aA, uint32_t aB, bool first) {
   constexpr uint32_t hi = smem_desc_hi(1024);
   constexpr uint32_t idesc = make_idesc_f16(1, OPS == 1, OPS == 1 || OPS == 2 || OPS == 3, 128, OPS == 4 ? 256 : 128);
@@ -151,7 +164,8 @@ mma_probe_kernel(int rounds, int wobble, long long* __restrict__ out, int* __res
           tc_fence_after();
         }
         if (elect_one()) {
-          issue_product<OPS>(tmem + 256, tmem, aA + (r & 1) * wobble, aB + (r & 1) * wobble, r == 0);
+          if constexpr (OPS >= 5) issue_pair<OPS>(tmem, aA + (r & 1) * wobble, aB + (r & 1) * wobble, r == 0);
+          else issue_product<OPS>(tmem + 256, tmem, aA + (r & 1) * wobble, aB + (r & 1) * wobble, r == 0);
           if constexpr (STYLE == 2) umma_commit(&bars->idle);
         }
         __syncwarp();
@@ -224,7 +238,7 @@ extern "C" {
 
 // out: device buffer of (number of SMs + 1) clock counts, one per CTA.  rounds <= 4096.
 int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
-  if (mode < 0 || mode > 13 || rounds < 1 || rounds > 4096) return -1;
+  if (mode < 0 || mode > 15 || rounds < 1 || rounds > 4096) return -1;
   int dev = 0;
   cudaGetDevice(&dev);
   switch (mode) {
@@ -241,7 +255,9 @@ int ft_mma_probe(int mode, int rounds, long long* out, cudaStream_t stream) {
     case 10: launch_probe<0, 3, 0>(rounds, out, dev, stream); break;
     case 11: launch_probe<0, 0, 3>(rounds, out, dev, stream); break;
     case 12: launch_probe<3, 0, 3>(rounds, out, dev, stream); break;
-    default: launch_probe<3, 0, 4>(rounds, out, dev, stream); break;
+    case 13: launch_probe<3, 0, 4>(rounds, out, dev, stream); break;
+    case 14: launch_probe<5, 0, 0>(rounds, out, dev, stream); break;
+    default: launch_probe<6, 0, 0>(rounds, out, dev, stream); break;
   }
   FT_LAUNCHED(1);
   FT_CUDA_RETURN_IF_ERROR();
