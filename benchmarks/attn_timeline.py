@@ -21,8 +21,8 @@ iteration period.  The roles:
 Forward.  The CTA ``--cta`` (CTA 0 is the pair of query blocks with the most K/V blocks) records
 eight consecutive K/V blocks j starting at ``--it0``:
 
-    mma    0 begin of block j | 1 PV(j) and QK(j+1) of tile 0 issued (after V_j landed and P0_j was
-           written) | 2 PV(j) and QK(j+1) of tile 1 issued
+    mma    0 begin of block j | 1 tile 0: V_j, P0_j and K_j+1 are there | 2 PV0(j) issued |
+           3 QK0(j+1) issued | 4 tile 1: P1_j is there | 5 PV1(j) issued | 6 QK1(j+1) issued
     smx0 / smx1 (first softmax warp of tile 0 / 1)
            0 begin | 1 S complete | 2 S in registers | 3 row maximum known, O rescaled if needed |
            4 exponentials done, P stored | 5 P signalled
@@ -68,7 +68,7 @@ def main():
         print(f"forward, shape {args.shape} cta {args.cta} K/V blocks {args.it0}..{args.it0 + 7}")
         period = (base[1:] - base[:-1]).float()
         print("block period (clocks):", [int(x) for x in period], "mean", int(period.mean()))
-        for r, (name, sites) in enumerate((("mma", 3), ("smx0", 6), ("smx1", 6))):
+        for r, (name, sites) in enumerate((("mma", 7), ("smx0", 6), ("smx1", 6))):
             for j in range(8):
                 print(f"{name:9s} j+{j}: {[int(t[r, s_, j] - base[j]) for s_ in range(sites)]}")
         return

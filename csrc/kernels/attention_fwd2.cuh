@@ -187,8 +187,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (!has_pv && !has_qk) return;
       tc_fence_after();
       if (elect_one()) {
+        stamp(0, 1 + 3 * t, j);
         if (has_pv) pv_issue(t, j);
+        stamp(0, 2 + 3 * t, j);
         if (has_qk) qk_issue(t, j + 1);
+        stamp(0, 3 + 3 * t, j);
       }
       __syncwarp();
     };
@@ -205,9 +208,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int j = 0; j < nmax && ok && !*abort_flag; ++j) {
       if (lane == 0) stamp(0, 0, j);
       tile_step(0, j, n0, true, true);
-      if (lane == 0) stamp(0, 1, j);
       if (ok) tile_step(1, j, n1, j >= n0, j + 1 >= n0);     // tile 1 is first only where tile 0 has no product
-      if (lane == 0) stamp(0, 2, j);
     }
     if (!ok) *abort_flag = 1;
   } else {

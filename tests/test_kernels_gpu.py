@@ -351,8 +351,8 @@ def test_attention_timeline_instantiations_compute_the_same_and_fill_the_trace()
     torch.cuda.synchronize()
     assert torch.equal(o, o2) and torch.equal(lse, lse2)
     f = fbuf.cpu().view(3, 8, 8)
-    assert (f[0, :3, :8] > 0).all() and (f[1, :6, :7] > 0).all()
-    assert (f[0, 1:3] >= f[0, 0:2]).all()                 # the product warp's sites follow one another
+    assert (f[0, :4, :7] > 0).all() and (f[0, 4:7, :8] > 0).all() and (f[1, :6, :7] > 0).all()
+    assert (f[0, 1:4, :7] >= f[0, 0:3, :7]).all()         # the product warp's sites follow one another
     assert (f[1, 1:6, :7] >= f[1, 0:5, :7]).all()         # so do the softmax warp's
     want = attention_backward(q, k, v, o, lse, do, scale)
     bbuf = torch.zeros(5 * 16 * 8, dtype=torch.int64, device=_dev())
