@@ -19,17 +19,17 @@ static_assert(Fwd2Smem<128>::BYTES <= kMaxDynamicSmem && BwdSmem<128>::BYTES <= 
               "an attention kernel outgrew the shared memory of an SM");
 
 // Forward: one CTA per pair of query blocks.
-template <typename T, int D, bool TRACE, int SPLIT = 1, unsigned POLY = 0x00u>
+template <typename T, int D, bool TRACE>
 int launch_fwd2_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
                   cudaStream_t s) {
-  auto kern = attn_fwd2_kernel<T, D, POLY, TRACE, SPLIT>;
+  auto kern = attn_fwd2_kernel<T, D, 0x00u, TRACE>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<D>::BYTES);
     configured = true;
   }
   const int num_pairs = ((P.S + BQ - 1) / BQ + 1) / 2;
-  kern<<<P.B * P.Hq * num_pairs, f2_threads(SPLIT), Fwd2Smem<D>::BYTES, s>>>(tq, tk, tv, P);
+  kern<<<P.B * P.Hq * num_pairs, F2_THREADS, Fwd2Smem<D>::BYTES, s>>>(tq, tk, tv, P);
   return 0;
 }
 
@@ -38,14 +38,7 @@ template <typename T, int D>
 int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& P,
                 cudaStream_t s) {
   if constexpr (std::is_same<T, __nv_bfloat16>::value && D == 128) {
-    static const int variant = std::getenv("FT_FWD_VARIANT") ? std::atoi(std::getenv("FT_FWD_VARIANT")) : 0;
-    if (P.trace != nullptr) {
-      if (variant == 0) return launch_fwd2_t<T, D, true>(tq, tk, tv, P, s);
-      return launch_fwd2_t<T, D, true, 2, 0xAAu>(tq, tk, tv, P, s);
-    }
-    if (variant == 1) return launch_fwd2_t<T, D, false, 2, 0x00u>(tq, tk, tv, P, s);
-    if (variant == 2) return launch_fwd2_t<T, D, false, 2, 0x22u>(tq, tk, tv, P, s);
-    if (variant == 3) return launch_fwd2_t<T, D, false, 2, 0xAAu>(tq, tk, tv, P, s);
+    if (P.trace != nullptr) return launch_fwd2_t<T, D, true>(tq, tk, tv, P, s);
   }
   return launch_fwd2_t<T, D, false>(tq, tk, tv, P, s);
 }

@@ -5,8 +5,7 @@
 // softmax of one tile runs the tensor core works on the other tile:
 //   warp 0      TMA producer (Q tiles once, then K_j / V_j)
 //   warp 1      MMA issuer, in the order  PV0(j) QK0(j+1) PV1(j) QK1(j+1)
-//   warps 2-5   softmax of tile 0;  warps 6-9  softmax of tile 1 (one row per thread; with SPLIT = 2
-//               eight warps per tile, two threads per row, each taking half of its columns)
+//   warps 2-5   softmax of tile 0;  warps 6-9  softmax of tile 1 (one row per thread)
 // Tensor memory (512 columns): S0 | S1 | O0 | O1.  The probabilities P_j are
 // written back into the first 64 columns of their S buffer as packed 16-bit pairs
 // and the P V product takes its A operand straight from tensor memory, so P never
@@ -24,17 +23,13 @@
 namespace ft {
 namespace attn {
 
-// 2 control warps + 4 * SPLIT softmax warps per tile: SPLIT threads share a score row, each taking
-// 128 / SPLIT of its columns (and D / SPLIT of the output's).
-constexpr int f2_threads(int split) { return 32 * (2 + 8 * split); }
+constexpr int F2_THREADS = 320;
 constexpr float kRescaleLog2 = 8.f;
 
 template <int D>
 struct Fwd2Smem {
   static constexpr int TILE = BQ * D * 2;
-  // + the exchange of row maxima / row sums between the threads of a row: [2 slots][2 tiles][2][128] floats
-  static constexpr int XCH_BYTES = 2 * 2 * 2 * BQ * 4;
-  static constexpr int BYTES = 2 * TILE + 2 * KV_STAGES * TILE + XCH_BYTES + 1024 + 256;
+  static constexpr int BYTES = 2 * TILE + 2 * KV_STAGES * TILE + 1024 + 256;
 };
 
 struct Fwd2Bars {
@@ -42,7 +37,6 @@ struct Fwd2Bars {
   uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
   uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
   uint64_t s_full[2], p_full[2], o_full[2];
-  uint64_t row_xch[2];     // the threads of a tile's rows have written their partial maximum / sum
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -51,8 +45,8 @@ struct Fwd2Bars {
 // (bit j = pair j) instead of the special-function unit.  None by default: with one thread per
 // score row the extra instructions cost more than the unit's 16 results per clock (13B shape:
 // 1.466 ms with none, 1.553 ms with four of eight, 1.699 ms with five).
-template <typename T, int D, unsigned POLY = 0x00u, bool TRACE = false, int SPLIT = 1>
-__global__ void __launch_bounds__(f2_threads(SPLIT), 1)
+template <typename T, int D, unsigned POLY = 0x00u, bool TRACE = false>
+__global__ void __launch_bounds__(F2_THREADS, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ FwdParams P) {
   constexpr int TILE = Fwd2Smem<D>::TILE;
@@ -64,8 +58,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* sQ = smem;                                // two tiles
   uint8_t* sK = sQ + 2 * TILE;
   uint8_t* sV = sK + KV_STAGES * TILE;
-  float* xch = reinterpret_cast<float*>(sV + KV_STAGES * TILE);
-  Fwd2Bars* bars = reinterpret_cast<Fwd2Bars*>(sV + KV_STAGES * TILE + Fwd2Smem<D>::XCH_BYTES);
+  Fwd2Bars* bars = reinterpret_cast<Fwd2Bars*>(sV + KV_STAGES * TILE);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_qb = (P.S + BQ - 1) / BQ;
@@ -94,8 +87,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t], 128 * SPLIT);
-      mbar_init(&bars->row_xch[t], 128 * SPLIT);
+      mbar_init(&bars->p_full[t], 128);
       mbar_init(&bars->o_full[t], 1);
     }
     bars->abort = 0;
@@ -221,25 +213,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (!ok) *abort_flag = 1;
   } else {
     // ------------------------------------------------------------ softmax
-    const int t = (warp - 2) / (4 * SPLIT);
-    const int h = ((warp - 2) >> 2) % SPLIT;         // which part of the row's columns this thread takes
-    constexpr int NCH = BKV / 32 / SPLIT;            // 32-column chunks of S per thread
-    constexpr int OCH = D / 32 / SPLIT;              // 32-column chunks of O per thread
-    static_assert(SPLIT == 1 || SPLIT == 2, "one or two threads per score row");
+    const int t = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    // The SPLIT threads of a row exchange their partial maxima / sums through shared memory; the
-    // tile's threads meet at an mbarrier (a bounded wait, like every other in this kernel).  `idx`
-    // counts the exchanges of the tile: it selects one of two slots and the barrier's phase.
-    bool xch_ok = true;
-    auto row_exchange = [&](int idx, float mine) -> float {
-      if constexpr (SPLIT == 1) return mine;
-      float* base = xch + (((idx & 1) * 2 + t) * 2) * BQ;
-      base[h * BQ + r] = mine;
-      mbar_arrive(&bars->row_xch[t]);
-      if (!mbar_wait(&bars->row_xch[t], idx & 1)) { atomicCAS(P.err, 0, 329); xch_ok = false; }
-      return base[(h ^ 1) * BQ + r];
-    };
     const int qb = t ? qb1 : qb0;
     const int n_t = t ? n1 : n0;
     const int q_pos = qb * BQ + r;
@@ -249,7 +225,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint64_t scale2 = pm::pack2(P.scale_log2, P.scale_log2);
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
-    const int trole = (lane == 0 && warp == 2 + t * 4 * SPLIT) ? 1 + t : -1;   // first softmax warp of a tile
+    const int trole = (lane == 0 && quarter == 2) ? 1 + t : -1;     // warps 2 and 6
     auto sstamp = [&](int site, int j) { if (TRACE && trole >= 0) stamp(trole, site, j); };
     for (int j = 0; j < n_t; ++j) {
       sstamp(0, j);
@@ -259,32 +235,27 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const bool diag = (j == qb);
       const int kv0 = j * BKV;
       // the whole S row goes to registers once: four loads in flight, one wait
-      uint32_t v[NCH][32];
+      uint32_t v[BKV / 32][32];
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) tmem_ld_32x32(tm_s + (h * NCH + c) * 32, v[c]);
+      for (int c = 0; c < BKV / 32; ++c) tmem_ld_32x32(tm_s + c * 32, v[c]);
       tmem_ld_wait();
       sstamp(2, j);
       if (diag) {
 #pragma unroll
-        for (int c = 0; c < NCH; ++c)
+        for (int c = 0; c < BKV / 32; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (kv0 + (h * NCH + c) * 32 + i > q_pos) v[c][i] = 0xff800000u;     // -inf
+            if (kv0 + c * 32 + i > q_pos) v[c][i] = 0xff800000u;     // -inf
       }
-      float mx[NCH];                                 // independent chains, one per chunk
+      float mx[BKV / 32];                            // independent chains, one per chunk
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
+      for (int c = 0; c < BKV / 32; ++c) {
         mx[c] = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 32; i += 2)
           mx[c] = pm::max3(mx[c], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
       }
-      float m_mine = mx[0];
-#pragma unroll
-      for (int c = 1; c < NCH; ++c) m_mine = fmaxf(m_mine, mx[c]);
-      // both threads of a row end up with the same maximum, hence the same decisions below
-      const float m_blk = fmaxf(m_mine, row_exchange(j, m_mine));
-      if (!xch_ok) { ok = false; break; }
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       // rescale O only when some row of the warp outgrew its maximum by more than 2^8
       const bool grow = (m_blk - m_used) * P.scale_log2 > kRescaleLog2;
       if (__any_sync(0xffffffffu, grow)) {
@@ -294,9 +265,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tc_fence_after();
           const float alpha = pm::ex2((m_used - m_new) * P.scale_log2);
           const uint64_t alpha2 = pm::pack2(alpha, alpha);
-          // sixteen columns at a time: this rare path must not cost the common one registers
+          // Sixteen columns at a time: this rare path must not cost the common one registers (with
+          // 32-column pieces the kernel spilled 230-250 bytes per thread and the 13B shape took
+          // 1.403 ms instead of 1.342).
 #pragma unroll 1
-          for (int c = 2 * h * OCH; c < 2 * (h + 1) * OCH; ++c) {
+          for (int c = 0; c < D / 16; ++c) {
             uint32_t w[16];
             tmem_ld_32x16(tm_o + c * 16, w);
             tmem_ld_wait();
@@ -317,9 +290,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // p = 2^((s - m) * scale), row sum, P written over the first half of S
       const float neg_m = -m_used * P.scale_log2;
       const uint64_t neg_m2 = pm::pack2(neg_m, neg_m);
-      uint64_t ls[NCH];
+      uint64_t ls[BKV / 32];
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
+      for (int c = 0; c < BKV / 32; ++c) {
         ls[c] = pm::pack2(0.f, 0.f);
         uint32_t pk[16];
 #pragma unroll
@@ -336,11 +309,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           ls[c] = pm::add2(ls[c], pm::pack2(a, b));
           pk[i] = pm::cvt2<T>(a, b);
         }
-        tmem_st_32x16(tm_s + (h * NCH + c) * 16, pk);
+        tmem_st_32x16(tm_s + c * 16, pk);
       }
-      uint64_t l2 = ls[0];
-#pragma unroll
-      for (int c = 1; c < NCH; ++c) l2 = pm::add2(l2, ls[c]);
+      const uint64_t l2 = pm::add2(pm::add2(ls[0], ls[1]), pm::add2(ls[2], ls[3]));
       float la, lb;
       pm::unpack2(l2, la, lb);
       l_run += la + lb;
@@ -355,12 +326,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     if (ok && n_t > 0) {
       tc_fence_after();
-      const float l_row = l_run + (SPLIT == 1 ? 0.f : row_exchange(n_t, l_run));
-      const float inv_l = 1.f / l_row;
+      const float inv_l = 1.f / l_run;
       const bool valid = q_pos < P.S;
       T* orow = reinterpret_cast<T*>(P.o) + ((int64_t)(batch * P.S + q_pos) * P.Hq + head) * D;
 #pragma unroll 1
-      for (int c = h * OCH; c < (h + 1) * OCH; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tm_o + c * 32, v);
         tmem_ld_wait();
@@ -376,8 +346,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
         }
       }
-      if (valid && h == 0)
-        P.lse[((int64_t)batch * P.Hq + head) * P.S + q_pos] = m_used * P.scale_ln + logf(l_row);
+      if (valid)
+        P.lse[((int64_t)batch * P.Hq + head) * P.S + q_pos] = m_used * P.scale_ln + logf(l_run);
     } else if (!ok) {
       *abort_flag = 1;
     }
