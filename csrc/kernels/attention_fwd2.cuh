@@ -44,7 +44,7 @@ struct Fwd2Bars {
 // POLY: which of every eight pairs of probabilities take the polynomial 2^x of packed_math.cuh
 // (bit j = pair j) instead of the special-function unit.  None by default: with one thread per
 // score row the extra instructions cost more than the unit's 16 results per clock (13B shape:
-// 1.466 ms with none, 1.553 ms with four of eight, 1.699 ms with five).
+// 1.362 ms with none, 1.387 / 1.412 / 1.427 ms with one / two / three pairs of eight).
 template <typename T, int D, unsigned POLY = 0x00u, bool TRACE = false>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
