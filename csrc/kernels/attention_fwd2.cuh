@@ -247,65 +247,20 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           for (int i = 0; i < 32; ++i)
             if (kv0 + c * 32 + i > q_pos) v[c][i] = 0xff800000u;     // -inf
       }
-      // p = 2^((s - m) * scale) for the whole row with m the maximum in use, P written over the
-      // first half of S, the row sum returned; with_max also yields the block's own maximum, its
-      // chains interleaved with the exponentials instead of a pass of their own in front of them.
       float mx[BKV / 32];                            // independent chains, one per chunk
-      auto exp_pass = [&](float m, auto with_max) -> float {
-        const float neg_m = -m * P.scale_log2;
-        const uint64_t neg_m2 = pm::pack2(neg_m, neg_m);
-        uint64_t ls[BKV / 32];
 #pragma unroll
-        for (int c = 0; c < BKV / 32; ++c) {
-          ls[c] = pm::pack2(0.f, 0.f);
-          if constexpr (decltype(with_max)::value) mx[c] = -INFINITY;
-          uint32_t pk[16];
+      for (int c = 0; c < BKV / 32; ++c) {
+        mx[c] = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float s0 = __uint_as_float(v[c][2 * i]), s1 = __uint_as_float(v[c][2 * i + 1]);
-            if constexpr (decltype(with_max)::value) mx[c] = pm::max3(mx[c], s0, s1);
-            float a, b;
-            pm::unpack2(pm::fma2(pm::pack2(s0, s1), scale2, neg_m2), a, b);
-            if ((POLY >> (i & 7)) & 1u) {
-              pm::ex2_poly2(a, b, a, b);
-            } else {
-              a = pm::ex2(a);
-              b = pm::ex2(b);
-            }
-            ls[c] = pm::add2(ls[c], pm::pack2(a, b));
-            pk[i] = pm::cvt2<T>(a, b);
-          }
-          tmem_st_32x16(tm_s + c * 16, pk);
-        }
-        const uint64_t l2 = pm::add2(pm::add2(ls[0], ls[1]), pm::add2(ls[2], ls[3]));
-        float la, lb;
-        pm::unpack2(l2, la, lb);
-        return la + lb;
-      };
-      float l_blk;
-      if (j == 0) {
-        // no maximum in use yet: find the block's first
-#pragma unroll
-        for (int c = 0; c < BKV / 32; ++c) {
-          mx[c] = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2)
-            mx[c] = pm::max3(mx[c], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
-        }
-        m_used = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        sstamp(3, j);
-        l_blk = exp_pass(m_used, std::false_type{});
-      } else {
-        // The maximum in use is allowed to lag the true one by 2^8, so the exponentials are
-        // computed with it at once; only when some row of the warp outgrew it by more (rare after
-        // the first blocks) is O rescaled and the block's P computed again.  The results are those
-        // of finding the maximum first.
-        sstamp(3, j);
-        l_blk = exp_pass(m_used, std::true_type{});
-        const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        const bool grow = (m_blk - m_used) * P.scale_log2 > kRescaleLog2;
-        if (__any_sync(0xffffffffu, grow)) {
-          const float m_new = fmaxf(m_used, m_blk);
+        for (int i = 0; i < 32; i += 2)
+          mx[c] = pm::max3(mx[c], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
+      }
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      // rescale O only when some row of the warp outgrew its maximum by more than 2^8
+      const bool grow = (m_blk - m_used) * P.scale_log2 > kRescaleLog2;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_used, m_blk);
+        if (j > 0) {
           if (!mbar_wait(&bars->o_full[t], (j - 1) & 1)) { atomicCAS(P.err, 0, 327); ok = false; break; }
           tc_fence_after();
           const float alpha = pm::ex2((m_used - m_new) * P.scale_log2);
@@ -328,11 +283,38 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tmem_st_32x16(tm_o + c * 16, w);
           }
           l_run *= alpha;
-          m_used = m_new;
-          l_blk = exp_pass(m_used, std::false_type{});
         }
+        m_used = m_new;
       }
-      l_run += l_blk;
+      sstamp(3, j);
+      // p = 2^((s - m) * scale), row sum, P written over the first half of S
+      const float neg_m = -m_used * P.scale_log2;
+      const uint64_t neg_m2 = pm::pack2(neg_m, neg_m);
+      uint64_t ls[BKV / 32];
+#pragma unroll
+      for (int c = 0; c < BKV / 32; ++c) {
+        ls[c] = pm::pack2(0.f, 0.f);
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float a, b;
+          pm::unpack2(pm::fma2(pm::pack2(__uint_as_float(v[c][2 * i]), __uint_as_float(v[c][2 * i + 1])), scale2,
+                               neg_m2), a, b);
+          if ((POLY >> (i & 7)) & 1u) {
+            pm::ex2_poly2(a, b, a, b);
+          } else {
+            a = pm::ex2(a);
+            b = pm::ex2(b);
+          }
+          ls[c] = pm::add2(ls[c], pm::pack2(a, b));
+          pk[i] = pm::cvt2<T>(a, b);
+        }
+        tmem_st_32x16(tm_s + c * 16, pk);
+      }
+      const uint64_t l2 = pm::add2(pm::add2(ls[0], ls[1]), pm::add2(ls[2], ls[3]));
+      float la, lb;
+      pm::unpack2(l2, la, lb);
+      l_run += la + lb;
       sstamp(4, j);
       tmem_st_wait();
       tc_fence_before();
