@@ -171,10 +171,18 @@ class FlexTrainOptsCoordinator:
         # state tiers
         self._gpu_opts: Dict[int, List[torch.Tensor]] = {}
         self._cpu_opts: Dict[int, List[torch.Tensor]] = {}
-        self._nvme_stage = [allocate_memory(on, torch.float32, "cpu", True) for _ in range(self.K)] \
-            if on else None
+        # Two sets of staging buffers for the NVMe share of the state: the host update of one unit
+        # leaves its write-back in flight and the next unit's update works in the other set, so
+        # the disk's write time (its slowest direction) overlaps the next update instead of
+        # standing between two of them.  _nvme_stage (set 0) serves start-up and state access.
+        self._nvme_stage_sets = [[allocate_memory(on, torch.float32, "cpu", True) for _ in range(self.K)]
+                                 for _ in range(2)] if on else None
+        self._nvme_stage = self._nvme_stage_sets[0] if on else None
+        self._nvme_writes = [None, None]             # (unit, handle) of the write in flight per set
+        self._nvme_turn = 0
         self._nvme_para_stage = allocate_memory(n, self.device_dtype, "cpu", True) if n else None
-        for stage in (self._nvme_stage or []) + ([self._nvme_para_stage] if n else []):
+        for stage in [t for ss in (self._nvme_stage_sets or []) for t in ss] + \
+                ([self._nvme_para_stage] if n else []):
             get_nvme_swapper().register_staging(stage)
         lo, hi = para.shard_range()
         self._segments: List[List[GroupSegment]] = [
@@ -245,15 +253,28 @@ class FlexTrainOptsCoordinator:
     def _opts_id(self, unit):
         return FlexTrainDataID(FlexTrainDataType.OPTS, unit)
 
-    def _write_nvme_states(self, unit):
+    def _write_nvme_states(self, unit, stage=None, async_op=False):
         from ..nvme_swapper import NVMeGroup
         on = self.opt_tiers[2]
-        NVMeGroup([on] * self.K).group_offload(self._opts_id(unit), self._nvme_stage)
+        return NVMeGroup([on] * self.K).group_offload(self._opts_id(unit), stage or self._nvme_stage,
+                                                      async_op=async_op)
 
-    def _read_nvme_states(self, unit):
+    def _read_nvme_states(self, unit, stage=None):
         from ..nvme_swapper import NVMeGroup
         on = self.opt_tiers[2]
-        NVMeGroup([on] * self.K).group_reload(self._opts_id(unit), self._nvme_stage)
+        self._nvme_settle(unit=unit)                 # never read a file whose write is still in flight
+        NVMeGroup([on] * self.K).group_reload(self._opts_id(unit), stage or self._nvme_stage)
+
+    def _nvme_settle(self, which=None, unit=None):
+        """Wait for write-backs in flight: of staging set ``which``, of ``unit``'s file, or (no
+        argument) all of them.  Called by the thread that owns the sets at that moment: the host
+        worker during updates, the main thread once ``wait_all`` has seen the worker idle."""
+        for i in range(2):
+            pend = self._nvme_writes[i]
+            if pend is None or (which is not None and i != which) or (unit is not None and pend[0] != unit):
+                continue
+            self._nvme_writes[i] = None
+            pend[1].wait()
 
     # ------------------------------------------------------- gradient hooks
     def pre_unit_backward(self, unit: int):
@@ -453,9 +474,13 @@ class FlexTrainOptsCoordinator:
                 opts = self._cpu_opts[unit]
                 run(og, og + oc, opts[0], opts[1:], og)
             if on:
-                self._read_nvme_states(unit)
-                run(og + oc, self.S, self._nvme_stage[0], self._nvme_stage[1:], og + oc)
-                self._write_nvme_states(unit)
+                i = self._nvme_turn
+                self._nvme_turn ^= 1
+                stage = self._nvme_stage_sets[i]
+                self._nvme_settle(which=i)           # the write that last used this set
+                self._read_nvme_states(unit, stage)
+                run(og + oc, self.S, stage[0], stage[1:], og + oc)
+                self._nvme_writes[i] = (unit, self._write_nvme_states(unit, stage, async_op=True))
             if n:
                 para.write_nvme_piece(unit, self._nvme_para_stage)
             if out_hbm_hi > og:
@@ -570,6 +595,8 @@ class FlexTrainOptsCoordinator:
         pend, self._pending = self._pending, []
         for f in pend:
             f.result()
+        if getattr(self, "_nvme_stage_sets", None):
+            self._nvme_settle()
 
     def prune_pending(self):
         done = [f for f in self._pending if f.done()]
