@@ -177,37 +177,42 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t id_s = make_idesc_f16(AB, 0, 0, BQ, BKV);     // K-major x K-major
-      constexpr uint32_t id_t = make_idesc_f16(AB, 1, 1, BKV, D);      // MN-major x MN-major
-      constexpr uint32_t id_q = make_idesc_f16(AB, 0, 1, BQ, D);       // K-major x MN-major
-      // Descriptor halves of the six tiles, prepared once: inside the loop an instruction costs
-      // this thread two integer adds, not two descriptor constructions.  A lone thread runs its
-      // dependent integer instructions several clocks apart, and with the constructions in the
-      // loop it fed the pipe one 128-wide instruction per ~105 clocks where the pipe takes 64
-      // (csrc/kernels/mma_probe.cu measures both).
-      constexpr uint32_t dhi = smem_desc_hi(1024);
-      const uint32_t q_k = smem_desc_lo(smem_u32(sQ), 16), k_k = smem_desc_lo(smem_u32(sK), 16),
-                     do_k = smem_desc_lo(smem_u32(sdO), 16), v_k = smem_desc_lo(smem_u32(sV), 16),
-                     ds_k = smem_desc_lo(smem_u32(sdS), 16);
-      const uint32_t p_m = smem_desc_lo(smem_u32(sP), CHUNK_BYTES), do_m = smem_desc_lo(smem_u32(sdO), CHUNK_BYTES),
-                     ds_m = smem_desc_lo(smem_u32(sdS), CHUNK_BYTES), q_m = smem_desc_lo(smem_u32(sQ), CHUNK_BYTES),
-                     k_m = smem_desc_lo(smem_u32(sK), CHUNK_BYTES);
-      auto desc = [&](uint32_t lo, uint32_t off_bytes) { return smem_desc_join(lo + (off_bytes >> 4), dhi); };
-      bool ok = mbar_wait(&bars->kv_full, 0);
-      if (!ok) atomicCAS(P.err, 0, 402);
-      for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
-        const uint32_t ph = it & 1;
-        stamp(1, 0, it);
-        if (!mbar_wait(&bars->q_full, ph)) { atomicCAS(P.err, 0, 403); ok = false; break; }
-        stamp(1, 1, it);
-        if (!mbar_wait(&bars->s_free, ph ^ 1)) { atomicCAS(P.err, 0, 404); ok = false; break; }
-        // dO landed before Q did (it is released first); waiting for it here keeps the sixteen
-        // instructions of S and dP back to back
-        if (!mbar_wait(&bars->do_full, ph)) { atomicCAS(P.err, 0, 414); ok = false; break; }
-        stamp(1, 2, it);
-        tc_fence_after();
+    // The whole warp runs this loop and an elected lane issues (warp-uniform control flow around
+    // the tensor instructions costs the issuer less, and what it spends between two products is
+    // time the pipe stands still; csrc/kernels/mma_probe.cu).
+    constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+    constexpr uint32_t id_s = make_idesc_f16(AB, 0, 0, BQ, BKV);     // K-major x K-major
+    constexpr uint32_t id_t = make_idesc_f16(AB, 1, 1, BKV, D);      // MN-major x MN-major
+    constexpr uint32_t id_q = make_idesc_f16(AB, 0, 1, BQ, D);       // K-major x MN-major
+    // descriptor halves of the six tiles, prepared once: an instruction then costs two integer adds
+    constexpr uint32_t dhi = smem_desc_hi(1024);
+    const uint32_t q_k = smem_desc_lo(smem_u32(sQ), 16), k_k = smem_desc_lo(smem_u32(sK), 16),
+                   do_k = smem_desc_lo(smem_u32(sdO), 16), v_k = smem_desc_lo(smem_u32(sV), 16),
+                   ds_k = smem_desc_lo(smem_u32(sdS), 16);
+    const uint32_t p_m = smem_desc_lo(smem_u32(sP), CHUNK_BYTES), do_m = smem_desc_lo(smem_u32(sdO), CHUNK_BYTES),
+                   ds_m = smem_desc_lo(smem_u32(sdS), CHUNK_BYTES), q_m = smem_desc_lo(smem_u32(sQ), CHUNK_BYTES),
+                   k_m = smem_desc_lo(smem_u32(sK), CHUNK_BYTES);
+    auto desc = [&](uint32_t lo, uint32_t off_bytes) { return smem_desc_join(lo + (off_bytes >> 4), dhi); };
+    // the lanes poll on their own, so a wait that runs out is made the whole warp's verdict
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
+    };
+    bool ok = true;
+    auto fail = [&](int code) { if (lane == 0) atomicCAS(P.err, 0, code); ok = false; };
+    auto mstamp = [&](int site, int it) { if (TRACE && lane == 0) stamp(1, site, it); };
+    if (!wait_all(&bars->kv_full, 0)) fail(402);
+    for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+      const uint32_t ph = it & 1;
+      mstamp(0, it);
+      if (!wait_all(&bars->q_full, ph)) { fail(403); break; }
+      mstamp(1, it);
+      if (!wait_all(&bars->s_free, ph ^ 1)) { fail(404); break; }
+      // dO landed before Q did (it is released first); waiting for it here keeps the sixteen
+      // instructions of S and dP back to back
+      if (!wait_all(&bars->do_full, ph)) { fail(414); break; }
+      mstamp(2, it);
+      tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
@@ -220,20 +225,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dp, desc(do_k, off), desc(v_k, off), id_s, kk != 0);
         }
         umma_commit(&bars->dp_full);
-        stamp(1, 3, it);
-        if (!mbar_wait(&bars->p_full, ph)) { atomicCAS(P.err, 0, 405); ok = false; break; }
-        stamp(1, 4, it);
-        tc_fence_after();
+      }
+      __syncwarp();
+      mstamp(3, it);
+      if (!wait_all(&bars->p_full, ph)) { fail(405); break; }
+      mstamp(4, it);
+      tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {       // reduction over the 128 query rows
           const uint32_t row_off = kk * 2048;
           umma_f16(tm_dv, desc(p_m, row_off), desc(do_m, row_off), id_t, (it | kk) != 0);
         }
         umma_commit(&bars->do_empty);
-        stamp(1, 5, it);
-        if (!mbar_wait(&bars->ds_full, ph)) { atomicCAS(P.err, 0, 409); ok = false; break; }
-        stamp(1, 6, it);
-        tc_fence_after();
+      }
+      __syncwarp();
+      mstamp(5, it);
+      if (!wait_all(&bars->ds_full, ph)) { fail(409); break; }
+      mstamp(6, it);
+      tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {
           const uint32_t row_off = kk * 2048;
@@ -246,10 +257,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dq, desc(ds_k, a_off), desc(k_m, kk * 2048), id_q, kk != 0);
         }
         umma_commit(&bars->dq_full);
-        stamp(1, 7, it);
       }
-      if (ok) umma_commit(&bars->acc_full);
-      else *abort_flag = 1;
+      __syncwarp();
+      mstamp(7, it);
+    }
+    if (ok) {
+      if (elect_one()) umma_commit(&bars->acc_full);
+      __syncwarp();
+    } else {
+      *abort_flag = 1;
     }
   } else if (warp == 2 + 4 * SPLIT) {
     // ------------------------------------------------------------ dQ store warp
