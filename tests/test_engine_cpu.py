@@ -147,6 +147,20 @@ def test_world1_nvme_tiers(ref_losses):
         assert any(n.startswith("rank0_OPTS_layer") and n.endswith(".swp.0") for n in names)
 
 
+def test_world1_nvme_optimizer_state_of_a_single_unit(ref_losses):
+    """All layers in one unit with its optimizer state half on NVMe: every step reads the file the
+    step before wrote, whose write-back is left in flight by the host update - the read must wait
+    for it (and the two sets of staging buffers must alternate without mixing steps)."""
+    from flextrain_b200.models.llama import preset as _preset
+    with tempfile.TemporaryDirectory() as d:
+        cfg = _config(nvme_swap={"swap_dir": d, "aio_thread_count": 2},
+                      checkpoint_interval=_preset("tiny").num_layers,
+                      split_ratio={"optimizer": [0.0, 0.5], "parameter": [0.0, 1.0],
+                                   "checkpoint": [0.0, 1.0], "gradient": [0.0, 1.0], "alpha": 0.0})
+        _check(_run(1, cfg), ref_losses)
+        assert sum(n.startswith("rank0_OPTS_layer") for n in os.listdir(d)) == 3      # master, m, v of one unit
+
+
 def test_world2_adamw_weight_decay():
     ref = _reference_losses(preset("tiny"), _data(6), weight_decay=0.1, adamw=True)
     cfg = _config(split_ratio={"optimizer": [0.5, 0.5], "parameter": [0.5, 0.5]})
