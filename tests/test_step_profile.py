@@ -38,7 +38,13 @@ def test_union_busy_time_gaps_and_ranking():
     assert gaps[0]["after"] == "copy" and gaps[0]["before"] == "gemm"
     assert gaps[1]["after"] == "norm" and gaps[1]["before"] == "adam"
     assert abs(s["idle_in_gaps_over_50us_ms"] - 0.1) < 1e-9
+    # the first gemm shares the GPU with the copy for half of its time, the second runs alone
+    g = s["top_kernels"][0]
+    assert (g["alone"], g["shared"]) == (1, 1) and g["alone_median_us"] == 400 and g["shared_median_us"] == 400
+    c = s["top_kernels"][1]
+    assert (c["alone"], c["shared"]) == (0, 1) and c["alone_median_us"] is None
     text = sp.format_summary(s)
+    assert "alone x1" in text and "shared x1" in text
     assert "idle 0.1" in text or "idle 0.2" in text
     assert sp.summarize_trace([]) == {"kernels": 0}
     assert "no device activity" in sp.format_summary({"kernels": 0})
